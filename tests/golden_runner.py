@@ -1,0 +1,189 @@
+"""Replays the transcribed reference known-answer cases against an engine.
+
+An engine is any object with the small interface used below (the CPU oracle adapter lives in
+this file; the CUDA adapter in tests/cuda_engine.py).  Buffers are 1-D numpy arrays holding the
+whole underlying storage; metas describe the view (shape, strides, offset in elements).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+NP = {"f32": np.float32, "f64": np.float64, "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
+      "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "bool": np.bool_}
+BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+UN = {"neg": 0, "relu": 1, "abs": 2, "sign": 3}
+RED = {"sum": 1, "prod": 2, "max": 3, "min": 4, "mean": 5}
+
+
+def build_tensor(spec, dtype, engine):
+    """-> (buffer, meta) for a tensor spec of tests/golden/reference_cases.py."""
+    dt = NP[dtype]
+    if "buf" in spec:
+        shape = tuple(spec["shape"])
+        buf = np.array(spec["buf"], dtype=dt)
+    elif "ones" in spec:
+        shape = tuple(spec["ones"])
+        buf = np.ones(int(np.prod(shape, dtype=np.int64)) if shape else 1, dtype=dt)
+    else:
+        shape = tuple(spec["zeros"])
+        buf = np.zeros(int(np.prod(shape, dtype=np.int64)) if shape else 1, dtype=dt)
+    meta = engine.Meta.contiguous(shape)
+    for coord, value in spec.get("set", []):
+        buf[sum(c * s for c, s in zip(coord, meta.strides))] = value
+    for v in spec.get("view", []):
+        if v[0] == "slice":
+            meta = meta.slice(v[1], v[2], v[3], v[4])
+        elif v[0] == "index":
+            meta = meta.index(v[1], v[2])
+        elif v[0] == "permute":
+            meta = meta.permute(v[1])
+        else:
+            raise ValueError(v)
+    return buf, meta
+
+
+def check_values(case, out, shape):
+    assert list(shape) == list(case["shape"]), (case["name"], shape)
+    n = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+    out = np.asarray(out)[:n]
+    if "values" in case:
+        exp = np.array(case["values"], dtype=out.dtype)
+        assert np.array_equal(out, exp), (case["name"], out, exp)
+    if "all" in case:
+        assert np.all(out == np.array(case["all"], dtype=out.dtype)), (case["name"], out)
+    if "spots" in case:
+        strides = [1] * len(shape)
+        for k in range(len(shape) - 2, -1, -1):
+            strides[k] = strides[k + 1] * shape[k + 1]
+        for coord, v in case["spots"]:
+            got = out[sum(c * s for c, s in zip(coord, strides))]
+            assert got == np.array(v, dtype=out.dtype), (case["name"], coord, got, v)
+
+
+def run_case(case, engine):
+    kind = case["kind"]
+    if kind == "scalar_assign":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        em = case.get("expect_meta")
+        if em:
+            assert list(meta.shape) == em["shape"] and list(meta.strides) == em["strides"]
+            assert meta.offset == em["offset"] and meta.is_contiguous() == em["contiguous"]
+        for op, value in case["ops"]:
+            buf = engine.scalar_assign(buf, meta, BIN[op], value)
+        assert np.array_equal(buf, np.array(case["buf"], dtype=buf.dtype)), (case["name"], buf)
+    elif kind == "scalar":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        before = buf.copy()
+        out, shape = engine.scalar_out(buf, meta, BIN[case["op"]], case["value"])
+        check_values(case, out, shape)
+        assert np.array_equal(buf, before), case["name"]
+    elif kind == "binary":
+        a, am = build_tensor(case["a"], case["dtype"], engine)
+        b, bm = build_tensor(case["b"], case["dtype"], engine)
+        out, shape = engine.binary(a, am, b, bm, BIN[case["op"]])
+        check_values(case, out, shape)
+    elif kind == "binary_assign":
+        a, am = build_tensor(case["a"], case["dtype"], engine)
+        b, bm = build_tensor(case["b"], case["dtype"], engine)
+        a = engine.binary_assign(a, am, b, bm, BIN[case["op"]])
+        assert np.array_equal(a, np.array(case["buf"], dtype=a.dtype)), (case["name"], a)
+    elif kind == "broadcast_error":
+        ma = engine.Meta.contiguous(case["a_shape"])
+        mb = engine.Meta.contiguous(case["b_shape"])
+        try:
+            engine.broadcast_params(ma, mb)
+        except Exception:
+            return
+        raise AssertionError(f"{case['name']}: shapes should not broadcast")
+    elif kind == "assign_shape_error":
+        # `a op= b` requires the broadcast shape to equal a's shape (ops/broadcast/add.rs:26-31)
+        ma = engine.Meta.contiguous(case["a_shape"])
+        mb = engine.Meta.contiguous(case["b_shape"])
+        shape, _, _ = engine.broadcast_params(ma, mb)
+        assert tuple(shape) != tuple(ma.shape)
+    elif kind == "reduce_total":
+        a, am = build_tensor(case["a"], case["dtype"], engine)
+        got = engine.reduce_total(a, am, RED[case["op"]])
+        assert got == np.array(case["value"], dtype=a.dtype), (case["name"], repr(got))
+    elif kind == "reduce_axis":
+        a, am = build_tensor(case["a"], case["dtype"], engine)
+        out, shape = engine.reduce_axis(a, am, case["axis"], RED[case["op"]])
+        check_values(case, out, shape)
+    elif kind == "unary_fixture":
+        dt = NP[case["dtype"]]
+        d = np.array(case["definition"], dtype=dt)
+        if case["layout"] == "contiguous":
+            meta = engine.Meta.contiguous((2, 1))
+        elif case["layout"] == "1d":
+            meta = engine.Meta.contiguous((3, 1)).slice(0, None, None, 2)
+        else:
+            meta = engine.Meta.contiguous((4, 4, 1)).slice(0, None, None, 2).slice(1, None, None, 2)
+        truth = {"neg": lambda x: -x, "max0": lambda x: np.maximum(x, 0.0), "signum": np.sign}[case["truth"]]
+        view = np.lib.stride_tricks.as_strided(d[meta.offset:], shape=meta.shape,
+                                               strides=[s * d.itemsize for s in meta.strides])
+        exp = d.copy()
+        expv = np.lib.stride_tricks.as_strided(exp[meta.offset:], shape=meta.shape,
+                                               strides=[s * d.itemsize for s in meta.strides])
+        expv[...] = truth(view)
+        got = engine.unary_assign(d.copy(), meta, UN[case["op"]])
+        assert np.array_equal(got, exp), (case["name"], got, exp)
+    else:
+        raise ValueError(kind)
+
+
+def gather_view(buf, meta):
+    """Row-major copy of the viewed elements (what `contiguous()` / `owned()` produce)."""
+    if meta.size == 0:
+        return np.zeros(0, dtype=buf.dtype)
+    idx = np.full(meta.shape if meta.shape else (), meta.offset, dtype=np.int64)
+    for k, (n, s) in enumerate(zip(meta.shape, meta.strides)):
+        shp = [1] * len(meta.shape)
+        shp[k] = n
+        idx = idx + (np.arange(n, dtype=np.int64) * s).reshape(shp)
+    return buf[idx.reshape(-1)].copy()
+
+
+class OracleEngine:
+    """Adapter: the CPU oracle behind the engine interface."""
+
+    def __init__(self, fast=False):
+        import oracle
+        self.o = oracle
+        self.Meta = oracle.Meta
+        self.fast = fast
+
+    def broadcast_params(self, a, b):
+        return self.o.broadcast_params(a, b)
+
+    def scalar_assign(self, buf, meta, op, value):
+        self.o.scalar_op(buf, op, value, meta, self.fast)
+        return buf
+
+    def unary_assign(self, buf, meta, op):
+        self.o.unary_op(buf, op, meta, self.fast)
+        return buf
+
+    def scalar_out(self, buf, meta, op, value):
+        # out-of-place scalar op = owned() copy, then in place (ops/scalar/add.rs:93-97)
+        out = gather_view(buf, meta)
+        m = self.Meta.contiguous(meta.shape)
+        self.o.scalar_op(out, op, value, m, self.fast)
+        return out, meta.shape
+
+    def binary(self, a, am, b, bm, op):
+        out, dm = self.o.binary(a, am, b, bm, op, self.fast)
+        return out, dm.shape
+
+    def binary_assign(self, a, am, b, bm, op):
+        shape, sa, sb = self.o.broadcast_params(am, bm)
+        assert tuple(shape) == tuple(am.shape)
+        ma = self.Meta(shape, sa, am.offset)
+        self.o.broadcast(a, ma, b, self.Meta(shape, sb, bm.offset), a, ma, op, self.fast)
+        return a
+
+    def reduce_total(self, a, am, op):
+        return self.o.reduce_flat(a, am.offset, am.size, op, self.fast)[0]
+
+    def reduce_axis(self, a, am, axis, op):
+        out, om = self.o.reduce_axis(a, am, axis, op, self.fast)
+        return out, om.shape
