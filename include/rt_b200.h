@@ -1,0 +1,208 @@
+/*
+ * rt_b200.h -- C ABI of librt_b200.so: the tensor hot path of rtensors (scalar elementwise ops,
+ * N-d broadcast binary ops over strided / permuted / negative-step views, axis and full
+ * reductions, mean_l1_loss, reduce-to-shape) as hand-written CUDA for sm_100a.
+ *
+ * Two layers:
+ *   v1  the `launch_*` symbols of the reference's own kernel library, with identical
+ *       signatures, so the reference's `backend/cuda.rs` (bindgen over cuda/include/kernels.h)
+ *       links against this library unchanged.  Declared in rt_b200_v1.h.
+ *   v2  `rtb_*`: status-returning, stream-aware, host-side shape/stride (no per-call device
+ *       uploads), out-of-place and fused forms.  This is what new host glue should call.
+ *
+ * Conventions (both layers): every data pointer is a DEVICE pointer owned by the caller; the
+ * library never frees or retains it.  Offsets, shapes and strides are in ELEMENTS; strides may
+ * be zero (broadcast) or negative (reversed slice).  Work is enqueued on a stream and returns
+ * before completion; the caller synchronises before reading results on the host.  Citations
+ * give the reference interface each entry point replaces (paths relative to libs/rtensors/ of
+ * aheschl1/rtensors).
+ */
+#ifndef RT_B200_H
+#define RT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes = the reference's DType discriminants (src/core/value.rs:567-581) */
+typedef enum {
+    RTB_U8 = 0, RTB_I8 = 1, RTB_U16 = 2, RTB_I16 = 3, RTB_U32 = 4, RTB_U128 = 5, RTB_I32 = 6,
+    RTB_U64 = 7, RTB_I64 = 8, RTB_I128 = 9, RTB_F32 = 10, RTB_F64 = 11, RTB_BOOL = 12
+} rtb_dtype;
+
+/* binary op codes = OpCode (cuda/include/common.h:6-11) = BinaryOpType (src/ops/base.rs:7-12) */
+typedef enum { RTB_ADD = 0, RTB_SUB = 1, RTB_MUL = 2, RTB_DIV = 3 } rtb_binop;
+
+/* unary ops on the hot path (src/backend/cpu.rs:549-557, 632-657: CPU formulae) */
+typedef enum { RTB_NEG = 0, RTB_RELU = 1, RTB_ABS = 2, RTB_SIGN = 3 } rtb_unop;
+
+/* reduction codes = ReductionOpCode (cuda/include/common.h:19-30) */
+typedef enum { RTB_SUM = 1, RTB_PROD = 2, RTB_MAX = 3, RTB_MIN = 4, RTB_MEAN = 5 } rtb_redop;
+
+/* status codes; rtb_last_error_string() gives the text for the calling thread's last failure */
+typedef enum {
+    RTB_OK = 0,
+    RTB_ERR_INVALID = -1,     /* bad argument (null pointer, rank too large, unknown code)          */
+    RTB_ERR_DTYPE = -2,       /* op not defined for this dtype (e.g. boolean division, int reduce)  */
+    RTB_ERR_BROADCAST = -3,   /* shapes are not broadcastable (TensorError::BroadcastError)          */
+    RTB_ERR_BOUNDS = -4,      /* slice / extent out of bounds (TensorError::IdxOutOfBounds)          */
+    RTB_ERR_DIM = -5,         /* dimension out of range (TensorError::InvalidDim / WrongDims)        */
+    RTB_ERR_SHAPE = -6,       /* invalid shape or zero step (TensorError::InvalidShape)              */
+    RTB_ERR_NONCONTIG = -7,   /* reduction input must be contiguous (src/backend/mod.rs:385-389)     */
+    RTB_ERR_CUDA = -8,        /* a CUDA runtime call failed (TensorError::CudaError)                 */
+    RTB_ERR_ALLOC = -9,       /* device allocation failed                                            */
+    RTB_ERR_TOO_LARGE = -10   /* size beyond a stated limit                                          */
+} rtb_status;
+
+#define RTB_MAX_RANK 128 /* rank cap of the reference (src/core/primitives.rs:377-383) */
+
+typedef struct rtb_ctx rtb_ctx;
+
+/* ---- context: one per device, created once (replaces the per-call CudaContext + cuBLAS handle
+ *      churn of `CUDA_BACKENDS`, src/backend/cuda.rs:38-51,155-162) ------------------------- */
+int rtb_ctx_create(int device, rtb_ctx **out);
+void rtb_ctx_destroy(rtb_ctx *ctx);
+/* stream all later calls on this ctx are enqueued on (a cudaStream_t; NULL = legacy default) */
+int rtb_ctx_set_stream(rtb_ctx *ctx, void *stream);
+void *rtb_ctx_get_stream(rtb_ctx *ctx);
+int rtb_ctx_device(rtb_ctx *ctx);
+int rtb_ctx_sm_count(rtb_ctx *ctx);
+/* waits for the ctx stream (Cuda::sync, src/backend/cuda.rs:164-185) */
+int rtb_ctx_sync(rtb_ctx *ctx);
+/* number of kernels this ctx has launched since creation (bench bookkeeping) */
+uint64_t rtb_ctx_launch_count(rtb_ctx *ctx);
+const char *rtb_last_error_string(void);
+
+/* ---- device memory: caching allocator (Backend::alloc / alloc_from_slice / dump / copy,
+ *      src/backend/cuda.rs:668-836).  rtb_alloc returns UNINITIALISED memory: out-of-place ops
+ *      write every output element, so the zero-upload of `zeros_on`
+ *      (src/core/primitives.rs:463-468) is not needed. ---------------------------------------- */
+int rtb_alloc(rtb_ctx *ctx, size_t bytes, void **out);
+int rtb_free(rtb_ctx *ctx, void *ptr);
+int rtb_release_cached(rtb_ctx *ctx);
+int rtb_h2d(rtb_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int rtb_d2h(rtb_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes); /* synchronises */
+int rtb_d2d(rtb_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+
+/* ---- view arithmetic (host only; no CUDA call).  out arrays need room for `rank` (+1 for
+ *      unsqueeze) entries. --------------------------------------------------------------------- */
+/* shape_to_stride, src/core/meta.rs:495-503 */
+void rtb_meta_contiguous_strides(size_t rank, const size_t *shape, ptrdiff_t *strides);
+/* is_contiguous_relaxed, src/core/meta.rs:526-541 (|stride| dense, size-1 dims ignored) */
+int rtb_meta_is_contiguous(size_t rank, const size_t *shape, const ptrdiff_t *strides);
+/* compute_sliced_parameters, src/core/slice.rs:145-239 */
+int rtb_meta_slice(size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset, size_t dim,
+                   int has_start, size_t start, int has_end, size_t end, ptrdiff_t step, size_t *out_rank,
+                   size_t *out_shape, ptrdiff_t *out_strides, size_t *out_offset);
+/* compute_permuted_parameters, src/core/tensor.rs:909-941 */
+int rtb_meta_permute(size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t ndims,
+                     const size_t *dims, size_t *out_shape, ptrdiff_t *out_strides);
+/* compute_unsqueezed_parameters / compute_squeezed_parameters, src/core/tensor.rs:973-1027
+ * (squeeze: dim < 0 removes every size-1 dim) */
+int rtb_meta_unsqueeze(size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t dim,
+                       size_t *out_shape, ptrdiff_t *out_strides);
+int rtb_meta_squeeze(size_t rank, const size_t *shape, const ptrdiff_t *strides, ptrdiff_t dim,
+                     size_t *out_rank, size_t *out_shape, ptrdiff_t *out_strides);
+/* compute_broadcasted_params, src/ops/broadcast/mod.rs:13-55 */
+int rtb_broadcast_params(size_t ra, const size_t *shape_a, const ptrdiff_t *strides_a, size_t rb,
+                         const size_t *shape_b, const ptrdiff_t *strides_b, size_t *out_rank,
+                         size_t *out_shape, ptrdiff_t *out_strides_a, ptrdiff_t *out_strides_b);
+/* check_extent, src/backend/remote/server.rs:241-270: every addressed element of the view lies
+ * inside a buffer of buf_len elements */
+int rtb_meta_check_extent(size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset,
+                          size_t buf_len);
+
+/* The launch plan the library derives for an elementwise / broadcast call: size-1 dims dropped,
+ * negative output strides flipped, dims sorted by output stride, adjacent dims merged.  Exposed
+ * so the planner can be tested without a GPU.  kernel: 0 = nothing to do, 1 = flat vectorised
+ * (one contiguous run, operands share their 16-byte phase), 3 = tiled row kernel. */
+typedef struct {
+    int kernel;
+    int rank;             /* collapsed rank, 1..8 */
+    uint64_t shape[8];    /* shape[rank-1] is the inner (fastest) dim */
+    int64_t stride_d[8], stride_l[8], stride_r[8];
+    int64_t base_d, base_l, base_r; /* element offsets after flipping */
+    int vec;              /* elements per 16-byte vector for this dtype */
+    int mode_d, mode_l, mode_r; /* inner-dim access: 0 contig-vector 1 contig-scalar 2 reversed-vector
+                                   3 reversed-scalar 4 broadcast(stride 0) 5 strided */
+    int tile_x, tile_y;   /* thread tile of the row kernel */
+    uint64_t n_rows, n_col_chunks, grid;
+} rtb_plan;
+int rtb_plan_elementwise(int dtype, int n_inputs, size_t rank, const size_t *shape, const ptrdiff_t *stride_d,
+                         size_t off_d, uintptr_t ptr_d, const ptrdiff_t *stride_l, size_t off_l, uintptr_t ptr_l,
+                         const ptrdiff_t *stride_r, size_t off_r, uintptr_t ptr_r, rtb_plan *out);
+
+/* ---- elementwise, in place over a view (Backend::scalar_apply_{add,sub,mul,div},
+ *      apply_{neg,relu,abs,sign}, fill: src/backend/mod.rs:146-177, 239-268; kernels
+ *      cuda/kernels/elementwise/{scalar,unary,fill}.cu).  `value` points at one host element of
+ *      the dtype.  The three layout classes of the reference dispatcher (contiguous, 1-D strided,
+ *      N-d) are one call here; a view whose strides are dense up to sign is walked from its
+ *      lowest address. --------------------------------------------------------------------------- */
+int rtb_scalar_op(rtb_ctx *ctx, int dtype, int binop, void *buf, const void *value, size_t rank,
+                  const size_t *shape, const ptrdiff_t *strides, size_t offset);
+int rtb_unary_op(rtb_ctx *ctx, int dtype, int unop, void *buf, size_t rank, const size_t *shape,
+                 const ptrdiff_t *strides, size_t offset);
+int rtb_fill(rtb_ctx *ctx, int dtype, void *buf, const void *value, size_t rank, const size_t *shape,
+             const ptrdiff_t *strides, size_t offset);
+/* row-major copy of a view into contiguous memory (view_to_contiguous,
+ * src/core/tensor.rs:299-325: one kernel instead of a memcpy per run / per element) */
+int rtb_copy_view(rtb_ctx *ctx, int dtype, const void *src, size_t rank, const size_t *shape,
+                  const ptrdiff_t *strides, size_t offset, void *dst);
+
+/* ---- broadcast binary op (Backend::broadcast, src/backend/mod.rs:296-309; kernel
+ *      cuda/kernels/elementwise/binary/broadcast.cu:3-109).  All three views carry the OUTPUT
+ *      shape; operands are pre-broadcast by stride 0 on broadcast dims.  dst may alias left with
+ *      the same strides and offset (in-place form). ------------------------------------------- */
+int rtb_broadcast(rtb_ctx *ctx, int dtype, int binop, const void *left, const ptrdiff_t *stride_l, size_t off_l,
+                  const void *right, const ptrdiff_t *stride_r, size_t off_r, void *dst,
+                  const ptrdiff_t *stride_d, size_t off_d, size_t rank, const size_t *shape);
+
+/* ---- reductions, f32 / f64 (Backend::apply_reduce_contiguous_flat / _nd,
+ *      src/backend/mod.rs:357-409; kernels cuda/kernels/reduction/reduce.cu:239-274, 463-513).
+ *      src is row-major contiguous; flat: src[start .. start+len] -> dst[0]; axis: src viewed as
+ *      [outer, r, inner] from `offset` -> dst[outer*inner].  mean divides by (T)(float)count
+ *      (src/core/value.rs:54-56).  max/min start from the lowest/highest finite value and use
+ *      the CPU comparisons `v > acc` / `v < acc` (src/ops/reduction/mod.rs:43-120). ------------ */
+int rtb_reduce_flat(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t start, size_t len, void *dst);
+int rtb_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t offset, size_t outer, size_t r,
+                    size_t inner, void *dst);
+
+/* ---- fused L1 loss of two same-length contiguous tensors (L1::l1 + attach_l1_grad,
+ *      src/ops/broadcast/l1.rs:16-77: five launches and two temporaries in the reference).
+ *      reduction: 0 mean, 1 sum.  grad_map (may be NULL) receives sign(a-b), divided by
+ *      (T)(float)n for the mean form; sign(0) = 0 as on the CPU backend. ----------------------- */
+int rtb_l1_loss(rtb_ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss,
+                void *grad_map);
+
+/* ---- reduce-to-shape for broadcast gradients (inverse_broadcast_gradient,
+ *      src/grad/backwards.rs:512-538): sums the contiguous `upstream` of `shape` over every dim
+ *      whose operand stride is 0; out receives prod(out_shape) elements, the reduced dims kept as
+ *      size 1.  f32 / f64. ------------------------------------------------------------------------ */
+int rtb_reduce_to_shape(rtb_ctx *ctx, int dtype, const void *upstream, size_t rank, const size_t *shape,
+                        const ptrdiff_t *operand_strides, void *out, size_t *out_shape);
+
+/* ---- fused pieces of the autograd MLP step (f32) --------------------------------------------
+ * relu with its gradient mask in one pass (relu_inplace + the per-element mask loop of
+ * src/ops/unary/mod.rs:213-252): x = x>0 ? x : 0, mask = x>0 ? 1 : 0 */
+int rtb_relu_mask_f32(rtb_ctx *ctx, float *x, float *mask, size_t n);
+/* SGD::step (src/grad/optim.rs:30-50): u = g*lr rounded, then p = p - u (no FMA) */
+int rtb_sgd_update_f32(rtb_ctx *ctx, float *p, const float *g, float lr, size_t n);
+/* Backend::convert u8 -> f32 followed by `/ divisor` (src/backend/cuda.rs:790-812,
+ * examples/mnist/src/main.rs:108-111) */
+int rtb_u8_to_f32_div(rtb_ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n);
+
+/* ---- multi-GPU sharding (new; the reference is single-device).  Host-only arithmetic: rank
+ *      `part` of `parts` gets the half-open slab [*begin, *end) of an extent, earlier ranks
+ *      taking the remainder. -------------------------------------------------------------------- */
+void rtb_shard_range(size_t extent, size_t parts, size_t part, size_t *begin, size_t *end);
+/* picks the outermost dim of an output shape with extent >= parts (src of the slab split);
+ * returns -1 if none */
+int rtb_shard_pick_dim(size_t rank, const size_t *shape, size_t parts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RT_B200_H */

@@ -1,0 +1,228 @@
+"""Host-side mirror of the reference's `Backend` trait for the hot path (src/backend/mod.rs:216-472)
+on top of the C ABI.  Device memory and streams come from PyTorch; every computation is a call
+into librt_b200.so.  Method names and argument meaning follow the trait: `scalar_apply_*`,
+`apply_*`, `fill`, `broadcast`, `apply_reduce_contiguous_flat`, `apply_reduce` ...
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from ._lib import check, diffs, lib, sizes
+from .meta import Meta, broadcast_params
+
+TORCH_TO_CODE = {
+    torch.uint8: L.U8, torch.int8: L.I8, torch.int16: L.I16, torch.int32: L.I32, torch.int64: L.I64,
+    torch.float32: L.F32, torch.float64: L.F64, torch.bool: L.BOOL,
+}
+for _name, _code in (("uint16", L.U16), ("uint32", L.U32), ("uint64", L.U64)):
+    if hasattr(torch, _name):
+        TORCH_TO_CODE[getattr(torch, _name)] = _code
+CODE_TO_TORCH = {v: k for k, v in TORCH_TO_CODE.items()}
+CODE_TO_NP = {L.U8: np.uint8, L.I8: np.int8, L.U16: np.uint16, L.I16: np.int16, L.U32: np.uint32, L.I32: np.int32,
+              L.U64: np.uint64, L.I64: np.int64, L.F32: np.float32, L.F64: np.float64, L.BOOL: np.bool_}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    return TORCH_TO_CODE[t.dtype]
+
+
+def _scalar_bytes(code: int, value):
+    np_dt = CODE_TO_NP[code]
+    return np.array([value], dtype=np_dt)
+
+
+class CudaB200:
+    """One instance per device (`Cuda` of the reference, src/backend/cuda.rs:38-186): owns the
+    library context (stream, workspace, allocator).  Calls are enqueued on torch's current
+    stream of that device."""
+
+    def __init__(self, device: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaB200 needs a CUDA device; there is no CPU fallback")
+        self.device = int(device)
+        torch.cuda.set_device(self.device)
+        self._ctx = C.c_void_p()
+        check(lib().rtb_ctx_create(C.c_int(self.device), C.byref(self._ctx)))
+        self._stream = None
+        self.sync_stream()
+
+    def close(self):
+        if self._ctx:
+            lib().rtb_ctx_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- plumbing ---------------------------------------------------------------------------
+    def sync_stream(self):
+        """Binds the context to torch's current stream (call after switching streams)."""
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        if s != self._stream:
+            check(lib().rtb_ctx_set_stream(self._ctx, C.c_void_p(s)))
+            self._stream = s
+
+    def sync(self):
+        check(lib().rtb_ctx_sync(self._ctx))
+
+    @property
+    def launches(self) -> int:
+        return int(lib().rtb_ctx_launch_count(self._ctx))
+
+    @property
+    def sm_count(self) -> int:
+        return int(lib().rtb_ctx_sm_count(self._ctx))
+
+    def alloc(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """Uninitialised device buffer (Backend::alloc)."""
+        return torch.empty(int(n), dtype=dtype, device=f"cuda:{self.device}")
+
+    def alloc_from_slice(self, host: np.ndarray) -> torch.Tensor:
+        return torch.from_numpy(np.ascontiguousarray(host).reshape(-1)).to(f"cuda:{self.device}")
+
+    def dump(self, buf: torch.Tensor) -> np.ndarray:
+        return buf.detach().cpu().numpy()
+
+    @staticmethod
+    def _p(t: Optional[torch.Tensor]):
+        return C.c_void_p(0 if t is None else t.data_ptr())
+
+    # -- elementwise over a view --------------------------------------------------------------
+    def scalar_apply(self, buf: torch.Tensor, op: int, value, meta: Meta, dtype: Optional[int] = None):
+        code = dtype_code(buf) if dtype is None else dtype
+        v = _scalar_bytes(code, value)
+        meta.check_extent(buf.numel())
+        check(lib().rtb_scalar_op(self._ctx, C.c_int(code), C.c_int(op), self._p(buf), v.ctypes.data_as(C.c_void_p),
+                                  C.c_size_t(meta.rank), sizes(meta.shape), diffs(meta.strides),
+                                  C.c_size_t(meta.offset)))
+
+    def scalar_apply_add(self, buf, value, meta): self.scalar_apply(buf, L.ADD, value, meta)
+    def scalar_apply_sub(self, buf, value, meta): self.scalar_apply(buf, L.SUB, value, meta)
+    def scalar_apply_mul(self, buf, value, meta): self.scalar_apply(buf, L.MUL, value, meta)
+    def scalar_apply_div(self, buf, value, meta): self.scalar_apply(buf, L.DIV, value, meta)
+
+    def apply_unary(self, buf: torch.Tensor, op: int, meta: Meta):
+        meta.check_extent(buf.numel())
+        check(lib().rtb_unary_op(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(meta.rank),
+                                 sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset)))
+
+    def apply_neg(self, buf, meta): self.apply_unary(buf, L.NEG, meta)
+    def apply_relu(self, buf, meta): self.apply_unary(buf, L.RELU, meta)
+    def apply_abs(self, buf, meta): self.apply_unary(buf, L.ABS, meta)
+    def apply_sign(self, buf, meta): self.apply_unary(buf, L.SIGN, meta)
+
+    def fill(self, buf: torch.Tensor, value, meta: Meta):
+        code = dtype_code(buf)
+        v = _scalar_bytes(code, value)
+        meta.check_extent(buf.numel())
+        check(lib().rtb_fill(self._ctx, C.c_int(code), self._p(buf), v.ctypes.data_as(C.c_void_p),
+                             C.c_size_t(meta.rank), sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset)))
+
+    def contiguous(self, buf: torch.Tensor, meta: Meta) -> torch.Tensor:
+        """Row-major copy of a view (view_to_contiguous, src/core/tensor.rs:299-325)."""
+        out = self.alloc(max(meta.size, 1), buf.dtype)
+        if meta.size:
+            meta.check_extent(buf.numel())
+            check(lib().rtb_copy_view(self._ctx, C.c_int(dtype_code(buf)), self._p(buf), C.c_size_t(meta.rank),
+                                      sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset), self._p(out)))
+        return out
+
+    # -- broadcast ----------------------------------------------------------------------------
+    def broadcast(self, left: Tuple[torch.Tensor, Meta], right: Tuple[torch.Tensor, Meta],
+                  dst: Tuple[torch.Tensor, Meta], op: int):
+        """Backend::broadcast: the three metas carry the output shape; dst may be left."""
+        (lb, lm), (rb, rm), (db, dm) = left, right, dst
+        assert lm.shape == rm.shape == dm.shape
+        lm.check_extent(lb.numel()); rm.check_extent(rb.numel()); dm.check_extent(db.numel())
+        check(lib().rtb_broadcast(self._ctx, C.c_int(dtype_code(db)), C.c_int(op), self._p(lb), diffs(lm.strides),
+                                  C.c_size_t(lm.offset), self._p(rb), diffs(rm.strides), C.c_size_t(rm.offset),
+                                  self._p(db), diffs(dm.strides), C.c_size_t(dm.offset), C.c_size_t(dm.rank),
+                                  sizes(dm.shape)))
+
+    def binary(self, a: torch.Tensor, am: Meta, b: torch.Tensor, bm: Meta, op: int):
+        """`a op b` as the operator impls do it (src/ops/broadcast/add.rs:441-477), except that the
+        output is allocated uninitialised instead of uploaded as zeros."""
+        shape, sa, sb = broadcast_params(am, bm)
+        dm = Meta.contiguous(shape)
+        out = self.alloc(max(dm.size, 1), a.dtype)
+        self.broadcast((a, Meta(shape, sa, am.offset)), (b, Meta(shape, sb, bm.offset)), (out, dm), op)
+        return out, dm
+
+    def binary_assign(self, a: torch.Tensor, am: Meta, b: torch.Tensor, bm: Meta, op: int):
+        """`a op= b` (src/ops/broadcast/add.rs:14-46): the broadcast shape must be a's shape."""
+        shape, sa, sb = broadcast_params(am, bm)
+        if tuple(shape) != tuple(am.shape):
+            raise ValueError(f"Incompatible shapes for in-place op: {bm.shape} does not broadcast to {am.shape}")
+        ma = Meta(shape, sa, am.offset)
+        self.broadcast((a, ma), (b, Meta(shape, sb, bm.offset)), (a, ma), op)
+
+    # -- reductions ---------------------------------------------------------------------------
+    def apply_reduce_contiguous_flat(self, src: torch.Tensor, dst: torch.Tensor, start: int, length: int, op: int):
+        if start + length > src.numel():
+            raise L.RtbError(-4, "flat reduction range exceeds the buffer")
+        check(lib().rtb_reduce_flat(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(start),
+                                    C.c_size_t(length), self._p(dst)))
+
+    def apply_reduce(self, src: Tuple[torch.Tensor, Meta], dst: torch.Tensor, dim: int, op: int):
+        """Backend::apply_reduce (src/backend/mod.rs:375-409): contiguous input; rank 1 -> flat."""
+        sb, sm = src
+        if not sm.is_contiguous():
+            raise L.RtbError(-7, "Reduction over non-contiguous tensors is not implemented yet.")
+        if sm.rank == 1:
+            return self.apply_reduce_contiguous_flat(sb, dst, sm.offset, sm.size, op)
+        outer = int(np.prod(sm.shape[:dim], dtype=np.int64)) if dim > 0 else 1
+        inner = max(int(np.prod(sm.shape[dim + 1:], dtype=np.int64)), 1)
+        r = sm.shape[dim]
+        if sm.offset + outer * r * inner > sb.numel():
+            raise L.RtbError(-4, "axis reduction range exceeds the buffer")
+        check(lib().rtb_reduce_axis(self._ctx, C.c_int(dtype_code(sb)), C.c_int(op), self._p(sb),
+                                    C.c_size_t(sm.offset), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
+                                    self._p(dst)))
+
+    def reduce_axis_ori(self, src: torch.Tensor, offset: int, outer: int, r: int, inner: int, op: int):
+        out = self.alloc(max(outer * inner, 1), src.dtype)
+        check(lib().rtb_reduce_axis(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(offset),
+                                    C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner), self._p(out)))
+        return out
+
+    def l1_loss(self, a: torch.Tensor, b: torch.Tensor, reduction: int = 0, with_grad: bool = False):
+        assert a.numel() == b.numel() and a.dtype == b.dtype
+        loss = self.alloc(1, a.dtype)
+        g = self.alloc(a.numel(), a.dtype) if with_grad else None
+        check(lib().rtb_l1_loss(self._ctx, C.c_int(dtype_code(a)), self._p(a), self._p(b), C.c_size_t(a.numel()),
+                                C.c_int(reduction), self._p(loss), self._p(g)))
+        return loss, g
+
+    def reduce_to_shape(self, upstream: torch.Tensor, shape: Sequence[int], operand_strides: Sequence[int]):
+        r = len(shape)
+        oshape = tuple(1 if s == 0 else n for n, s in zip(shape, operand_strides))
+        n_out = int(np.prod(oshape, dtype=np.int64)) if r else 1
+        out = self.alloc(max(n_out, 1), upstream.dtype)
+        osh = (C.c_size_t * max(r, 1))()
+        check(lib().rtb_reduce_to_shape(self._ctx, C.c_int(dtype_code(upstream)), self._p(upstream), C.c_size_t(r),
+                                        sizes(shape), diffs(operand_strides), self._p(out), osh))
+        assert tuple(osh[:r]) == oshape
+        return out, oshape
+
+    # -- fused MLP pieces ---------------------------------------------------------------------
+    def relu_mask(self, x: torch.Tensor) -> torch.Tensor:
+        mask = torch.empty_like(x)
+        check(lib().rtb_relu_mask_f32(self._ctx, self._p(x), self._p(mask), C.c_size_t(x.numel())))
+        return mask
+
+    def sgd_update(self, p: torch.Tensor, g: torch.Tensor, lr: float):
+        check(lib().rtb_sgd_update_f32(self._ctx, self._p(p), self._p(g), C.c_float(lr), C.c_size_t(p.numel())))
+
+    def u8_to_f32_div(self, src: torch.Tensor, divisor: float = 255.0) -> torch.Tensor:
+        out = self.alloc(src.numel(), torch.float32)
+        check(lib().rtb_u8_to_f32_div(self._ctx, self._p(src), self._p(out), C.c_float(divisor),
+                                      C.c_size_t(src.numel())))
+        return out

@@ -1,0 +1,250 @@
+// C ABI v2 (`rtb_*`) compute entry points: argument checks, planning, dispatch to the kernels.
+#include <vector>
+
+#include "rtb_internal.h"
+
+namespace rtb {
+
+#define RTB_DECL_EW(S) int ew_dispatch_##S(Ctx *, const EwCall &, const rtb_plan &);
+RTB_DECL_EW(u8) RTB_DECL_EW(i8) RTB_DECL_EW(u16) RTB_DECL_EW(i16) RTB_DECL_EW(u32) RTB_DECL_EW(u128) RTB_DECL_EW(i32)
+RTB_DECL_EW(u64) RTB_DECL_EW(i64) RTB_DECL_EW(i128) RTB_DECL_EW(f32) RTB_DECL_EW(f64) RTB_DECL_EW(boolean)
+
+int launch_elementwise(Ctx *ctx, const EwCall &c, const rtb_plan &plan) {
+    if (plan.kernel == kNothing) return RTB_OK;
+    switch (c.dtype) {
+        case RTB_U8: return ew_dispatch_u8(ctx, c, plan);
+        case RTB_I8: return ew_dispatch_i8(ctx, c, plan);
+        case RTB_U16: return ew_dispatch_u16(ctx, c, plan);
+        case RTB_I16: return ew_dispatch_i16(ctx, c, plan);
+        case RTB_U32: return ew_dispatch_u32(ctx, c, plan);
+        case RTB_U128: return ew_dispatch_u128(ctx, c, plan);
+        case RTB_I32: return ew_dispatch_i32(ctx, c, plan);
+        case RTB_U64: return ew_dispatch_u64(ctx, c, plan);
+        case RTB_I64: return ew_dispatch_i64(ctx, c, plan);
+        case RTB_I128: return ew_dispatch_i128(ctx, c, plan);
+        case RTB_F32: return ew_dispatch_f32(ctx, c, plan);
+        case RTB_F64: return ew_dispatch_f64(ctx, c, plan);
+        case RTB_BOOL: return ew_dispatch_boolean(ctx, c, plan);
+    }
+    return fail(RTB_ERR_DTYPE, "unknown dtype %d", c.dtype);
+}
+
+static int n_inputs_of(int family) { return family == kFamBinary ? 2 : family == kFamFill ? 0 : 1; }
+
+int run_elementwise(Ctx *ctx, const EwCall &call, size_t rank, const size_t *shape, const ptrdiff_t *sd, size_t od,
+                    const ptrdiff_t *sl, size_t ol, const ptrdiff_t *sr, size_t orr) {
+    const size_t es = dtype_size(call.dtype);
+    if (!es) return fail(RTB_ERR_DTYPE, "unknown dtype %d", call.dtype);
+    const int nin = n_inputs_of(call.family);
+    ViewArg d{sd, od, (uintptr_t)call.d}, l{sl, ol, (uintptr_t)call.l}, r{sr, orr, (uintptr_t)call.r};
+    rtb_plan plan;
+    int rc = make_plan(es, nin, rank, shape, d, l, r, &plan);
+    if (rc == RTB_OK) return launch_elementwise(ctx, call, plan);
+    if (rc != RTB_ERR_TOO_LARGE || rank == 0) return rc;
+    // More dims (or rows) than one launch takes: peel the outermost dim on the host.
+    size_t k0 = 0;
+    while (k0 < rank && shape[k0] == 1) ++k0;
+    if (k0 == rank) return rc;
+    std::vector<size_t> sub(shape, shape + rank);
+    sub[k0] = 1;
+    for (size_t i = 0; i < shape[k0]; ++i) {
+        int64_t dd = (int64_t)od + (int64_t)i * sd[k0];
+        int64_t dl = nin >= 1 ? (int64_t)ol + (int64_t)i * sl[k0] : 0;
+        int64_t dr = nin >= 2 ? (int64_t)orr + (int64_t)i * sr[k0] : 0;
+        rc = run_elementwise(ctx, call, rank, sub.data(), sd, (size_t)dd, sl, (size_t)dl, sr, (size_t)dr);
+        if (rc != RTB_OK) return rc;
+    }
+    return RTB_OK;
+}
+
+static int use_device(Ctx *ctx) {
+    int cur = -1;
+    RTB_CUDA(cudaGetDevice(&cur));
+    if (cur != ctx->device) RTB_CUDA(cudaSetDevice(ctx->device));
+    return RTB_OK;
+}
+
+static int check_view_args(rtb_ctx *c, const void *buf, size_t rank, const size_t *shape, const ptrdiff_t *strides) {
+    if (!c) return fail(RTB_ERR_INVALID, "null ctx");
+    if (!buf) return fail(RTB_ERR_INVALID, "null buffer");
+    if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
+    if (rank && (!shape || !strides)) return fail(RTB_ERR_INVALID, "null shape or strides");
+    return RTB_OK;
+}
+
+}  // namespace rtb
+
+using namespace rtb;
+
+static inline Ctx *C(rtb_ctx *c) { return reinterpret_cast<Ctx *>(c); }
+
+RTB_API int rtb_scalar_op(rtb_ctx *c, int dtype, int binop, void *buf, const void *value, size_t rank,
+                          const size_t *shape, const ptrdiff_t *strides, size_t offset) {
+    int rc = check_view_args(c, buf, rank, shape, strides);
+    if (rc) return rc;
+    if (!value) return fail(RTB_ERR_INVALID, "null scalar value");
+    size_t es = dtype_size(dtype);
+    if (!es) return fail(RTB_ERR_DTYPE, "unknown dtype %d", dtype);
+    if ((rc = use_device(C(c)))) return rc;
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamScalar; call.op = binop;
+    std::memcpy(call.value, value, es);
+    call.d = buf; call.l = buf; call.r = nullptr;
+    return run_elementwise(C(c), call, rank, shape, strides, offset, strides, offset, nullptr, 0);
+}
+
+RTB_API int rtb_unary_op(rtb_ctx *c, int dtype, int unop, void *buf, size_t rank, const size_t *shape,
+                         const ptrdiff_t *strides, size_t offset) {
+    int rc = check_view_args(c, buf, rank, shape, strides);
+    if (rc) return rc;
+    if ((rc = use_device(C(c)))) return rc;
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamUnary; call.op = unop;
+    call.d = buf; call.l = buf; call.r = nullptr;
+    return run_elementwise(C(c), call, rank, shape, strides, offset, strides, offset, nullptr, 0);
+}
+
+RTB_API int rtb_fill(rtb_ctx *c, int dtype, void *buf, const void *value, size_t rank, const size_t *shape,
+                     const ptrdiff_t *strides, size_t offset) {
+    int rc = check_view_args(c, buf, rank, shape, strides);
+    if (rc) return rc;
+    if (!value) return fail(RTB_ERR_INVALID, "null fill value");
+    size_t es = dtype_size(dtype);
+    if (!es) return fail(RTB_ERR_DTYPE, "unknown dtype %d", dtype);
+    if ((rc = use_device(C(c)))) return rc;
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamFill; call.op = 0;
+    std::memcpy(call.value, value, es);
+    call.d = buf; call.l = nullptr; call.r = nullptr;
+    return run_elementwise(C(c), call, rank, shape, strides, offset, nullptr, 0, nullptr, 0);
+}
+
+RTB_API int rtb_copy_view(rtb_ctx *c, int dtype, const void *src, size_t rank, const size_t *shape,
+                          const ptrdiff_t *strides, size_t offset, void *dst) {
+    int rc = check_view_args(c, src, rank, shape, strides);
+    if (rc) return rc;
+    if (!dst) return fail(RTB_ERR_INVALID, "null destination");
+    if ((rc = use_device(C(c)))) return rc;
+    std::vector<ptrdiff_t> dense(rank ? rank : 1);
+    rtb_meta_contiguous_strides(rank, shape, dense.data());
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamCopy; call.op = 0;
+    call.d = dst; call.l = src; call.r = nullptr;
+    return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
+}
+
+RTB_API int rtb_broadcast(rtb_ctx *c, int dtype, int binop, const void *left, const ptrdiff_t *sl, size_t ol,
+                          const void *right, const ptrdiff_t *sr, size_t orr, void *dst, const ptrdiff_t *sd,
+                          size_t od, size_t rank, const size_t *shape) {
+    if (!c) return fail(RTB_ERR_INVALID, "null ctx");
+    if (!left || !right || !dst) return fail(RTB_ERR_INVALID, "null operand");
+    if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
+    if (rank && (!shape || !sl || !sr || !sd)) return fail(RTB_ERR_INVALID, "null shape or strides");
+    if (binop < RTB_ADD || binop > RTB_DIV) return fail(RTB_ERR_INVALID, "unknown binary op %d", binop);
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamBinary; call.op = binop;
+    call.d = dst; call.l = left; call.r = right;
+    return run_elementwise(C(c), call, rank, shape, sd, od, sl, ol, sr, orr);
+}
+
+RTB_API int rtb_reduce_flat(rtb_ctx *c, int dtype, int redop, const void *src, size_t start, size_t len, void *dst) {
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    size_t es = dtype_size(dtype);
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_reduce_flat(C(c), dtype, redop, (const char *)src + start * es, len, dst);
+}
+
+RTB_API int rtb_reduce_axis(rtb_ctx *c, int dtype, int redop, const void *src, size_t offset, size_t outer, size_t r,
+                            size_t inner, void *dst) {
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    size_t es = dtype_size(dtype);
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    if (outer == 0 || inner == 0) return RTB_OK;  // no outputs: nothing to launch
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_reduce_axis(C(c), dtype, redop, (const char *)src + offset * es, outer, r, inner, dst);
+}
+
+RTB_API int rtb_l1_loss(rtb_ctx *c, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss,
+                        void *grad_map) {
+    if (!c || !a || !b || !loss) return fail(RTB_ERR_INVALID, "null argument");
+    if (reduction != 0 && reduction != 1) return fail(RTB_ERR_INVALID, "reduction must be 0 (mean) or 1 (sum)");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_l1(C(c), dtype, a, b, n, reduction, loss, grad_map);
+}
+
+RTB_API int rtb_reduce_to_shape(rtb_ctx *c, int dtype, const void *upstream, size_t rank, const size_t *shape,
+                                const ptrdiff_t *operand_strides, void *out, size_t *out_shape) {
+    if (!c || !upstream || !out || !out_shape) return fail(RTB_ERR_INVALID, "null argument");
+    if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
+    size_t es = dtype_size(dtype);
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reduce_to_shape is defined for f32 and f64 only");
+    Ctx *ctx = C(c);
+    int rc = use_device(ctx);
+    if (rc) return rc;
+    std::vector<size_t> cur(shape, shape + rank);
+    size_t total = 1;
+    for (size_t k = 0; k < rank; ++k) total *= shape[k];
+    // Runs of adjacent broadcast dims are summed in one pass each; between passes the running
+    // tensor lives in allocator blocks (the reduction workspace is busy inside a pass).
+    std::vector<std::pair<size_t, size_t>> runs;  // [first, last] dims with operand stride 0
+    for (size_t k = 0; k < rank; ++k) {
+        if (operand_strides[k] != 0) continue;
+        if (!runs.empty() && runs.back().second + 1 == k) runs.back().second = k;
+        else runs.emplace_back(k, k);
+    }
+    for (size_t k = 0; k < rank; ++k) out_shape[k] = operand_strides[k] == 0 ? 1 : shape[k];
+    if (total == 0) return RTB_OK;
+    if (runs.empty()) return rtb_d2d(c, out, upstream, total * es);
+    const void *src = upstream;
+    void *tmp[2] = {nullptr, nullptr};
+    int which = 0;
+    rc = RTB_OK;
+    for (size_t i = 0; i < runs.size() && rc == RTB_OK; ++i) {
+        size_t outer = 1, r = 1, inner = 1;
+        for (size_t k = 0; k < runs[i].first; ++k) outer *= cur[k];
+        for (size_t k = runs[i].first; k <= runs[i].second; ++k) r *= cur[k];
+        for (size_t k = runs[i].second + 1; k < rank; ++k) inner *= cur[k];
+        void *dst = out;
+        if (i + 1 < runs.size()) {
+            if (tmp[which]) rtb_free(c, tmp[which]);
+            tmp[which] = nullptr;
+            rc = rtb_alloc(c, outer * inner * es, &tmp[which]);
+            if (rc != RTB_OK) break;
+            dst = tmp[which];
+        }
+        rc = launch_reduce_axis(ctx, dtype, RTB_SUM, src, outer, r, inner, dst);
+        for (size_t k = runs[i].first; k <= runs[i].second; ++k) cur[k] = 1;
+        src = dst;
+        which ^= 1;
+    }
+    for (int k = 0; k < 2; ++k)
+        if (tmp[k]) rtb_free(c, tmp[k]);
+    return rc;
+}
+
+RTB_API int rtb_relu_mask_f32(rtb_ctx *c, float *x, float *mask, size_t n) {
+    if (!c || !x || !mask) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_relu_mask(C(c), x, mask, n);
+}
+
+RTB_API int rtb_sgd_update_f32(rtb_ctx *c, float *p, const float *g, float lr, size_t n) {
+    if (!c || !p || !g) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_sgd(C(c), p, g, lr, n);
+}
+
+RTB_API int rtb_u8_to_f32_div(rtb_ctx *c, const uint8_t *src, float *dst, float divisor, size_t n) {
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_u8_f32(C(c), src, dst, divisor, n);
+}

@@ -1,0 +1,405 @@
+// Elementwise engine for ONE dtype: compiled once per dtype with -DRTB_EW_DTYPE=<rtb_dtype code>.
+//
+// Two kernels serve every elementwise family (broadcast binary, scalar op, unary op, fill, copy):
+//
+//   flat_kernel  one contiguous run per operand, all operands in the same 16-byte phase.
+//                A scalar head brings the pointers to a 16-byte boundary, the body moves 128-bit
+//                vectors (four independent loads in flight per thread before the first store),
+//                a scalar tail finishes.  HBM-bound: 2*s bytes per element in place, 3*s for a
+//                same-shape binary op.
+//   rows_kernel  everything else, after the planner collapsed the view to <= 8 dims.  A CTA owns
+//                a tile of (rows x 128-bit columns); the row index is decoded once per vector
+//                with multiply-shift division, never per element.  Each operand's walk along the
+//                inner dim is one of: contiguous (vector or scalar), reversed (vector load at the
+//                mirrored address + lane reversal), broadcast (one load, splat) or strided.
+//
+// Arithmetic follows the reference CPU backend (src/backend/cpu.rs:549-557, 632-657, 679-696;
+// src/ops/base.rs:29-36; src/core/value.rs:515-548, 708-764): integers wrap, boolean + - * are
+// OR XOR AND, relu is `x > 0 ? x : 0`, sign(0) = 0.  Built with --fmad=false and precise division
+// so each float op is the single IEEE operation the CPU performs.
+#include "rtb_internal.h"
+
+#ifndef RTB_EW_DTYPE
+#error "compile with -DRTB_EW_DTYPE=<code>"
+#endif
+
+namespace rtb {
+namespace {
+
+#if RTB_EW_DTYPE == 0
+using T = uint8_t; using UT = uint8_t;
+#define RTB_KIND 0 /* unsigned */
+#define RTB_SUFFIX u8
+#elif RTB_EW_DTYPE == 1
+using T = int8_t; using UT = uint8_t;
+#define RTB_KIND 1 /* signed */
+#define RTB_SUFFIX i8
+#elif RTB_EW_DTYPE == 2
+using T = uint16_t; using UT = uint16_t;
+#define RTB_KIND 0
+#define RTB_SUFFIX u16
+#elif RTB_EW_DTYPE == 3
+using T = int16_t; using UT = uint16_t;
+#define RTB_KIND 1
+#define RTB_SUFFIX i16
+#elif RTB_EW_DTYPE == 4
+using T = uint32_t; using UT = uint32_t;
+#define RTB_KIND 0
+#define RTB_SUFFIX u32
+#elif RTB_EW_DTYPE == 5
+using T = unsigned __int128; using UT = unsigned __int128;
+#define RTB_KIND 0
+#define RTB_SUFFIX u128
+#elif RTB_EW_DTYPE == 6
+using T = int32_t; using UT = uint32_t;
+#define RTB_KIND 1
+#define RTB_SUFFIX i32
+#elif RTB_EW_DTYPE == 7
+using T = uint64_t; using UT = uint64_t;
+#define RTB_KIND 0
+#define RTB_SUFFIX u64
+#elif RTB_EW_DTYPE == 8
+using T = int64_t; using UT = uint64_t;
+#define RTB_KIND 1
+#define RTB_SUFFIX i64
+#elif RTB_EW_DTYPE == 9
+using T = __int128; using UT = unsigned __int128;
+#define RTB_KIND 1
+#define RTB_SUFFIX i128
+#elif RTB_EW_DTYPE == 10
+using T = float; using UT = float;
+#define RTB_KIND 2 /* float */
+#define RTB_SUFFIX f32
+#elif RTB_EW_DTYPE == 11
+using T = double; using UT = double;
+#define RTB_KIND 2
+#define RTB_SUFFIX f64
+#elif RTB_EW_DTYPE == 12
+using T = uint8_t; using UT = uint8_t;
+#define RTB_KIND 3 /* boolean, stored as one byte 0/1 */
+#define RTB_SUFFIX boolean
+#else
+#error "unknown dtype code"
+#endif
+
+constexpr int VEC = sizeof(T) >= 16 ? 1 : 16 / (int)sizeof(T);
+
+union Vec {
+    uint4 q;
+    T e[VEC];
+};
+
+// ---- arithmetic --------------------------------------------------------------------------------
+template <int OP>
+__device__ __forceinline__ T bin(T a, T b) {
+#if RTB_KIND == 3
+    if (OP == RTB_ADD) return (T)((a != 0) | (b != 0));
+    if (OP == RTB_SUB) return (T)((a != 0) ^ (b != 0));
+    return (T)((a != 0) & (b != 0));
+#elif RTB_KIND == 2
+    if (OP == RTB_ADD) return a + b;
+    if (OP == RTB_SUB) return a - b;
+    if (OP == RTB_MUL) return a * b;
+    return a / b;
+#else
+    if (OP == RTB_ADD) return (T)((UT)a + (UT)b);
+    if (OP == RTB_SUB) return (T)((UT)a - (UT)b);
+    if (OP == RTB_MUL) return (T)((UT)a * (UT)b);
+    return b == (T)0 ? (T)0 : (T)(a / b);  // the reference panics on /0; here the result is 0
+#endif
+}
+
+template <int OP>
+__device__ __forceinline__ T una(T x) {
+#if RTB_KIND == 2
+    if (OP == RTB_NEG) return -x;
+    if (OP == RTB_RELU) return x > (T)0 ? x : (T)0;
+    if (OP == RTB_ABS) return sizeof(T) == 4 ? (T)fabsf((float)x) : (T)fabs((double)x);
+    return x < (T)0 ? (T)-1 : (x > (T)0 ? (T)1 : (T)0);
+#elif RTB_KIND == 1
+    if (OP == RTB_NEG) return (T)((UT)0 - (UT)x);
+    if (OP == RTB_RELU) return x > (T)0 ? x : (T)0;
+    if (OP == RTB_ABS) return x < (T)0 ? (T)((UT)0 - (UT)x) : x;
+    return x < (T)0 ? (T)-1 : (x > (T)0 ? (T)1 : (T)0);
+#else
+    if (OP == RTB_SIGN) return x > (T)0 ? (T)1 : (T)0;
+    return x;  // relu / abs of an unsigned or boolean value is the value
+#endif
+}
+
+// family functors: f(left, right) -> out
+template <int OP> struct FBinary { __device__ __forceinline__ T operator()(T a, T b) const { return bin<OP>(a, b); } };
+template <int OP> struct FScalar { T v; __device__ __forceinline__ T operator()(T a, T) const { return bin<OP>(a, v); } };
+template <int OP> struct FUnary { __device__ __forceinline__ T operator()(T a, T) const { return una<OP>(a); } };
+struct FFill { T v; __device__ __forceinline__ T operator()(T, T) const { return v; } };
+struct FCopy { __device__ __forceinline__ T operator()(T a, T) const { return a; } };
+
+// ---- flat kernel -------------------------------------------------------------------------------
+constexpr int kBlock = 256;
+constexpr int kUnroll = 4;
+
+template <typename F, int NIN>
+__global__ void __launch_bounds__(kBlock) flat_kernel(T *d, const T *l, const T *r, size_t n, F f) {
+    // head = elements before the first 16-byte boundary of d (l and r share d's phase)
+    size_t head = ((16u - (unsigned)((uintptr_t)d & 15u)) & 15u) / sizeof(T);
+    if (head > n) head = n;
+    const size_t nvec = (n - head) / VEC;
+    const size_t tail0 = head + nvec * VEC;
+    if (blockIdx.x == 0) {
+        size_t t = threadIdx.x;
+        if (t < head) d[t] = f(NIN >= 1 ? l[t] : T(), NIN >= 2 ? r[t] : T());
+        size_t k = tail0 + t;
+        if (k < n) d[k] = f(NIN >= 1 ? l[k] : T(), NIN >= 2 ? r[k] : T());
+    }
+    uint4 *dv = reinterpret_cast<uint4 *>(d + head);
+    const uint4 *lv = reinterpret_cast<const uint4 *>(l + head);
+    const uint4 *rv = reinterpret_cast<const uint4 *>(r + head);
+    const size_t base = (size_t)blockIdx.x * (kBlock * kUnroll) + threadIdx.x;
+    Vec a[kUnroll], b[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        size_t i = base + (size_t)u * kBlock;
+        if (i < nvec) {
+            if (NIN >= 1) a[u].q = lv[i];
+            if (NIN >= 2) b[u].q = rv[i];
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        size_t i = base + (size_t)u * kBlock;
+        if (i < nvec) {
+            Vec o;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? a[u].e[j] : T(), NIN >= 2 ? b[u].e[j] : T());
+            dv[i] = o.q;
+        }
+    }
+}
+
+// ---- rows kernel -------------------------------------------------------------------------------
+struct FastDiv {
+    uint32_t d, m, s;
+};
+// valid for n < 2^31
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, FastDiv f) { return (__umulhi(n, f.m) + n) >> f.s; }
+
+struct RowParams {
+    int rank;         // >= 1; dims 0..rank-2 are row dims, dim rank-1 is the inner dim
+    int ux_log2;      // columns per thread = 1 << ux_log2, rows per thread = 4 >> ux_log2
+    int tx_log2;      // tile_x = 1 << tx_log2 threads along the inner dim, tile_y = 256 / tile_x
+    int mode_d, mode_l, mode_r;
+    uint32_t n_col_chunks;
+    uint32_t n_rows;
+    uint64_t inner;
+    FastDiv div[kMaxPlanRank - 1];
+    int64_t sd[kMaxPlanRank], sl[kMaxPlanRank], sr[kMaxPlanRank];
+};
+
+__device__ __forceinline__ void load_operand(const T *row, int mode, int64_t stride, uint64_t col, int cnt, Vec &out) {
+    if (mode == kContigVec && cnt == VEC) {
+        out.q = *reinterpret_cast<const uint4 *>(row + col);
+    } else if (mode == kRevVec && cnt == VEC) {
+        Vec t;
+        t.q = *reinterpret_cast<const uint4 *>(row - (int64_t)col - (VEC - 1));
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) out.e[j] = t.e[VEC - 1 - j];
+    } else if (mode == kBroadcast) {
+        T x = row[0];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) out.e[j] = x;
+    } else {
+        int64_t s = (mode == kContigVec || mode == kContigScalar) ? 1 : (mode == kRevVec || mode == kRevScalar) ? -1 : stride;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j)
+            if (j < cnt) out.e[j] = row[(int64_t)(col + j) * s];
+    }
+}
+
+template <typename F, int NIN>
+__global__ void __launch_bounds__(kBlock) rows_kernel(T *d, const T *l, const T *r, RowParams p, F f) {
+    const uint32_t chunk = blockIdx.x % p.n_col_chunks;
+    const uint32_t row_tile = blockIdx.x / p.n_col_chunks;
+    const uint32_t tx = threadIdx.x & ((1u << p.tx_log2) - 1u);
+    const uint32_t ty = threadIdx.x >> p.tx_log2;
+    const uint32_t tile_y = kBlock >> p.tx_log2;
+    const uint32_t ux_n = 1u << p.ux_log2, uy_n = 4u >> p.ux_log2;
+
+    int64_t od[4], ol[4], orr[4];
+    uint64_t col[4];
+    int cnt[4];
+    Vec a[4], b[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const uint32_t ux = u & (ux_n - 1u), uy = u >> p.ux_log2;
+        const uint64_t row = ((uint64_t)row_tile * uy_n + uy) * tile_y + ty;
+        const uint64_t cv = ((uint64_t)chunk * ux_n + ux) * (1u << p.tx_log2) + tx;
+        col[u] = cv * VEC;
+        cnt[u] = 0;
+        if (row < p.n_rows && col[u] < p.inner) {
+            uint64_t left = p.inner - col[u];
+            cnt[u] = left < (uint64_t)VEC ? (int)left : VEC;
+            if (ux == 0 || u == 0) {
+                uint32_t rem = (uint32_t)row;
+                int64_t xd = 0, xl = 0, xr = 0;
+                for (int k = p.rank - 2; k >= 0; --k) {
+                    uint32_t q = fdiv(rem, p.div[k]);
+                    uint32_t c = rem - q * p.div[k].d;
+                    rem = q;
+                    xd += (int64_t)c * p.sd[k];
+                    if (NIN >= 1) xl += (int64_t)c * p.sl[k];
+                    if (NIN >= 2) xr += (int64_t)c * p.sr[k];
+                }
+                od[u] = xd; ol[u] = xl; orr[u] = xr;
+            } else {
+                od[u] = od[u - 1]; ol[u] = ol[u - 1]; orr[u] = orr[u - 1];
+            }
+            if (NIN >= 1) load_operand(l + ol[u], p.mode_l, p.sl[p.rank - 1], col[u], cnt[u], a[u]);
+            if (NIN >= 2) load_operand(r + orr[u], p.mode_r, p.sr[p.rank - 1], col[u], cnt[u], b[u]);
+        } else if (u > 0) {
+            od[u] = od[u - 1]; ol[u] = ol[u - 1]; orr[u] = orr[u - 1];
+        } else {
+            od[u] = 0; ol[u] = 0; orr[u] = 0;
+        }
+    }
+    const int64_t sdi = p.sd[p.rank - 1];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if (cnt[u] == 0) continue;
+        Vec o;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? a[u].e[j] : T(), NIN >= 2 ? b[u].e[j] : T());
+        T *row = d + od[u];
+        if (p.mode_d == kContigVec && cnt[u] == VEC) {
+            *reinterpret_cast<uint4 *>(row + col[u]) = o.q;
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                if (j < cnt[u]) row[(int64_t)(col[u] + j) * sdi] = o.e[j];
+        }
+    }
+}
+
+// ---- host launch -------------------------------------------------------------------------------
+FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    uint32_t s = 0;
+    while (s < 32 && (1ull << s) < d) ++s;
+    f.s = s;
+    f.m = (uint32_t)(((1ull << 32) * ((1ull << s) - d)) / d + 1);
+    return f;
+}
+
+int ilog2(uint64_t v) {
+    int k = 0;
+    while ((1ull << k) < v) ++k;
+    return k;
+}
+
+template <typename F, int NIN>
+int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
+    T *d = reinterpret_cast<T *>(c.d) + plan.base_d;
+    const T *l = NIN >= 1 ? reinterpret_cast<const T *>(c.l) + plan.base_l : reinterpret_cast<const T *>(d);
+    const T *r = NIN >= 2 ? reinterpret_cast<const T *>(c.r) + plan.base_r : reinterpret_cast<const T *>(d);
+    if (plan.kernel == kFlatVec) {
+        size_t n = (size_t)plan.shape[0];
+        size_t nvec = n / VEC + 1;
+        size_t blocks = (nvec + (size_t)kBlock * kUnroll - 1) / ((size_t)kBlock * kUnroll);
+        if (blocks >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "flat launch too large");
+        flat_kernel<F, NIN><<<(unsigned)blocks, kBlock, 0, ctx->stream>>>(d, l, r, n, f);
+        return check_launch(ctx, "flat_kernel");
+    }
+    RowParams p;
+    std::memset(&p, 0, sizeof p);
+    p.rank = plan.rank;
+    p.tx_log2 = ilog2((uint64_t)plan.tile_x);
+    const int R = plan.rank;
+    uint64_t inner_vecs = (plan.shape[R - 1] + VEC - 1) / VEC;
+    int ux = inner_vecs >= 4ull * plan.tile_x ? 4 : inner_vecs >= 2ull * plan.tile_x ? 2 : 1;
+    p.ux_log2 = ux == 4 ? 2 : ux == 2 ? 1 : 0;
+    p.mode_d = plan.mode_d; p.mode_l = plan.mode_l; p.mode_r = plan.mode_r;
+    p.n_col_chunks = (uint32_t)plan.n_col_chunks;
+    p.n_rows = (uint32_t)plan.n_rows;
+    p.inner = plan.shape[R - 1];
+    for (int k = 0; k < R; ++k) {
+        p.sd[k] = plan.stride_d[k]; p.sl[k] = plan.stride_l[k]; p.sr[k] = plan.stride_r[k];
+        if (k < R - 1) p.div[k] = make_fastdiv((uint32_t)plan.shape[k]);
+    }
+    rows_kernel<F, NIN><<<(unsigned)plan.grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+    return check_launch(ctx, "rows_kernel");
+}
+
+template <template <int> class Fam, int NIN>
+int launch_by_binop(Ctx *ctx, const EwCall &c, const rtb_plan &plan, T v) {
+    (void)v;
+    switch (c.op) {
+        case RTB_ADD: { Fam<RTB_ADD> f{}; return launch<Fam<RTB_ADD>, NIN>(ctx, c, plan, f); }
+        case RTB_SUB: { Fam<RTB_SUB> f{}; return launch<Fam<RTB_SUB>, NIN>(ctx, c, plan, f); }
+        case RTB_MUL: { Fam<RTB_MUL> f{}; return launch<Fam<RTB_MUL>, NIN>(ctx, c, plan, f); }
+        case RTB_DIV:
+#if RTB_KIND == 3
+            return fail(RTB_ERR_DTYPE, "division is not defined for boolean tensors");
+#else
+            { Fam<RTB_DIV> f{}; return launch<Fam<RTB_DIV>, NIN>(ctx, c, plan, f); }
+#endif
+    }
+    return fail(RTB_ERR_INVALID, "unknown binary op %d", c.op);
+}
+
+int launch_scalar(Ctx *ctx, const EwCall &c, const rtb_plan &plan, T v) {
+    switch (c.op) {
+        case RTB_ADD: return launch<FScalar<RTB_ADD>, 1>(ctx, c, plan, FScalar<RTB_ADD>{v});
+        case RTB_SUB: return launch<FScalar<RTB_SUB>, 1>(ctx, c, plan, FScalar<RTB_SUB>{v});
+        case RTB_MUL: return launch<FScalar<RTB_MUL>, 1>(ctx, c, plan, FScalar<RTB_MUL>{v});
+        case RTB_DIV:
+#if RTB_KIND == 3
+            return fail(RTB_ERR_DTYPE, "division is not defined for boolean tensors");
+#else
+            return launch<FScalar<RTB_DIV>, 1>(ctx, c, plan, FScalar<RTB_DIV>{v});
+#endif
+    }
+    return fail(RTB_ERR_INVALID, "unknown scalar op %d", c.op);
+}
+
+int launch_unary(Ctx *ctx, const EwCall &c, const rtb_plan &plan) {
+    switch (c.op) {
+        case RTB_NEG:
+#if RTB_KIND == 0 || RTB_KIND == 3
+            return fail(RTB_ERR_DTYPE, "negation is not defined for unsigned or boolean tensors");
+#else
+            return launch<FUnary<RTB_NEG>, 1>(ctx, c, plan, FUnary<RTB_NEG>{});
+#endif
+        case RTB_RELU: return launch<FUnary<RTB_RELU>, 1>(ctx, c, plan, FUnary<RTB_RELU>{});
+        case RTB_ABS: return launch<FUnary<RTB_ABS>, 1>(ctx, c, plan, FUnary<RTB_ABS>{});
+        case RTB_SIGN:
+#if RTB_KIND == 3
+            return fail(RTB_ERR_DTYPE, "sign is not defined for boolean tensors");
+#else
+            return launch<FUnary<RTB_SIGN>, 1>(ctx, c, plan, FUnary<RTB_SIGN>{});
+#endif
+    }
+    return fail(RTB_ERR_INVALID, "unknown unary op %d", c.op);
+}
+
+}  // namespace
+
+#define RTB_CAT2(a, b) a##b
+#define RTB_CAT(a, b) RTB_CAT2(a, b)
+
+int RTB_CAT(ew_dispatch_, RTB_SUFFIX)(Ctx *ctx, const EwCall &c, const rtb_plan &plan) {
+    T v;
+    std::memcpy(&v, c.value, sizeof v);
+#if RTB_KIND == 3
+    v = v != 0 ? 1 : 0;
+#endif
+    switch (c.family) {
+        case kFamBinary: return launch_by_binop<FBinary, 2>(ctx, c, plan, v);
+        case kFamScalar: return launch_scalar(ctx, c, plan, v);
+        case kFamUnary: return launch_unary(ctx, c, plan);
+        case kFamFill: return launch<FFill, 0>(ctx, c, plan, FFill{v});
+        case kFamCopy: return launch<FCopy, 1>(ctx, c, plan, FCopy{});
+    }
+    return fail(RTB_ERR_INVALID, "unknown elementwise family %d", c.family);
+}
+
+}  // namespace rtb

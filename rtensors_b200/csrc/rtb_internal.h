@@ -1,0 +1,99 @@
+// Internal declarations shared by the translation units of librt_b200.so.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "rt_b200.h"
+
+#define RTB_API extern "C" __attribute__((visibility("default")))
+
+namespace rtb {
+
+// ---- per-thread error text -------------------------------------------------------------------
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define RTB_CUDA(call)                                                       \
+    do {                                                                     \
+        cudaError_t e__ = (call);                                            \
+        if (e__ != cudaSuccess) return ::rtb::cuda_fail(e__, #call);         \
+    } while (0)
+
+// ---- dtype properties ------------------------------------------------------------------------
+size_t dtype_size(int dtype);  // 0 for an unknown code
+
+// ---- context -----------------------------------------------------------------------------------
+struct Ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t l2_bytes = 0;
+    cudaStream_t stream = nullptr;
+    uint64_t launches = 0;
+    // reduction workspace (partials + completion counters), grown on demand
+    void *ws = nullptr;
+    size_t ws_bytes = 0;
+    // caching allocator: free blocks by rounded size; live blocks by pointer
+    std::mutex mu;
+    std::multimap<size_t, void *> free_blocks;
+    std::map<void *, size_t> live_blocks;
+};
+
+// Returns a workspace of at least `bytes` bytes (256-byte aligned).  The first 256 bytes are
+// completion counters that kernels leave at zero; they are zeroed when the workspace is created.
+int workspace(Ctx *ctx, size_t bytes, void **out);
+Ctx *default_ctx();  // ctx on the current device bound to the legacy default stream (ABI v1)
+
+inline void count_launch(Ctx *ctx) { ctx->launches += 1; }
+int check_launch(Ctx *ctx, const char *what);
+
+// ---- planner (host) ----------------------------------------------------------------------------
+constexpr int kMaxPlanRank = 8;
+enum AccessMode { kContigVec = 0, kContigScalar = 1, kRevVec = 2, kRevScalar = 3, kBroadcast = 4, kStrided = 5 };
+enum PlanKernel { kNothing = 0, kFlatVec = 1, kFlatScalar = 2, kRows = 3 };
+
+struct ViewArg {
+    const ptrdiff_t *strides;  // rank entries (elements)
+    size_t offset;             // elements
+    uintptr_t ptr;             // buffer base address (only its alignment matters to the planner)
+};
+
+// Builds the plan; returns RTB_OK, or RTB_ERR_TOO_LARGE when more than kMaxPlanRank dims remain
+// after collapsing (the caller then peels outer dims).
+int make_plan(size_t elem_size, int n_inputs, size_t rank, const size_t *shape, const ViewArg &d, const ViewArg &l,
+              const ViewArg &r, rtb_plan *out);
+
+// ---- launchers implemented in the .cu files ----------------------------------------------------
+// op families for the elementwise engine
+enum EwFamily { kFamBinary = 0, kFamScalar = 1, kFamUnary = 2, kFamFill = 3, kFamCopy = 4 };
+
+struct EwCall {
+    int dtype;
+    int family;  // EwFamily
+    int op;      // rtb_binop or rtb_unop
+    unsigned char value[16];  // scalar operand / fill value
+    void *d;
+    const void *l;
+    const void *r;
+};
+// Runs one planned elementwise call (any family) on ctx->stream.
+int launch_elementwise(Ctx *ctx, const EwCall &call, const rtb_plan &plan);
+// Plans and runs, peeling outer dims on the host if the collapsed rank exceeds kMaxPlanRank.
+int run_elementwise(Ctx *ctx, const EwCall &call, size_t rank, const size_t *shape, const ptrdiff_t *sd, size_t od,
+                    const ptrdiff_t *sl, size_t ol, const ptrdiff_t *sr, size_t orr);
+
+int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t len, void *dst);
+int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
+                       void *dst);
+int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap);
+int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n);
+int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n);
+int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n);
+
+}  // namespace rtb

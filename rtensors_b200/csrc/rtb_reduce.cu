@@ -1,0 +1,532 @@
+// Reductions for f32 / f64: flat (whole range -> one value), inner-axis (rows), outer-axis
+// (columns, threads along the contiguous inner dim), fused L1 loss, and the small fused kernels
+// of the autograd MLP step.  All HBM-bound: each input element is read exactly once.
+//
+// Accumulator semantics follow the reference CPU backend (src/ops/reduction/mod.rs:9-137):
+// sum / mean start at 0, prod at 1, max at the lowest finite value with `v > acc`, min at the
+// highest finite value with `v < acc` (so NaNs are skipped); mean divides by (T)(float)count
+// (src/core/value.rs:54-56).  Float sums are tree-ordered here (sequential on the CPU), which is
+// why sums carry a tolerance while max / min are exact.  Every kernel combines in a fixed order,
+// so results are run-to-run deterministic.
+#include <cfloat>
+
+#include "rtb_internal.h"
+
+namespace rtb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kWarps = kBlock / 32;
+
+template <typename T> struct Limits;
+template <> struct Limits<float> {
+    static __host__ __device__ float lowest() { return -FLT_MAX; }
+    static __host__ __device__ float highest() { return FLT_MAX; }
+};
+template <> struct Limits<double> {
+    static __host__ __device__ double lowest() { return -DBL_MAX; }
+    static __host__ __device__ double highest() { return DBL_MAX; }
+};
+
+// OP: rtb_redop without MEAN (mean = SUM + divide at the end)
+template <typename T, int OP> struct Comb {
+    static __device__ __forceinline__ T identity() {
+        if (OP == RTB_PROD) return (T)1;
+        if (OP == RTB_MAX) return Limits<T>::lowest();
+        if (OP == RTB_MIN) return Limits<T>::highest();
+        return (T)0;
+    }
+    // `a` is the running value, `b` the incoming one
+    static __device__ __forceinline__ T apply(T a, T b) {
+        if (OP == RTB_PROD) return a * b;
+        if (OP == RTB_MAX) return b > a ? b : a;
+        if (OP == RTB_MIN) return b < a ? b : a;
+        return a + b;
+    }
+};
+
+template <typename T> struct VecOf {
+    static constexpr int N = 16 / (int)sizeof(T);
+    union U {
+        uint4 q;
+        T e[N];
+    };
+};
+
+template <typename T> __device__ __forceinline__ T shfl_down(T v, int delta) { return __shfl_down_sync(0xffffffffu, v, delta); }
+
+template <typename T, int OP> __device__ __forceinline__ T warp_reduce(T v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = Comb<T, OP>::apply(v, shfl_down(v, d));
+    return v;
+}
+
+// result valid in thread 0
+template <typename T, int OP> __device__ __forceinline__ T block_reduce(T v, T *smem /* kWarps */) {
+    v = warp_reduce<T, OP>(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    T out = Comb<T, OP>::identity();
+    if (warp == 0) {
+        out = lane < kWarps ? smem[lane] : Comb<T, OP>::identity();
+#pragma unroll
+        for (int d = kWarps / 2; d > 0; d >>= 1) out = Comb<T, OP>::apply(out, shfl_down(out, d));
+    }
+    __syncthreads();
+    return out;
+}
+
+template <typename T> __device__ __forceinline__ T finish(T acc, int mean, size_t count) {
+    return mean ? acc / (T)(float)count : acc;
+}
+
+// Element sources for the flat kernel.
+template <typename T> struct SrcPlain {
+    const T *p;
+    __device__ __forceinline__ T scalar(size_t i) const { return p[i]; }
+    __device__ __forceinline__ void vec(size_t iv, T out[VecOf<T>::N]) const {
+        typename VecOf<T>::U u;
+        u.q = reinterpret_cast<const uint4 *>(p)[iv];
+#pragma unroll
+        for (int j = 0; j < VecOf<T>::N; ++j) out[j] = u.e[j];
+    }
+    __device__ __forceinline__ uintptr_t phase() const { return (uintptr_t)p & 15u; }
+    __device__ __forceinline__ SrcPlain advanced(size_t n) const { return SrcPlain{p + n}; }
+    __device__ __forceinline__ bool vector_ok() const { return true; }
+};
+
+// |a - b| with an optional gradient map sign(a - b) [/ count] written on the way (L1 loss).
+template <typename T> struct SrcL1 {
+    const T *a;
+    const T *b;
+    T *g;       // may be null
+    T scale;    // divisor for the gradient map (1 for the sum form)
+    int same_phase;
+    __device__ __forceinline__ T one(T x, T y, T *gout) const {
+        T d = x - y;
+        T s = d < (T)0 ? (T)-1 : (d > (T)0 ? (T)1 : (T)0);
+        if (gout) *gout = s / scale;
+        return sizeof(T) == 4 ? (T)fabsf((float)d) : (T)fabs((double)d);
+    }
+    __device__ __forceinline__ T scalar(size_t i) const { return one(a[i], b[i], g ? g + i : nullptr); }
+    __device__ __forceinline__ void vec(size_t iv, T out[VecOf<T>::N]) const {
+        typename VecOf<T>::U x, y, s;
+        x.q = reinterpret_cast<const uint4 *>(a)[iv];
+        y.q = reinterpret_cast<const uint4 *>(b)[iv];
+#pragma unroll
+        for (int j = 0; j < VecOf<T>::N; ++j) out[j] = one(x.e[j], y.e[j], g ? &s.e[j] : nullptr);
+        if (g) reinterpret_cast<uint4 *>(g)[iv] = s.q;
+    }
+    __device__ __forceinline__ uintptr_t phase() const { return (uintptr_t)a & 15u; }
+    __device__ __forceinline__ SrcL1 advanced(size_t n) const { return SrcL1{a + n, b + n, g ? g + n : nullptr, scale, same_phase}; }
+    __device__ __forceinline__ bool vector_ok() const { return same_phase != 0; }
+};
+
+// ---- flat: grid-wide partials, the last CTA to finish folds them ---------------------------------
+// ws layout: [0] completion counter (left at zero), partials start 256 bytes in.
+template <typename T, int OP, typename Src>
+__global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, T *partials, unsigned int *counter,
+                                                             T *out, int mean) {
+    __shared__ T smem[kWarps];
+    __shared__ bool is_last;
+    constexpr int N = VecOf<T>::N;
+    T acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::identity();
+
+    size_t head = 0, nvec = 0;
+    if (src.vector_ok()) {
+        head = ((16u - (unsigned)src.phase()) & 15u) / sizeof(T);
+        if (head > n) head = n;
+        nvec = (n - head) / N;
+    }
+    const size_t tail0 = head + nvec * N;
+    const Src body = src.advanced(head);
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        T v[4][N];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) body.vec(i + u * stride, v[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[u] = Comb<T, OP>::apply(acc[u], v[u][j]);
+    }
+    for (; i < nvec; i += stride) {
+        T v[N];
+        body.vec(i, v);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[0] = Comb<T, OP>::apply(acc[0], v[j]);
+    }
+    // scalar head and tail (at most 2*(N-1) elements when vectorised; everything otherwise)
+    for (size_t k = (size_t)blockIdx.x * kBlock + threadIdx.x; k < head; k += stride)
+        acc[1] = Comb<T, OP>::apply(acc[1], src.scalar(k));
+    for (size_t k = tail0 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride)
+        acc[2] = Comb<T, OP>::apply(acc[2], src.scalar(k));
+
+    T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
+    v = block_reduce<T, OP>(v, smem);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = v;
+        __threadfence();
+        unsigned int done = atomicAdd(counter, 1u);
+        is_last = (done == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    T t = Comb<T, OP>::identity();
+    for (unsigned int k = threadIdx.x; k < gridDim.x; k += kBlock) t = Comb<T, OP>::apply(t, __ldcg(partials + k));
+    t = block_reduce<T, OP>(t, smem);
+    if (threadIdx.x == 0) {
+        out[0] = finish(t, mean, n);
+        *counter = 0;  // ready for the next launch on this stream
+    }
+}
+
+// ---- inner axis (inner == 1): src is [rows, R], one value per row --------------------------------
+// GROUP threads cooperate on a row (32 = a warp, 256 = the CTA); split > 1 cuts R into `split`
+// chunks whose partial results go to dst[row * split + chunk] for a second pass.
+template <typename T, int OP, int GROUP>
+__global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t rows, size_t R, size_t split,
+                                                            T *dst, int mean, size_t count) {
+    __shared__ T smem[kWarps];
+    constexpr int N = VecOf<T>::N;
+    constexpr int rows_per_block = kBlock / GROUP;
+    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+    const size_t item = (size_t)blockIdx.x * rows_per_block + g;  // (row, chunk)
+    const size_t row = item / split, chunk = item % split;
+    const bool live = row < rows;
+    T acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::identity();
+    if (live) {
+        const size_t per = (R + split - 1) / split;
+        const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+        const T *p = src + row * R;
+        // vector body over the 16-byte aligned part of [k0, k1)
+        size_t a0 = k0 + (((16u - (unsigned)((uintptr_t)(p + k0) & 15u)) & 15u) / sizeof(T));
+        if (a0 > k1) a0 = k1;
+        const size_t nvec = (k1 - a0) / N;
+        const uint4 *pv = reinterpret_cast<const uint4 *>(p + a0);
+        size_t i = t;
+        for (; i + 3 * GROUP < nvec; i += 4 * GROUP) {
+            typename VecOf<T>::U v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u].q = pv[i + u * GROUP];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc[u] = Comb<T, OP>::apply(acc[u], v[u].e[j]);
+        }
+        for (; i < nvec; i += GROUP) {
+            typename VecOf<T>::U v;
+            v.q = pv[i];
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[0] = Comb<T, OP>::apply(acc[0], v.e[j]);
+        }
+        for (size_t k = k0 + t; k < a0; k += GROUP) acc[1] = Comb<T, OP>::apply(acc[1], p[k]);
+        for (size_t k = a0 + nvec * N + t; k < k1; k += GROUP) acc[2] = Comb<T, OP>::apply(acc[2], p[k]);
+    }
+    T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
+    if (GROUP == 32) {
+        v = warp_reduce<T, OP>(v);
+    } else {
+        v = block_reduce<T, OP>(v, smem);
+    }
+    if (t == 0 && live) dst[item] = split == 1 ? finish(v, mean, count) : v;
+}
+
+// ---- outer axis (inner > 1): src is [outer, R, inner]; threads run along inner ---------------------
+// CTA = 32 lanes along inner (VW columns each) x 8 lanes along R.  split cuts R into chunks; with
+// split > 1 the partial for chunk c goes to dst[(o * split + c) * inner + i] for a second pass.
+template <typename T, int OP, int VW>
+__global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t outer, size_t R, size_t inner,
+                                                            size_t split, size_t col_tiles, T *dst, int mean,
+                                                            size_t count) {
+    __shared__ T smem[8][32 * VW + 1];
+    const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
+    size_t b = blockIdx.x;
+    const size_t tile = b % col_tiles; b /= col_tiles;
+    const size_t chunk = b % split;
+    const size_t o = b / split;
+    const size_t col = (tile * 32 + lx) * VW;
+    const size_t per = (R + split - 1) / split;
+    const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+    T acc[VW];
+#pragma unroll
+    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
+    if (col < inner) {
+        const T *p = src + (o * R) * inner + col;
+        size_t k = k0 + ly;
+        if (VW > 1) {
+            for (; k + 24 < k1; k += 32) {
+                typename VecOf<T>::U v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + 8 * u) * inner);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v[u].e[j]);
+            }
+            for (; k < k1; k += 8) {
+                typename VecOf<T>::U v;
+                v.q = *reinterpret_cast<const uint4 *>(p + k * inner);
+#pragma unroll
+                for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
+            }
+        } else {
+            for (; k + 24 < k1; k += 32) {
+                T v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = p[(k + 8 * u) * inner];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
+            }
+            for (; k < k1; k += 8) acc[0] = Comb<T, OP>::apply(acc[0], p[k * inner]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
+    __syncthreads();
+    // 8 partial rows -> 1, by the first warp(s): thread t owns column t of the tile
+    for (int c = threadIdx.x; c < 32 * VW; c += kBlock) {
+        T v = smem[0][c];
+#pragma unroll
+        for (int y = 1; y < 8; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
+        const size_t gc = tile * 32 * VW + c;
+        if (gc < inner) dst[(o * split + chunk) * inner + gc] = split == 1 ? finish(v, mean, count) : v;
+    }
+}
+
+// ---- fused MLP pieces ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask, size_t n) {
+    const size_t nvec = n / 4;
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
+        float4 v = reinterpret_cast<float4 *>(x)[i];
+        float4 m, o;
+        m.x = v.x > 0.f ? 1.f : 0.f; o.x = v.x > 0.f ? v.x : 0.f;
+        m.y = v.y > 0.f ? 1.f : 0.f; o.y = v.y > 0.f ? v.y : 0.f;
+        m.z = v.z > 0.f ? 1.f : 0.f; o.z = v.z > 0.f ? v.z : 0.f;
+        m.w = v.w > 0.f ? 1.f : 0.f; o.w = v.w > 0.f ? v.w : 0.f;
+        reinterpret_cast<float4 *>(x)[i] = o;
+        reinterpret_cast<float4 *>(mask)[i] = m;
+    }
+    for (size_t k = nvec * 4 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride) {
+        float v = x[k];
+        mask[k] = v > 0.f ? 1.f : 0.f;
+        x[k] = v > 0.f ? v : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) sgd_kernel(float *p, const float *g, float lr, size_t n) {
+    const size_t nvec = n / 4;
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
+        float4 w = reinterpret_cast<float4 *>(p)[i];
+        float4 q = reinterpret_cast<const float4 *>(g)[i];
+        // two roundings, as `update = grad * lr; param -= update` on the CPU (no FMA)
+        w.x = w.x - __fmul_rn(q.x, lr); w.y = w.y - __fmul_rn(q.y, lr);
+        w.z = w.z - __fmul_rn(q.z, lr); w.w = w.w - __fmul_rn(q.w, lr);
+        reinterpret_cast<float4 *>(p)[i] = w;
+    }
+    for (size_t k = nvec * 4 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride)
+        p[k] = p[k] - __fmul_rn(g[k], lr);
+}
+
+__global__ void __launch_bounds__(kBlock) u8_f32_kernel(const uint8_t *src, float *dst, float divisor, size_t n) {
+    const size_t nvec = n / 4;
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
+        uchar4 v = reinterpret_cast<const uchar4 *>(src)[i];
+        float4 o;
+        o.x = __fdiv_rn((float)v.x, divisor); o.y = __fdiv_rn((float)v.y, divisor);
+        o.z = __fdiv_rn((float)v.z, divisor); o.w = __fdiv_rn((float)v.w, divisor);
+        reinterpret_cast<float4 *>(dst)[i] = o;
+    }
+    for (size_t k = nvec * 4 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride)
+        dst[k] = __fdiv_rn((float)src[k], divisor);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+unsigned grid_for(Ctx *ctx, size_t work_items, unsigned per_sm) {
+    size_t cap = (size_t)ctx->sm_count * per_sm;
+    size_t g = work_items < cap ? work_items : cap;
+    return (unsigned)(g ? g : 1);
+}
+
+template <typename T, int OP, typename Src>
+int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
+    constexpr int N = VecOf<T>::N;
+    // one CTA per 4 KiB-vector-iterations, capped at 8 CTAs per SM (2048 threads = full occupancy)
+    size_t items = (n / N + (size_t)kBlock * 4 - 1) / ((size_t)kBlock * 4);
+    unsigned grid = grid_for(ctx, items, 8);
+    void *ws = nullptr;
+    int rc = workspace(ctx, (size_t)grid * sizeof(T), &ws);
+    if (rc != RTB_OK) return rc;
+    unsigned int *counter = reinterpret_cast<unsigned int *>(ws);
+    T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+    flat_reduce_kernel<T, OP, Src><<<grid, kBlock, 0, ctx->stream>>>(src, n, partials, counter, out, mean);
+    return check_launch(ctx, "flat_reduce_kernel");
+}
+
+template <typename T, typename Src>
+int flat_by_op(Ctx *ctx, int redop, Src src, size_t n, T *out) {
+    switch (redop) {
+        case RTB_SUM: return flat_launch<T, RTB_SUM, Src>(ctx, src, n, out, 0);
+        case RTB_MEAN: return flat_launch<T, RTB_SUM, Src>(ctx, src, n, out, 1);
+        case RTB_PROD: return flat_launch<T, RTB_PROD, Src>(ctx, src, n, out, 0);
+        case RTB_MAX: return flat_launch<T, RTB_MAX, Src>(ctx, src, n, out, 0);
+        case RTB_MIN: return flat_launch<T, RTB_MIN, Src>(ctx, src, n, out, 0);
+    }
+    return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+}
+
+template <typename T, int OP>
+int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean) {
+    // few long rows: cut each row into chunks so every SM has work, then fold the chunks
+    size_t split = 1;
+    const size_t min_items = (size_t)ctx->sm_count * 4;
+    if (rows < min_items && R >= 8192) {
+        split = (min_items + rows - 1) / rows;
+        size_t max_split = R / 4096;
+        if (split > max_split) split = max_split;
+        if (split < 1) split = 1;
+    }
+    T *target = dst;
+    if (split > 1) {
+        void *ws = nullptr;
+        int rc = workspace(ctx, rows * split * sizeof(T), &ws);
+        if (rc != RTB_OK) return rc;
+        target = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+    }
+    const size_t items = rows * split;
+    const size_t chunk_len = (R + split - 1) / split;
+    if (chunk_len >= 1024) {
+        if (items >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "too many rows for one launch");
+        row_reduce_kernel<T, OP, kBlock><<<(unsigned)items, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+    } else {
+        size_t blocks = (items + kWarps - 1) / kWarps;
+        if (blocks >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "too many rows for one launch");
+        row_reduce_kernel<T, OP, 32><<<(unsigned)blocks, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+    }
+    int rc = check_launch(ctx, "row_reduce_kernel");
+    if (rc != RTB_OK || split == 1) return rc;
+    size_t blocks = (rows + kWarps - 1) / kWarps;
+    row_reduce_kernel<T, OP, 32><<<(unsigned)blocks, kBlock, 0, ctx->stream>>>(target, rows, split, 1, dst, mean, R);
+    return check_launch(ctx, "row_reduce_kernel(fold)");
+}
+
+template <typename T, int OP>
+int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+    constexpr int N = VecOf<T>::N;
+    const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0);
+    const size_t tile_cols = vec ? 32 * N : 32;
+    const size_t col_tiles = (inner + tile_cols - 1) / tile_cols;
+    size_t split = 1;
+    const size_t base_ctas = outer * col_tiles;
+    const size_t want = (size_t)ctx->sm_count * 8;
+    if (base_ctas < want && R >= 128) {
+        split = (want + base_ctas - 1) / base_ctas;
+        size_t max_split = R / 64;
+        if (split > max_split) split = max_split;
+        if (split < 1) split = 1;
+    }
+    T *target = dst;
+    if (split > 1) {
+        void *ws = nullptr;
+        int rc = workspace(ctx, outer * split * inner * sizeof(T), &ws);
+        if (rc != RTB_OK) return rc;
+        target = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+    }
+    size_t grid = base_ctas * split;
+    if (grid >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "axis reduction too large for one launch");
+    if (vec)
+        col_reduce_kernel<T, OP, N><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, target, mean, R);
+    else
+        col_reduce_kernel<T, OP, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, target, mean, R);
+    int rc = check_launch(ctx, "col_reduce_kernel");
+    if (rc != RTB_OK || split == 1) return rc;
+    // fold [outer, split, inner] -> [outer, inner]; the workspace start is 256-byte aligned
+    const bool vec2 = (inner % N == 0) && (((uintptr_t)target & 15u) == 0);
+    const size_t tiles2 = (inner + (vec2 ? 32 * N : 32) - 1) / (vec2 ? 32 * N : 32);
+    size_t grid2 = outer * tiles2;
+    if (vec2)
+        col_reduce_kernel<T, OP, N><<<(unsigned)grid2, kBlock, 0, ctx->stream>>>(target, outer, split, inner, 1, tiles2, dst, mean, R);
+    else
+        col_reduce_kernel<T, OP, 1><<<(unsigned)grid2, kBlock, 0, ctx->stream>>>(target, outer, split, inner, 1, tiles2, dst, mean, R);
+    return check_launch(ctx, "col_reduce_kernel(fold)");
+}
+
+template <typename T, int OP>
+int axis_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+    if (inner == 1) return rows_launch<T, OP>(ctx, src, outer, R, dst, mean);
+    return cols_launch<T, OP>(ctx, src, outer, R, inner, dst, mean);
+}
+
+template <typename T>
+int axis_by_op(Ctx *ctx, int redop, const T *src, size_t outer, size_t R, size_t inner, T *dst) {
+    switch (redop) {
+        case RTB_SUM: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, dst, 0);
+        case RTB_MEAN: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, dst, 1);
+        case RTB_PROD: return axis_launch<T, RTB_PROD>(ctx, src, outer, R, inner, dst, 0);
+        case RTB_MAX: return axis_launch<T, RTB_MAX>(ctx, src, outer, R, inner, dst, 0);
+        case RTB_MIN: return axis_launch<T, RTB_MIN>(ctx, src, outer, R, inner, dst, 0);
+    }
+    return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+}
+
+}  // namespace
+
+int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t len, void *dst) {
+    if (dtype == RTB_F32) return flat_by_op<float>(ctx, redop, SrcPlain<float>{(const float *)src}, len, (float *)dst);
+    if (dtype == RTB_F64) return flat_by_op<double>(ctx, redop, SrcPlain<double>{(const double *)src}, len, (double *)dst);
+    return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+}
+
+int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
+                       void *dst) {
+    if (dtype == RTB_F32) return axis_by_op<float>(ctx, redop, (const float *)src, outer, r, inner, (float *)dst);
+    if (dtype == RTB_F64) return axis_by_op<double>(ctx, redop, (const double *)src, outer, r, inner, (double *)dst);
+    return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+}
+
+template <typename T>
+static int l1_typed(Ctx *ctx, const T *a, const T *b, size_t n, int reduction, T *loss, T *g) {
+    uintptr_t pa = (uintptr_t)a & 15u, pb = (uintptr_t)b & 15u, pg = g ? ((uintptr_t)g & 15u) : pa;
+    SrcL1<T> src{a, b, g, reduction == 0 ? (T)(float)n : (T)1, (pa == pb && pa == pg) ? 1 : 0};
+    return flat_launch<T, RTB_SUM, SrcL1<T>>(ctx, src, n, loss, reduction == 0 ? 1 : 0);
+}
+
+int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap) {
+    if (dtype == RTB_F32) return l1_typed<float>(ctx, (const float *)a, (const float *)b, n, reduction, (float *)loss, (float *)gmap);
+    if (dtype == RTB_F64) return l1_typed<double>(ctx, (const double *)a, (const double *)b, n, reduction, (double *)loss, (double *)gmap);
+    return fail(RTB_ERR_DTYPE, "l1 loss is defined for f32 and f64 only");
+}
+
+int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n) {
+    if ((((uintptr_t)x | (uintptr_t)mask) & 15u) != 0) return fail(RTB_ERR_INVALID, "relu_mask needs 16-byte aligned buffers");
+    unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
+    relu_mask_kernel<<<grid, kBlock, 0, ctx->stream>>>(x, mask, n);
+    return check_launch(ctx, "relu_mask_kernel");
+}
+
+int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n) {
+    if ((((uintptr_t)p | (uintptr_t)g) & 15u) != 0) return fail(RTB_ERR_INVALID, "sgd_update needs 16-byte aligned buffers");
+    unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
+    sgd_kernel<<<grid, kBlock, 0, ctx->stream>>>(p, g, lr, n);
+    return check_launch(ctx, "sgd_kernel");
+}
+
+int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n) {
+    if (((uintptr_t)src & 3u) != 0 || ((uintptr_t)dst & 15u) != 0) return fail(RTB_ERR_INVALID, "u8_to_f32 needs aligned buffers");
+    unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
+    u8_f32_kernel<<<grid, kBlock, 0, ctx->stream>>>(src, dst, divisor, n);
+    return check_launch(ctx, "u8_f32_kernel");
+}
+
+}  // namespace rtb

@@ -1,0 +1,193 @@
+"""`Tensor`: the host mirror of the reference's `TensorBase<T, B>` / `TensorView` API surface that
+the hot path exercises (src/core/primitives.rs:367-484, src/core/tensor.rs:66-105, 418-524,
+src/ops/{scalar,unary,broadcast,reduction}).  A Tensor is (backend, flat device buffer, Meta);
+views share the buffer.  Semantics follow the reference operators: `a + 3` copies then works in
+place, `a += b` requires b to broadcast to a's shape, `sum_at(k)` keeps dim k as size 1 and first
+copies a non-contiguous view, full reductions return a rank-0 tensor.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .backend import CODE_TO_NP, CudaB200, dtype_code
+from .meta import Meta
+
+_NP_TO_TORCH = {np.dtype(np.float32): torch.float32, np.dtype(np.float64): torch.float64,
+                np.dtype(np.int8): torch.int8, np.dtype(np.int16): torch.int16, np.dtype(np.int32): torch.int32,
+                np.dtype(np.int64): torch.int64, np.dtype(np.uint8): torch.uint8, np.dtype(np.bool_): torch.bool}
+for _n in ("uint16", "uint32", "uint64"):
+    if hasattr(torch, _n):
+        _NP_TO_TORCH[np.dtype(getattr(np, _n))] = getattr(torch, _n)
+
+_default_backend: Optional[CudaB200] = None
+
+
+def default_backend() -> CudaB200:
+    global _default_backend
+    if _default_backend is None:
+        _default_backend = CudaB200(torch.cuda.current_device() if torch.cuda.is_available() else 0)
+    return _default_backend
+
+
+class Tensor:
+    def __init__(self, backend: CudaB200, buf: torch.Tensor, meta: Meta):
+        self.backend, self.buf, self.meta = backend, buf, meta
+
+    # ---- constructors -----------------------------------------------------------------------
+    @staticmethod
+    def from_buf(data, shape: Sequence[int], dtype=np.float32, backend: Optional[CudaB200] = None) -> "Tensor":
+        b = backend or default_backend()
+        host = np.ascontiguousarray(np.asarray(data, dtype=dtype).reshape(-1))
+        meta = Meta.contiguous(shape)
+        if host.size != meta.size:
+            raise ValueError(f"Element count mismatch: shape {tuple(shape)} vs buffer of {host.size}")
+        return Tensor(b, b.alloc_from_slice(host), meta)
+
+    @staticmethod
+    def full(shape, value, dtype=np.float32, backend=None) -> "Tensor":
+        b = backend or default_backend()
+        meta = Meta.contiguous(shape)
+        t = Tensor(b, b.alloc(max(meta.size, 1), _NP_TO_TORCH[np.dtype(dtype)]), meta)
+        b.fill(t.buf, value, meta)
+        return t
+
+    @staticmethod
+    def zeros(shape, dtype=np.float32, backend=None): return Tensor.full(shape, 0, dtype, backend)
+
+    @staticmethod
+    def ones(shape, dtype=np.float32, backend=None): return Tensor.full(shape, 1, dtype, backend)
+
+    @staticmethod
+    def scalar(value, dtype=np.float32, backend=None): return Tensor.from_buf([value], (), dtype, backend)
+
+    # ---- meta -------------------------------------------------------------------------------
+    @property
+    def shape(self): return self.meta.shape
+    @property
+    def strides(self): return self.meta.strides
+    @property
+    def offset(self): return self.meta.offset
+    @property
+    def size(self): return self.meta.size
+    @property
+    def rank(self): return self.meta.rank
+    def is_contiguous(self): return self.meta.is_contiguous()
+
+    def _view(self, meta: Meta) -> "Tensor": return Tensor(self.backend, self.buf, meta)
+    def view(self): return self._view(self.meta)
+    def slice(self, dim, start=None, end=None, step=1): return self._view(self.meta.slice(dim, start, end, step))
+    def index(self, dim, i): return self._view(self.meta.index(dim, i))
+    def permute(self, dims): return self._view(self.meta.permute(dims))
+    def transpose(self): return self._view(self.meta.transpose())
+    def squeeze(self, dim=None): return self._view(self.meta.squeeze(dim))
+    def unsqueeze(self, dim): return self._view(self.meta.unsqueeze(dim))
+    def view_as(self, shape): return self._view(self.meta.view_as(shape))
+
+    def contiguous(self) -> "Tensor":
+        return Tensor(self.backend, self.backend.contiguous(self.buf, self.meta), Meta.contiguous(self.shape))
+
+    owned = contiguous
+
+    # ---- host access ------------------------------------------------------------------------
+    def cpu(self) -> np.ndarray:
+        flat = self.backend.dump(self.contiguous().buf)[: max(self.size, 1) if self.rank == 0 else self.size]
+        return flat.reshape(self.shape)
+
+    def item(self):
+        if self.size != 1:
+            raise ValueError("item() needs a single-element tensor")
+        return self.cpu().reshape(-1)[0]
+
+    def get(self, coord):
+        return self.backend.dump(self.buf[self.offset + sum(c * s for c, s in zip(coord, self.strides))].reshape(1))[0]
+
+    def set(self, coord, value):
+        self.buf[self.offset + sum(c * s for c, s in zip(coord, self.strides))] = value
+
+    def fill(self, value): self.backend.fill(self.buf, value, self.meta)
+
+    # ---- scalar / tensor operators ----------------------------------------------------------
+    def _binary(self, other, op: int) -> "Tensor":
+        if isinstance(other, Tensor):
+            out, dm = self.backend.binary(self.buf, self.meta, other.buf, other.meta, op)
+            return Tensor(self.backend, out, dm)
+        t = self.owned()
+        t.backend.scalar_apply(t.buf, op, other, t.meta)
+        return t
+
+    def _assign(self, other, op: int) -> "Tensor":
+        if isinstance(other, Tensor):
+            self.backend.binary_assign(self.buf, self.meta, other.buf, other.meta, op)
+        else:
+            self.backend.scalar_apply(self.buf, op, other, self.meta)
+        return self
+
+    def __add__(self, o): return self._binary(o, L.ADD)
+    def __sub__(self, o): return self._binary(o, L.SUB)
+    def __mul__(self, o): return self._binary(o, L.MUL)
+    def __truediv__(self, o): return self._binary(o, L.DIV)
+    def __iadd__(self, o): return self._assign(o, L.ADD)
+    def __isub__(self, o): return self._assign(o, L.SUB)
+    def __imul__(self, o): return self._assign(o, L.MUL)
+    def __itruediv__(self, o): return self._assign(o, L.DIV)
+
+    # ---- unary ------------------------------------------------------------------------------
+    def _unary_inplace(self, op):
+        self.backend.apply_unary(self.buf, op, self.meta)
+        return self
+
+    def relu_inplace(self): return self._unary_inplace(L.RELU)
+    def abs_inplace(self): return self._unary_inplace(L.ABS)
+    def sign_inplace(self): return self._unary_inplace(L.SIGN)
+    def neg_inplace(self): return self._unary_inplace(L.NEG)
+    def relu(self): return self.owned().relu_inplace()
+    def abs(self): return self.owned().abs_inplace()
+    def sign(self): return self.owned().sign_inplace()
+    def neg(self): return self.owned().neg_inplace()
+    def __neg__(self): return self.neg()
+
+    # ---- reductions -------------------------------------------------------------------------
+    def _reduce(self, op: int, axis: Optional[int]) -> "Tensor":
+        t = self if self.is_contiguous() else self.contiguous()
+        b = t.backend
+        if axis is None:
+            out = b.alloc(1, t.buf.dtype)
+            b.apply_reduce_contiguous_flat(t.buf, out, t.offset, t.size, op)
+            return Tensor(b, out, Meta.contiguous(()))
+        if not 0 <= axis < t.rank:
+            raise L.RtbError(-5, f"axis {axis} out of range for rank {t.rank}")
+        om = Meta.contiguous(tuple(1 if k == axis else s for k, s in enumerate(t.shape)))
+        out = b.alloc(max(om.size, 1), t.buf.dtype)
+        if om.size:
+            b.apply_reduce((t.buf, t.meta), out, axis, op)
+        return Tensor(b, out, om)
+
+    def sum(self): return self._reduce(L.SUM, None)
+    def mean(self): return self._reduce(L.MEAN, None)
+    def max(self): return self._reduce(L.MAX, None)
+    def min(self): return self._reduce(L.MIN, None)
+    def prod(self): return self._reduce(L.PROD, None)
+    def sum_at(self, axis): return self._reduce(L.SUM, axis)
+    def mean_at(self, axis): return self._reduce(L.MEAN, axis)
+    def max_at(self, axis): return self._reduce(L.MAX, axis)
+    def min_at(self, axis): return self._reduce(L.MIN, axis)
+    def prod_at(self, axis): return self._reduce(L.PROD, axis)
+
+
+def mean_l1_loss(a: Tensor, b: Tensor, with_grad: bool = False):
+    """mean(|a - b|) as a rank-0 tensor (src/ops/broadcast/l1.rs:79-84); with_grad also returns the
+    gradient map sign(a - b) / N the reference stores on the tape."""
+    if a.shape != b.shape:
+        raise ValueError("mean_l1_loss needs equal shapes")
+    ca = a if a.is_contiguous() else a.contiguous()
+    cb = b if b.is_contiguous() else b.contiguous()
+    n = a.size
+    loss, g = a.backend.l1_loss(ca.buf[ca.offset: ca.offset + n], cb.buf[cb.offset: cb.offset + n], 0, with_grad)
+    lt = Tensor(a.backend, loss, Meta.contiguous(()))
+    if with_grad:
+        return lt, Tensor(a.backend, g, Meta.contiguous(a.shape))
+    return lt

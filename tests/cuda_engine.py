@@ -1,0 +1,74 @@
+"""Adapter: the CUDA library (through the C ABI) behind the engine interface of golden_runner."""
+import numpy as np
+import torch
+
+import rtensors_b200 as rt
+from rtensors_b200.backend import CudaB200
+from rtensors_b200.meta import Meta, broadcast_params
+
+_backend = None
+
+
+def backend() -> CudaB200:
+    global _backend
+    if _backend is None:
+        _backend = CudaB200(0)
+    return _backend
+
+
+def to_dev(a: np.ndarray) -> torch.Tensor:
+    return backend().alloc_from_slice(a)
+
+
+def to_host(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().numpy()
+
+
+class CudaEngine:
+    Meta = Meta
+
+    def __init__(self):
+        self.b = backend()
+
+    def broadcast_params(self, a, b):
+        return broadcast_params(a, b)
+
+    def scalar_assign(self, buf, meta, op, value):
+        d = to_dev(buf)
+        self.b.scalar_apply(d, op, value, meta)
+        return to_host(d)
+
+    def unary_assign(self, buf, meta, op):
+        d = to_dev(buf)
+        self.b.apply_unary(d, op, meta)
+        return to_host(d)
+
+    def scalar_out(self, buf, meta, op, value):
+        d = to_dev(buf)
+        out = self.b.contiguous(d, meta)
+        m = Meta.contiguous(meta.shape)
+        self.b.scalar_apply(out, op, value, m)
+        buf[...] = to_host(d)  # the source must be left unchanged: hand it back for the caller's check
+        return to_host(out), meta.shape
+
+    def binary(self, a, am, b, bm, op):
+        out, dm = self.b.binary(to_dev(a), am, to_dev(b), bm, op)
+        return to_host(out), dm.shape
+
+    def binary_assign(self, a, am, b, bm, op):
+        d = to_dev(a)
+        self.b.binary_assign(d, am, to_dev(b), bm, op)
+        return to_host(d)
+
+    def reduce_total(self, a, am, op):
+        d = to_dev(a)
+        out = self.b.alloc(1, d.dtype)
+        self.b.apply_reduce_contiguous_flat(d, out, am.offset, am.size, op)
+        return to_host(out)[0]
+
+    def reduce_axis(self, a, am, axis, op):
+        d = to_dev(a)
+        oshape = tuple(1 if k == axis else s for k, s in enumerate(am.shape))
+        out = self.b.alloc(max(int(np.prod(oshape)), 1), d.dtype)
+        self.b.apply_reduce((d, am), out, axis, op)
+        return to_host(out), oshape
