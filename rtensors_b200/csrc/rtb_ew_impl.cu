@@ -8,10 +8,12 @@
 //                a scalar tail finishes.  HBM-bound: 2*s bytes per element in place, 3*s for a
 //                same-shape binary op.
 //   rows_kernel  everything else, after the planner collapsed the view to <= 8 dims.  A CTA owns
-//                a tile of (rows x 128-bit columns); the row index is decoded once per vector
-//                with multiply-shift division, never per element.  Each operand's walk along the
-//                inner dim is one of: contiguous (vector or scalar), reversed (vector load at the
-//                mirrored address + lane reversal), broadcast (one load, splat) or strided.
+//                a tile of (rows x 128-bit columns) and walks several row tiles: the row index is
+//                decoded once per CTA with multiply-shift division and then advanced by adds,
+//                never per element.  Each operand's walk along the inner dim is one of:
+//                contiguous (vector or scalar), reversed (vector load at the mirrored address +
+//                lane reversal), broadcast (one load, splat) or strided.  A lean instantiation
+//                serves the all-vector case (no per-element paths).
 //
 // Arithmetic follows the reference CPU backend (src/backend/cpu.rs:549-557, 632-657, 679-696;
 // src/ops/base.rs:29-36; src/core/value.rs:515-548, 708-764): integers wrap, boolean + - * are
@@ -185,11 +187,13 @@ __device__ __forceinline__ uint32_t fdiv(uint32_t n, FastDiv f) { return (__umul
 
 struct RowParams {
     int rank;         // >= 1; dims 0..rank-2 are row dims, dim rank-1 is the inner dim
-    int ux_log2;      // columns per thread = 1 << ux_log2, rows per thread = 4 >> ux_log2
+    int ux_log2;      // 128-bit columns per thread per row = 1 << ux_log2 (1, 2 or 4)
     int tx_log2;      // tile_x = 1 << tx_log2 threads along the inner dim, tile_y = 256 / tile_x
+    int iters;        // rows each thread walks (row loop length); a CTA covers tile_y * iters rows
     int mode_d, mode_l, mode_r;
     uint32_t n_col_chunks;
     uint32_t n_rows;
+    uint32_t n_last;  // extent of the innermost row dim (dim rank-2), 1 when rank == 1
     uint64_t inner;
     FastDiv div[kMaxPlanRank - 1];
     int64_t sd[kMaxPlanRank], sl[kMaxPlanRank], sr[kMaxPlanRank];
@@ -215,67 +219,124 @@ __device__ __forceinline__ void load_operand(const T *row, int mode, int64_t str
     }
 }
 
-template <typename F, int NIN>
-__global__ void __launch_bounds__(kBlock) rows_kernel(T *d, const T *l, const T *r, RowParams p, F f) {
+// Lean form for the common case (every operand walks the inner dim as whole aligned vectors,
+// reversed vectors or a broadcast scalar): no per-element paths.
+__device__ __forceinline__ void load_operand_fast(const T *row, int mode, uint32_t col, Vec &out) {
+    if (mode == kBroadcast) {
+        T x = row[0];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) out.e[j] = x;
+    } else {
+        const bool rev = mode == kRevVec;
+        Vec t;
+        t.q = *reinterpret_cast<const uint4 *>(rev ? row - (int64_t)col - (VEC - 1) : row + col);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) out.e[j] = rev ? t.e[VEC - 1 - j] : t.e[j];
+    }
+}
+
+// Row cursor of one thread: linear row index, its coordinate in the innermost row dim and the
+// three element offsets.  Stepping to the next row of the thread is an add unless the innermost
+// row dim wraps, in which case the row index is decoded again (multiply-shift division).
+template <int NIN>
+struct RowCursor {
+    uint32_t row, c_last;
+    int64_t od, ol, orr;
+    __device__ __forceinline__ void decode(const RowParams &p) {
+        uint32_t rem = row;
+        int64_t xd = 0, xl = 0, xr = 0;
+        uint32_t c = 0;
+        for (int k = p.rank - 2; k >= 0; --k) {
+            if (k > 0) {
+                uint32_t q = fdiv(rem, p.div[k]);
+                c = rem - q * p.div[k].d;
+                rem = q;
+            } else {
+                c = rem;
+            }
+            if (k == p.rank - 2) c_last = c;
+            xd += (int64_t)c * p.sd[k];
+            if (NIN >= 1) xl += (int64_t)c * p.sl[k];
+            if (NIN >= 2) xr += (int64_t)c * p.sr[k];
+        }
+        if (p.rank < 2) c_last = 0;
+        od = xd; ol = xl; orr = xr;
+    }
+    __device__ __forceinline__ void advance(const RowParams &p, uint32_t step, int64_t step_d, int64_t step_l, int64_t step_r) {
+        row += step;
+        c_last += step;
+        if (row >= p.n_rows) return;
+        if (c_last < p.n_last) {
+            od += step_d;
+            if (NIN >= 1) ol += step_l;
+            if (NIN >= 2) orr += step_r;
+        } else {
+            decode(p);
+        }
+    }
+};
+
+template <typename F, int NIN, bool FAST>
+__global__ void __launch_bounds__(kBlock) rows_kernel(T *d, const T *l, const T *r, const __grid_constant__ RowParams p, F f) {
     const uint32_t chunk = blockIdx.x % p.n_col_chunks;
-    const uint32_t row_tile = blockIdx.x / p.n_col_chunks;
+    const uint32_t row_block = blockIdx.x / p.n_col_chunks;
     const uint32_t tx = threadIdx.x & ((1u << p.tx_log2) - 1u);
     const uint32_t ty = threadIdx.x >> p.tx_log2;
     const uint32_t tile_y = kBlock >> p.tx_log2;
-    const uint32_t ux_n = 1u << p.ux_log2, uy_n = 4u >> p.ux_log2;
+    const uint32_t ux_n = 1u << p.ux_log2;
+    const int last = p.rank - 2;
+    const int64_t step_d = last >= 0 ? (int64_t)tile_y * p.sd[last] : 0;
+    const int64_t step_l = last >= 0 ? (int64_t)tile_y * p.sl[last] : 0;
+    const int64_t step_r = last >= 0 ? (int64_t)tile_y * p.sr[last] : 0;
+    const int64_t sdi = p.sd[p.rank - 1], sli = p.sl[p.rank - 1], sri = p.sr[p.rank - 1];
 
-    int64_t od[4], ol[4], orr[4];
+    // up to four 128-bit columns of this thread: fixed for the whole row loop
     uint64_t col[4];
     int cnt[4];
-    Vec a[4], b[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const uint32_t ux = u & (ux_n - 1u), uy = u >> p.ux_log2;
-        const uint64_t row = ((uint64_t)row_tile * uy_n + uy) * tile_y + ty;
-        const uint64_t cv = ((uint64_t)chunk * ux_n + ux) * (1u << p.tx_log2) + tx;
-        col[u] = cv * VEC;
-        cnt[u] = 0;
-        if (row < p.n_rows && col[u] < p.inner) {
-            uint64_t left = p.inner - col[u];
-            cnt[u] = left < (uint64_t)VEC ? (int)left : VEC;
-            if (ux == 0 || u == 0) {
-                uint32_t rem = (uint32_t)row;
-                int64_t xd = 0, xl = 0, xr = 0;
-                for (int k = p.rank - 2; k >= 0; --k) {
-                    uint32_t q = fdiv(rem, p.div[k]);
-                    uint32_t c = rem - q * p.div[k].d;
-                    rem = q;
-                    xd += (int64_t)c * p.sd[k];
-                    if (NIN >= 1) xl += (int64_t)c * p.sl[k];
-                    if (NIN >= 2) xr += (int64_t)c * p.sr[k];
-                }
-                od[u] = xd; ol[u] = xl; orr[u] = xr;
-            } else {
-                od[u] = od[u - 1]; ol[u] = ol[u - 1]; orr[u] = orr[u - 1];
-            }
-            if (NIN >= 1) load_operand(l + ol[u], p.mode_l, p.sl[p.rank - 1], col[u], cnt[u], a[u]);
-            if (NIN >= 2) load_operand(r + orr[u], p.mode_r, p.sr[p.rank - 1], col[u], cnt[u], b[u]);
-        } else if (u > 0) {
-            od[u] = od[u - 1]; ol[u] = ol[u - 1]; orr[u] = orr[u - 1];
-        } else {
-            od[u] = 0; ol[u] = 0; orr[u] = 0;
-        }
+        col[u] = (((uint64_t)chunk * ux_n + u) * (1u << p.tx_log2) + tx) * VEC;
+        cnt[u] = ((uint32_t)u < ux_n && col[u] < p.inner) ? (p.inner - col[u] < (uint64_t)VEC ? (int)(p.inner - col[u]) : VEC) : 0;
     }
-    const int64_t sdi = p.sd[p.rank - 1];
+
+    RowCursor<NIN> cur;
+    const uint64_t first = (uint64_t)row_block * tile_y * (uint32_t)p.iters + ty;
+    if (first >= p.n_rows) return;
+    cur.row = (uint32_t)first;
+    cur.decode(p);
+
+#pragma unroll 1
+    for (int it = 0; it < p.iters; ++it) {
+        Vec a[4], b[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        if (cnt[u] == 0) continue;
-        Vec o;
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? a[u].e[j] : T(), NIN >= 2 ? b[u].e[j] : T());
-        T *row = d + od[u];
-        if (p.mode_d == kContigVec && cnt[u] == VEC) {
-            *reinterpret_cast<uint4 *>(row + col[u]) = o.q;
-        } else {
-#pragma unroll
-            for (int j = 0; j < VEC; ++j)
-                if (j < cnt[u]) row[(int64_t)(col[u] + j) * sdi] = o.e[j];
+        for (int u = 0; u < 4; ++u) {
+            if (cnt[u] > 0) {
+                if (FAST) {
+                    if (NIN >= 1) load_operand_fast(l + cur.ol, p.mode_l, (uint32_t)col[u], a[u]);
+                    if (NIN >= 2) load_operand_fast(r + cur.orr, p.mode_r, (uint32_t)col[u], b[u]);
+                } else {
+                    if (NIN >= 1) load_operand(l + cur.ol, p.mode_l, sli, col[u], cnt[u], a[u]);
+                    if (NIN >= 2) load_operand(r + cur.orr, p.mode_r, sri, col[u], cnt[u], b[u]);
+                }
+            }
         }
+        T *row = d + cur.od;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (cnt[u] == 0) continue;
+            Vec o;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? a[u].e[j] : T(), NIN >= 2 ? b[u].e[j] : T());
+            if (FAST || (p.mode_d == kContigVec && cnt[u] == VEC)) {
+                *reinterpret_cast<uint4 *>(row + col[u]) = o.q;
+            } else {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j)
+                    if (j < cnt[u]) row[(int64_t)(col[u] + j) * sdi] = o.e[j];
+            }
+        }
+        cur.advance(p, tile_y, step_d, step_l, step_r);
+        if (cur.row >= p.n_rows) break;
     }
 }
 
@@ -320,12 +381,28 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     p.mode_d = plan.mode_d; p.mode_l = plan.mode_l; p.mode_r = plan.mode_r;
     p.n_col_chunks = (uint32_t)plan.n_col_chunks;
     p.n_rows = (uint32_t)plan.n_rows;
+    p.n_last = R >= 2 ? (uint32_t)plan.shape[R - 2] : 1u;
     p.inner = plan.shape[R - 1];
     for (int k = 0; k < R; ++k) {
         p.sd[k] = plan.stride_d[k]; p.sl[k] = plan.stride_l[k]; p.sr[k] = plan.stride_r[k];
         if (k < R - 1) p.div[k] = make_fastdiv((uint32_t)plan.shape[k]);
     }
-    rows_kernel<F, NIN><<<(unsigned)plan.grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+    // a CTA walks `iters` consecutive row tiles so that the row decode is paid once per CTA,
+    // while the grid stays at >= 16 CTAs per SM
+    const uint64_t row_tiles = (plan.n_rows + (uint64_t)plan.tile_y - 1) / (uint64_t)plan.tile_y;
+    uint64_t iters = (row_tiles * plan.n_col_chunks) / ((uint64_t)ctx->sm_count * 16);
+    if (iters < 1) iters = 1;
+    if (iters > 32) iters = 32;
+    p.iters = (int)iters;
+    const uint64_t grid = ((row_tiles + iters - 1) / iters) * plan.n_col_chunks;
+    if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
+    auto lean = [](int mode) { return mode == kContigVec || mode == kRevVec || mode == kBroadcast; };
+    const bool fast = plan.mode_d == kContigVec && (NIN < 1 || lean(plan.mode_l)) && (NIN < 2 || lean(plan.mode_r)) &&
+                      p.inner % VEC == 0 && p.inner < (1ull << 31);
+    if (fast)
+        rows_kernel<F, NIN, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+    else
+        rows_kernel<F, NIN, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
     return check_launch(ctx, "rows_kernel");
 }
 

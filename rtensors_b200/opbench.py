@@ -1,0 +1,156 @@
+"""Per-op timing table used by bench.py: every named op of the hot path, timed with CUDA events on
+the launching stream, with the algorithmic HBM bytes that define its roofline.
+
+Algorithmic bytes (s = element size): in-place scalar/unary op 2*s*n; same-shape binary 3*s*n;
+broadcast binary s*(n_out + n_A + n_B) (each operand's unique elements once); axis reduce
+s*(outer*R*inner + outer*inner); flat reduce s*n + s; fused mean_l1_loss 2*s*n + s; reduce-to-shape
+s*(rows*cols + cols); relu with mask 3*s*n; SGD update 3*s*n.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .meta import Meta, broadcast_params
+
+_FLUSH = None
+
+
+def _flush_l2(dev):
+    global _FLUSH
+    if _FLUSH is None or _FLUSH.device != torch.device(dev):
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    _FLUSH.add_(1)
+
+
+def _time(fn, iters=10, warm=3, flush=False, dev=None):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush_l2(dev)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return float(np.median(ts)), float(np.min(ts))
+
+
+def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False):
+    dev = f"cuda:{be.device}"
+    rows = []
+
+    def add(name, shape, nbytes, elems, fn, flush=False, note=None):
+        med, best = _time(fn, flush=flush, dev=dev)
+        gbs = nbytes / (med * 1e-3) / 1e9
+        row = {"op": name, "shape": shape, "ms": med, "ms_best": best, "gbs": gbs, "elements_per_s": elems / (med * 1e-3),
+               "frac": gbs / peak_gbs, "bytes": nbytes}
+        if flush:
+            row["l2"] = "flushed between iterations (working set could sit in L2)"
+        if note:
+            row["note"] = note
+        rows.append(row)
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED)
+    f32 = torch.float32
+
+    # ---- config 1: (4096,1) + (1,4096) -> (4096,4096), then sum over axis 1
+    A = torch.rand(4096, device=dev, generator=g) * 2 - 1
+    B = torch.rand(4096, device=dev, generator=g) * 2 - 1
+    am, bm = Meta.contiguous((4096, 1)), Meta.contiguous((1, 4096))
+    shape, sa, sb = broadcast_params(am, bm)
+    dm = Meta.contiguous(shape)
+    out = be.alloc(dm.size, f32)
+    add("broadcast_add f32", "(4096,1)+(1,4096)", 4 * (dm.size + 8192), dm.size,
+        lambda: be.broadcast((A, Meta(shape, sa, 0)), (B, Meta(shape, sb, 0)), (out, dm), L.ADD), flush=True)
+    red = be.alloc(4096, f32)
+    add("sum_at(1) f32", "(4096,4096)", 4 * (dm.size + 4096), dm.size,
+        lambda: be.apply_reduce((out, dm), red, 1, L.SUM), flush=True)
+    del out
+
+    # ---- config 2 parts
+    n2 = 1 << (24 if quick else 28)
+    x = torch.rand(n2, device=dev, generator=g) * 2 - 1
+    m2 = Meta.contiguous((n2,))
+    add("scalar_mul f32 in place", f"2^{int(np.log2(n2))}", 8 * n2, n2, lambda: be.scalar_apply(x, L.MUL, 1.0001, m2))
+    add("relu f32 in place", f"2^{int(np.log2(n2))}", 8 * n2, n2, lambda: be.apply_unary(x, L.RELU, m2))
+    ia = torch.randint(-(1 << 20), 1 << 20, (n2,), device=dev, generator=g, dtype=torch.int32)
+    ib = torch.randint(-(1 << 20), 1 << 20, (n2,), device=dev, generator=g, dtype=torch.int32)
+    io = torch.empty_like(ia)
+    add("tensor_add i32", f"2^{int(np.log2(n2))}", 12 * n2, n2, lambda: be.broadcast((ia, m2), (ib, m2), (io, m2), L.ADD))
+    add("fill f32", f"2^{int(np.log2(n2))}", 4 * n2, n2, lambda: be.fill(x, 1.5, m2), note="pure-write probe")
+    del ia, ib, io
+
+    # ---- config 3: strided / negative-step broadcast add -> (16,64,K,1024)
+    K = 64 if quick else 1024
+    bufa = torch.rand(K * 16, device=dev, generator=g) * 2 - 1
+    bufb = torch.rand(64 * 1024, device=dev, generator=g) * 2 - 1
+    Am = Meta.contiguous((K, 16, 1, 1)).view_as((1, K, 16, 1)).permute((2, 0, 1, 3))
+    Bm = Meta.contiguous((1, 64, 1, 1024)).slice(3, None, None, -1)
+    shape3, sa3, sb3 = broadcast_params(Am, Bm)
+    dm3 = Meta.contiguous(shape3)
+    out3 = be.alloc(dm3.size, f32)
+    add("broadcast_add f32 permuted A, step -1 B", str(shape3), 4 * (dm3.size + K * 16 + 65536), dm3.size,
+        lambda: be.broadcast((bufa, Meta(shape3, sa3, Am.offset)), (bufb, Meta(shape3, sb3, Bm.offset)), (out3, dm3), L.ADD))
+
+    # ---- config 4: reductions (reuse out3's storage as normal(0,1) input)
+    n4 = dm3.size
+    src = out3
+    src.normal_(generator=g)
+    S = 2048 if quick else 8192
+    msq = Meta.contiguous((S, S))
+    r1 = be.alloc(S, f32)
+    for opn, op in (("sum", L.SUM), ("mean", L.MEAN), ("max", L.MAX), ("min", L.MIN)):
+        for axis in (0, 1):
+            add(f"{opn}_at({axis}) f32", f"({S},{S})", 4 * (S * S + S), S * S,
+                (lambda op=op, axis=axis: be.apply_reduce((src, msq), r1, axis, op)), flush=S * S * 4 < (200 << 20))
+    d3 = (64, 512, 1024) if quick else (64, 4096, 1024)
+    m3 = Meta.contiguous(d3)
+    r3 = be.alloc(d3[0] * d3[2], f32)
+    for opn, op in (("sum", L.SUM), ("mean", L.MEAN), ("max", L.MAX), ("min", L.MIN)):
+        add(f"{opn}_at(1) f32", str(d3), 4 * (m3.size + d3[0] * d3[2]), m3.size,
+            (lambda op=op: be.apply_reduce((src, m3), r3, 1, op)))
+    r0 = be.alloc(1, f32)
+    nflat = n4
+    if world == 1:
+        add("sum (full) f32", f"2^{int(np.log2(nflat))}", 4 * nflat + 4, nflat,
+            lambda: be.apply_reduce_contiguous_flat(src, r0, 0, nflat, L.SUM))
+    else:
+        import torch.distributed as dist
+        per = nflat // world
+
+        def sharded_sum():
+            be.apply_reduce_contiguous_flat(src, r0, 0, per, L.SUM)
+            dist.all_reduce(r0, op=dist.ReduceOp.SUM)
+        add("sum (full) f32, per-GPU partial + NCCL allreduce", f"2^{int(np.log2(nflat))} over {world} GPUs",
+            4 * nflat + 4, nflat, sharded_sum, note="aggregate bytes over all GPUs / this rank's time")
+    nl = (1024 if quick else 4096) ** 2
+    ta, tb = src[:nl], src[nl:2 * nl]
+    add("mean_l1_loss f32", f"two ({int(nl ** 0.5)},{int(nl ** 0.5)})", 8 * nl + 4, nl,
+        lambda: be.l1_loss(ta, tb, 0, False), flush=True)
+    add("mean_l1_loss f32 + grad map", f"two ({int(nl ** 0.5)},{int(nl ** 0.5)})", 12 * nl + 4, nl,
+        lambda: be.l1_loss(ta, tb, 0, True), flush=True)
+
+    # ---- config 5 pieces: bias add, relu+mask, bias-grad reduce-to-shape, SGD update
+    Bt, H = 4096, 1024
+    act = src[: Bt * H]
+    bias = torch.zeros(H, device=dev)
+    ma, mb = Meta.contiguous((Bt, H)), Meta.contiguous((1, H))
+    shp, s_a, s_b = broadcast_params(ma, mb)
+    add("bias add in place f32", "(4096,1024)+=(1,1024)", 4 * (2 * Bt * H + H), Bt * H,
+        lambda: be.binary_assign(act, ma, bias, mb, L.ADD), flush=True)
+    add("relu + mask f32", "(4096,1024)", 12 * Bt * H, Bt * H, lambda: be.relu_mask(act), flush=True)
+    add("reduce_to_shape (bias grad) f32", "(4096,1024)->(1,1024)", 4 * (Bt * H + H), Bt * H,
+        lambda: be.reduce_to_shape(act, (Bt, H), (0, 1)), flush=True)
+    nw = 784 * 1024 + 1024 * 1024 + 1024 * 10 + 2058
+    nw -= nw % 4
+    w, gw = src[:nw], src[nw:2 * nw]
+    add("sgd_update f32", f"{nw} params", 12 * nw, nw, lambda: be.sgd_update(w, gw, 0.0), flush=True)
+    torch.cuda.synchronize()
+    return rows

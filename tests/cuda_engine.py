@@ -26,6 +26,7 @@ def to_host(t: torch.Tensor) -> np.ndarray:
 
 class CudaEngine:
     Meta = Meta
+    tree_sums = True  # float sums are tree-ordered on the GPU (sequential on the CPU backend)
 
     def __init__(self):
         self.b = backend()

@@ -1,0 +1,462 @@
+"""Parity of the CUDA library (through the C ABI) with the CPU oracle on seeded inputs.
+
+Bar: bit-exact for integer ops and for single-IEEE-op float elementwise work; float sums within
+1e-5 * log2(n) relative to sum(|x|) (the reference CPU sum is one sequential accumulator, the GPU
+sum is a tree); max / min exact.
+"""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from golden_runner import gather_view
+
+pytestmark = pytest.mark.gpu
+
+NP_DTYPES = [np.float32, np.float64, np.int8, np.int16, np.int32, np.int64, np.uint8, np.uint16, np.uint32,
+             np.uint64, np.bool_]
+
+
+def _b():
+    from cuda_engine import backend
+    return backend()
+
+
+def _dev(a):
+    return _b().alloc_from_slice(a)
+
+
+def _host(t):
+    return t.detach().cpu().numpy()
+
+
+def _rand(rng, n, dt):
+    dt = np.dtype(dt)
+    if dt.kind == "f":
+        return rng.uniform(-1, 1, n).astype(dt)
+    if dt.kind == "b":
+        return rng.integers(0, 2, n).astype(dt)
+    info = np.iinfo(dt)
+    lo, hi = max(info.min, -(1 << 20)), min(info.max, 1 << 20)
+    return rng.integers(lo, hi, n, endpoint=True).astype(dt)
+
+
+def _meta_pair(m):
+    from rtensors_b200.meta import Meta
+    return Meta(m.shape, m.strides, m.offset)
+
+
+# ------------------------------------------------------------------------------------- scalar ops
+@pytest.mark.parametrize("dt", NP_DTYPES, ids=lambda d: np.dtype(d).name)
+@pytest.mark.parametrize("n,off", [(1, 0), (3, 1), (1023, 0), (4099, 3), (1 << 16, 0), ((1 << 18) + 5, 7)])
+def test_scalar_chain_contiguous(dt, n, off):
+    rng = np.random.default_rng(n * 31 + off)
+    buf = _rand(rng, n + off + 2, dt)
+    meta = O.Meta((n,), (1,), off)
+    ref = buf.copy()
+    d = _dev(buf)
+    chain = [(O.MUL, 3), (O.ADD, 2), (O.SUB, 1)] if np.dtype(dt).kind != "b" else [(O.MUL, 1), (O.ADD, 0), (O.SUB, 1)]
+    if np.dtype(dt).kind in "fiu":
+        chain.append((O.DIV, 7))
+    for op, v in chain:
+        O.scalar_op(ref, op, v, meta)
+        _b().scalar_apply(d, op, v, _meta_pair(meta))
+    assert _host(d).tobytes() == ref.tobytes()
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.int32, np.int64, np.int8])
+@pytest.mark.parametrize("op", [O.NEG, O.RELU, O.ABS, O.SIGN])
+def test_unary_layouts(dt, op):
+    rng = np.random.default_rng(5)
+    base = O.Meta.contiguous((6, 10, 12))
+    views = [base, base.slice(2, None, None, 2), base.slice(0, None, None, -1).slice(2, None, None, -3),
+             base.permute((2, 0, 1)), base.index(1, 3), base.slice(1, 8, 1, -2).index(2, 5),
+             base.slice(0, None, None, -1).slice(1, None, None, -1).slice(2, None, None, -1)]
+    for m in views:
+        buf = _rand(rng, base.size, dt)
+        if np.dtype(dt).kind == "f":
+            buf[::7] = 0.0
+            buf[3::11] = -0.0
+        ref = buf.copy()
+        if m.is_contiguous() and any(s < 0 for s in m.strides):
+            # The reference dispatcher walks such a view forward from its offset (out of bounds);
+            # the intended result is the op applied to every viewed element.
+            idx = gather_index(m)
+            tmp = ref[idx].copy()
+            O.unary_op(tmp, op, O.Meta.contiguous((tmp.size,)))
+            ref[idx] = tmp
+        else:
+            O.unary_op(ref, op, m)
+        d = _dev(buf)
+        _b().apply_unary(d, op, _meta_pair(m))
+        assert _host(d).tobytes() == ref.tobytes(), m
+
+
+def gather_index(m):
+    idx = np.full(m.shape if m.shape else (), m.offset, dtype=np.int64)
+    for k, (n, s) in enumerate(zip(m.shape, m.strides)):
+        shp = [1] * len(m.shape)
+        shp[k] = n
+        idx = idx + (np.arange(n, dtype=np.int64) * s).reshape(shp)
+    return idx.reshape(-1)
+
+
+def test_relu_special_values_follow_cpu_backend():
+    x = np.array([np.nan, -0.0, 0.0, -1.5, 2.5, np.inf, -np.inf], dtype=np.float32)
+    ref = x.copy()
+    O.unary_op(ref, O.RELU, O.Meta.contiguous((x.size,)))
+    d = _dev(x)
+    _b().apply_unary(d, O.RELU, _meta_pair(O.Meta.contiguous((x.size,))))
+    assert _host(d).tobytes() == ref.tobytes()  # NaN -> 0 and -0 -> +0, as `x > 0 ? x : 0`
+    s = x.copy()
+    O.unary_op(s, O.SIGN, O.Meta.contiguous((x.size,)))
+    d = _dev(x)
+    _b().apply_unary(d, O.SIGN, _meta_pair(O.Meta.contiguous((x.size,))))
+    assert _host(d).tobytes() == s.tobytes()
+
+
+def test_fill_and_copy_view():
+    rng = np.random.default_rng(9)
+    base = O.Meta.contiguous((5, 8, 16))
+    for m in [base, base.slice(2, 1, 15, 3), base.permute((1, 2, 0)).slice(0, None, None, -1), base.index(0, 2)]:
+        buf = _rand(rng, base.size, np.float32)
+        ref = buf.copy()
+        O.fill(ref, 4.25, m)
+        d = _dev(buf)
+        _b().fill(d, 4.25, _meta_pair(m))
+        assert _host(d).tobytes() == ref.tobytes()
+        src = _rand(rng, base.size, np.int32)
+        got = _host(_b().contiguous(_dev(src), _meta_pair(m)))[: m.size]
+        assert np.array_equal(got, gather_view(src, m))
+
+
+# ------------------------------------------------------------------------------------- broadcast
+def _check_binary(a, am, b, bm, op):
+    want, dm = O.binary(a, am, b, bm, op)
+    out, gm = _b().binary(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), op)
+    assert tuple(gm.shape) == tuple(dm.shape)
+    assert _host(out)[: dm.size].tobytes() == want.tobytes(), (am, bm, op)
+
+
+def test_config_outer_product_add_then_axis_sum():
+    rng = np.random.default_rng(0x5EED)
+    a = rng.uniform(-1, 1, 4096).astype(np.float32)
+    b = rng.uniform(-1, 1, 4096).astype(np.float32)
+    am, bm = O.Meta.contiguous((4096, 1)), O.Meta.contiguous((1, 4096))
+    want, dm = O.binary(a, am, b, bm, O.ADD)
+    out, gm = _b().binary(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), O.ADD)
+    assert _host(out).tobytes() == want.tobytes()
+    ref, om = O.reduce_axis(want, dm, 1, O.SUM)
+    dst = _b().alloc(4096, torch.float32)
+    _b().apply_reduce((out, gm), dst, 1, O.SUM)
+    got = _host(dst)
+    tol = 1e-5 * math.log2(4096)
+    scale = np.abs(want.reshape(4096, 4096)).sum(axis=1, dtype=np.float64)
+    assert np.all(np.abs(got.astype(np.float64) - ref.astype(np.float64)) <= tol * scale)
+
+
+@pytest.mark.parametrize("scale", [16, 1])
+def test_config_strided_negative_step_broadcast(scale):
+    """A = permuted view of a (K,16,1,1) buffer, B = step -1 slice: the 4.3 GB configuration at
+    full size (scale 1: checked on sampled rows) and 1/16 of it (checked everywhere)."""
+    K, J, Lc = 1024 // scale, 64, 1024
+    rng = np.random.default_rng(0x5EED + 3)
+    bufa = rng.uniform(-1, 1, K * 16).astype(np.float32)
+    bufb = rng.uniform(-1, 1, J * Lc).astype(np.float32)
+    A = O.Meta.contiguous((K, 16, 1, 1)).view_as((1, K, 16, 1)).permute((2, 0, 1, 3))
+    B = O.Meta.contiguous((1, J, 1, Lc)).slice(3, None, None, -1)
+    out, gm = _b().binary(_dev(bufa), _meta_pair(A), _dev(bufb), _meta_pair(B), O.ADD)
+    assert tuple(gm.shape) == (16, J, K, Lc)
+    if scale > 1:
+        want, _ = O.binary(bufa, A, bufb, B, O.ADD)
+        assert _host(out).tobytes() == want.tobytes()
+    else:
+        o4 = out.view(16, J, K, Lc)
+        ta = torch.from_numpy(bufa).cuda().view(K, 16).t().contiguous()  # [i, k] = bufa[16k + i]
+        tb = torch.from_numpy(bufb).cuda().view(J, Lc).flip(1)           # [j, l] = bufb[1024 j + 1023 - l]
+        # out[i,j,k,l] = bufa[16k+i] + bufb[1024j + 1023 - l]: one IEEE add, checked slab by slab
+        for i in range(16):
+            ref = ta[i].view(1, K, 1) + tb.view(J, 1, Lc)
+            assert torch.equal(o4[i], ref)
+        # and a sample of rows against the oracle's coordinate walk
+        sub = O.Meta((1, 2, 3, Lc), (0, 0, 16, 0), 5)
+        wa, _ = O.binary(bufa, O.Meta((2, 1, 3, 1), (1, 16384, 16, 1), 5), bufb, B.slice(1, 0, 2, 1), O.ADD)
+        got = _host(o4[5:7, 0:2, 0:3, :].contiguous()).reshape(-1)
+        assert got.tobytes() == wa.tobytes()
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.int32, np.float64, np.uint8, np.int64, np.bool_])
+def test_random_broadcast_views(dt):
+    rng = np.random.default_rng(77)
+    for trial in range(40):
+        rank = int(rng.integers(1, 5))
+        full = [int(rng.choice([1, 2, 3, 5, 8, 33, 130])) for _ in range(rank)]
+        sha = [d if rng.random() < 0.7 else 1 for d in full]
+        shb = [d if rng.random() < 0.7 else 1 for d in full]
+        shb = shb[int(rng.integers(0, rank)):] if rng.random() < 0.3 else shb
+
+        def view_of(shape):
+            # a buffer with padding, then random reversals / steps / permutes that keep the shape
+            pad = [s * int(rng.choice([1, 2])) + int(rng.integers(0, 2)) for s in shape]
+            m = O.Meta.contiguous(pad)
+            for dim, s in enumerate(shape):
+                step = int(rng.choice([1, 1, -1, 2, -2])) if pad[dim] >= 2 * s else int(rng.choice([1, -1]))
+                if step > 0:
+                    m = m.slice(dim, 0, min(pad[dim], (s - 1) * step + 1), step)
+                else:
+                    start = (s - 1) * (-step)
+                    m = m.slice(dim, start, None, step)
+                assert m.shape[dim] == s, (m, shape, dim, step)
+            return int(np.prod(pad)), m
+        na, am = view_of(sha)
+        nb, bm = view_of(shb)
+        a, b = _rand(rng, na, dt), _rand(rng, nb, dt)
+        ops = [O.ADD, O.SUB, O.MUL] + ([O.DIV] if np.dtype(dt).kind == "f" else [])
+        _check_binary(a, am, b, bm, int(rng.choice(ops)))
+
+
+def test_broadcast_in_place_forms():
+    rng = np.random.default_rng(3)
+    from rtensors_b200.meta import Meta
+    for am, bshape in [(O.Meta.contiguous((64, 48)), (48,)), (O.Meta.contiguous((64, 48)).slice(1, None, None, -1), (1, 1)),
+                       (O.Meta.contiguous((8, 64, 48)).permute((2, 0, 1)), (8, 1)),
+                       (O.Meta.contiguous((64, 48)).slice(0, None, None, 2), (32, 48))]:
+        a = _rand(rng, 8 * 64 * 48, np.float32)
+        b = _rand(rng, int(np.prod(bshape)), np.float32)
+        bm = O.Meta.contiguous(bshape)
+        ref = a.copy()
+        shape, sa, sb = O.broadcast_params(am, bm)
+        ma = O.Meta(shape, sa, am.offset)
+        O.broadcast(ref, ma, b, O.Meta(shape, sb, bm.offset), ref, ma, O.MUL)
+        d = _dev(a)
+        _b().binary_assign(d, _meta_pair(am), _dev(b), _meta_pair(bm), O.MUL)
+        assert _host(d).tobytes() == ref.tobytes()
+
+
+def test_i32_same_shape_add_bit_exact():
+    rng = np.random.default_rng(0x5EED + 2)
+    n = (1 << 22) + 3
+    a = rng.integers(-(1 << 20), 1 << 20, n, endpoint=True).astype(np.int32)
+    b = rng.integers(-(1 << 20), 1 << 20, n, endpoint=True).astype(np.int32)
+    m = O.Meta.contiguous((n,))
+    _check_binary(a, m, b, m, O.ADD)
+    # wrap-around
+    a[:4] = [2**31 - 1, -2**31, 2**31 - 1, 5]
+    b[:4] = [1, -1, 2**31 - 1, -7]
+    _check_binary(a, m, b, m, O.ADD)
+    _check_binary(a, m, b, m, O.MUL)
+
+
+def test_rank_above_plan_limit_is_peeled():
+    rng = np.random.default_rng(4)
+    shape = (2, 3) * 5  # rank 10; alternating strides below block merging
+    pad = tuple(s + 1 for s in shape)
+    m = O.Meta.contiguous(pad)
+    for dim, s in enumerate(shape):
+        m = m.slice(dim, 0, s, 1)
+    a = _rand(rng, int(np.prod(pad)), np.float32)
+    b = _rand(rng, 3, np.float32)
+    _check_binary(a, m, b, O.Meta.contiguous((3,)), O.ADD)
+
+
+def test_empty_and_scalar_shapes():
+    a = np.array([2.5], dtype=np.float32)
+    _check_binary(a, O.Meta.contiguous(()), a, O.Meta.contiguous(()), O.MUL)
+    from rtensors_b200.meta import Meta
+    z = _b().alloc(1, torch.float32)
+    _b().scalar_apply(z, O.ADD, 1.0, Meta((0, 4), (4, 1), 0))  # empty view: no launch, no error
+    out = _b().alloc(4, torch.float32)
+    _b().apply_reduce((z, Meta((0, 4), (4, 1), 0)), out, 1, O.SUM)  # zero outputs: no launch
+
+
+# ------------------------------------------------------------------------------------- reductions
+def _sum_tol(n):
+    return 1e-5 * max(math.log2(max(n, 2)), 1.0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("n,start", [(1, 0), (2, 1), (31, 0), (1025, 3), (4096, 0), ((1 << 20) + 7, 1), (1 << 24, 0)])
+def test_flat_reductions(dt, n, start):
+    rng = np.random.default_rng(n + start)
+    x = rng.standard_normal(n + start + 1).astype(dt)
+    d = _dev(x)
+    absum = float(np.abs(x[start:start + n]).sum(dtype=np.float64))
+    for op in (O.SUM, O.MEAN, O.MAX, O.MIN):
+        want = O.reduce_flat(x, start, n, op)[0]
+        out = _b().alloc(1, d.dtype)
+        _b().apply_reduce_contiguous_flat(d, out, start, n, op)
+        got = _host(out)[0]
+        if op in (O.MAX, O.MIN):
+            assert got.tobytes() == want.tobytes()
+        else:
+            scale = absum if op == O.SUM else absum / n
+            assert abs(float(got) - float(want)) <= _sum_tol(n) * scale + 1e-30, (op, got, want)
+
+
+@pytest.mark.parametrize("outer,r,inner", [(1, 8192, 1), (37, 1000, 1), (4096, 33, 1), (3, 70000, 1), (8, 5, 1),
+                                           (1, 4096, 1024), (64, 128, 48), (5, 777, 130), (2, 3, 7), (300, 2, 4096),
+                                           (1, 4096, 10), (7, 1, 9)])
+def test_axis_reductions(outer, r, inner):
+    rng = np.random.default_rng(outer * 7 + r + inner)
+    x = rng.standard_normal(outer * r * inner).astype(np.float32)
+    d = _dev(x)
+    absum = np.abs(x.reshape(outer, r, inner)).sum(axis=1, dtype=np.float64).reshape(-1)
+    for op in (O.SUM, O.MEAN, O.MAX, O.MIN):
+        want = O.reduce_ori(x, outer, r, inner, op)
+        got = _host(_b().reduce_axis_ori(d, 0, outer, r, inner, op))[: outer * inner]
+        if op in (O.MAX, O.MIN):
+            assert got.tobytes() == want.tobytes(), (op,)
+        else:
+            scale = absum if op == O.SUM else absum / r
+            err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+            assert np.all(err <= _sum_tol(r) * scale + 1e-30), (op, err.max())
+
+
+def test_axis_reduction_misaligned_offset_and_f64():
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal(3 + 16 * 100 * 12).astype(np.float64)
+    for off in (0, 1, 3):
+        want = O.reduce_ori(x[off:off + 16 * 100 * 12].copy(), 16, 100, 12, O.SUM)
+        got = _host(_b().reduce_axis_ori(_dev(x), off, 16, 100, 12, O.SUM))
+        assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
+        want = O.reduce_ori(x[off:off + 16 * 100 * 12].copy(), 16 * 100, 12, 1, O.MAX)
+        got = _host(_b().reduce_axis_ori(_dev(x), off, 16 * 100, 12, 1, O.MAX))
+        assert got.tobytes() == want.tobytes()
+
+
+def test_max_ignores_nan_and_starts_from_lowest_finite():
+    x = np.array([np.nan, -np.inf, -np.inf, np.nan], dtype=np.float32)
+    for op in (O.MAX, O.MIN):
+        want = O.reduce_flat(x, 0, 4, op)
+        out = _b().alloc(1, torch.float32)
+        _b().apply_reduce_contiguous_flat(_dev(x), out, 0, 4, op)
+        assert _host(out).tobytes() == want.tobytes()
+
+
+def test_tensor_api_reductions_on_views():
+    from rtensors_b200.tensor import Tensor
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((12, 20, 16)).astype(np.float32)
+    t = Tensor.from_buf(x, x.shape, np.float32, _b())
+    v = t.slice(2, None, None, -2).permute((1, 0, 2))  # non-contiguous: copied first, as the reference does
+    xv = x[:, :, ::-2].transpose(1, 0, 2)
+    got = v.sum_at(1).cpu()
+    assert got.shape == (20, 1, 8)
+    assert np.allclose(got[:, 0, :], xv.sum(axis=1), rtol=1e-5, atol=1e-5)
+    assert v.max().item() == xv.max()
+    assert abs(float(v.mean().item()) - float(xv.mean())) < 1e-5
+
+
+# ------------------------------------------------------------------------------------- fused ops
+@pytest.mark.parametrize("n", [1, 5, 4096, (1 << 20) + 3])
+def test_l1_loss(n):
+    rng = np.random.default_rng(n)
+    a = rng.standard_normal(n).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    b[::5] = a[::5]  # exact zeros in the difference: sign(0) = 0
+    for reduction in (0, 1):
+        want, wg = O.l1_loss(a, b, reduction, True)
+        loss, g = _b().l1_loss(_dev(a), _dev(b), reduction, True)
+        scale = float(np.abs(a - b).sum(dtype=np.float64)) / (n if reduction == 0 else 1)
+        assert abs(float(_host(loss)[0]) - float(want[0])) <= _sum_tol(n) * scale + 1e-30
+        assert _host(g).tobytes() == wg.tobytes()
+        loss2, _ = _b().l1_loss(_dev(a), _dev(b), reduction, False)
+        assert _host(loss2).tobytes() == _host(loss).tobytes()
+
+
+def test_reduce_to_shape():
+    rng = np.random.default_rng(2)
+    for shape, strides in [((4096, 1024), (0, 1)), ((4096, 10), (0, 1)), ((6, 5, 4, 3), (0, 12, 0, 1)),
+                           ((6, 5, 4, 3), (0, 0, 3, 1)), ((8, 16), (16, 0)), ((7, 9), (0, 0)), ((3, 4), (4, 1))]:
+        up = rng.standard_normal(int(np.prod(shape))).astype(np.float32)
+        want, wshape = O.reduce_to_shape(up, shape, strides, intended=True)
+        got, gshape = _b().reduce_to_shape(_dev(up), shape, strides)
+        assert tuple(gshape) == tuple(wshape)
+        g = _host(got)[: want.size]
+        red = tuple(k for k, s in enumerate(strides) if s == 0)
+        scale = np.abs(up.reshape(shape)).sum(axis=red, dtype=np.float64).reshape(-1) if red else np.abs(up)
+        cnt = int(np.prod([shape[k] for k in red])) if red else 1
+        assert np.all(np.abs(g.astype(np.float64) - want.astype(np.float64)) <= _sum_tol(cnt) * scale + 1e-30)
+
+
+def test_relu_mask_sgd_and_u8_convert():
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal(4096 * 33 + 4).astype(np.float32)
+    x[::9] = 0.0
+    ref = x.copy()
+    wm = O.relu_mask(ref)
+    d = _dev(x)
+    m = _b().relu_mask(d)
+    assert _host(d).tobytes() == ref.tobytes() and _host(m).tobytes() == wm.tobytes()
+    p = rng.standard_normal(100003).astype(np.float32)
+    g = rng.standard_normal(100003).astype(np.float32)
+    rp = p.copy()
+    O.sgd_update(rp, g, 0.01)
+    dp = _dev(p)
+    _b().sgd_update(dp, _dev(g), 0.01)
+    assert _host(dp).tobytes() == rp.tobytes()
+    u = rng.integers(0, 256, 28 * 28 * 17 + 1).astype(np.uint8)
+    assert _host(_b().u8_to_f32_div(_dev(u), 255.0)).tobytes() == O.u8_to_f32_div(u, 255.0).tobytes()
+
+
+# ------------------------------------------------------------------------------------- v1 launchers
+def test_v1_reference_launchers():
+    import rtensors_b200 as rt
+    lib = rt.lib()
+    rng = np.random.default_rng(10)
+    torch.cuda.synchronize()
+    x = rng.uniform(-1, 1, 5000).astype(np.float32)
+    d = _dev(x)
+    torch.cuda.synchronize()
+    ref = x.copy()
+    # contiguous scalar op: pointer already advanced by `start`
+    lib.launch_mul_contiguous_f32(C.c_void_p(d.data_ptr() + 4 * 3), C.c_size_t(4000), C.c_float(3.0), C.c_uint(256))
+    O.scalar_op(ref, O.MUL, 3.0, O.Meta((4000,), (1,), 3))
+    lib.launch_add_strided_f32(C.c_void_p(d.data_ptr()), C.c_size_t(4999), C.c_ssize_t(-3), C.c_size_t(1000),
+                               C.c_float(2.0), C.c_uint(256))
+    O.scalar_op(ref, O.ADD, 2.0, O.Meta((1000,), (-3,), 4999))
+    lib.launch_relu_contiguous_f32(C.c_void_p(d.data_ptr()), C.c_size_t(10), C.c_size_t(300), C.c_uint(256))
+    O.unary_op(ref, O.RELU, O.Meta((300,), (1,), 10))
+    # nd_affine takes shape / stride arrays in device memory
+    shape = torch.tensor([10, 20], dtype=torch.int64, device="cuda")
+    stride = torch.tensor([200, -2], dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    lib.launch_sub_nd_affine_f32(C.c_void_p(d.data_ptr()), C.c_size_t(100), C.c_void_p(stride.data_ptr()),
+                                 C.c_void_p(shape.data_ptr()), C.c_size_t(2), C.c_size_t(200), C.c_float(1.0),
+                                 C.c_uint(256))
+    O.scalar_op(ref, O.SUB, 1.0, O.Meta((10, 20), (200, -2), 100))
+    torch.cuda.synchronize()
+    assert _host(d).tobytes() == ref.tobytes()
+    # broadcast through the v1 symbol: (8,1) + (1,16)
+    a, b = x[:8].copy(), x[8:24].copy()
+    da, db, dd = _dev(a), _dev(b), _b().alloc(128, torch.float32)
+    ls = torch.tensor([1, 0], dtype=torch.int64, device="cuda")
+    rs = torch.tensor([0, 1], dtype=torch.int64, device="cuda")
+    ds = torch.tensor([16, 1], dtype=torch.int64, device="cuda")
+    sh = torch.tensor([8, 16], dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    lib.launch_binary_broadcast_elementwise_f32(C.c_void_p(da.data_ptr()), C.c_void_p(db.data_ptr()),
+                                                C.c_void_p(dd.data_ptr()), C.c_size_t(0), C.c_size_t(0), C.c_size_t(0),
+                                                C.c_size_t(2), C.c_size_t(128), C.c_void_p(ls.data_ptr()),
+                                                C.c_void_p(rs.data_ptr()), C.c_void_p(ds.data_ptr()),
+                                                C.c_void_p(sh.data_ptr()), C.c_uint8(0), C.c_uint(256))
+    torch.cuda.synchronize()
+    want, _ = O.binary(a, O.Meta.contiguous((8, 1)), b, O.Meta.contiguous((1, 16)), O.ADD)
+    assert _host(dd).tobytes() == want.tobytes()
+    # reductions
+    out = _b().alloc(1, torch.float32)
+    torch.cuda.synchronize()
+    lib.launch_flat_contiguous_reduce_f32(C.c_void_p(d.data_ptr()), C.c_void_p(out.data_ptr()), C.c_size_t(5),
+                                          C.c_size_t(4000), C.c_uint8(3), None, C.c_uint(256))
+    torch.cuda.synchronize()
+    assert _host(out).tobytes() == O.reduce_flat(ref, 5, 4000, O.MAX).tobytes()
+    out2 = _b().alloc(50, torch.float32)
+    lib.launch_nd_reduce_contiguous_f32(C.c_void_p(d.data_ptr()), C.c_void_p(out2.data_ptr()), C.c_size_t(0),
+                                        C.c_size_t(5), C.c_size_t(100), C.c_size_t(10), C.c_uint8(4), None,
+                                        C.c_uint(256))
+    torch.cuda.synchronize()
+    assert _host(out2).tobytes() == O.reduce_ori(ref[:5000], 5, 100, 10, O.MIN).tobytes()
+    assert lib.rtensors_take_cuda_alloc_error() == 0
