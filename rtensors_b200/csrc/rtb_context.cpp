@@ -6,7 +6,7 @@
 
 namespace rtb {
 
-static constexpr size_t kCounterBytes = 256;
+static constexpr size_t kCounterBytes = 65536;  // header of completion counters, kept at zero by the kernels
 
 int workspace(Ctx *ctx, size_t bytes, void **out) {
     size_t need = kCounterBytes + ((bytes + 255) & ~size_t(255));

@@ -187,7 +187,6 @@ __device__ __forceinline__ uint32_t fdiv(uint32_t n, FastDiv f) { return (__umul
 
 struct RowParams {
     int rank;         // >= 1; dims 0..rank-2 are row dims, dim rank-1 is the inner dim
-    int ux_log2;      // 128-bit columns per thread per row = 1 << ux_log2 (1, 2 or 4)
     int tx_log2;      // tile_x = 1 << tx_log2 threads along the inner dim, tile_y = 256 / tile_x
     int iters;        // rows each thread walks (row loop length); a CTA covers tile_y * iters rows
     int mode_d, mode_l, mode_r;
@@ -199,6 +198,7 @@ struct RowParams {
     int64_t sd[kMaxPlanRank], sl[kMaxPlanRank], sr[kMaxPlanRank];
 };
 
+// General operand walk: any mode, partial vectors allowed.
 __device__ __forceinline__ void load_operand(const T *row, int mode, int64_t stride, uint64_t col, int cnt, Vec &out) {
     if (mode == kContigVec && cnt == VEC) {
         out.q = *reinterpret_cast<const uint4 *>(row + col);
@@ -219,8 +219,7 @@ __device__ __forceinline__ void load_operand(const T *row, int mode, int64_t str
     }
 }
 
-// Lean form for the common case (every operand walks the inner dim as whole aligned vectors,
-// reversed vectors or a broadcast scalar): no per-element paths.
+// Lean operand walk (whole aligned vectors, reversed vectors or a broadcast scalar).
 __device__ __forceinline__ void load_operand_fast(const T *row, int mode, uint32_t col, Vec &out) {
     if (mode == kBroadcast) {
         T x = row[0];
@@ -236,16 +235,19 @@ __device__ __forceinline__ void load_operand_fast(const T *row, int mode, uint32
 }
 
 // Row cursor of one thread: linear row index, its coordinate in the innermost row dim and the
-// three element offsets.  Stepping to the next row of the thread is an add unless the innermost
-// row dim wraps, in which case the row index is decoded again (multiply-shift division).
+// three row pointers.  Stepping to the thread's next row is a handful of adds unless the
+// innermost row dim wraps; then the row index is decoded again (multiply-shift division).
 template <int NIN>
 struct RowCursor {
     uint32_t row, c_last;
-    int64_t od, ol, orr;
-    __device__ __forceinline__ void decode(const RowParams &p) {
+    T *pd;
+    const T *pl;
+    const T *pr;
+    __device__ __forceinline__ void decode(const RowParams &p, T *d, const T *l, const T *r) {
         uint32_t rem = row;
         int64_t xd = 0, xl = 0, xr = 0;
         uint32_t c = 0;
+        c_last = 0;
         for (int k = p.rank - 2; k >= 0; --k) {
             if (k > 0) {
                 uint32_t q = fdiv(rem, p.div[k]);
@@ -259,83 +261,92 @@ struct RowCursor {
             if (NIN >= 1) xl += (int64_t)c * p.sl[k];
             if (NIN >= 2) xr += (int64_t)c * p.sr[k];
         }
-        if (p.rank < 2) c_last = 0;
-        od = xd; ol = xl; orr = xr;
+        pd = d + xd; pl = l + xl; pr = r + xr;
     }
-    __device__ __forceinline__ void advance(const RowParams &p, uint32_t step, int64_t step_d, int64_t step_l, int64_t step_r) {
+    // returns true when the row pointers were recomputed from scratch
+    __device__ __forceinline__ bool advance(const RowParams &p, uint32_t step, int64_t step_d, int64_t step_l,
+                                            int64_t step_r, T *d, const T *l, const T *r) {
         row += step;
         c_last += step;
-        if (row >= p.n_rows) return;
+        if (row >= p.n_rows) return false;
         if (c_last < p.n_last) {
-            od += step_d;
-            if (NIN >= 1) ol += step_l;
-            if (NIN >= 2) orr += step_r;
-        } else {
-            decode(p);
+            pd += step_d;
+            if (NIN >= 1) pl += step_l;
+            if (NIN >= 2) pr += step_r;
+            return false;
         }
+        decode(p, d, l, r);
+        return true;
     }
 };
 
-template <typename F, int NIN, bool FAST>
-__global__ void __launch_bounds__(kBlock) rows_kernel(T *d, const T *l, const T *r, const __grid_constant__ RowParams p, F f) {
+// UX = 128-bit columns per thread per row.  FAST: every operand is in a lean mode, the inner
+// extent is a whole number of vectors below 2^31 and the output is a vector store.  Operands
+// that do not move between consecutive rows of the thread (zero stride along the innermost row
+// dim: a broadcast row or column) stay in registers until that dim wraps.
+template <typename F, int NIN, bool FAST, int UX>
+__global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) rows_kernel(T *d, const T *l, const T *r, const __grid_constant__ RowParams p, F f) {
     const uint32_t chunk = blockIdx.x % p.n_col_chunks;
     const uint32_t row_block = blockIdx.x / p.n_col_chunks;
     const uint32_t tx = threadIdx.x & ((1u << p.tx_log2) - 1u);
     const uint32_t ty = threadIdx.x >> p.tx_log2;
     const uint32_t tile_y = kBlock >> p.tx_log2;
-    const uint32_t ux_n = 1u << p.ux_log2;
     const int last = p.rank - 2;
     const int64_t step_d = last >= 0 ? (int64_t)tile_y * p.sd[last] : 0;
     const int64_t step_l = last >= 0 ? (int64_t)tile_y * p.sl[last] : 0;
     const int64_t step_r = last >= 0 ? (int64_t)tile_y * p.sr[last] : 0;
     const int64_t sdi = p.sd[p.rank - 1], sli = p.sl[p.rank - 1], sri = p.sr[p.rank - 1];
 
-    // up to four 128-bit columns of this thread: fixed for the whole row loop
-    uint64_t col[4];
-    int cnt[4];
+    uint64_t col[UX];
+    int cnt[UX];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        col[u] = (((uint64_t)chunk * ux_n + u) * (1u << p.tx_log2) + tx) * VEC;
-        cnt[u] = ((uint32_t)u < ux_n && col[u] < p.inner) ? (p.inner - col[u] < (uint64_t)VEC ? (int)(p.inner - col[u]) : VEC) : 0;
+    for (int u = 0; u < UX; ++u) {
+        col[u] = (((uint64_t)chunk * UX + u) * (1u << p.tx_log2) + tx) * VEC;
+        cnt[u] = col[u] < p.inner ? (p.inner - col[u] < (uint64_t)VEC ? (int)(p.inner - col[u]) : VEC) : 0;
     }
+    if (cnt[0] == 0) return;
 
     RowCursor<NIN> cur;
     const uint64_t first = (uint64_t)row_block * tile_y * (uint32_t)p.iters + ty;
     if (first >= p.n_rows) return;
     cur.row = (uint32_t)first;
-    cur.decode(p);
+    cur.decode(p, d, l, r);
 
+    Vec a[UX], b[UX];
+    bool fresh = true;
 #pragma unroll 1
     for (int it = 0; it < p.iters; ++it) {
-        Vec a[4], b[4];
+        if (NIN >= 1 && (fresh || step_l != 0)) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (cnt[u] > 0) {
-                if (FAST) {
-                    if (NIN >= 1) load_operand_fast(l + cur.ol, p.mode_l, (uint32_t)col[u], a[u]);
-                    if (NIN >= 2) load_operand_fast(r + cur.orr, p.mode_r, (uint32_t)col[u], b[u]);
-                } else {
-                    if (NIN >= 1) load_operand(l + cur.ol, p.mode_l, sli, col[u], cnt[u], a[u]);
-                    if (NIN >= 2) load_operand(r + cur.orr, p.mode_r, sri, col[u], cnt[u], b[u]);
+            for (int u = 0; u < UX; ++u)
+                if (cnt[u] > 0) {
+                    if (FAST) load_operand_fast(cur.pl, p.mode_l, (uint32_t)col[u], a[u]);
+                    else load_operand(cur.pl, p.mode_l, sli, col[u], cnt[u], a[u]);
                 }
-            }
         }
-        T *row = d + cur.od;
+        if (NIN >= 2 && (fresh || step_r != 0)) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < UX; ++u)
+                if (cnt[u] > 0) {
+                    if (FAST) load_operand_fast(cur.pr, p.mode_r, (uint32_t)col[u], b[u]);
+                    else load_operand(cur.pr, p.mode_r, sri, col[u], cnt[u], b[u]);
+                }
+        }
+#pragma unroll
+        for (int u = 0; u < UX; ++u) {
             if (cnt[u] == 0) continue;
             Vec o;
 #pragma unroll
             for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? a[u].e[j] : T(), NIN >= 2 ? b[u].e[j] : T());
             if (FAST || (p.mode_d == kContigVec && cnt[u] == VEC)) {
-                *reinterpret_cast<uint4 *>(row + col[u]) = o.q;
+                *reinterpret_cast<uint4 *>(cur.pd + col[u]) = o.q;
             } else {
 #pragma unroll
                 for (int j = 0; j < VEC; ++j)
-                    if (j < cnt[u]) row[(int64_t)(col[u] + j) * sdi] = o.e[j];
+                    if (j < cnt[u]) cur.pd[(int64_t)(col[u] + j) * sdi] = o.e[j];
             }
         }
-        cur.advance(p, tile_y, step_d, step_l, step_r);
+        fresh = cur.advance(p, tile_y, step_d, step_l, step_r, d, l, r);
         if (cur.row >= p.n_rows) break;
     }
 }
@@ -375,11 +386,7 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     p.rank = plan.rank;
     p.tx_log2 = ilog2((uint64_t)plan.tile_x);
     const int R = plan.rank;
-    uint64_t inner_vecs = (plan.shape[R - 1] + VEC - 1) / VEC;
-    int ux = inner_vecs >= 4ull * plan.tile_x ? 4 : inner_vecs >= 2ull * plan.tile_x ? 2 : 1;
-    p.ux_log2 = ux == 4 ? 2 : ux == 2 ? 1 : 0;
     p.mode_d = plan.mode_d; p.mode_l = plan.mode_l; p.mode_r = plan.mode_r;
-    p.n_col_chunks = (uint32_t)plan.n_col_chunks;
     p.n_rows = (uint32_t)plan.n_rows;
     p.n_last = R >= 2 ? (uint32_t)plan.shape[R - 2] : 1u;
     p.inner = plan.shape[R - 1];
@@ -387,22 +394,29 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         p.sd[k] = plan.stride_d[k]; p.sl[k] = plan.stride_l[k]; p.sr[k] = plan.stride_r[k];
         if (k < R - 1) p.div[k] = make_fastdiv((uint32_t)plan.shape[k]);
     }
-    // a CTA walks `iters` consecutive row tiles so that the row decode is paid once per CTA,
-    // while the grid stays at >= 16 CTAs per SM
-    const uint64_t row_tiles = (plan.n_rows + (uint64_t)plan.tile_y - 1) / (uint64_t)plan.tile_y;
-    uint64_t iters = (row_tiles * plan.n_col_chunks) / ((uint64_t)ctx->sm_count * 16);
-    if (iters < 1) iters = 1;
-    if (iters > 32) iters = 32;
-    p.iters = (int)iters;
-    const uint64_t grid = ((row_tiles + iters - 1) / iters) * plan.n_col_chunks;
-    if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
     auto lean = [](int mode) { return mode == kContigVec || mode == kRevVec || mode == kBroadcast; };
     const bool fast = plan.mode_d == kContigVec && (NIN < 1 || lean(plan.mode_l)) && (NIN < 2 || lean(plan.mode_r)) &&
                       p.inner % VEC == 0 && p.inner < (1ull << 31);
-    if (fast)
-        rows_kernel<F, NIN, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+    // four 128-bit columns per thread when the row is long enough, else one
+    const uint64_t inner_vecs = (p.inner + VEC - 1) / VEC;
+    const int ux = (fast && inner_vecs >= 4ull * plan.tile_x) ? 4 : 1;
+    const uint64_t chunks = (inner_vecs + (uint64_t)plan.tile_x * ux - 1) / ((uint64_t)plan.tile_x * ux);
+    p.n_col_chunks = (uint32_t)chunks;
+    // a CTA walks `iters` consecutive row tiles: the row decode and any broadcast operand held in
+    // registers are paid once per CTA, while the grid stays at >= 8 CTAs per SM
+    const uint64_t row_tiles = (plan.n_rows + (uint64_t)plan.tile_y - 1) / (uint64_t)plan.tile_y;
+    uint64_t iters = (row_tiles * chunks) / ((uint64_t)ctx->sm_count * 8);
+    if (iters < 1) iters = 1;
+    if (iters > 64) iters = 64;
+    p.iters = (int)iters;
+    const uint64_t grid = ((row_tiles + iters - 1) / iters) * chunks;
+    if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
+    if (fast && ux == 4)
+        rows_kernel<F, NIN, true, 4><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+    else if (fast)
+        rows_kernel<F, NIN, true, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
     else
-        rows_kernel<F, NIN, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        rows_kernel<F, NIN, false, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
     return check_launch(ctx, "rows_kernel");
 }
 

@@ -45,8 +45,9 @@ struct Ctx {
     std::map<void *, size_t> live_blocks;
 };
 
-// Returns a workspace of at least `bytes` bytes (256-byte aligned).  The first 256 bytes are
-// completion counters that kernels leave at zero; they are zeroed when the workspace is created.
+// Returns a workspace with a 64 KiB header followed by at least `bytes` bytes of scratch.  The
+// header holds completion counters that kernels leave at zero; it is zeroed when the workspace is
+// created.
 int workspace(Ctx *ctx, size_t bytes, void **out);
 Ctx *default_ctx();  // ctx on the current device bound to the legacy default stream (ABI v1)
 

@@ -160,11 +160,11 @@ int make_plan(size_t es, int n_inputs, size_t rank, const size_t *shape, const V
         if (rows >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "more than 2^31 rows in one launch");
     }
     out->n_rows = rows;
-    // each thread handles 4 vectors: 4 columns of one row when the row is long, else 4 rows
-    int ux = inner_vecs >= 4ull * out->tile_x ? 4 : inner_vecs >= 2ull * out->tile_x ? 2 : 1;
-    int uy = 4 / ux;
+    // four 128-bit columns per thread when the row is long enough, else one; the launcher lets a
+    // CTA walk several row tiles, so `grid` here is the upper bound (one row tile per CTA)
+    int ux = inner_vecs >= 4ull * out->tile_x ? 4 : 1;
     out->n_col_chunks = (inner_vecs + (uint64_t)out->tile_x * ux - 1) / ((uint64_t)out->tile_x * ux);
-    uint64_t row_tiles = (rows + (uint64_t)out->tile_y * uy - 1) / ((uint64_t)out->tile_y * uy);
+    uint64_t row_tiles = (rows + (uint64_t)out->tile_y - 1) / (uint64_t)out->tile_y;
     out->grid = row_tiles * out->n_col_chunks;
     if (out->grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
     return RTB_OK;

@@ -17,6 +17,12 @@ namespace {
 
 constexpr int kBlock = 256;
 constexpr int kWarps = kBlock / 32;
+// Workspace header (see workspace()): 64 completion counters for the flat kernel, then
+// kMaxTileCounters per-tile counters for the axis kernels; scratch data starts after the header.
+// Kernels leave every counter at zero.
+constexpr size_t kTileCounterOffset = 64;      // in counters
+constexpr size_t kMaxTileCounters = 16384 - 64;
+constexpr size_t kWorkspaceHeader = 65536;     // bytes
 
 template <typename T> struct Limits;
 template <> struct Limits<float> {
@@ -124,7 +130,7 @@ template <typename T> struct SrcL1 {
 };
 
 // ---- flat: grid-wide partials, the last CTA to finish folds them ---------------------------------
-// ws layout: [0] completion counter (left at zero), partials start 256 bytes in.
+// ws layout: counter [0] of the header (left at zero), partials start after the header.
 template <typename T, int OP, typename Src>
 __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, T *partials, unsigned int *counter,
                                                              T *out, int mean) {
@@ -241,65 +247,97 @@ __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t
 }
 
 // ---- outer axis (inner > 1): src is [outer, R, inner]; threads run along inner ---------------------
-// CTA = 32 lanes along inner (VW columns each) x 8 lanes along R.  split cuts R into chunks; with
-// split > 1 the partial for chunk c goes to dst[(o * split + c) * inner + i] for a second pass.
+// CTA = 32 lanes along inner (VW columns each) x 8 lanes along R.  `split` cuts R into chunks, one
+// CTA each.  With split > 1 every CTA stores its partial row, and the last CTA of a column tile to
+// finish (per-tile completion counter) folds the `split` partial rows in chunk order -- one launch,
+// and the fold order does not depend on which CTA came last.
+template <typename T, int OP, int VW>
+__device__ __forceinline__ void col_accumulate(const T *p, size_t row_stride, size_t k0, size_t k1, int ly, T acc[VW]) {
+    size_t k = k0 + ly;
+    if (VW > 1) {
+        for (; k + 24 < k1; k += 32) {
+            typename VecOf<T>::U v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + 8 * u) * row_stride);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v[u].e[j]);
+        }
+        for (; k < k1; k += 8) {
+            typename VecOf<T>::U v;
+            v.q = *reinterpret_cast<const uint4 *>(p + k * row_stride);
+#pragma unroll
+            for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
+        }
+    } else {
+        for (; k + 24 < k1; k += 32) {
+            T v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = p[(k + 8 * u) * row_stride];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
+        }
+        for (; k < k1; k += 8) acc[0] = Comb<T, OP>::apply(acc[0], p[k * row_stride]);
+    }
+}
+
 template <typename T, int OP, int VW>
 __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t outer, size_t R, size_t inner,
-                                                            size_t split, size_t col_tiles, T *dst, int mean,
-                                                            size_t count) {
+                                                            size_t split, size_t col_tiles, T *partial,
+                                                            unsigned int *counters, T *dst, int mean, size_t count) {
     __shared__ T smem[8][32 * VW + 1];
+    __shared__ bool is_last;
     const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
     size_t b = blockIdx.x;
-    const size_t tile = b % col_tiles; b /= col_tiles;
-    const size_t chunk = b % split;
-    const size_t o = b / split;
+    const size_t chunk = b % split; b /= split;   // the chunks of one tile are neighbours in the grid
+    const size_t tile = b % col_tiles;
+    const size_t o = b / col_tiles;
     const size_t col = (tile * 32 + lx) * VW;
     const size_t per = (R + split - 1) / split;
     const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
     T acc[VW];
 #pragma unroll
     for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-    if (col < inner) {
-        const T *p = src + (o * R) * inner + col;
-        size_t k = k0 + ly;
-        if (VW > 1) {
-            for (; k + 24 < k1; k += 32) {
-                typename VecOf<T>::U v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + 8 * u) * inner);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v[u].e[j]);
-            }
-            for (; k < k1; k += 8) {
-                typename VecOf<T>::U v;
-                v.q = *reinterpret_cast<const uint4 *>(p + k * inner);
-#pragma unroll
-                for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
-            }
-        } else {
-            for (; k + 24 < k1; k += 32) {
-                T v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = p[(k + 8 * u) * inner];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
-            }
-            for (; k < k1; k += 8) acc[0] = Comb<T, OP>::apply(acc[0], p[k * inner]);
-        }
-    }
+    if (col < inner && k0 < k1) col_accumulate<T, OP, VW>(src + (o * R) * inner + col, inner, k0, k1, ly, acc);
 #pragma unroll
     for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
     __syncthreads();
-    // 8 partial rows -> 1, by the first warp(s): thread t owns column t of the tile
+    // 8 partial rows -> 1: thread c owns column c of the tile
     for (int c = threadIdx.x; c < 32 * VW; c += kBlock) {
         T v = smem[0][c];
 #pragma unroll
         for (int y = 1; y < 8; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
         const size_t gc = tile * 32 * VW + c;
-        if (gc < inner) dst[(o * split + chunk) * inner + gc] = split == 1 ? finish(v, mean, count) : v;
+        if (gc < inner) {
+            if (split == 1) dst[o * inner + gc] = finish(v, mean, count);
+            else partial[(o * split + chunk) * inner + gc] = v;
+        }
     }
+    if (split == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int done = atomicAdd(counters + o * col_tiles + tile, 1u);
+        is_last = done == (unsigned int)split - 1u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+#pragma unroll
+    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
+    if (col < inner) col_accumulate<T, OP, VW>(partial + (o * split) * inner + col, inner, 0, split, ly, acc);
+#pragma unroll
+    for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < 32 * VW; c += kBlock) {
+        T v = smem[0][c];
+#pragma unroll
+        for (int y = 1; y < 8; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
+        const size_t gc = tile * 32 * VW + c;
+        if (gc < inner) dst[o * inner + gc] = finish(v, mean, count);
+    }
+    if (threadIdx.x == 0) counters[o * col_tiles + tile] = 0;  // ready for the next launch
 }
 
 // ---- fused MLP pieces ----------------------------------------------------------------------------
@@ -369,7 +407,7 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
     int rc = workspace(ctx, (size_t)grid * sizeof(T), &ws);
     if (rc != RTB_OK) return rc;
     unsigned int *counter = reinterpret_cast<unsigned int *>(ws);
-    T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+    T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     flat_reduce_kernel<T, OP, Src><<<grid, kBlock, 0, ctx->stream>>>(src, n, partials, counter, out, mean);
     return check_launch(ctx, "flat_reduce_kernel");
 }
@@ -402,7 +440,7 @@ int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean)
         void *ws = nullptr;
         int rc = workspace(ctx, rows * split * sizeof(T), &ws);
         if (rc != RTB_OK) return rc;
-        target = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+        target = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     }
     const size_t items = rows * split;
     const size_t chunk_len = (R + split - 1) / split;
@@ -421,45 +459,58 @@ int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean)
     return check_launch(ctx, "row_reduce_kernel(fold)");
 }
 
+// Number of R-chunks per column tile.  CTAs do equal work, so the launch takes ceil(waves) rounds
+// of `resident` CTAs: pick the split whose last round is fullest, preferring fewer chunks.
+size_t pick_split(size_t base_ctas, size_t resident, size_t max_split) {
+    if (max_split < 1) max_split = 1;
+    if (base_ctas >= 4 * resident) return 1;
+    size_t best = 1;
+    double best_eff = 0.0;
+    for (size_t sp = 1; sp <= max_split && base_ctas * sp <= 6 * resident; ++sp) {
+        double waves = (double)(base_ctas * sp) / (double)resident;
+        double rounds = (double)(size_t)((base_ctas * sp + resident - 1) / resident);
+        double eff = waves / rounds;
+        if (eff > best_eff + 0.02) {
+            best_eff = eff;
+            best = sp;
+        }
+    }
+    return best;
+}
+
+template <typename K>
+size_t resident_ctas(Ctx *ctx, K kernel) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    return (size_t)ctx->sm_count * (size_t)per_sm;
+}
+
 template <typename T, int OP>
 int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
     constexpr int N = VecOf<T>::N;
     const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0);
     const size_t tile_cols = vec ? 32 * N : 32;
     const size_t col_tiles = (inner + tile_cols - 1) / tile_cols;
-    size_t split = 1;
     const size_t base_ctas = outer * col_tiles;
-    const size_t want = (size_t)ctx->sm_count * 8;
-    if (base_ctas < want && R >= 128) {
-        split = (want + base_ctas - 1) / base_ctas;
-        size_t max_split = R / 64;
-        if (split > max_split) split = max_split;
-        if (split < 1) split = 1;
-    }
-    T *target = dst;
+    const size_t resident = vec ? resident_ctas(ctx, col_reduce_kernel<T, OP, N>) : resident_ctas(ctx, col_reduce_kernel<T, OP, 1>);
+    size_t split = 1;
+    if (base_ctas <= kMaxTileCounters) split = pick_split(base_ctas, resident, R / 64);
+    T *partial = nullptr;
+    unsigned int *counters = nullptr;
     if (split > 1) {
         void *ws = nullptr;
         int rc = workspace(ctx, outer * split * inner * sizeof(T), &ws);
         if (rc != RTB_OK) return rc;
-        target = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + 256);
+        counters = reinterpret_cast<unsigned int *>(ws) + kTileCounterOffset;
+        partial = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     }
     size_t grid = base_ctas * split;
     if (grid >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "axis reduction too large for one launch");
     if (vec)
-        col_reduce_kernel<T, OP, N><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, target, mean, R);
+        col_reduce_kernel<T, OP, N><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial, counters, dst, mean, R);
     else
-        col_reduce_kernel<T, OP, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, target, mean, R);
-    int rc = check_launch(ctx, "col_reduce_kernel");
-    if (rc != RTB_OK || split == 1) return rc;
-    // fold [outer, split, inner] -> [outer, inner]; the workspace start is 256-byte aligned
-    const bool vec2 = (inner % N == 0) && (((uintptr_t)target & 15u) == 0);
-    const size_t tiles2 = (inner + (vec2 ? 32 * N : 32) - 1) / (vec2 ? 32 * N : 32);
-    size_t grid2 = outer * tiles2;
-    if (vec2)
-        col_reduce_kernel<T, OP, N><<<(unsigned)grid2, kBlock, 0, ctx->stream>>>(target, outer, split, inner, 1, tiles2, dst, mean, R);
-    else
-        col_reduce_kernel<T, OP, 1><<<(unsigned)grid2, kBlock, 0, ctx->stream>>>(target, outer, split, inner, 1, tiles2, dst, mean, R);
-    return check_launch(ctx, "col_reduce_kernel(fold)");
+        col_reduce_kernel<T, OP, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial, counters, dst, mean, R);
+    return check_launch(ctx, "col_reduce_kernel");
 }
 
 template <typename T, int OP>

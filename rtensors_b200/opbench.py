@@ -1,5 +1,6 @@
 """Per-op timing table used by bench.py: every named op of the hot path, timed with CUDA events on
-the launching stream, with the algorithmic HBM bytes that define its roofline.
+the launching stream (10 back-to-back launches per event pair, median of 5 pairs), with the
+algorithmic HBM bytes that define its roofline.
 
 Algorithmic bytes (s = element size): in-place scalar/unary op 2*s*n; same-shape binary 3*s*n;
 broadcast binary s*(n_out + n_A + n_B) (each operand's unique elements once); axis reduce
@@ -24,20 +25,35 @@ def _flush_l2(dev):
     _FLUSH.add_(1)
 
 
-def _time(fn, iters=10, warm=3, flush=False, dev=None):
+def _span(fn, reps):
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e)
+
+
+def _time(fn, reps=10, rounds=5, warm=3, flush=False, dev=None):
+    """Device time per call in ms: `reps` calls are enqueued back to back between one pair of CUDA
+    events, so the host-side enqueue cost of a call is not counted as kernel time.  With
+    flush=True every call is preceded by a write of a 256 MiB buffer (larger than L2) and the
+    time of the same number of flushes alone is subtracted."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
     ts = []
-    for _ in range(iters):
+    for _ in range(rounds):
         if flush:
-            _flush_l2(dev)
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        fn()
-        e.record()
-        torch.cuda.synchronize()
-        ts.append(s.elapsed_time(e))
+            def both():
+                _flush_l2(dev)
+                fn()
+            t1 = _span(both, reps)
+            t0 = _span(lambda: _flush_l2(dev), reps)
+            ts.append(max(t1 - t0, 1e-6) / reps)
+        else:
+            ts.append(_span(fn, reps) / reps)
     return float(np.median(ts)), float(np.min(ts))
 
 

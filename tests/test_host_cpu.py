@@ -173,7 +173,7 @@ def test_plan_config_strided_negative_step_broadcast():
     p = plan_elementwise(L.F32, 2, shape, d, Meta(shape, sa, A.offset), Meta(shape, sb, B.offset))
     assert p.kernel == 3 and p.rank == 4
     assert (p.mode_d, p.mode_l, p.mode_r) == (0, 4, 2)  # vector store, broadcast, reversed vector load
-    assert p.n_rows == 16 * 64 * 1024 and p.grid == p.n_rows // 4
+    assert p.n_rows == 16 * 64 * 1024 and p.grid == p.n_rows and p.n_col_chunks == 1
 
 
 def test_plan_flips_and_merges_reversed_inplace_view():
