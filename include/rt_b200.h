@@ -170,6 +170,24 @@ int rtb_reduce_flat(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t 
 int rtb_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t offset, size_t outer, size_t r,
                     size_t inner, void *dst);
 
+/* ---- full reduction without any device allocation.  NO COUNTERPART IN THE REFERENCE (its flat
+ *      reduction allocates and frees CUB scratch on every call, cuda/kernels/reduction/reduce.cu:
+ *      239-274).  For hosts that must not, or cannot, call cudaMalloc: all device memory already
+ *      given to their own pool, a loop that may not take cudaMalloc's device-wide synchronisation,
+ *      or a runtime that forbids allocations by foreign libraries.  Same result contract as
+ *      rtb_reduce_flat (src[start .. start+len] -> dst[0], f32 / f64, SUM PROD MAX MIN MEAN), but
+ *      the partial results live in a 64.25 KiB array inside the library image instead of the
+ *      context workspace; it needs no rtb_ctx and runs on `stream` (a cudaStream_t, NULL = legacy
+ *      default) of the CURRENT device.
+ *      Limits and rules: len <= RTB_NOALLOC_MAX_LEN, larger is refused with RTB_ERR_TOO_LARGE;
+ *      every GPU that loads the library holds the array until exit; all calls on a device share
+ *      it, so calls whose kernels could overlap (other streams, other threads) race and must be
+ *      ordered by the caller; the first call on each device looks up the array's device address
+ *      and should be made outside any stream capture.  Calls no cudaMalloc / cudaFree. --------- */
+#define RTB_NOALLOC_MAX_LEN ((size_t)1 << 29)
+int rtb_reduce_flat_noalloc(int dtype, int redop, const void *src, size_t start, size_t len, void *dst,
+                            void *stream);
+
 /* ---- fused L1 loss of two same-length contiguous tensors (L1::l1 + attach_l1_grad,
  *      src/ops/broadcast/l1.rs:16-77: five launches and two temporaries in the reference).
  *      reduction: 0 mean, 1 sum.  grad_map (may be NULL) receives sign(a-b), divided by
