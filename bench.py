@@ -190,6 +190,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     be = CudaB200(local)
     dev = f"cuda:{local}"

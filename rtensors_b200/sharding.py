@@ -1,0 +1,136 @@
+"""Multi-GPU layer (new: the reference is single-device, `Cuda::new()` -> device 0,
+src/backend/cuda.rs:155-162, 815-818).  One process per GPU; the path shards by outer-dimension
+slabs with NO data-path collective for elementwise / broadcast work.  A collective appears only
+where the path has a real exchange: a reduction over the sharded dim combines per-GPU partials with
+one all-reduce (NCCL over NVLink on GPUs, gloo in the CPU tests).
+
+Everything here is host logic over an `engine` with the Backend-mirror methods (`broadcast`,
+`apply_reduce_contiguous_flat`, `reduce_axis_ori`, `l1_loss`, `alloc`), so the slab arithmetic is
+testable on CPU with any engine that implements them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from .meta import Meta, broadcast_params, shard_range
+
+
+def world_info() -> Tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(), dist.get_rank()
+    return 1, 0
+
+
+def pick_shard_dim(shape, parts: int) -> Optional[int]:
+    """Outermost dim with extent >= parts (the slab dim), or None if the tensor is too small."""
+    for k, n in enumerate(shape):
+        if n >= parts:
+            return k
+    return None
+
+
+@dataclass(frozen=True)
+class BinarySlab:
+    """This rank's part of `a op b`: the output slab [begin, end) along `dim` and the operand views
+    restricted to it (a broadcast operand keeps stride 0 there and is simply replicated)."""
+    full_shape: Tuple[int, ...]
+    dim: Optional[int]
+    begin: int
+    end: int
+    shape: Tuple[int, ...]
+    left: Meta
+    right: Meta
+
+
+def binary_slab(am: Meta, bm: Meta, world: int, rank: int) -> BinarySlab:
+    shape, sa, sb = broadcast_params(am, bm)
+    dim = pick_shard_dim(shape, world) if world > 1 else None
+    if dim is None:
+        # not shardable (or single rank): rank 0 owns everything, the others an empty slab on dim 0
+        if world > 1 and rank > 0:
+            eshape = (0,) + tuple(shape[1:]) if shape else (0,)
+            return BinarySlab(tuple(shape), None, 0, 0, eshape, Meta(eshape, sa if shape else (0,), am.offset),
+                              Meta(eshape, sb if shape else (0,), bm.offset))
+        return BinarySlab(tuple(shape), None, 0, shape[0] if shape else 1, tuple(shape), Meta(shape, sa, am.offset),
+                          Meta(shape, sb, bm.offset))
+    b, e = shard_range(shape[dim], world, rank)
+    sshape = tuple(e - b if k == dim else n for k, n in enumerate(shape))
+    return BinarySlab(tuple(shape), dim, b, e, sshape, Meta(sshape, sa, am.offset + b * sa[dim]),
+                      Meta(sshape, sb, bm.offset + b * sb[dim]))
+
+
+def sharded_binary(engine, a, am: Meta, b, bm: Meta, op: int, world: Optional[int] = None, rank: Optional[int] = None):
+    """Computes this rank's slab of the out-of-place broadcast op.  -> (slab buffer, slab Meta, BinarySlab)"""
+    if world is None:
+        world, rank = world_info()
+    slab = binary_slab(am, bm, world, rank)
+    dm = Meta.contiguous(slab.shape)
+    out = engine.alloc(max(dm.size, 1), a.dtype)
+    if dm.size:
+        engine.broadcast((a, slab.left), (b, slab.right), (out, dm), op)
+    return out, dm, slab
+
+
+def scalar_slab(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """Flat range [begin, end) of a contiguous tensor of n elements owned by this rank."""
+    return shard_range(n, world, rank)
+
+
+_RED = {L.SUM: "sum", L.MEAN: "sum", L.MAX: "max", L.MIN: "min", L.PROD: "prod"}
+
+
+def _all_reduce(t: torch.Tensor, kind: str, group=None):
+    op = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN,
+          "prod": dist.ReduceOp.PRODUCT}[kind]
+    dist.all_reduce(t, op=op, group=group)
+
+
+def _as_torch(x):
+    return x if isinstance(x, torch.Tensor) else torch.from_numpy(x)
+
+
+def finish_mean(total: torch.Tensor, count: int) -> torch.Tensor:
+    """mean = sum / (T)(float)count, the reference's `from_usize` (src/core/value.rs:54-56)."""
+    div = torch.tensor(float(np.float32(count)), dtype=total.dtype, device=total.device)
+    return total / div
+
+
+def sharded_reduce_flat(engine, local, local_len: int, global_len: int, op: int, group=None):
+    """Full reduction of a tensor whose flat range is split across ranks: per-GPU partial (one
+    launch) + one all-reduce of a single element.  `local` holds this rank's elements."""
+    world, _ = world_info()
+    part = engine.alloc(1, local.dtype)
+    engine.apply_reduce_contiguous_flat(local, part, 0, local_len, L.SUM if op == L.MEAN else op)
+    t = _as_torch(part)
+    if world > 1:
+        _all_reduce(t, _RED[op], group)
+    return finish_mean(t, global_len) if op == L.MEAN else t
+
+
+def sharded_reduce_axis(engine, local, outer: int, r: int, inner: int, op: int, sharded: str, global_r: int,
+                        group=None):
+    """Axis reduction of the local [outer, r, inner] block.  sharded = "outer": ranks own disjoint
+    outputs, no communication.  sharded = "r": the reduced dim is split, so the partial vectors are
+    combined with one all-reduce of outer*inner elements."""
+    world, _ = world_info()
+    if sharded == "outer" or world == 1:
+        return _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, op))
+    part = _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, L.SUM if op == L.MEAN else op))
+    _all_reduce(part, _RED[op], group)
+    return finish_mean(part, global_r) if op == L.MEAN else part
+
+
+def sharded_mean_l1_loss(engine, a_local, b_local, global_n: int, group=None):
+    """mean(|a-b|) over tensors split across ranks: local sum of |a-b| -> all-reduce -> / (T)(float)N."""
+    world, _ = world_info()
+    loss, _ = engine.l1_loss(a_local, b_local, 1, False)  # reduction 1 = sum
+    t = _as_torch(loss)
+    if world > 1:
+        _all_reduce(t, "sum", group)
+    return finish_mean(t, global_n)
