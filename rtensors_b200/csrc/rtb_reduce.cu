@@ -290,9 +290,10 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
     __shared__ bool is_last;
     const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
     size_t b = blockIdx.x;
-    const size_t chunk = b % split; b /= split;   // the chunks of one tile are neighbours in the grid
-    const size_t tile = b % col_tiles;
-    const size_t o = b / col_tiles;
+    // neighbouring CTAs read neighbouring column tiles of the same rows (DRAM page locality)
+    const size_t tile = b % col_tiles; b /= col_tiles;
+    const size_t chunk = b % split;
+    const size_t o = b / split;
     const size_t col = (tile * 32 + lx) * VW;
     const size_t per = (R + split - 1) / split;
     const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;

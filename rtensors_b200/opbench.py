@@ -168,5 +168,18 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     nw -= nw % 4
     w, gw = src[:nw], src[nw:2 * nw]
     add("sgd_update f32", f"{nw} params", 12 * nw, nw, lambda: be.sgd_update(w, gw, 0.0), flush=True)
+    # ---- config 5 as a whole: one SGD step of the 784-1024-1024-10 MLP, global batch 4096 split
+    # across the ranks (data parallel: loss all-reduce + one flat gradient bucket all-reduce)
+    from .mlp import DenseMlp, synthetic_batch
+    torch.backends.cuda.matmul.allow_tf32 = False
+    model = DenseMlp(be, (784, 1024, 1024, 10), lr=0.01)
+    local_b = 4096 // world
+    img, tgt, _, _ = synthetic_batch(local_b, dev, rank=rank)
+    med, best = _time(lambda: model.step(img, tgt, 4096), reps=5, rounds=5)
+    gemm_flops = 2 * 4096 * (784 * 1024 + 1024 * 1024 + 1024 * 10) * 3 - 2 * 4096 * 784 * 1024
+    rows.append({"op": "MLP SGD step 784-1024-1024-10 (GEMMs on cuBLAS, rest on this library)",
+                 "shape": f"global batch 4096, {local_b} per GPU x {world}", "ms": med, "ms_best": best,
+                 "samples_per_s": 4096 / (med * 1e-3), "gemm_tflops": gemm_flops / (med * 1e-3) / 1e12,
+                 "note": "whole step incl. cuBLAS GEMMs and, at N>1, two NCCL all-reduces (loss, 7.45 MB gradient bucket)"})
     torch.cuda.synchronize()
     return rows
