@@ -37,8 +37,8 @@ STEP_BYTES = 3 * 2 * 4 * N_ELEMS + 3 * 4 * N_ELEMS  # three in-place passes + on
 STEP_ELEMS = 4 * N_ELEMS
 FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the in-place f32 kernel, from the ncu
-# capture summarised under profiles/ (captured at 2^26 elements, scaled by 4: traffic is linear in n)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# capture summarised under profiles/ (captured at 2^27 elements, scaled by 2: traffic is linear in n)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.026e9  # at 2^28 elements: 2 x (536.9 MB read + 476.1 MB written) measured at 2^27
 
 
 def peak_gbs():
