@@ -1,0 +1,362 @@
+// rtensors_b200.hpp -- C++17 host-side mirror of the reference's API for the hot path, on top of the
+// C ABI in rt_b200.h.  Header only; link with -lrt_b200 (no CUDA headers needed by the caller).
+//
+// It restates, with the reference's names and argument meaning:
+//   MetaTensor {shape, strides, offset}, Slice            src/core/meta.rs:155-159, src/core/slice.rs:9-52
+//   trait Backend (the methods on the hot path) as class Cuda   src/backend/mod.rs:216-472
+//   TensorBase<T, B>: constructors, views, operators, reductions, mean_l1_loss
+//                                                           src/core/primitives.rs:367-484, src/core/tensor.rs:66-105,
+//                                                           418-524, src/ops/{scalar,unary,broadcast,reduction}
+// Errors are exceptions carrying the library status (TensorError variants map to status codes).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include "rt_b200.h"
+
+namespace rtb200 {
+
+struct TensorError : std::runtime_error {
+    int code;
+    TensorError(int c, const std::string &m) : std::runtime_error(m), code(c) {}
+};
+inline void check(int rc) {
+    if (rc != RTB_OK) throw TensorError(rc, rtb_last_error_string());
+}
+
+template <typename T> struct DTypeOf;
+#define RTB200_DT(T, CODE) template <> struct DTypeOf<T> { static constexpr int value = CODE; };
+RTB200_DT(uint8_t, RTB_U8) RTB200_DT(int8_t, RTB_I8) RTB200_DT(uint16_t, RTB_U16) RTB200_DT(int16_t, RTB_I16)
+RTB200_DT(uint32_t, RTB_U32) RTB200_DT(int32_t, RTB_I32) RTB200_DT(uint64_t, RTB_U64) RTB200_DT(int64_t, RTB_I64)
+RTB200_DT(float, RTB_F32) RTB200_DT(double, RTB_F64) RTB200_DT(bool, RTB_BOOL)
+RTB200_DT(unsigned __int128, RTB_U128) RTB200_DT(__int128, RTB_I128)
+#undef RTB200_DT
+
+enum class BinaryOpType { Add = 0, Sub = 1, Mul = 2, Div = 3 };
+enum class ReductionOpTypes { Sum = 1, Prod = 2, Max = 3, Min = 4, Mean = 5 };
+
+struct Slice {
+    std::optional<size_t> start, end;
+    ptrdiff_t step_ = 1;
+    static Slice full() { return Slice{}; }
+    static Slice range(size_t a, size_t b) { return Slice{a, b, a > b ? -1 : 1}; }  // From<Range<usize>>
+    static Slice index(size_t i) { return Slice{i, i, 1}; }                          // From<usize>
+    Slice step(ptrdiff_t s) const { Slice r = *this; r.step_ = s; return r; }
+    Slice from(size_t s) const { Slice r = *this; r.start = s; return r; }
+    Slice to(size_t e) const { Slice r = *this; r.end = e; return r; }
+};
+
+struct MetaTensor {
+    std::vector<size_t> shape;
+    std::vector<ptrdiff_t> strides;
+    size_t offset = 0;
+
+    static MetaTensor contiguous(std::vector<size_t> shape) {
+        MetaTensor m;
+        m.shape = std::move(shape);
+        m.strides.resize(m.shape.size());
+        rtb_meta_contiguous_strides(m.shape.size(), m.shape.data(), m.strides.data());
+        return m;
+    }
+    size_t rank() const { return shape.size(); }
+    size_t size() const { size_t n = 1; for (size_t s : shape) n *= s; return n; }
+    bool is_contiguous() const { return rtb_meta_is_contiguous(rank(), shape.data(), strides.data()) != 0; }
+    MetaTensor slice(size_t dim, const Slice &s) const {
+        MetaTensor o;
+        o.shape.resize(rank() ? rank() : 1); o.strides.resize(rank() ? rank() : 1);
+        size_t r = 0;
+        check(rtb_meta_slice(rank(), shape.data(), strides.data(), offset, dim, s.start.has_value(), s.start.value_or(0),
+                             s.end.has_value(), s.end.value_or(0), s.step_, &r, o.shape.data(), o.strides.data(), &o.offset));
+        o.shape.resize(r); o.strides.resize(r);
+        return o;
+    }
+    MetaTensor permute(const std::vector<size_t> &dims) const {
+        MetaTensor o = *this;
+        check(rtb_meta_permute(rank(), shape.data(), strides.data(), dims.size(), dims.data(), o.shape.data(), o.strides.data()));
+        return o;
+    }
+    MetaTensor unsqueeze(size_t dim) const {
+        MetaTensor o;
+        o.offset = offset; o.shape.resize(rank() + 1); o.strides.resize(rank() + 1);
+        check(rtb_meta_unsqueeze(rank(), shape.data(), strides.data(), dim, o.shape.data(), o.strides.data()));
+        return o;
+    }
+    MetaTensor squeeze(ptrdiff_t dim = -1) const {
+        MetaTensor o = *this;
+        size_t r = 0;
+        if (rank() == 0) return o;
+        check(rtb_meta_squeeze(rank(), shape.data(), strides.data(), dim, &r, o.shape.data(), o.strides.data()));
+        o.shape.resize(r); o.strides.resize(r);
+        return o;
+    }
+};
+
+// ---- Backend ------------------------------------------------------------------------------------
+class Cuda {
+  public:
+    explicit Cuda(int device = 0) { check(rtb_ctx_create(device, &ctx_)); }
+    ~Cuda() { rtb_ctx_destroy(ctx_); }
+    Cuda(const Cuda &) = delete;
+    Cuda &operator=(const Cuda &) = delete;
+    rtb_ctx *ctx() const { return ctx_; }
+    void sync() const { check(rtb_ctx_sync(ctx_)); }
+
+    template <typename T> struct Buf {
+        T *ptr = nullptr;
+        size_t len = 0;
+        const Cuda *owner = nullptr;
+        ~Buf() { if (ptr && owner) rtb_free(owner->ctx(), ptr); }
+    };
+    template <typename T> using BufPtr = std::shared_ptr<Buf<T>>;
+
+    template <typename T> BufPtr<T> alloc(size_t len) const {  // uninitialised
+        auto b = std::make_shared<Buf<T>>();
+        void *p = nullptr;
+        check(rtb_alloc(ctx_, (len ? len : 1) * sizeof(T), &p));
+        b->ptr = static_cast<T *>(p); b->len = len; b->owner = this;
+        return b;
+    }
+    template <typename T> BufPtr<T> alloc_from_slice(const std::vector<T> &src) const {
+        auto b = alloc<T>(src.size());
+        if (!src.empty()) check(rtb_h2d(ctx_, b->ptr, src.data(), src.size() * sizeof(T)));
+        sync();  // the host vector may go away
+        return b;
+    }
+    template <typename T> std::vector<T> dump(const Buf<T> &b) const {
+        std::vector<T> out(b.len);
+        if (b.len) check(rtb_d2h(ctx_, out.data(), b.ptr, b.len * sizeof(T)));
+        return out;
+    }
+    template <typename T> T read(const Buf<T> &b, size_t offset) const {
+        T v;
+        check(rtb_d2h(ctx_, &v, b.ptr + offset, sizeof(T)));
+        return v;
+    }
+    template <typename T> void write(Buf<T> &b, size_t offset, T v) const {
+        check(rtb_h2d(ctx_, b.ptr + offset, &v, sizeof(T)));
+        sync();
+    }
+    template <typename T> BufPtr<T> copy(const Buf<T> &b) const {
+        auto o = alloc<T>(b.len);
+        if (b.len) check(rtb_d2d(ctx_, o->ptr, b.ptr, b.len * sizeof(T)));
+        return o;
+    }
+
+    template <typename T> void scalar_apply(Buf<T> &buf, BinaryOpType op, T value, const MetaTensor &m) const {
+        check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, buf.len));
+        check(rtb_scalar_op(ctx_, DTypeOf<T>::value, (int)op, buf.ptr, &value, m.rank(), m.shape.data(), m.strides.data(), m.offset));
+    }
+    template <typename T> void scalar_apply_add(Buf<T> &b, T v, const MetaTensor &m) const { scalar_apply(b, BinaryOpType::Add, v, m); }
+    template <typename T> void scalar_apply_sub(Buf<T> &b, T v, const MetaTensor &m) const { scalar_apply(b, BinaryOpType::Sub, v, m); }
+    template <typename T> void scalar_apply_mul(Buf<T> &b, T v, const MetaTensor &m) const { scalar_apply(b, BinaryOpType::Mul, v, m); }
+    template <typename T> void scalar_apply_div(Buf<T> &b, T v, const MetaTensor &m) const { scalar_apply(b, BinaryOpType::Div, v, m); }
+
+    template <typename T> void apply_unary(Buf<T> &buf, int unop, const MetaTensor &m) const {
+        check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, buf.len));
+        check(rtb_unary_op(ctx_, DTypeOf<T>::value, unop, buf.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset));
+    }
+    template <typename T> void apply_neg(Buf<T> &b, const MetaTensor &m) const { apply_unary(b, RTB_NEG, m); }
+    template <typename T> void apply_relu(Buf<T> &b, const MetaTensor &m) const { apply_unary(b, RTB_RELU, m); }
+    template <typename T> void apply_abs(Buf<T> &b, const MetaTensor &m) const { apply_unary(b, RTB_ABS, m); }
+    template <typename T> void apply_sign(Buf<T> &b, const MetaTensor &m) const { apply_unary(b, RTB_SIGN, m); }
+
+    template <typename T> void fill(Buf<T> &buf, T value, const MetaTensor &m) const {
+        check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, buf.len));
+        check(rtb_fill(ctx_, DTypeOf<T>::value, buf.ptr, &value, m.rank(), m.shape.data(), m.strides.data(), m.offset));
+    }
+    // Backend::broadcast: all three metas carry the output shape; dst may be left (in place)
+    template <typename T>
+    void broadcast(const Buf<T> &l, const MetaTensor &lm, const Buf<T> &r, const MetaTensor &rm, Buf<T> &d,
+                   const MetaTensor &dm, BinaryOpType op) const {
+        check(rtb_meta_check_extent(lm.rank(), lm.shape.data(), lm.strides.data(), lm.offset, l.len));
+        check(rtb_meta_check_extent(rm.rank(), rm.shape.data(), rm.strides.data(), rm.offset, r.len));
+        check(rtb_meta_check_extent(dm.rank(), dm.shape.data(), dm.strides.data(), dm.offset, d.len));
+        check(rtb_broadcast(ctx_, DTypeOf<T>::value, (int)op, l.ptr, lm.strides.data(), lm.offset, r.ptr, rm.strides.data(),
+                            rm.offset, d.ptr, dm.strides.data(), dm.offset, dm.rank(), dm.shape.data()));
+    }
+    template <typename T>
+    void apply_reduce_contiguous_flat(const Buf<T> &src, Buf<T> &dst, size_t start, size_t len, ReductionOpTypes op) const {
+        if (start + len > src.len) throw TensorError(RTB_ERR_BOUNDS, "flat reduction range exceeds the buffer");
+        check(rtb_reduce_flat(ctx_, DTypeOf<T>::value, (int)op, src.ptr, start, len, dst.ptr));
+    }
+    template <typename T>
+    void apply_reduce(const Buf<T> &src, const MetaTensor &sm, Buf<T> &dst, size_t dim, ReductionOpTypes op) const {
+        if (!sm.is_contiguous()) throw TensorError(RTB_ERR_NONCONTIG, "Reduction over non-contiguous tensors is not implemented yet.");
+        if (sm.rank() == 1) return apply_reduce_contiguous_flat(src, dst, sm.offset, sm.size(), op);
+        size_t outer = 1, inner = 1;
+        for (size_t k = 0; k < dim; ++k) outer *= sm.shape[k];
+        for (size_t k = dim + 1; k < sm.rank(); ++k) inner *= sm.shape[k];
+        check(rtb_reduce_axis(ctx_, DTypeOf<T>::value, (int)op, src.ptr, sm.offset, outer, sm.shape[dim], inner, dst.ptr));
+    }
+    template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
+        check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
+    }
+
+  private:
+    rtb_ctx *ctx_ = nullptr;
+};
+
+inline void broadcast_params(const MetaTensor &a, const MetaTensor &b, std::vector<size_t> &shape,
+                             std::vector<ptrdiff_t> &sa, std::vector<ptrdiff_t> &sb) {
+    size_t r = a.rank() > b.rank() ? a.rank() : b.rank(), out_r = 0;
+    shape.assign(r ? r : 1, 0); sa.assign(r ? r : 1, 0); sb.assign(r ? r : 1, 0);
+    check(rtb_broadcast_params(a.rank(), a.shape.data(), a.strides.data(), b.rank(), b.shape.data(), b.strides.data(), &out_r,
+                               shape.data(), sa.data(), sb.data()));
+    shape.resize(out_r); sa.resize(out_r); sb.resize(out_r);
+}
+
+// ---- TensorBase<T, Cuda> (owned tensors and views share this type; views share the buffer) -------
+template <typename T> class TensorBase {
+  public:
+    using Buf = typename Cuda::template Buf<T>;
+    const Cuda *backend = nullptr;
+    std::shared_ptr<Buf> buf;
+    MetaTensor meta;
+
+    static TensorBase from_buf(const Cuda &b, const std::vector<T> &data, std::vector<size_t> shape) {
+        MetaTensor m = MetaTensor::contiguous(std::move(shape));
+        if (m.size() != data.size()) throw TensorError(RTB_ERR_SHAPE, "Element count mismatch");
+        return TensorBase{&b, b.alloc_from_slice(data), m};
+    }
+    static TensorBase full(const Cuda &b, std::vector<size_t> shape, T v) {
+        MetaTensor m = MetaTensor::contiguous(std::move(shape));
+        TensorBase t{&b, b.alloc<T>(m.size()), m};
+        b.fill(*t.buf, v, m);
+        return t;
+    }
+    static TensorBase zeros(const Cuda &b, std::vector<size_t> shape) { return full(b, std::move(shape), T(0)); }
+    static TensorBase ones(const Cuda &b, std::vector<size_t> shape) { return full(b, std::move(shape), T(1)); }
+    static TensorBase scalar(const Cuda &b, T v) { return from_buf(b, {v}, {}); }
+
+    const std::vector<size_t> &shape() const { return meta.shape; }
+    const std::vector<ptrdiff_t> &strides() const { return meta.strides; }
+    size_t offset() const { return meta.offset; }
+    size_t size() const { return meta.size(); }
+    bool is_contiguous() const { return meta.is_contiguous(); }
+
+    TensorBase view_of(MetaTensor m) const { return TensorBase{backend, buf, std::move(m)}; }
+    TensorBase slice(size_t dim, const Slice &s) const { return view_of(meta.slice(dim, s)); }
+    TensorBase permute(const std::vector<size_t> &dims) const { return view_of(meta.permute(dims)); }
+    TensorBase squeeze() const { return view_of(meta.squeeze()); }
+    TensorBase unsqueeze(size_t dim) const { return view_of(meta.unsqueeze(dim)); }
+
+    TensorBase contiguous() const {
+        MetaTensor m = MetaTensor::contiguous(meta.shape);
+        TensorBase t{backend, backend->template alloc<T>(m.size()), m};
+        if (m.size()) backend->copy_view(*buf, meta, *t.buf);
+        return t;
+    }
+    TensorBase owned() const { return contiguous(); }
+    std::vector<T> cpu() const {
+        TensorBase c = contiguous();
+        std::vector<T> all = backend->dump(*c.buf);
+        all.resize(size());
+        return all;
+    }
+    T item() const {
+        if (size() != 1) throw TensorError(RTB_ERR_SHAPE, "item() needs a single-element tensor");
+        return backend->read(*buf, meta.offset);
+    }
+    T get(const std::vector<size_t> &coord) const {
+        size_t o = meta.offset;
+        for (size_t k = 0; k < coord.size(); ++k) o += (ptrdiff_t)coord[k] * meta.strides[k];
+        return backend->read(*buf, o);
+    }
+    void set(const std::vector<size_t> &coord, T v) {
+        size_t o = meta.offset;
+        for (size_t k = 0; k < coord.size(); ++k) o += (ptrdiff_t)coord[k] * meta.strides[k];
+        backend->write(*buf, o, v);
+    }
+
+    // tensor (op) tensor: broadcast into a fresh row-major tensor
+    TensorBase binary(const TensorBase &rhs, BinaryOpType op) const {
+        std::vector<size_t> shape; std::vector<ptrdiff_t> sa, sb;
+        broadcast_params(meta, rhs.meta, shape, sa, sb);
+        MetaTensor dm = MetaTensor::contiguous(shape);
+        TensorBase out{backend, backend->template alloc<T>(dm.size()), dm};
+        backend->broadcast(*buf, MetaTensor{shape, sa, meta.offset}, *rhs.buf, MetaTensor{shape, sb, rhs.meta.offset}, *out.buf, dm, op);
+        return out;
+    }
+    TensorBase &assign(const TensorBase &rhs, BinaryOpType op) {
+        std::vector<size_t> shape; std::vector<ptrdiff_t> sa, sb;
+        broadcast_params(meta, rhs.meta, shape, sa, sb);
+        if (shape != meta.shape) throw TensorError(RTB_ERR_BROADCAST, "Incompatible shapes for in-place op");
+        MetaTensor ma{shape, sa, meta.offset};
+        backend->broadcast(*buf, ma, *rhs.buf, MetaTensor{shape, sb, rhs.meta.offset}, *buf, ma, op);
+        return *this;
+    }
+    TensorBase operator+(const TensorBase &r) const { return binary(r, BinaryOpType::Add); }
+    TensorBase operator-(const TensorBase &r) const { return binary(r, BinaryOpType::Sub); }
+    TensorBase operator*(const TensorBase &r) const { return binary(r, BinaryOpType::Mul); }
+    TensorBase operator/(const TensorBase &r) const { return binary(r, BinaryOpType::Div); }
+    TensorBase &operator+=(const TensorBase &r) { return assign(r, BinaryOpType::Add); }
+    TensorBase &operator-=(const TensorBase &r) { return assign(r, BinaryOpType::Sub); }
+    TensorBase &operator*=(const TensorBase &r) { return assign(r, BinaryOpType::Mul); }
+    TensorBase &operator/=(const TensorBase &r) { return assign(r, BinaryOpType::Div); }
+    // tensor (op) scalar: copy, then in place (src/ops/scalar/add.rs:93-97)
+    TensorBase scalar_op(T v, BinaryOpType op) const { TensorBase t = owned(); t.backend->scalar_apply(*t.buf, op, v, t.meta); return t; }
+    TensorBase operator+(T v) const { return scalar_op(v, BinaryOpType::Add); }
+    TensorBase operator-(T v) const { return scalar_op(v, BinaryOpType::Sub); }
+    TensorBase operator*(T v) const { return scalar_op(v, BinaryOpType::Mul); }
+    TensorBase operator/(T v) const { return scalar_op(v, BinaryOpType::Div); }
+    TensorBase &operator+=(T v) { backend->scalar_apply(*buf, BinaryOpType::Add, v, meta); return *this; }
+    TensorBase &operator-=(T v) { backend->scalar_apply(*buf, BinaryOpType::Sub, v, meta); return *this; }
+    TensorBase &operator*=(T v) { backend->scalar_apply(*buf, BinaryOpType::Mul, v, meta); return *this; }
+    TensorBase &operator/=(T v) { backend->scalar_apply(*buf, BinaryOpType::Div, v, meta); return *this; }
+
+    TensorBase &relu_inplace() { backend->apply_relu(*buf, meta); return *this; }
+    TensorBase &abs_inplace() { backend->apply_abs(*buf, meta); return *this; }
+    TensorBase &sign_inplace() { backend->apply_sign(*buf, meta); return *this; }
+    TensorBase &neg_inplace() { backend->apply_neg(*buf, meta); return *this; }
+    TensorBase relu() const { TensorBase t = owned(); t.relu_inplace(); return t; }
+    TensorBase abs() const { TensorBase t = owned(); t.abs_inplace(); return t; }
+    TensorBase sign() const { TensorBase t = owned(); t.sign_inplace(); return t; }
+    TensorBase neg() const { TensorBase t = owned(); t.neg_inplace(); return t; }
+
+    // reductions: a non-contiguous view is copied first; `_at` keeps the reduced dim as size 1
+    TensorBase reduce(ReductionOpTypes op) const {
+        TensorBase t = is_contiguous() ? *this : contiguous();
+        TensorBase out{backend, backend->template alloc<T>(1), MetaTensor::contiguous({})};
+        backend->apply_reduce_contiguous_flat(*t.buf, *out.buf, t.meta.offset, t.size(), op);
+        return out;
+    }
+    TensorBase reduce_at(size_t axis, ReductionOpTypes op) const {
+        TensorBase t = is_contiguous() ? *this : contiguous();
+        if (axis >= t.meta.rank()) throw TensorError(RTB_ERR_DIM, "axis out of range");
+        std::vector<size_t> os = t.meta.shape;
+        os[axis] = 1;
+        MetaTensor om = MetaTensor::contiguous(os);
+        TensorBase out{backend, backend->template alloc<T>(om.size()), om};
+        if (om.size()) backend->apply_reduce(*t.buf, t.meta, *out.buf, axis, op);
+        return out;
+    }
+    TensorBase sum() const { return reduce(ReductionOpTypes::Sum); }
+    TensorBase mean() const { return reduce(ReductionOpTypes::Mean); }
+    TensorBase max() const { return reduce(ReductionOpTypes::Max); }
+    TensorBase min() const { return reduce(ReductionOpTypes::Min); }
+    TensorBase prod() const { return reduce(ReductionOpTypes::Prod); }
+    TensorBase sum_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Sum); }
+    TensorBase mean_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Mean); }
+    TensorBase max_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Max); }
+    TensorBase min_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Min); }
+    TensorBase prod_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Prod); }
+};
+
+// mean(|input - target|) as a rank-0 tensor (src/ops/broadcast/l1.rs:79-84), fused
+template <typename T> TensorBase<T> mean_l1_loss(const TensorBase<T> &input, const TensorBase<T> &target) {
+    if (input.shape() != target.shape()) throw TensorError(RTB_ERR_SHAPE, "mean_l1_loss needs equal shapes");
+    TensorBase<T> a = input.is_contiguous() ? input : input.contiguous();
+    TensorBase<T> b = target.is_contiguous() ? target : target.contiguous();
+    TensorBase<T> out{input.backend, input.backend->template alloc<T>(1), MetaTensor::contiguous({})};
+    check(rtb_l1_loss(input.backend->ctx(), DTypeOf<T>::value, a.buf->ptr + a.meta.offset, b.buf->ptr + b.meta.offset, a.size(), 0,
+                      out.buf->ptr, nullptr));
+    return out;
+}
+
+}  // namespace rtb200

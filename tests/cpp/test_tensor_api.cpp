@@ -1,0 +1,148 @@
+// The reference's own tensor tests, restated against the C++ host mirror (include/rtensors_b200.hpp).
+// Each block cites the test it mirrors (paths relative to libs/rtensors/src/ of the reference).
+// Exit code 0 = all passed; prints the first failure otherwise.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "rtensors_b200.hpp"
+
+using namespace rtb200;
+template <typename T> using Tensor = TensorBase<T>;
+
+static int g_checks = 0;
+#define ASSERT_EQ(a, b)                                                                          \
+    do {                                                                                         \
+        ++g_checks;                                                                              \
+        if (!((a) == (b))) { std::printf("FAIL %s:%d: %s != %s\n", __FILE__, __LINE__, #a, #b); std::exit(1); } \
+    } while (0)
+#define ASSERT_TRUE(x) ASSERT_EQ(static_cast<bool>(x), true)
+
+template <typename T> static std::vector<T> iota(int lo, int hi) {
+    std::vector<T> v;
+    for (int i = lo; i <= hi; ++i) v.push_back((T)i);
+    return v;
+}
+
+int main() {
+    Cuda cuda(0);
+
+    {  // ops/mod.rs:127-142 test_add_after_slice
+        auto tensor = Tensor<int32_t>::from_buf(cuda, {1, 2, 3, 4, 5, 6}, {2, 3});
+        auto slice = tensor.slice(0, Slice::range(1, 1));  // second row
+        ASSERT_EQ(slice.get({0}), 4);
+        slice += 100;
+        ASSERT_EQ(cuda.dump(*tensor.buf), (std::vector<int32_t>{1, 2, 3, 104, 105, 106}));
+    }
+    {  // ops/mod.rs:200-215 test_mul_after_column_slice
+        auto tensor = Tensor<int32_t>::from_buf(cuda, {1, 2, 3, 4, 5, 6}, {2, 3});
+        auto col = tensor.slice(1, Slice::range(1, 1));
+        ASSERT_TRUE(!col.is_contiguous());
+        col *= 3;
+        ASSERT_EQ(cuda.dump(*tensor.buf), (std::vector<int32_t>{1, 6, 3, 4, 15, 6}));
+    }
+    {  // ops/mod.rs:922-951 test_3d_noncontiguous_slice
+        auto tensor = Tensor<int32_t>::from_buf(cuda, iota<int32_t>(1, 24), {2, 3, 4});
+        auto slice = tensor.slice(1, Slice::range(1, 1));
+        ASSERT_EQ(slice.shape(), (std::vector<size_t>{2, 4}));
+        ASSERT_EQ(slice.strides(), (std::vector<ptrdiff_t>{12, 1}));
+        ASSERT_EQ(slice.offset(), (size_t)4);
+        slice += 100;
+        auto expect = iota<int32_t>(1, 24);
+        for (int i : {5, 6, 7, 8, 17, 18, 19, 20}) expect[i - 1] += 100;
+        ASSERT_EQ(cuda.dump(*tensor.buf), expect);
+    }
+    {  // ops/mod.rs:340-357 test_mul_not_inplace_with_noncontiguous_slice
+        auto tensor = Tensor<int32_t>::from_buf(cuda, {1, 2, 3, 4, 5, 6}, {2, 3});
+        auto result = tensor.slice(1, Slice::range(1, 1)) * 3;
+        ASSERT_EQ(result.cpu(), (std::vector<int32_t>{6, 15}));
+        ASSERT_TRUE(result.is_contiguous());
+        ASSERT_EQ(cuda.dump(*tensor.buf), (std::vector<int32_t>{1, 2, 3, 4, 5, 6}));
+    }
+    {  // ops/mod.rs:1154-1171 test_broadcast_flipped
+        auto veca = Tensor<float>::ones(cuda, {1, 3});
+        auto vecb = Tensor<float>::ones(cuda, {3, 1});
+        veca.set({0, 0}, 22.0f);
+        auto vecc = veca + vecb;
+        ASSERT_EQ(vecc.shape(), (std::vector<size_t>{3, 3}));
+        for (size_t i = 0; i < 3; ++i)
+            for (size_t j = 0; j < 3; ++j) ASSERT_EQ(vecc.get({i, j}), j == 0 ? 23.0f : 2.0f);
+    }
+    {  // ops/mod.rs:1474-1487 test_broadcast_div_2d_matrices
+        auto veca = Tensor<float>::from_buf(cuda, {100, 200, 300, 400}, {2, 2});
+        auto vecb = Tensor<float>::from_buf(cuda, {10, 20}, {1, 2});
+        ASSERT_EQ((veca / vecb).cpu(), (std::vector<float>{10, 10, 30, 20}));
+    }
+    {  // ops/mod.rs:1491-1498 test_broadcast_incompatible_dimensions_3d (should_panic)
+        auto veca = Tensor<float>::ones(cuda, {3, 4});
+        auto vecb = Tensor<float>::ones(cuda, {2, 5, 6});
+        bool threw = false;
+        try { auto c = veca + vecb; } catch (const TensorError &e) { threw = e.code == RTB_ERR_BROADCAST; }
+        ASSERT_TRUE(threw);
+    }
+    {  // ops/mod.rs:2455-2479 test_broadcast_with_negative_step_slice
+        auto a = Tensor<float>::from_buf(cuda, iota<float>(1, 12), {4, 3});
+        auto sliced = a.slice(0, Slice::full().step(-1));
+        auto b = Tensor<float>::from_buf(cuda, {10, 20, 30}, {3});
+        ASSERT_EQ((sliced + b).cpu(), (std::vector<float>{20, 31, 42, 17, 28, 39, 14, 25, 36, 11, 22, 33}));
+    }
+    {  // ops/mod.rs:2580-2601 test_broadcast_inplace_with_negative_step
+        auto a = Tensor<float>::from_buf(cuda, {1, 2, 3, 4, 5, 6}, {2, 3});
+        auto sliced = a.slice(1, Slice::full().step(-1));
+        sliced += Tensor<float>::from_buf(cuda, {10}, {1, 1});
+        ASSERT_EQ(cuda.dump(*a.buf), (std::vector<float>{11, 12, 13, 14, 15, 16}));
+    }
+    {  // ops/mod.rs:2604-2635 test_broadcast_chained_slices_with_negative_steps
+        auto a = Tensor<float>::from_buf(cuda, iota<float>(1, 16), {4, 4});
+        auto s2 = a.slice(0, Slice::full().step(-1)).slice(1, Slice::full().step(2));
+        ASSERT_EQ(s2.shape(), (std::vector<size_t>{4, 2}));
+        auto b = Tensor<float>::from_buf(cuda, {100, 200}, {1, 2});
+        ASSERT_EQ((s2 + b).cpu(), (std::vector<float>{113, 215, 109, 211, 105, 207, 101, 203}));
+    }
+    {  // ops/mod.rs:2638-2656 test_broadcast_scalar_with_complex_negative_slice
+        auto a = Tensor<int32_t>::from_buf(cuda, iota<int32_t>(1, 10), {10});
+        auto sliced = a.slice(0, Slice{8, 2, -2});
+        ASSERT_EQ((sliced + 100).cpu(), (std::vector<int32_t>{109, 107, 105}));
+    }
+    {  // backend/cpu.rs:1174-1196 reduce total max / min / prod; backend/cuda.rs:2304-2309 total sum
+        auto t = Tensor<double>::from_buf(cuda, {0.2, 0.3, 0.1, 0.3, 0.3, -0.1, -0.3, 0.3}, {4, 2});
+        ASSERT_EQ(t.max().item(), 0.3);
+        ASSERT_EQ(t.sum().item(), 1.1);
+        auto u = Tensor<double>::from_buf(cuda, {0.2, 0.3, 0.1, -0.9, 0.3, -0.1, -0.3, 0.3}, {4, 2});
+        ASSERT_EQ(u.min().item(), -0.9);
+        auto p = Tensor<double>::from_buf(cuda, {1, 2, 3, 4, 5, 6, 7, 8}, {4, 2});
+        ASSERT_EQ(p.prod().item(), 40320.0);
+    }
+    {  // backend/cpu.rs:1199-1278 axis reductions keep the reduced dim as size 1
+        auto t = Tensor<double>::from_buf(cuda, {3, 5, 6, 8, 1, 2, -1, 4}, {4, 2});
+        ASSERT_EQ(t.max_at(0).cpu(), (std::vector<double>{6, 8}));
+        ASSERT_EQ(t.max_at(0).shape(), (std::vector<size_t>{1, 2}));
+        ASSERT_EQ(t.min_at(0).cpu(), (std::vector<double>{-1, 2}));
+        ASSERT_EQ(t.prod_at(0).cpu(), (std::vector<double>{-18, 320}));
+        auto m = Tensor<double>::from_buf(cuda, {1, 2, 3, 4, 5, 6, 7, 8}, {4, 2});
+        ASSERT_EQ(m.mean_at(0).cpu(), (std::vector<double>{4, 5}));
+        ASSERT_EQ(m.mean_at(1).cpu(), (std::vector<double>{1.5, 3.5, 5.5, 7.5}));
+        ASSERT_EQ(m.mean_at(1).shape(), (std::vector<size_t>{4, 1}));
+    }
+    {  // ops/unary/mod.rs:442-451 relu on the N-d strided fixture (testing/mod.rs:159-195)
+        std::vector<double> def = {-1.0, 1.0, 0.0, 2.0, 1.0, 2.3, -0.3, 0.4, 0.0, -0.3, 0.4, 0.5, -0.2, 0.1, 0.2, -0.5};
+        auto t = Tensor<double>::from_buf(cuda, def, {4, 4, 1});
+        auto l2 = t.slice(0, Slice::full().step(2)).slice(1, Slice::full().step(2));
+        l2.relu_inplace();
+        auto got = cuda.dump(*t.buf);
+        for (size_t i = 0; i < 4; ++i)
+            for (size_t j = 0; j < 4; ++j) {
+                double x = def[i * 4 + j];
+                double want = (i % 2 == 0 && j % 2 == 0) ? std::fmax(x, 0.0) : x;
+                ASSERT_EQ(got[i * 4 + j], want);
+            }
+    }
+    {  // mean_l1_loss (ops/broadcast/l1.rs:79-84); no reference test pins a value: small exact case
+        auto a = Tensor<float>::from_buf(cuda, {1, 2, 3, 4}, {2, 2});
+        auto b = Tensor<float>::from_buf(cuda, {2, 2, 1, 8}, {2, 2});
+        ASSERT_EQ(mean_l1_loss(a, b).item(), 1.75f);
+    }
+    std::printf("ok: %d checks\n", g_checks);
+    return 0;
+}

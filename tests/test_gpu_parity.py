@@ -500,3 +500,156 @@ def test_mlp_loss_decreases_over_steps():
     img, tgt, _, _ = synthetic_batch(256, "cuda:0")
     losses = [float(model.step(img, tgt).item()) for _ in range(30)]
     assert losses[-1] < losses[0]  # the reference's own autograd tests assert exactly this
+
+
+# ------------------------------------------------------------------------------------- context / allocator
+def test_context_allocator_and_copies():
+    import rtensors_b200 as rt
+    lib = rt.lib()
+    ctx = C.c_void_p()
+    assert lib.rtb_ctx_create(C.c_int(0), C.byref(ctx)) == 0
+    try:
+        assert lib.rtb_ctx_device(ctx) == 0 and lib.rtb_ctx_sm_count(ctx) > 0
+        ptrs = []
+        for nbytes in (1, 4096, 1 << 20, (3 << 20) + 5):
+            p = C.c_void_p()
+            assert lib.rtb_alloc(ctx, C.c_size_t(nbytes), C.byref(p)) == 0 and p.value
+            assert p.value % 256 == 0
+            ptrs.append(p)
+        # round trip through the context's copy calls, with a kernel in between
+        x = np.arange(1000, dtype=np.float32)
+        p = ptrs[2]
+        assert lib.rtb_h2d(ctx, p, x.ctypes.data_as(C.c_void_p), C.c_size_t(x.nbytes)) == 0
+        v = np.array([2.0], dtype=np.float32)
+        shape = (C.c_size_t * 1)(1000)
+        strides = (C.c_ssize_t * 1)(1)
+        assert lib.rtb_scalar_op(ctx, C.c_int(10), C.c_int(2), p, v.ctypes.data_as(C.c_void_p), C.c_size_t(1), shape,
+                                 strides, C.c_size_t(0)) == 0
+        assert lib.rtb_d2d(ctx, ptrs[3], p, C.c_size_t(x.nbytes)) == 0
+        y = np.zeros_like(x)
+        assert lib.rtb_d2h(ctx, y.ctypes.data_as(C.c_void_p), ptrs[3], C.c_size_t(x.nbytes)) == 0
+        assert np.array_equal(y, x * 2)
+        assert lib.rtb_ctx_launch_count(ctx) == 1
+        # freed blocks are reused (caching) and foreign pointers are refused
+        old = ptrs[1].value
+        assert lib.rtb_free(ctx, ptrs[1]) == 0
+        q = C.c_void_p()
+        assert lib.rtb_alloc(ctx, C.c_size_t(4000), C.byref(q)) == 0 and q.value == old
+        assert lib.rtb_free(ctx, C.c_void_p(12345)) == -1
+        assert b"not allocated" in lib.rtb_last_error_string()
+        for p in (ptrs[0], q, ptrs[2], ptrs[3]):
+            assert lib.rtb_free(ctx, p) == 0
+        assert lib.rtb_release_cached(ctx) == 0
+        # a non-default stream
+        s = torch.cuda.Stream()
+        assert lib.rtb_ctx_set_stream(ctx, C.c_void_p(s.cuda_stream)) == 0
+        assert lib.rtb_ctx_get_stream(ctx) == s.cuda_stream
+        t = torch.ones(1 << 16, device="cuda")
+        s.wait_stream(torch.cuda.current_stream())
+        shape = (C.c_size_t * 1)(t.numel())
+        assert lib.rtb_scalar_op(ctx, C.c_int(10), C.c_int(0), C.c_void_p(t.data_ptr()), v.ctypes.data_as(C.c_void_p),
+                                 C.c_size_t(1), shape, strides, C.c_size_t(0)) == 0
+        assert lib.rtb_ctx_sync(ctx) == 0
+        assert float(t.sum().item()) == 3.0 * t.numel()
+    finally:
+        lib.rtb_ctx_destroy(ctx)
+
+
+def test_error_codes_for_bad_arguments():
+    import rtensors_b200 as rt
+    from rtensors_b200.meta import Meta
+    x = _b().alloc(16, torch.float32)
+    with pytest.raises(rt.RtbError) as e:  # view runs past the buffer
+        _b().scalar_apply(x, O.ADD, 1.0, Meta((4, 8), (8, 1), 0))
+    assert e.value.code == -4
+    flag = _b().alloc(4, torch.bool)
+    with pytest.raises(rt.RtbError) as e:  # boolean division is not defined (todo!() in the reference)
+        _b().scalar_apply(flag, O.DIV, True, Meta.contiguous((4,)))
+    assert e.value.code == -2
+    u = _b().alloc(4, torch.uint8)
+    with pytest.raises(rt.RtbError):       # negation needs a signed type
+        _b().apply_unary(u, O.NEG, Meta.contiguous((4,)))
+    i = _b().alloc(4, torch.int32)
+    with pytest.raises(rt.RtbError) as e:  # reductions are float-only, as in the reference
+        _b().apply_reduce_contiguous_flat(i, i, 0, 4, O.SUM)
+    assert e.value.code == -2
+    with pytest.raises(rt.RtbError) as e:
+        _b().apply_reduce((x, Meta.contiguous((4, 4)).permute((1, 0))), x, 0, O.SUM)
+    assert e.value.code == -7
+
+
+# ------------------------------------------------------------------------------------- 128-bit integers
+def test_128_bit_integer_ops():
+    """u128 / i128 have no numpy or torch dtype: drive them as raw 16-byte little-endian words."""
+    import rtensors_b200 as rt
+    from rtensors_b200.meta import Meta
+    lib = rt.lib()
+    rng = np.random.default_rng(128)
+    n = 1000
+    mask = (1 << 128) - 1
+
+    def to_bytes(vals):
+        return np.frombuffer(b"".join(int(v & mask).to_bytes(16, "little") for v in vals), dtype=np.uint8).copy()
+
+    def from_bytes(buf):
+        raw = buf.tobytes()
+        return [int.from_bytes(raw[k:k + 16], "little") for k in range(0, len(raw), 16)]
+
+    a = [int(rng.integers(0, 1 << 62)) << int(rng.integers(0, 66)) for _ in range(n)]
+    b = [int(rng.integers(1, 1 << 62)) << int(rng.integers(0, 60)) for _ in range(n)]
+    da, db = _dev(to_bytes(a)), _dev(to_bytes(b))
+    out = _b().alloc(16 * n, torch.uint8)
+    m = Meta.contiguous((n,))
+    ctx = _b()._ctx
+    for code, op, fn in ((5, 0, lambda x, y: (x + y) & mask), (5, 1, lambda x, y: (x - y) & mask),
+                         (5, 2, lambda x, y: (x * y) & mask), (5, 3, lambda x, y: x // y)):
+        rc = lib.rtb_broadcast(ctx, C.c_int(code), C.c_int(op), C.c_void_p(da.data_ptr()), (C.c_ssize_t * 1)(1),
+                               C.c_size_t(0), C.c_void_p(db.data_ptr()), (C.c_ssize_t * 1)(1), C.c_size_t(0),
+                               C.c_void_p(out.data_ptr()), (C.c_ssize_t * 1)(1), C.c_size_t(0), C.c_size_t(1),
+                               (C.c_size_t * 1)(n))
+        assert rc == 0
+        assert from_bytes(_host(out)) == [fn(x, y) for x, y in zip(a, b)], op
+    # signed: negate and relu through a reversed strided view
+    sa = [int(rng.integers(-(1 << 62), 1 << 62)) * int(rng.integers(1, 1 << 40)) for _ in range(n)]
+    ds = _dev(to_bytes(sa))
+    view = Meta.contiguous((n,)).slice(0, None, None, -3)
+    assert lib.rtb_unary_op(ctx, C.c_int(9), C.c_int(1), C.c_void_p(ds.data_ptr()), C.c_size_t(1),
+                            (C.c_size_t * 1)(view.shape[0]), (C.c_ssize_t * 1)(view.strides[0]),
+                            C.c_size_t(view.offset)) == 0
+    want = list(sa)
+    for k in range(view.shape[0]):
+        idx = view.offset + k * view.strides[0]
+        want[idx] = max(want[idx], 0)
+    got = [v - (1 << 128) if v >> 127 else v for v in from_bytes(_host(ds))]
+    assert got == want
+
+
+def test_host_pipeline_matches_oracle():
+    from rtensors_b200.host import HostPipeline
+    from rtensors_b200.meta import Meta
+    rng = np.random.default_rng(31)
+    n = (1 << 20) + 777
+    ha = torch.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)).pin_memory()
+    hi = torch.from_numpy(rng.integers(-(1 << 20), 1 << 20, n).astype(np.int32)).pin_memory()
+    hj = torch.from_numpy(rng.integers(-(1 << 20), 1 << 20, n).astype(np.int32)).pin_memory()
+    ra, ri = torch.empty_like(ha).pin_memory(), torch.empty_like(hi).pin_memory()
+    be = _b()
+    a, ia, ib, io = (be.alloc(n, torch.float32), be.alloc(n, torch.int32), be.alloc(n, torch.int32),
+                     be.alloc(n, torch.int32))
+
+    def compute(v, length):
+        mc = Meta.contiguous((length,))
+        be.scalar_apply(v["a"], O.MUL, 3.0, mc)
+        be.scalar_apply(v["a"], O.ADD, 2.0, mc)
+        be.scalar_apply(v["a"], O.SUB, 1.0, mc)
+        be.broadcast((v["ia"], mc), (v["ib"], mc), (v["iout"], mc), O.ADD)
+    pipe = HostPipeline(be, chunk_elems=100_000)  # ragged last chunk, unaligned chunk starts
+    for _ in range(2):
+        pipe.run(n, {"a": (ha, a), "ia": (hi, ia), "ib": (hj, ib)}, {"a": (ra, a), "iout": (ri, io)}, compute)
+    torch.cuda.synchronize()
+    ref = ha.numpy().copy()
+    m = O.Meta.contiguous((n,))
+    for op, v in ((O.MUL, 3.0), (O.ADD, 2.0), (O.SUB, 1.0)):
+        O.scalar_op(ref, op, v, m)
+    assert ra.numpy().tobytes() == ref.tobytes()
+    assert np.array_equal(ri.numpy(), hi.numpy() + hj.numpy())
