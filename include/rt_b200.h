@@ -130,6 +130,7 @@ typedef struct {
                                    3 reversed-scalar 4 broadcast(stride 0) 5 strided */
     int tile_x, tile_y;   /* thread tile of the row kernel */
     uint64_t n_rows, n_col_chunks, grid;
+    int fast, ux;         /* row kernel: lean instantiation? 128-bit columns per thread per row (1 or 4) */
 } rtb_plan;
 int rtb_plan_elementwise(int dtype, int n_inputs, size_t rank, const size_t *shape, const ptrdiff_t *stride_d,
                          size_t off_d, uintptr_t ptr_d, const ptrdiff_t *stride_l, size_t off_l, uintptr_t ptr_l,

@@ -29,7 +29,8 @@ class Plan(C.Structure):
                 ("stride_l", C.c_int64 * 8), ("stride_r", C.c_int64 * 8), ("base_d", C.c_int64),
                 ("base_l", C.c_int64), ("base_r", C.c_int64), ("vec", C.c_int), ("mode_d", C.c_int),
                 ("mode_l", C.c_int), ("mode_r", C.c_int), ("tile_x", C.c_int), ("tile_y", C.c_int),
-                ("n_rows", C.c_uint64), ("n_col_chunks", C.c_uint64), ("grid", C.c_uint64)]
+                ("n_rows", C.c_uint64), ("n_col_chunks", C.c_uint64), ("grid", C.c_uint64),
+                ("fast", C.c_int), ("ux", C.c_int)]
 
 
 _lib = None

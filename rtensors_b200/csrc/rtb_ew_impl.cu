@@ -394,13 +394,9 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         p.sd[k] = plan.stride_d[k]; p.sl[k] = plan.stride_l[k]; p.sr[k] = plan.stride_r[k];
         if (k < R - 1) p.div[k] = make_fastdiv((uint32_t)plan.shape[k]);
     }
-    auto lean = [](int mode) { return mode == kContigVec || mode == kRevVec || mode == kBroadcast; };
-    const bool fast = plan.mode_d == kContigVec && (NIN < 1 || lean(plan.mode_l)) && (NIN < 2 || lean(plan.mode_r)) &&
-                      p.inner % VEC == 0 && p.inner < (1ull << 31);
-    // four 128-bit columns per thread when the row is long enough, else one
-    const uint64_t inner_vecs = (p.inner + VEC - 1) / VEC;
-    const int ux = (fast && inner_vecs >= 4ull * plan.tile_x) ? 4 : 1;
-    const uint64_t chunks = (inner_vecs + (uint64_t)plan.tile_x * ux - 1) / ((uint64_t)plan.tile_x * ux);
+    const bool fast = plan.fast != 0;
+    const int ux = plan.ux;
+    const uint64_t chunks = plan.n_col_chunks;
     p.n_col_chunks = (uint32_t)chunks;
     // a CTA walks `iters` consecutive row tiles: the row decode and any broadcast operand held in
     // registers are paid once per CTA, while the grid stays at >= 8 CTAs per SM

@@ -151,8 +151,16 @@ int make_plan(size_t es, int n_inputs, size_t rank, const size_t *shape, const V
     out->mode_l = n_inputs >= 1 ? mode_of(1, l, bl, in.sl) : (int)kBroadcast;
     out->mode_r = n_inputs >= 2 ? mode_of(2, r, br, in.sr) : (int)kBroadcast;
 
+    // lean form: every operand walks the inner dim as whole aligned vectors / reversed vectors / a
+    // broadcast scalar, and the output is a vector store -> the kernel instantiation without
+    // per-element paths, with four 128-bit columns per thread once a row holds >= 128 vectors
+    auto lean = [](int mode) { return mode == kContigVec || mode == kRevVec || mode == kBroadcast; };
+    const bool fast = out->mode_d == kContigVec && (n_inputs < 1 || lean(out->mode_l)) &&
+                      (n_inputs < 2 || lean(out->mode_r)) && in.n % vec == 0 && in.n < (1ull << 31);
     uint64_t inner_vecs = (in.n + vec - 1) / vec;
-    out->tile_x = pow2_ceil(inner_vecs, 256);
+    out->fast = fast ? 1 : 0;
+    out->ux = (fast && inner_vecs >= 128) ? 4 : 1;
+    out->tile_x = pow2_ceil((inner_vecs + out->ux - 1) / out->ux, 256);
     out->tile_y = 256 / out->tile_x;
     uint64_t rows = 1;
     for (int k = 0; k + 1 < R; ++k) {
@@ -160,10 +168,8 @@ int make_plan(size_t es, int n_inputs, size_t rank, const size_t *shape, const V
         if (rows >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "more than 2^31 rows in one launch");
     }
     out->n_rows = rows;
-    // four 128-bit columns per thread when the row is long enough, else one; the launcher lets a
-    // CTA walk several row tiles, so `grid` here is the upper bound (one row tile per CTA)
-    int ux = inner_vecs >= 4ull * out->tile_x ? 4 : 1;
-    out->n_col_chunks = (inner_vecs + (uint64_t)out->tile_x * ux - 1) / ((uint64_t)out->tile_x * ux);
+    // the launcher lets a CTA walk several row tiles, so `grid` is the upper bound (one tile per CTA)
+    out->n_col_chunks = (inner_vecs + (uint64_t)out->tile_x * out->ux - 1) / ((uint64_t)out->tile_x * out->ux);
     uint64_t row_tiles = (rows + (uint64_t)out->tile_y - 1) / (uint64_t)out->tile_y;
     out->grid = row_tiles * out->n_col_chunks;
     if (out->grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");

@@ -159,7 +159,7 @@ def test_plan_config_outer_product():
     p = plan_elementwise(L.F32, 2, shape, d, Meta(shape, sa, 0), Meta(shape, sb, 0))
     assert p.kernel == 3 and p.rank == 2
     assert (p.mode_d, p.mode_l, p.mode_r) == (0, 4, 0)  # vector store, broadcast scalar, vector load
-    assert p.tile_x == 256 and p.n_rows == 4096 and p.n_col_chunks == 1
+    assert p.tile_x == 256 and p.ux == 4 and p.n_rows == 4096 and p.n_col_chunks == 1
 
 
 def test_plan_config_strided_negative_step_broadcast():
@@ -173,7 +173,8 @@ def test_plan_config_strided_negative_step_broadcast():
     p = plan_elementwise(L.F32, 2, shape, d, Meta(shape, sa, A.offset), Meta(shape, sb, B.offset))
     assert p.kernel == 3 and p.rank == 4
     assert (p.mode_d, p.mode_l, p.mode_r) == (0, 4, 2)  # vector store, broadcast, reversed vector load
-    assert p.n_rows == 16 * 64 * 1024 and p.grid == p.n_rows and p.n_col_chunks == 1
+    assert p.fast == 1 and p.ux == 4 and p.tile_x == 64 and p.tile_y == 4  # 4 rows x (64 x 4) vectors per CTA pass
+    assert p.n_rows == 16 * 64 * 1024 and p.grid == p.n_rows // 4 and p.n_col_chunks == 1
 
 
 def test_plan_flips_and_merges_reversed_inplace_view():
