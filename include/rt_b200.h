@@ -33,11 +33,24 @@ typedef enum {
     RTB_U64 = 7, RTB_I64 = 8, RTB_I128 = 9, RTB_F32 = 10, RTB_F64 = 11, RTB_BOOL = 12
 } rtb_dtype;
 
-/* binary op codes = OpCode (cuda/include/common.h:6-11) = BinaryOpType (src/ops/base.rs:7-12) */
-typedef enum { RTB_ADD = 0, RTB_SUB = 1, RTB_MUL = 2, RTB_DIV = 3 } rtb_binop;
+/* binary op codes = OpCode (cuda/include/common.h:6-11) = BinaryOpType (src/ops/base.rs:7-12).
+ * Codes 4..7 exist for rtb_scalar_op only: the remaining scalar families of the Backend trait
+ * (src/backend/mod.rs:339-346; log / log1p / elu are f32 / f64 only, leaky_relu any dtype). */
+typedef enum {
+    RTB_ADD = 0, RTB_SUB = 1, RTB_MUL = 2, RTB_DIV = 3,
+    RTB_LOG = 4, RTB_LOG1P = 5, RTB_LEAKY_RELU = 6, RTB_ELU = 7
+} rtb_binop;
 
-/* unary ops on the hot path (src/backend/cpu.rs:549-557, 632-657: CPU formulae) */
-typedef enum { RTB_NEG = 0, RTB_RELU = 1, RTB_ABS = 2, RTB_SIGN = 3 } rtb_unop;
+/* unary ops (src/backend/mod.rs:311-368), computed with the CPU backend's formulae
+ * (src/backend/cpu.rs:485-724).  0..3 are on the hot path and exist for integer types too;
+ * 4..30 are the remaining float-only families. */
+typedef enum {
+    RTB_NEG = 0, RTB_RELU = 1, RTB_ABS = 2, RTB_SIGN = 3,
+    RTB_SIGMOID = 4, RTB_TANH = 5, RTB_SQRT = 6, RTB_SIN = 7, RTB_COS = 8, RTB_TAN = 9, RTB_ASIN = 10,
+    RTB_ACOS = 11, RTB_ATAN = 12, RTB_SINH = 13, RTB_COSH = 14, RTB_ASINH = 15, RTB_ACOSH = 16, RTB_ATANH = 17,
+    RTB_RSQRT = 18, RTB_RECIPROCAL = 19, RTB_SQUARE = 20, RTB_CUBE = 21, RTB_EXP = 22, RTB_LN = 23, RTB_LN1P = 24,
+    RTB_FLOOR = 25, RTB_CEIL = 26, RTB_ROUND = 27, RTB_TRUNC = 28, RTB_EXPM1 = 29, RTB_SILU = 30
+} rtb_unop;
 
 /* reduction codes = ReductionOpCode (cuda/include/common.h:19-30) */
 typedef enum { RTB_SUM = 1, RTB_PROD = 2, RTB_MAX = 3, RTB_MIN = 4, RTB_MEAN = 5 } rtb_redop;

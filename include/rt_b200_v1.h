@@ -10,11 +10,12 @@
  * (errors surface at the caller's next synchronisation), except the scratch-allocation flag.
  * `block_size` is accepted and ignored.
  *
- * Covered: scalar add/sub/mul/div (scalar.h:9-96), negate/relu (scalar.h:99-148), abs/sign
- * (scalar.h:173-184 family), fill (fill.h:9-12), broadcast (binary.h:8-20), flat / N-d
- * reductions SUM PROD MAX MIN MEAN for f32/f64 and the allocation flag (scalar.h:213-228).
- * Not provided (outside the hot path): the other unary/scalar families, variance / norm /
- * logsumexp / argmax reductions, integer matmul, buffer_equal.
+ * Covered: every scalar family (add sub mul div log log1p leaky_relu elu, scalar.h:9-96), every
+ * unary family (negate relu, scalar.h:99-148; the 29 float-only ones, scalar.h:150-211), fill
+ * (fill.h:9-12), broadcast (binary.h:8-20), flat / N-d reductions SUM PROD MAX MIN MEAN for
+ * f32/f64 and the allocation flag (scalar.h:213-228).
+ * Not provided (outside the path, and absent from the reference CPU backend that defines parity):
+ * variance / norm / logsumexp / argmax reductions; integer matmul; buffer_equal.
  */
 #ifndef RT_B200_V1_H
 #define RT_B200_V1_H
@@ -86,8 +87,21 @@ RTB_V1_ALL_TYPES(RTB_V1_SCALAR, mul RTB_V1_COMMA)
 RTB_V1_ALL_TYPES(RTB_V1_SCALAR, div RTB_V1_COMMA)
 RTB_V1_SIGNED_TYPES(RTB_V1_UNARY, negate RTB_V1_COMMA)
 RTB_V1_SIGNED_TYPES(RTB_V1_UNARY, relu RTB_V1_COMMA)
-RTB_V1_UNARY(abs, float, f32) RTB_V1_UNARY(abs, double, f64)
-RTB_V1_UNARY(sign, float, f32) RTB_V1_UNARY(sign, double, f64)
+/* the 29 float-only unary families, scalar.h:150-211 */
+#define RTB_V1_FLOAT_UNARY(OP) RTB_V1_UNARY(OP, float, f32) RTB_V1_UNARY(OP, double, f64)
+RTB_V1_FLOAT_UNARY(abs) RTB_V1_FLOAT_UNARY(sign) RTB_V1_FLOAT_UNARY(sigmoid) RTB_V1_FLOAT_UNARY(tanh)
+RTB_V1_FLOAT_UNARY(sqrt) RTB_V1_FLOAT_UNARY(sin) RTB_V1_FLOAT_UNARY(cos) RTB_V1_FLOAT_UNARY(tan)
+RTB_V1_FLOAT_UNARY(asin) RTB_V1_FLOAT_UNARY(acos) RTB_V1_FLOAT_UNARY(atan) RTB_V1_FLOAT_UNARY(sinh)
+RTB_V1_FLOAT_UNARY(cosh) RTB_V1_FLOAT_UNARY(asinh) RTB_V1_FLOAT_UNARY(acosh) RTB_V1_FLOAT_UNARY(atanh)
+RTB_V1_FLOAT_UNARY(rsqrt) RTB_V1_FLOAT_UNARY(reciprocal) RTB_V1_FLOAT_UNARY(square) RTB_V1_FLOAT_UNARY(cube)
+RTB_V1_FLOAT_UNARY(exp) RTB_V1_FLOAT_UNARY(ln) RTB_V1_FLOAT_UNARY(ln1p) RTB_V1_FLOAT_UNARY(floor)
+RTB_V1_FLOAT_UNARY(ceil) RTB_V1_FLOAT_UNARY(round) RTB_V1_FLOAT_UNARY(trunc) RTB_V1_FLOAT_UNARY(expm1)
+RTB_V1_FLOAT_UNARY(silu)
+/* remaining scalar families, scalar.h:74-96: log / log1p / elu for f32, f64; leaky_relu for all */
+RTB_V1_SCALAR(log, float, f32) RTB_V1_SCALAR(log, double, f64)
+RTB_V1_SCALAR(log1p, float, f32) RTB_V1_SCALAR(log1p, double, f64)
+RTB_V1_SCALAR(elu, float, f32) RTB_V1_SCALAR(elu, double, f64)
+RTB_V1_ALL_TYPES(RTB_V1_SCALAR, leaky_relu RTB_V1_COMMA)
 RTB_V1_ALL_TYPES(RTB_V1_FILL)
 RTB_V1_ALL_TYPES(RTB_V1_BROADCAST)
 RTB_V1_REDUCE(float, f32) RTB_V1_REDUCE(double, f64)

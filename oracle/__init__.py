@@ -18,8 +18,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 # dtype codes = DType discriminants of the reference (core/value.rs:567-581)
 U8, I8, U16, I16, U32, U128, I32, U64, I64, I128, F32, F64, BOOL = range(13)
-ADD, SUB, MUL, DIV = range(4)
-NEG, RELU, ABS, SIGN = range(4)
+ADD, SUB, MUL, DIV, LOG, LOG1P, LEAKY_RELU, ELU = range(8)
+(NEG, RELU, ABS, SIGN, SIGMOID, TANH, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, ASINH, ACOSH, ATANH, RSQRT,
+ RECIPROCAL, SQUARE, CUBE, EXP, LN, LN1P, FLOOR, CEIL, ROUND, TRUNC, EXPM1, SILU) = range(31)
 SUM, PROD, MAX, MIN, MEAN = 1, 2, 3, 4, 5
 
 NP_TO_CODE = {
@@ -177,6 +178,11 @@ def _ptr(arr: np.ndarray):
 def elementwise(buf: np.ndarray, kind: int, op: int, value, meta: Meta, fast: bool = False) -> None:
     """In-place scalar op (kind 0), unary op (kind 1) or fill (kind 2) over the view `meta` of `buf`."""
     assert buf.flags.c_contiguous and buf.ndim == 1
+    if meta.is_contiguous() and meta.offset + meta.size > buf.size:
+        # A view whose strides are dense up to sign counts as "contiguous" in the reference
+        # (core/meta.rs:526-541) and is then walked FORWARD from its offset: the Rust slice index
+        # `buf[start..start+len]` panics.  Refuse here instead of writing past the numpy buffer.
+        raise OracleError(-2)
     v = np.array([0 if value is None else value], dtype=buf.dtype)
     _chk(lib(fast).orc_elementwise(C.c_int(_code(buf)), _ptr(buf), C.c_int(kind), C.c_int(op), _ptr(v),
                                    C.c_size_t(meta.rank), _sizes(meta.shape), _diffs(meta.strides),

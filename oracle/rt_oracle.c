@@ -30,10 +30,15 @@
 /* dtype codes = DType discriminants, core/value.rs:567-581 */
 enum { ORC_U8 = 0, ORC_I8 = 1, ORC_U16 = 2, ORC_I16 = 3, ORC_U32 = 4, ORC_U128 = 5, ORC_I32 = 6,
        ORC_U64 = 7, ORC_I64 = 8, ORC_I128 = 9, ORC_F32 = 10, ORC_F64 = 11, ORC_BOOL = 12 };
-/* BinaryOpType, ops/base.rs:7-12 */
-enum { ORC_ADD = 0, ORC_SUB = 1, ORC_MUL = 2, ORC_DIV = 3 };
-/* unary functor ids (oracle-local numbering) */
-enum { ORC_NEG = 0, ORC_RELU = 1, ORC_ABS = 2, ORC_SIGN = 3 };
+/* BinaryOpType, ops/base.rs:7-12; 4..7 = the other scalar families of the Backend trait
+ * (backend/mod.rs:339-346), scalar-op form only */
+enum { ORC_ADD = 0, ORC_SUB = 1, ORC_MUL = 2, ORC_DIV = 3, ORC_LOG = 4, ORC_LOG1P = 5, ORC_LEAKY_RELU = 6, ORC_ELU = 7 };
+/* unary functor ids (same numbering as the CUDA library's rtb_unop) */
+enum { ORC_NEG = 0, ORC_RELU = 1, ORC_ABS = 2, ORC_SIGN = 3,
+       ORC_SIGMOID = 4, ORC_TANH = 5, ORC_SQRT = 6, ORC_SIN = 7, ORC_COS = 8, ORC_TAN = 9, ORC_ASIN = 10, ORC_ACOS = 11,
+       ORC_ATAN = 12, ORC_SINH = 13, ORC_COSH = 14, ORC_ASINH = 15, ORC_ACOSH = 16, ORC_ATANH = 17, ORC_RSQRT = 18,
+       ORC_RECIPROCAL = 19, ORC_SQUARE = 20, ORC_CUBE = 21, ORC_EXP = 22, ORC_LN = 23, ORC_LN1P = 24, ORC_FLOOR = 25,
+       ORC_CEIL = 26, ORC_ROUND = 27, ORC_TRUNC = 28, ORC_EXPM1 = 29, ORC_SILU = 30 };
 /* ReductionOpTypes::get_code, ops/reduction/mod.rs:161-175 */
 enum { ORC_SUM = 1, ORC_PROD = 2, ORC_MAX = 3, ORC_MIN = 4, ORC_MEAN = 5 };
 
@@ -264,6 +269,7 @@ typedef __int128 i128_t;
             case ORC_ADD: return (T)((UT)a + (UT)b);                                         \
             case ORC_SUB: return (T)((UT)a - (UT)b);                                         \
             case ORC_MUL: return (T)((UT)a * (UT)b);                                         \
+            case ORC_LEAKY_RELU: return a > (T)0 ? a : (T)((UT)a * (UT)b);                   \
             default: return (T)(a / b);                                                      \
         }                                                                                    \
     }                                                                                        \
@@ -276,13 +282,55 @@ typedef __int128 i128_t;
         }                                                                                    \
     }
 
-#define DEF_FLOAT_OPS(S, T)                                                                  \
+/* Remaining float unary families with the CPU backend's own formulas (backend/cpu.rs:485-724,
+ * core/primops/exp.rs, core/value.rs:62-140): exp-based tanh/sinh/cosh, ln/sqrt-based inverse
+ * hyperbolics, sigmoid = 1/(1+exp(-x)), silu = x*sigmoid(x), round = half away from zero.
+ * Scalar families: log(base) = ln(x)/ln(base) (Rust f32::log), log1p(base) = ln_1p(x)/ln(base),
+ * leaky_relu = x>0 ? x : x*slope, elu = x>=0 ? x : alpha*expm1(x) (backend/cpu.rs:699-724). */
+#define DEF_FLOAT_OPS(S, T, SFX)                                                             \
+    static inline T ext_##S(int op, T x) {                                                   \
+        const T one = (T)1;                                                                  \
+        switch (op) {                                                                        \
+            case ORC_SIGMOID: return one / (one + exp##SFX(-x));                             \
+            case ORC_SILU: return x * (one / (one + exp##SFX(-x)));                          \
+            case ORC_TANH: { T a = exp##SFX(x), b = exp##SFX(-x); return (a - b) / (a + b); } \
+            case ORC_SINH: { T a = exp##SFX(x), b = exp##SFX(-x); return (a - b) / (one + one); } \
+            case ORC_COSH: { T a = exp##SFX(x), b = exp##SFX(-x); return (a + b) / (one + one); } \
+            case ORC_ASINH: return log##SFX(x + sqrt##SFX(x * x + one));                     \
+            case ORC_ACOSH: return log##SFX(x + sqrt##SFX(x * x - one));                     \
+            case ORC_ATANH: return log##SFX((one + x) / (one - x)) / (one + one);            \
+            case ORC_SQRT: return sqrt##SFX(x);                                              \
+            case ORC_RSQRT: return one / sqrt##SFX(x);                                       \
+            case ORC_RECIPROCAL: return one / x;                                             \
+            case ORC_SQUARE: return x * x;                                                   \
+            case ORC_CUBE: return x * x * x;                                                 \
+            case ORC_EXP: return exp##SFX(x);                                                \
+            case ORC_EXPM1: return expm1##SFX(x);                                            \
+            case ORC_LN: return log##SFX(x);                                                 \
+            case ORC_LN1P: return log1p##SFX(x);                                             \
+            case ORC_SIN: return sin##SFX(x);                                                \
+            case ORC_COS: return cos##SFX(x);                                                \
+            case ORC_TAN: return tan##SFX(x);                                                \
+            case ORC_ASIN: return asin##SFX(x);                                              \
+            case ORC_ACOS: return acos##SFX(x);                                              \
+            case ORC_ATAN: return atan##SFX(x);                                              \
+            case ORC_FLOOR: return floor##SFX(x);                                            \
+            case ORC_CEIL: return ceil##SFX(x);                                              \
+            case ORC_ROUND: return round##SFX(x);                                            \
+            case ORC_TRUNC: return trunc##SFX(x);                                            \
+        }                                                                                    \
+        return x;                                                                            \
+    }                                                                                        \
     static inline T bin_##S(int op, T a, T b) {                                              \
         switch (op) {                                                                        \
             case ORC_ADD: return a + b;                                                      \
             case ORC_SUB: return a - b;                                                      \
             case ORC_MUL: return a * b;                                                      \
-            default: return a / b;                                                           \
+            case ORC_DIV: return a / b;                                                      \
+            case ORC_LOG: return log##SFX(a) / log##SFX(b);                                  \
+            case ORC_LOG1P: return log1p##SFX(a) / log##SFX(b);                              \
+            case ORC_LEAKY_RELU: return a > (T)0 ? a : a * b;                                \
+            default: return a >= (T)0 ? a : b * expm1##SFX(a); /* ELU */                     \
         }                                                                                    \
     }                                                                                        \
     static inline T un_##S(int op, T x) {                                                    \
@@ -290,7 +338,8 @@ typedef __int128 i128_t;
             case ORC_NEG: return -x;                                                         \
             case ORC_RELU: return x > (T)0 ? x : (T)0;                                       \
             case ORC_ABS: return sizeof(T) == 4 ? (T)fabsf((float)x) : (T)fabs((double)x);   \
-            default: return x < (T)0 ? (T)-1 : (x > (T)0 ? (T)1 : (T)0);                     \
+            case ORC_SIGN: return x < (T)0 ? (T)-1 : (x > (T)0 ? (T)1 : (T)0);               \
+            default: return ext_##S(op, x);                                                  \
         }                                                                                    \
     }
 
@@ -304,14 +353,15 @@ DEF_INT_OPS(u64, uint64_t, uint64_t, 0)
 DEF_INT_OPS(i64, int64_t, uint64_t, 1)
 DEF_INT_OPS(u128, u128_t, u128_t, 0)
 DEF_INT_OPS(i128, i128_t, u128_t, 1)
-DEF_FLOAT_OPS(f32, float)
-DEF_FLOAT_OPS(f64, double)
+DEF_FLOAT_OPS(f32, float, f)
+DEF_FLOAT_OPS(f64, double, )
 
 /* boolean: + OR, - XOR, * AND, / unimplemented in the reference (core/value.rs:708-764) */
 static inline uint8_t bin_boolean(int op, uint8_t a, uint8_t b) {
     switch (op) {
         case ORC_ADD: return (uint8_t)((a != 0) || (b != 0));
         case ORC_SUB: return (uint8_t)((a != 0) != (b != 0));
+        case ORC_LEAKY_RELU: return a; /* x > false ? x : x AND slope == x */
         default: return (uint8_t)((a != 0) && (b != 0));
     }
 }
@@ -373,6 +423,10 @@ ORC_API int orc_elementwise(int dtype, void *buf, int kind, int op, const void *
                             const size_t *shape, const ptrdiff_t *strides, size_t offset) {
     if (rank > ORC_MAX_RANK) return ORC_ERR_DIM;
     if (dtype == ORC_BOOL && kind == 0 && op == ORC_DIV) return ORC_ERR_OP;
+    if (dtype != ORC_F32 && dtype != ORC_F64) {
+        if (kind == 1 && op > ORC_SIGN) return ORC_ERR_DTYPE;
+        if (kind == 0 && (op == ORC_LOG || op == ORC_LOG1P || op == ORC_ELU)) return ORC_ERR_DTYPE;
+    }
     switch (dtype) {
 #define CASE_EW(S, T, CODE)                                                                  \
     case CODE: {                                                                             \

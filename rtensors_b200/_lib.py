@@ -10,8 +10,9 @@ LIB_PATH = os.path.join(_PKG, "librt_b200.so")
 # dtype codes (rtb_dtype) = DType discriminants of the reference, src/core/value.rs:567-581
 U8, I8, U16, I16, U32, U128, I32, U64, I64, I128, F32, F64, BOOL = range(13)
 DTYPE_SIZE = {U8: 1, I8: 1, BOOL: 1, U16: 2, I16: 2, U32: 4, I32: 4, F32: 4, U64: 8, I64: 8, F64: 8, U128: 16, I128: 16}
-ADD, SUB, MUL, DIV = range(4)
-NEG, RELU, ABS, SIGN = range(4)
+ADD, SUB, MUL, DIV, LOG, LOG1P, LEAKY_RELU, ELU = range(8)
+(NEG, RELU, ABS, SIGN, SIGMOID, TANH, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, ASINH, ACOSH, ATANH, RSQRT,
+ RECIPROCAL, SQUARE, CUBE, EXP, LN, LN1P, FLOOR, CEIL, ROUND, TRUNC, EXPM1, SILU) = range(31)
 SUM, PROD, MAX, MIN, MEAN = 1, 2, 3, 4, 5
 OK = 0
 

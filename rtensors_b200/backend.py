@@ -114,10 +114,22 @@ class CudaB200:
         check(lib().rtb_unary_op(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(meta.rank),
                                  sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset)))
 
+    def scalar_apply_log(self, buf, value, meta): self.scalar_apply(buf, L.LOG, value, meta)
+    def scalar_apply_log1p(self, buf, value, meta): self.scalar_apply(buf, L.LOG1P, value, meta)
+    def scalar_apply_leaky_relu(self, buf, value, meta): self.scalar_apply(buf, L.LEAKY_RELU, value, meta)
+    def scalar_apply_elu(self, buf, value, meta): self.scalar_apply(buf, L.ELU, value, meta)
+
     def apply_neg(self, buf, meta): self.apply_unary(buf, L.NEG, meta)
     def apply_relu(self, buf, meta): self.apply_unary(buf, L.RELU, meta)
     def apply_abs(self, buf, meta): self.apply_unary(buf, L.ABS, meta)
     def apply_sign(self, buf, meta): self.apply_unary(buf, L.SIGN, meta)
+
+    def __getattr__(self, name):
+        # apply_sigmoid, apply_tanh, ... apply_silu: the remaining unary families of the trait
+        if name.startswith("apply_") and hasattr(L, name[6:].upper()):
+            code = getattr(L, name[6:].upper())
+            return lambda buf, meta: self.apply_unary(buf, code, meta)
+        raise AttributeError(name)
 
     def fill(self, buf: torch.Tensor, value, meta: Meta):
         code = dtype_code(buf)

@@ -142,6 +142,7 @@ void reduce_nd_v1(int dtype, const void *data, void *out, size_t offset, size_t 
     V1_SCALAR_IMPL(sub, RTB_SUB, TYPE, S, DT)                                                                     \
     V1_SCALAR_IMPL(mul, RTB_MUL, TYPE, S, DT)                                                                     \
     V1_SCALAR_IMPL(div, RTB_DIV, TYPE, S, DT)                                                                     \
+    V1_SCALAR_IMPL(leaky_relu, RTB_LEAKY_RELU, TYPE, S, DT)                                                       \
     V1_FILL_IMPL(TYPE, S, DT)                                                                                     \
     V1_BROADCAST_IMPL(TYPE, S, DT)
 
@@ -169,10 +170,22 @@ V1_SIGNED(int16_t, i16, RTB_I16)
 V1_SIGNED(int32_t, i32, RTB_I32)
 V1_SIGNED(int64_t, i64, RTB_I64)
 V1_SIGNED(__int128_t, i128, RTB_I128)
-V1_UNARY_IMPL(abs, RTB_ABS, float, f32, RTB_F32)
-V1_UNARY_IMPL(abs, RTB_ABS, double, f64, RTB_F64)
-V1_UNARY_IMPL(sign, RTB_SIGN, float, f32, RTB_F32)
-V1_UNARY_IMPL(sign, RTB_SIGN, double, f64, RTB_F64)
+#define V1_FLOAT_UNARY(OPNAME, OPCODE)                                                                            \
+    V1_UNARY_IMPL(OPNAME, OPCODE, float, f32, RTB_F32)                                                            \
+    V1_UNARY_IMPL(OPNAME, OPCODE, double, f64, RTB_F64)
+V1_FLOAT_UNARY(abs, RTB_ABS) V1_FLOAT_UNARY(sign, RTB_SIGN) V1_FLOAT_UNARY(sigmoid, RTB_SIGMOID)
+V1_FLOAT_UNARY(tanh, RTB_TANH) V1_FLOAT_UNARY(sqrt, RTB_SQRT) V1_FLOAT_UNARY(sin, RTB_SIN) V1_FLOAT_UNARY(cos, RTB_COS)
+V1_FLOAT_UNARY(tan, RTB_TAN) V1_FLOAT_UNARY(asin, RTB_ASIN) V1_FLOAT_UNARY(acos, RTB_ACOS) V1_FLOAT_UNARY(atan, RTB_ATAN)
+V1_FLOAT_UNARY(sinh, RTB_SINH) V1_FLOAT_UNARY(cosh, RTB_COSH) V1_FLOAT_UNARY(asinh, RTB_ASINH)
+V1_FLOAT_UNARY(acosh, RTB_ACOSH) V1_FLOAT_UNARY(atanh, RTB_ATANH) V1_FLOAT_UNARY(rsqrt, RTB_RSQRT)
+V1_FLOAT_UNARY(reciprocal, RTB_RECIPROCAL) V1_FLOAT_UNARY(square, RTB_SQUARE) V1_FLOAT_UNARY(cube, RTB_CUBE)
+V1_FLOAT_UNARY(exp, RTB_EXP) V1_FLOAT_UNARY(ln, RTB_LN) V1_FLOAT_UNARY(ln1p, RTB_LN1P) V1_FLOAT_UNARY(floor, RTB_FLOOR)
+V1_FLOAT_UNARY(ceil, RTB_CEIL) V1_FLOAT_UNARY(round, RTB_ROUND) V1_FLOAT_UNARY(trunc, RTB_TRUNC)
+V1_FLOAT_UNARY(expm1, RTB_EXPM1) V1_FLOAT_UNARY(silu, RTB_SILU)
+
+V1_SCALAR_IMPL(log, RTB_LOG, float, f32, RTB_F32) V1_SCALAR_IMPL(log, RTB_LOG, double, f64, RTB_F64)
+V1_SCALAR_IMPL(log1p, RTB_LOG1P, float, f32, RTB_F32) V1_SCALAR_IMPL(log1p, RTB_LOG1P, double, f64, RTB_F64)
+V1_SCALAR_IMPL(elu, RTB_ELU, float, f32, RTB_F32) V1_SCALAR_IMPL(elu, RTB_ELU, double, f64, RTB_F64)
 
 #define V1_REDUCE_IMPL(TYPE, S, DT)                                                                               \
     RTB_API void launch_flat_contiguous_reduce_##S(const TYPE *data, TYPE *out, size_t start, size_t len,         \

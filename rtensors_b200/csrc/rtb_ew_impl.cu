@@ -136,6 +136,62 @@ template <int OP> struct FUnary { __device__ __forceinline__ T operator()(T a, T
 struct FFill { T v; __device__ __forceinline__ T operator()(T, T) const { return v; } };
 struct FCopy { __device__ __forceinline__ T operator()(T a, T) const { return a; } };
 
+// Extended families with a run-time op code (one instantiation each; the switch is noise next to
+// the transcendental it selects).  Formulas are the reference CPU backend's, not libm shortcuts
+// (src/backend/cpu.rs:485-724): tanh / sinh / cosh from exp(x) and exp(-x), asinh / acosh / atanh
+// from ln and sqrt, sigmoid = 1 / (1 + exp(-x)), silu = x * sigmoid(x), cube = (x*x)*x,
+// log(base) = ln(x) / ln(base), log1p(base) = ln_1p(x) / ln(base), elu = x >= 0 ? x : alpha * expm1(x),
+// leaky_relu = x > 0 ? x : x * slope.
+#if RTB_KIND == 2
+__device__ __forceinline__ T una_ext(int op, T x) {
+    const T one = (T)1;
+    switch (op) {
+        case RTB_SIGMOID: return one / (one + exp(-x));
+        case RTB_SILU: return x * (one / (one + exp(-x)));
+        case RTB_TANH: { T a = exp(x), b = exp(-x); return (a - b) / (a + b); }
+        case RTB_SINH: { T a = exp(x), b = exp(-x); return (a - b) / (one + one); }
+        case RTB_COSH: { T a = exp(x), b = exp(-x); return (a + b) / (one + one); }
+        case RTB_ASINH: return log(x + sqrt(x * x + one));
+        case RTB_ACOSH: return log(x + sqrt(x * x - one));
+        case RTB_ATANH: return log((one + x) / (one - x)) / (one + one);
+        case RTB_SQRT: return sqrt(x);
+        case RTB_RSQRT: return one / sqrt(x);
+        case RTB_RECIPROCAL: return one / x;
+        case RTB_SQUARE: return x * x;
+        case RTB_CUBE: return x * x * x;
+        case RTB_EXP: return exp(x);
+        case RTB_EXPM1: return expm1(x);
+        case RTB_LN: return log(x);
+        case RTB_LN1P: return log1p(x);
+        case RTB_SIN: return sin(x);
+        case RTB_COS: return cos(x);
+        case RTB_TAN: return tan(x);
+        case RTB_ASIN: return asin(x);
+        case RTB_ACOS: return acos(x);
+        case RTB_ATAN: return atan(x);
+        case RTB_FLOOR: return floor(x);
+        case RTB_CEIL: return ceil(x);
+        case RTB_ROUND: return round(x);  // half away from zero, as Rust's f32::round
+        case RTB_TRUNC: return trunc(x);
+    }
+    return x;
+}
+struct FUnaryRt { int op; __device__ __forceinline__ T operator()(T a, T) const { return una_ext(op, a); } };
+#endif
+
+struct FScalarRt {
+    int op;
+    T v;
+    __device__ __forceinline__ T operator()(T x, T) const {
+#if RTB_KIND == 2
+        if (op == RTB_LOG) return log(x) / log(v);
+        if (op == RTB_LOG1P) return log1p(x) / log(v);
+        if (op == RTB_ELU) return x >= (T)0 ? x : v * expm1(x);
+#endif
+        return x > (T)0 ? x : bin<RTB_MUL>(x, v);  // leaky_relu
+    }
+};
+
 // ---- flat kernel -------------------------------------------------------------------------------
 constexpr int kBlock = 256;
 constexpr int kUnroll = 4;
@@ -444,6 +500,13 @@ int launch_scalar(Ctx *ctx, const EwCall &c, const rtb_plan &plan, T v) {
 #else
             return launch<FScalar<RTB_DIV>, 1>(ctx, c, plan, FScalar<RTB_DIV>{v});
 #endif
+        case RTB_LEAKY_RELU: return launch<FScalarRt, 1>(ctx, c, plan, FScalarRt{c.op, v});
+        case RTB_LOG: case RTB_LOG1P: case RTB_ELU:
+#if RTB_KIND == 2
+            return launch<FScalarRt, 1>(ctx, c, plan, FScalarRt{c.op, v});
+#else
+            return fail(RTB_ERR_DTYPE, "log / log1p / elu are defined for f32 and f64 only");
+#endif
     }
     return fail(RTB_ERR_INVALID, "unknown scalar op %d", c.op);
 }
@@ -463,6 +526,13 @@ int launch_unary(Ctx *ctx, const EwCall &c, const rtb_plan &plan) {
             return fail(RTB_ERR_DTYPE, "sign is not defined for boolean tensors");
 #else
             return launch<FUnary<RTB_SIGN>, 1>(ctx, c, plan, FUnary<RTB_SIGN>{});
+#endif
+    }
+    if (c.op >= RTB_SIGMOID && c.op <= RTB_SILU) {
+#if RTB_KIND == 2
+        return launch<FUnaryRt, 1>(ctx, c, plan, FUnaryRt{c.op});
+#else
+        return fail(RTB_ERR_DTYPE, "unary op %d is defined for f32 and f64 only", c.op);
 #endif
     }
     return fail(RTB_ERR_INVALID, "unknown unary op %d", c.op);

@@ -271,4 +271,38 @@ CASES = [
          layout="1d", definition=[-0.125, 0.5, -0.25], op="sign", truth="signum"),
     dict(name="unary_sign_nd_strided", cite="ops/unary/mod.rs:960-962", kind="unary_fixture", dtype="f64",
          layout="nd", definition=[0.5] * 16, op="sign", truth="signum"),
+    # ---------------------------------------------------------------- remaining float unary families
+    # Same three-layout fixtures; the reference compares with eps_eq at TEST_TOLERANCE = 1e-5
+    # (testing/mod.rs:97-195, core/value.rs:496-497), the truth being a Rust std function.
 ]
+
+
+def _ext(name, op, truth, c2, c3, c16, lines):
+    out = []
+    for layout, d, ln in (("contiguous", c2, lines[0]), ("1d", c3, lines[1]), ("nd", c16, lines[2])):
+        out.append(dict(name=f"unary_{name}_{layout}", cite=f"ops/unary/mod.rs:{ln}", kind="unary_fixture", dtype="f64",
+                        layout=layout, definition=list(d), op=op, truth=truth, tol=1e-5))
+    return out
+
+
+CASES += _ext("sigmoid", "sigmoid", "sigmoid", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("453-459", "462-468", "471-477"))
+CASES += _ext("silu", "silu", "silu", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("480-486", "489-495", "498-504"))
+CASES += _ext("tanh", "tanh", "tanh", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("507-513", "516-522", "525-531"))
+CASES += _ext("sqrt", "sqrt", "sqrt", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("534-536", "539-545", "534-536"))
+CASES += _ext("ln", "ln", "ln", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("553-555", "558-564", "553-555"))
+CASES += _ext("sin", "sin", "sin", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("705-707", "710-714", "716-718"))
+CASES += _ext("cos", "cos", "cos", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("721-723", "726-729", "731-733"))
+CASES += _ext("tan", "tan", "tan", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("736-738", "741-744", "746-748"))
+CASES += _ext("asin", "asin", "asin", [0.5, 0.5], [0.5] * 3, [0.5] * 16, ("752-754", "757-760", "762-764"))
+CASES += _ext("acos", "acos", "acos", [0.5, 0.5], [0.5] * 3, [0.5] * 16, ("767-769", "772-775", "777-779"))
+CASES += _ext("atan", "atan", "atan", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("782-784", "787-790", "792-794"))
+CASES += _ext("sinh", "sinh", "sinh", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("798-800", "803-806", "808-810"))
+CASES += _ext("cosh", "cosh", "cosh", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("813-815", "818-821", "823-825"))
+CASES += _ext("asinh", "asinh", "asinh", [1.0, 1.0], [0.5] * 3, [0.5] * 16, ("829-831", "834-837", "839-841"))
+CASES += _ext("acosh", "acosh", "acosh", [1.0, 1.0], [1.0] * 3, [1.0] * 16, ("844-846", "849-852", "854-856"))
+CASES += _ext("atanh", "atanh", "atanh", [0.5, 0.25], [0.5] * 3, [0.5] * 16, ("859-861", "864-867", "869-871"))
+CASES += _ext("rsqrt", "rsqrt", "rsqrt", [0.5, 0.25], [0.5] * 3, [0.5] * 16, ("875-877", "880-883", "885-887"))
+CASES += _ext("reciprocal", "reciprocal", "reciprocal", [0.5, 0.25], [0.5] * 3, [0.5] * 16, ("890-892", "895-898", "900-902"))
+CASES += _ext("square", "square", "square", [0.5, 0.25], [0.5] * 3, [0.5] * 16, ("905-907", "910-913", "915-917"))
+CASES += _ext("cube", "cube", "cube", [0.5, 0.25], [0.5] * 3, [0.5] * 16, ("920-922", "925-928", "930-932"))
+CASES += _ext("exp", "exp", "exp", [0.5, 0.25], [0.125, 0.5, 0.25], [0.5] * 16, ("935-937", "940-942", "945-947"))

@@ -11,7 +11,18 @@ import numpy as np
 NP = {"f32": np.float32, "f64": np.float64, "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
       "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "bool": np.bool_}
 BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
-UN = {"neg": 0, "relu": 1, "abs": 2, "sign": 3}
+UN = {n: i for i, n in enumerate(
+    ["neg", "relu", "abs", "sign", "sigmoid", "tanh", "sqrt", "sin", "cos", "tan", "asin", "acos", "atan", "sinh", "cosh",
+     "asinh", "acosh", "atanh", "rsqrt", "reciprocal", "square", "cube", "exp", "ln", "ln1p", "floor", "ceil", "round",
+     "trunc", "expm1", "silu"])}
+TRUTH = {
+    "neg": lambda x: -x, "max0": lambda x: np.maximum(x, 0.0), "signum": np.sign,
+    "sigmoid": lambda x: 1.0 / (1.0 + np.exp(-x)), "silu": lambda x: x / (1.0 + np.exp(-x)), "tanh": np.tanh,
+    "sqrt": np.sqrt, "ln": np.log, "sin": np.sin, "cos": np.cos, "tan": np.tan, "asin": np.arcsin, "acos": np.arccos,
+    "atan": np.arctan, "sinh": np.sinh, "cosh": np.cosh, "asinh": np.arcsinh, "acosh": np.arccosh, "atanh": np.arctanh,
+    "rsqrt": lambda x: 1.0 / np.sqrt(x), "reciprocal": lambda x: 1.0 / x, "square": lambda x: x * x,
+    "cube": lambda x: x * x * x, "exp": np.exp,
+}
 RED = {"sum": 1, "prod": 2, "max": 3, "min": 4, "mean": 5}
 
 
@@ -119,7 +130,7 @@ def run_case(case, engine):
             meta = engine.Meta.contiguous((3, 1)).slice(0, None, None, 2)
         else:
             meta = engine.Meta.contiguous((4, 4, 1)).slice(0, None, None, 2).slice(1, None, None, 2)
-        truth = {"neg": lambda x: -x, "max0": lambda x: np.maximum(x, 0.0), "signum": np.sign}[case["truth"]]
+        truth = TRUTH[case["truth"]]
         view = np.lib.stride_tricks.as_strided(d[meta.offset:], shape=meta.shape,
                                                strides=[s * d.itemsize for s in meta.strides])
         exp = d.copy()
@@ -127,7 +138,10 @@ def run_case(case, engine):
                                                strides=[s * d.itemsize for s in meta.strides])
         expv[...] = truth(view)
         got = engine.unary_assign(d.copy(), meta, UN[case["op"]])
-        assert np.array_equal(got, exp), (case["name"], got, exp)
+        if "tol" in case:  # eps_eq of the reference: |a - b| < tolerance
+            assert np.all(np.abs(got - exp) < case["tol"]), (case["name"], got, exp)
+        else:
+            assert np.array_equal(got, exp), (case["name"], got, exp)
     else:
         raise ValueError(kind)
 

@@ -653,3 +653,83 @@ def test_host_pipeline_matches_oracle():
         O.scalar_op(ref, op, v, m)
     assert ra.numpy().tobytes() == ref.tobytes()
     assert np.array_equal(ri.numpy(), hi.numpy() + hj.numpy())
+
+
+# ------------------------------------------------------------------------------------- remaining float families
+_EXT_DOMAIN = {"SQRT": (0.01, 4), "RSQRT": (0.01, 4), "LN": (0.01, 4), "LN1P": (-0.9, 4), "ASIN": (-0.99, 0.99),
+               "ACOS": (-0.99, 0.99), "ACOSH": (1.01, 5), "ATANH": (-0.99, 0.99), "RECIPROCAL": (0.05, 4)}
+
+
+@pytest.mark.parametrize("dt,tol", [(np.float32, 2e-6), (np.float64, 1e-14)], ids=["f32", "f64"])
+def test_remaining_unary_families_match_cpu_formulas(dt, tol):
+    """The CUDA math library and glibc round transcendentals differently, so these are compared at
+    a relative tolerance (the reference's own tests use |a-b| < 1e-5); the formulas are the CPU
+    backend's (exp-based tanh, ln/sqrt-based asinh, ...), checked on all three layouts."""
+    rng = np.random.default_rng(17)
+    base = O.Meta.contiguous((37, 24))
+    views = [base, base.slice(1, None, None, -2), base.permute((1, 0)).slice(0, 2, 20, 3)]
+    names = ["SIGMOID", "TANH", "SQRT", "SIN", "COS", "TAN", "ASIN", "ACOS", "ATAN", "SINH", "COSH", "ASINH", "ACOSH",
+             "ATANH", "RSQRT", "RECIPROCAL", "SQUARE", "CUBE", "EXP", "LN", "LN1P", "FLOOR", "CEIL", "ROUND", "TRUNC",
+             "EXPM1", "SILU"]
+    for name in names:
+        lo, hi = _EXT_DOMAIN.get(name, (-3, 3))
+        for m in views:
+            buf = rng.uniform(lo, hi, base.size).astype(dt)
+            if name in ("FLOOR", "CEIL", "ROUND", "TRUNC"):
+                buf[:8] = [0.5, -0.5, 1.5, -1.5, 2.5, -2.5, 0.0, -0.0]
+            ref = buf.copy()
+            O.unary_op(ref, getattr(O, name), m)
+            d = _dev(buf)
+            _b().apply_unary(d, getattr(O, name), _meta_pair(m))
+            got = _host(d)
+            if name in ("FLOOR", "CEIL", "ROUND", "TRUNC", "SQUARE", "CUBE", "RECIPROCAL", "SQRT"):
+                assert got.tobytes() == ref.tobytes(), name  # single IEEE ops: exact
+            else:
+                assert np.allclose(got, ref, rtol=tol * 8, atol=tol), (name, np.abs(got - ref).max())
+
+
+def test_remaining_scalar_families():
+    rng = np.random.default_rng(18)
+    m = O.Meta.contiguous((50, 100)).slice(1, None, None, -2).slice(0, 3, None, -1)
+    for dt, tol in ((np.float32, 2e-6), (np.float64, 1e-14)):
+        for op, v, lo in ((O.LOG, 2.0, 0.01), (O.LOG1P, 10.0, -0.9), (O.LEAKY_RELU, 0.1, -3), (O.ELU, 1.5, -3)):
+            buf = rng.uniform(lo, 3, 5000).astype(dt)
+            ref = buf.copy()
+            O.scalar_op(ref, op, v, m)
+            d = _dev(buf)
+            _b().scalar_apply(d, op, v, _meta_pair(m))
+            if op == O.LEAKY_RELU:
+                assert _host(d).tobytes() == ref.tobytes()
+            else:
+                assert np.allclose(_host(d), ref, rtol=tol * 8, atol=tol), op
+    # leaky_relu exists for integer types too (wrapping multiply on the negative side)
+    for dt in (np.int32, np.int8, np.uint16):
+        buf = _rand(rng, 5000, dt)
+        ref = buf.copy()
+        O.scalar_op(ref, O.LEAKY_RELU, 3, m)
+        d = _dev(buf)
+        _b().scalar_apply(d, O.LEAKY_RELU, 3, _meta_pair(m))
+        assert _host(d).tobytes() == ref.tobytes()
+    with pytest.raises(Exception):
+        _b().scalar_apply(_dev(np.zeros(4, np.int32)), O.ELU, 1, _meta_pair(O.Meta.contiguous((4,))))
+    with pytest.raises(Exception):
+        _b().apply_unary(_dev(np.zeros(4, np.int32)), O.EXP, _meta_pair(O.Meta.contiguous((4,))))
+
+
+def test_sign_dense_reversed_view_is_walked_from_its_lowest_address():
+    """A fully reversed view counts as contiguous in the reference, whose dispatcher then walks
+    forward from the view's offset and runs out of bounds (the Rust slice index panics; the oracle
+    refuses).  The library applies the op to exactly the viewed elements."""
+    x = np.arange(12, dtype=np.float32)
+    m = O.Meta.contiguous((3, 4)).slice(0, None, None, -1).slice(1, None, None, -1)
+    assert m.is_contiguous() and m.offset == 11
+    with pytest.raises(O.OracleError):
+        O.scalar_op(x.copy(), O.ADD, 1.0, m)
+    d = _dev(x)
+    _b().scalar_apply(d, O.ADD, 1.0, _meta_pair(m))
+    assert np.array_equal(_host(d), x + 1)
+    sub = O.Meta.contiguous((12,)).slice(0, 7, None, -1)  # elements 7..0 reversed
+    d = _dev(x)
+    _b().scalar_apply(d, O.MUL, 2.0, _meta_pair(sub))
+    want = x.copy(); want[:8] *= 2
+    assert np.array_equal(_host(d), want)
