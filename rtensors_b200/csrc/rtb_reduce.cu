@@ -23,6 +23,13 @@ constexpr int kWarps = kBlock / 32;
 constexpr size_t kTileCounterOffset = 64;      // in counters
 constexpr size_t kMaxTileCounters = 16384 - 64;
 constexpr size_t kWorkspaceHeader = 65536;     // bytes
+// Resident CTAs per SM for the streaming reductions.  Measured on B200 with a read-only probe:
+// 7.29 TB/s at 4 CTAs of 256 threads per SM, 7.14 at 8, 6.97 at 16 -- fewer concurrent streams keep
+// DRAM pages open longer -- so the flat reduction runs a persistent grid of 4 CTAs per SM.
+constexpr unsigned kStreamCtasPerSm = 4;
+// The axis kernels end every item with a block-wide barrier; they run one CTA per item (measured
+// faster than a persistent grid), bounded only by the 2^31 grid limit: 2^31 / 256 SMs.
+constexpr unsigned kAxisGridCap = 1u << 22;
 
 template <typename T> struct Limits;
 template <> struct Limits<float> {
@@ -203,142 +210,170 @@ __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t
     constexpr int N = VecOf<T>::N;
     constexpr int rows_per_block = kBlock / GROUP;
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
-    const size_t item = (size_t)blockIdx.x * rows_per_block + g;  // (row, chunk)
-    const size_t row = item / split, chunk = item % split;
-    const bool live = row < rows;
-    T acc[4];
+    const size_t items = rows * split;
+    const size_t per = (R + split - 1) / split;
+    // persistent: a CTA walks items b, b + grid, ... (the grid is capped at a few CTAs per SM)
+    for (size_t first = (size_t)blockIdx.x * rows_per_block; first < items; first += (size_t)gridDim.x * rows_per_block) {
+        const size_t item = first + g;  // (row, chunk)
+        const bool live = item < items;
+        T acc[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::identity();
-    if (live) {
-        const size_t per = (R + split - 1) / split;
-        const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
-        const T *p = src + row * R;
-        // vector body over the 16-byte aligned part of [k0, k1)
-        size_t a0 = k0 + (((16u - (unsigned)((uintptr_t)(p + k0) & 15u)) & 15u) / sizeof(T));
-        if (a0 > k1) a0 = k1;
-        const size_t nvec = (k1 - a0) / N;
-        const uint4 *pv = reinterpret_cast<const uint4 *>(p + a0);
-        size_t i = t;
-        for (; i + 3 * GROUP < nvec; i += 4 * GROUP) {
-            typename VecOf<T>::U v[4];
+        for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::identity();
+        if (live) {
+            const size_t row = item / split, chunk = item % split;
+            const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+            const T *p = src + row * R;
+            // vector body over the 16-byte aligned part of [k0, k1)
+            size_t a0 = k0 + (((16u - (unsigned)((uintptr_t)(p + k0) & 15u)) & 15u) / sizeof(T));
+            if (a0 > k1) a0 = k1;
+            const size_t nvec = (k1 - a0) / N;
+            const uint4 *pv = reinterpret_cast<const uint4 *>(p + a0);
+            size_t i = t;
+            for (; i + 7 * GROUP < nvec; i += 8 * GROUP) {  // eight 16-byte loads in flight per thread
+                typename VecOf<T>::U v[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u].q = pv[i + u * GROUP];
+                for (int u = 0; u < 8; ++u) v[u].q = pv[i + u * GROUP];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+                for (int u = 0; u < 8; ++u)
 #pragma unroll
-                for (int j = 0; j < N; ++j) acc[u] = Comb<T, OP>::apply(acc[u], v[u].e[j]);
+                    for (int j = 0; j < N; ++j) acc[u & 3] = Comb<T, OP>::apply(acc[u & 3], v[u].e[j]);
+            }
+            for (; i + 3 * GROUP < nvec; i += 4 * GROUP) {
+                typename VecOf<T>::U v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u].q = pv[i + u * GROUP];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[u] = Comb<T, OP>::apply(acc[u], v[u].e[j]);
+            }
+            for (; i < nvec; i += GROUP) {
+                typename VecOf<T>::U v;
+                v.q = pv[i];
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc[0] = Comb<T, OP>::apply(acc[0], v.e[j]);
+            }
+            for (size_t k = k0 + t; k < a0; k += GROUP) acc[1] = Comb<T, OP>::apply(acc[1], p[k]);
+            for (size_t k = a0 + nvec * N + t; k < k1; k += GROUP) acc[2] = Comb<T, OP>::apply(acc[2], p[k]);
         }
-        for (; i < nvec; i += GROUP) {
-            typename VecOf<T>::U v;
-            v.q = pv[i];
-#pragma unroll
-            for (int j = 0; j < N; ++j) acc[0] = Comb<T, OP>::apply(acc[0], v.e[j]);
+        T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
+        if (GROUP == 32) {
+            v = warp_reduce<T, OP>(v);
+        } else {
+            v = block_reduce<T, OP>(v, smem);
         }
-        for (size_t k = k0 + t; k < a0; k += GROUP) acc[1] = Comb<T, OP>::apply(acc[1], p[k]);
-        for (size_t k = a0 + nvec * N + t; k < k1; k += GROUP) acc[2] = Comb<T, OP>::apply(acc[2], p[k]);
+        if (t == 0 && live) dst[item] = split == 1 ? finish(v, mean, count) : v;
     }
-    T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
-    if (GROUP == 32) {
-        v = warp_reduce<T, OP>(v);
-    } else {
-        v = block_reduce<T, OP>(v, smem);
-    }
-    if (t == 0 && live) dst[item] = split == 1 ? finish(v, mean, count) : v;
 }
 
 // ---- outer axis (inner > 1): src is [outer, R, inner]; threads run along inner ---------------------
-// CTA = 32 lanes along inner (VW columns each) x 8 lanes along R.  `split` cuts R into chunks, one
-// CTA each.  With split > 1 every CTA stores its partial row, and the last CTA of a column tile to
+// CTA = TX lanes along inner (VW columns each) x TY = 256/TX lanes along R (TX = 32 in use).
+// `split` cuts R into chunks, one CTA each.  With split > 1 every CTA stores its partial row, and the last CTA of a column tile to
 // finish (per-tile completion counter) folds the `split` partial rows in chunk order -- one launch,
 // and the fold order does not depend on which CTA came last.
-template <typename T, int OP, int VW>
+template <typename T, int OP, int VW, int TY>
 __device__ __forceinline__ void col_accumulate(const T *p, size_t row_stride, size_t k0, size_t k1, int ly, T acc[VW]) {
+    constexpr int B = 8;  // rows in flight per thread
     size_t k = k0 + ly;
     if (VW > 1) {
-        for (; k + 24 < k1; k += 32) {
-            typename VecOf<T>::U v[4];
+        for (; k + (B - 1) * TY < k1; k += B * TY) {
+            typename VecOf<T>::U v[B];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + 8 * u) * row_stride);
+            for (int u = 0; u < B; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + TY * u) * row_stride);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < B; ++u)
 #pragma unroll
                 for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v[u].e[j]);
         }
-        for (; k < k1; k += 8) {
+        for (; k < k1; k += TY) {
             typename VecOf<T>::U v;
             v.q = *reinterpret_cast<const uint4 *>(p + k * row_stride);
 #pragma unroll
             for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
         }
     } else {
-        for (; k + 24 < k1; k += 32) {
-            T v[4];
+        for (; k + (B - 1) * TY < k1; k += B * TY) {
+            T v[B];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = p[(k + 8 * u) * row_stride];
+            for (int u = 0; u < B; ++u) v[u] = p[(k + TY * u) * row_stride];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
+            for (int u = 0; u < B; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
         }
-        for (; k < k1; k += 8) acc[0] = Comb<T, OP>::apply(acc[0], p[k * row_stride]);
+        for (; k < k1; k += TY) acc[0] = Comb<T, OP>::apply(acc[0], p[k * row_stride]);
     }
 }
 
-template <typename T, int OP, int VW>
+// TY partial rows of the tile (in shared memory) -> 1; thread c owns column c
+template <typename T, int OP, int TW, int TY>
+__device__ __forceinline__ T col_combine(const T (*smem)[TW + 1], int c) {
+    T v = smem[0][c];
+#pragma unroll
+    for (int y = 1; y < TY; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
+    return v;
+}
+
+template <typename T, int OP, int VW, int TX>
 __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t outer, size_t R, size_t inner,
                                                             size_t split, size_t col_tiles, T *partial,
                                                             unsigned int *counters, T *dst, int mean, size_t count) {
-    __shared__ T smem[8][32 * VW + 1];
+    constexpr int TY = kBlock / TX;
+    constexpr int TW = TX * VW;  // columns per tile
+    __shared__ T smem[TY][TW + 1];
     __shared__ bool is_last;
-    const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
-    size_t b = blockIdx.x;
-    // neighbouring CTAs read neighbouring column tiles of the same rows (DRAM page locality)
-    const size_t tile = b % col_tiles; b /= col_tiles;
-    const size_t chunk = b % split;
-    const size_t o = b / split;
-    const size_t col = (tile * 32 + lx) * VW;
+    const int lx = threadIdx.x % TX, ly = threadIdx.x / TX;
+    const size_t items = outer * split * col_tiles;
     const size_t per = (R + split - 1) / split;
-    const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
-    T acc[VW];
+    // a CTA walks items b, b + grid, ... (normally one); neighbouring CTAs read neighbouring column
+    // tiles of the same rows
+    for (size_t b = blockIdx.x; b < items; b += gridDim.x) {
+        size_t q = b;
+        const size_t tile = q % col_tiles; q /= col_tiles;
+        const size_t chunk = q % split;
+        const size_t o = q / split;
+        const size_t col = (tile * TX + lx) * VW;
+        const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+        T acc[VW];
 #pragma unroll
-    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-    if (col < inner && k0 < k1) col_accumulate<T, OP, VW>(src + (o * R) * inner + col, inner, k0, k1, ly, acc);
+        for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
+        if (col < inner && k0 < k1) col_accumulate<T, OP, VW, TY>(src + (o * R) * inner + col, inner, k0, k1, ly, acc);
 #pragma unroll
-    for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
-    __syncthreads();
-    // 8 partial rows -> 1: thread c owns column c of the tile
-    for (int c = threadIdx.x; c < 32 * VW; c += kBlock) {
-        T v = smem[0][c];
-#pragma unroll
-        for (int y = 1; y < 8; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
-        const size_t gc = tile * 32 * VW + c;
-        if (gc < inner) {
-            if (split == 1) dst[o * inner + gc] = finish(v, mean, count);
-            else partial[(o * split + chunk) * inner + gc] = v;
+        for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
+        __syncthreads();
+        for (int c = threadIdx.x; c < TW; c += kBlock) {
+            T v = col_combine<T, OP, TW, TY>(smem, c);
+            const size_t gc = tile * TW + c;
+            if (gc < inner) {
+                if (split == 1) dst[o * inner + gc] = finish(v, mean, count);
+                else partial[(o * split + chunk) * inner + gc] = v;
+            }
         }
-    }
-    if (split == 1) return;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned int done = atomicAdd(counters + o * col_tiles + tile, 1u);
-        is_last = done == (unsigned int)split - 1u;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
+        if (split == 1) {
+            __syncthreads();  // smem is reused by the next item
+            continue;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int done = atomicAdd(counters + o * col_tiles + tile, 1u);
+            is_last = done == (unsigned int)split - 1u;
+        }
+        __syncthreads();
+        if (!is_last) continue;  // uniform per CTA
+        __threadfence();
 #pragma unroll
-    for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-    if (col < inner) col_accumulate<T, OP, VW>(partial + (o * split) * inner + col, inner, 0, split, ly, acc);
+        for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
+        if (col < inner) col_accumulate<T, OP, VW, TY>(partial + (o * split) * inner + col, inner, 0, split, ly, acc);
 #pragma unroll
-    for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
-    __syncthreads();
-    for (int c = threadIdx.x; c < 32 * VW; c += kBlock) {
-        T v = smem[0][c];
-#pragma unroll
-        for (int y = 1; y < 8; ++y) v = Comb<T, OP>::apply(v, smem[y][c]);
-        const size_t gc = tile * 32 * VW + c;
-        if (gc < inner) dst[o * inner + gc] = finish(v, mean, count);
+        for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
+        __syncthreads();
+        for (int c = threadIdx.x; c < TW; c += kBlock) {
+            T v = col_combine<T, OP, TW, TY>(smem, c);
+            const size_t gc = tile * TW + c;
+            if (gc < inner) dst[o * inner + gc] = finish(v, mean, count);
+        }
+        if (threadIdx.x == 0) counters[o * col_tiles + tile] = 0;  // ready for the next launch
+        __syncthreads();
     }
-    if (threadIdx.x == 0) counters[o * col_tiles + tile] = 0;  // ready for the next launch
 }
 
 // ---- fused MLP pieces ----------------------------------------------------------------------------
@@ -404,7 +439,7 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
     // one CTA per 4 KiB-vector-iterations, capped at 4 CTAs per SM: a read-bandwidth probe on B200 gives
     // 7.29 TB/s at 4 CTAs/SM, 7.14 at 8 and 6.97 at 16 (fewer concurrent streams, better DRAM locality)
     size_t items = (n / N + (size_t)kBlock * 4 - 1) / ((size_t)kBlock * 4);
-    unsigned grid = grid_for(ctx, items, 4);
+    unsigned grid = grid_for(ctx, items, kStreamCtasPerSm);
     void *ws = nullptr;
     int rc = workspace(ctx, (size_t)grid * sizeof(T), &ws);
     if (rc != RTB_OK) return rc;
@@ -446,38 +481,34 @@ int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean)
     }
     const size_t items = rows * split;
     const size_t chunk_len = (R + split - 1) / split;
+    // One CTA (or warp) per row.  A persistent grid of 4 CTAs/SM was measured and is slower here
+    // (8192x8192 axis 1: 5.9 vs 6.3 TB/s): every row ends in a block-wide tree reduction, and with few
+    // resident CTAs nothing hides that barrier.  The kernel still loops, so any grid size is legal.
     if (chunk_len >= 1024) {
-        if (items >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "too many rows for one launch");
-        row_reduce_kernel<T, OP, kBlock><<<(unsigned)items, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+        unsigned grid = grid_for(ctx, items, kAxisGridCap);
+        row_reduce_kernel<T, OP, kBlock><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
     } else {
-        size_t blocks = (items + kWarps - 1) / kWarps;
-        if (blocks >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "too many rows for one launch");
-        row_reduce_kernel<T, OP, 32><<<(unsigned)blocks, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+        unsigned grid = grid_for(ctx, (items + kWarps - 1) / kWarps, kAxisGridCap);
+        row_reduce_kernel<T, OP, 32><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
     }
     int rc = check_launch(ctx, "row_reduce_kernel");
     if (rc != RTB_OK || split == 1) return rc;
-    size_t blocks = (rows + kWarps - 1) / kWarps;
-    row_reduce_kernel<T, OP, 32><<<(unsigned)blocks, kBlock, 0, ctx->stream>>>(target, rows, split, 1, dst, mean, R);
+    unsigned fold_grid = grid_for(ctx, (rows + kWarps - 1) / kWarps, kAxisGridCap);
+    row_reduce_kernel<T, OP, 32><<<fold_grid, kBlock, 0, ctx->stream>>>(target, rows, split, 1, dst, mean, R);
     return check_launch(ctx, "row_reduce_kernel(fold)");
 }
 
-// Number of R-chunks per column tile.  CTAs do equal work, so the launch takes ceil(waves) rounds
-// of `resident` CTAs: pick the split whose last round is fullest, preferring fewer chunks.
+// Number of R-chunks per column tile.  CTAs do equal work, so a launch that needs slightly more
+// than one wave of resident CTAs takes two rounds.  Measured on B200 (sweep over the split factor,
+// (8192,8192) axis 0 = 64 tiles): the kernel is fastest when all CTAs are resident at once and the
+// wave is nearly full -- 10 chunks (640 CTAs, 740 resident) 5.5 TB/s, 8 chunks 5.2, 12 chunks
+// (768 CTAs, two rounds) 4.0.  So: as many chunks as fit in ONE wave, each at least 64 rows.
 size_t pick_split(size_t base_ctas, size_t resident, size_t max_split) {
     if (max_split < 1) max_split = 1;
-    if (base_ctas >= 4 * resident) return 1;
-    size_t best = 1;
-    double best_eff = 0.0;
-    for (size_t sp = 1; sp <= max_split && base_ctas * sp <= 6 * resident; ++sp) {
-        double waves = (double)(base_ctas * sp) / (double)resident;
-        double rounds = (double)(size_t)((base_ctas * sp + resident - 1) / resident);
-        double eff = waves / rounds;
-        if (eff > best_eff + 0.02) {
-            best_eff = eff;
-            best = sp;
-        }
-    }
-    return best;
+    size_t split = resident / (base_ctas ? base_ctas : 1);
+    if (split < 1) split = 1;
+    if (split > max_split) split = max_split;
+    return split;
 }
 
 template <typename K>
@@ -487,16 +518,13 @@ size_t resident_ctas(Ctx *ctx, K kernel) {
     return (size_t)ctx->sm_count * (size_t)per_sm;
 }
 
-template <typename T, int OP>
-int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
-    constexpr int N = VecOf<T>::N;
-    const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0);
-    const size_t tile_cols = vec ? 32 * N : 32;
+template <typename T, int OP, int VW, int TX>
+int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+    const size_t tile_cols = (size_t)TX * VW;
     const size_t col_tiles = (inner + tile_cols - 1) / tile_cols;
     const size_t base_ctas = outer * col_tiles;
-    const size_t resident = vec ? resident_ctas(ctx, col_reduce_kernel<T, OP, N>) : resident_ctas(ctx, col_reduce_kernel<T, OP, 1>);
     size_t split = 1;
-    if (base_ctas <= kMaxTileCounters) split = pick_split(base_ctas, resident, R / 64);
+    if (base_ctas <= kMaxTileCounters) split = pick_split(base_ctas, resident_ctas(ctx, col_reduce_kernel<T, OP, VW, TX>), R / 64);
     T *partial = nullptr;
     unsigned int *counters = nullptr;
     if (split > 1) {
@@ -506,13 +534,22 @@ int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T 
         counters = reinterpret_cast<unsigned int *>(ws) + kTileCounterOffset;
         partial = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     }
-    size_t grid = base_ctas * split;
-    if (grid >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "axis reduction too large for one launch");
-    if (vec)
-        col_reduce_kernel<T, OP, N><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial, counters, dst, mean, R);
-    else
-        col_reduce_kernel<T, OP, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial, counters, dst, mean, R);
+    const unsigned grid = grid_for(ctx, base_ctas * split, kAxisGridCap);  // one CTA per (tile, chunk)
+    col_reduce_kernel<T, OP, VW, TX><<<grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial,
+                                                                       counters, dst, mean, R);
     return check_launch(ctx, "col_reduce_kernel");
+}
+
+template <typename T, int OP>
+int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+    constexpr int N = VecOf<T>::N;
+    const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0);
+    // TX = 32 (tile = 32 x 128-bit columns, 8 rows in flight per CTA).  A 256-lane tile (whole 4 KiB
+    // row segments per CTA) was measured and is not faster: (64,4096,1024) axis 1 6.50 vs 6.5-6.7 TB/s,
+    // (8192,8192) axis 0 4.72 vs 5.3-5.5 TB/s -- the fold of many chunk partials by one CTA per wide
+    // tile costs more than the longer DRAM bursts gain.
+    if (vec) return cols_launch_t<T, OP, N, 32>(ctx, src, outer, R, inner, dst, mean);
+    return cols_launch_t<T, OP, 1, 32>(ctx, src, outer, R, inner, dst, mean);
 }
 
 template <typename T, int OP>
