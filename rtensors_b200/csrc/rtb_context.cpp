@@ -102,7 +102,7 @@ RTB_API int rtb_ctx_set_stream(rtb_ctx *c, void *stream) {
 RTB_API void *rtb_ctx_get_stream(rtb_ctx *c) { return c ? (void *)C(c)->stream : nullptr; }
 RTB_API int rtb_ctx_device(rtb_ctx *c) { return c ? C(c)->device : -1; }
 RTB_API int rtb_ctx_sm_count(rtb_ctx *c) { return c ? C(c)->sm_count : 0; }
-RTB_API uint64_t rtb_ctx_launch_count(rtb_ctx *c) { return c ? C(c)->launches : 0; }
+RTB_API uint64_t rtb_ctx_launch_count(rtb_ctx *c) { return c ? C(c)->launches.load() : 0; }
 
 RTB_API int rtb_ctx_sync(rtb_ctx *c) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <atomic>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -35,8 +36,11 @@ struct Ctx {
     int sm_count = 0;
     size_t l2_bytes = 0;
     cudaStream_t stream = nullptr;
-    uint64_t launches = 0;
-    // reduction workspace (partials + completion counters), grown on demand
+    std::atomic<uint64_t> launches{0};
+    // reduction workspace (partials + completion counters), grown on demand.  ws_mu serialises the
+    // host threads that enqueue workspace-using kernels on this context: the kernels share the
+    // counters and partial slots and rely on stream order, so their enqueue order must be total.
+    std::mutex ws_mu;
     void *ws = nullptr;
     size_t ws_bytes = 0;
     // caching allocator: free blocks by rounded size; live blocks by pointer
@@ -51,7 +55,7 @@ struct Ctx {
 int workspace(Ctx *ctx, size_t bytes, void **out);
 Ctx *default_ctx();  // ctx on the current device bound to the legacy default stream (ABI v1)
 
-inline void count_launch(Ctx *ctx) { ctx->launches += 1; }
+inline void count_launch(Ctx *ctx) { ctx->launches.fetch_add(1, std::memory_order_relaxed); }
 int check_launch(Ctx *ctx, const char *what);
 
 // ---- planner (host) ----------------------------------------------------------------------------

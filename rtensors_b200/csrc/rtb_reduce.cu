@@ -573,6 +573,7 @@ int axis_by_op(Ctx *ctx, int redop, const T *src, size_t outer, size_t R, size_t
 }  // namespace
 
 int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t len, void *dst) {
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
     if (dtype == RTB_F32) return flat_by_op<float>(ctx, redop, SrcPlain<float>{(const float *)src}, len, (float *)dst);
     if (dtype == RTB_F64) return flat_by_op<double>(ctx, redop, SrcPlain<double>{(const double *)src}, len, (double *)dst);
     return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
@@ -580,6 +581,7 @@ int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t l
 
 int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
                        void *dst) {
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
     if (dtype == RTB_F32) return axis_by_op<float>(ctx, redop, (const float *)src, outer, r, inner, (float *)dst);
     if (dtype == RTB_F64) return axis_by_op<double>(ctx, redop, (const double *)src, outer, r, inner, (double *)dst);
     return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
@@ -593,6 +595,7 @@ static int l1_typed(Ctx *ctx, const T *a, const T *b, size_t n, int reduction, T
 }
 
 int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap) {
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
     if (dtype == RTB_F32) return l1_typed<float>(ctx, (const float *)a, (const float *)b, n, reduction, (float *)loss, (float *)gmap);
     if (dtype == RTB_F64) return l1_typed<double>(ctx, (const double *)a, (const double *)b, n, reduction, (double *)loss, (double *)gmap);
     return fail(RTB_ERR_DTYPE, "l1 loss is defined for f32 and f64 only");

@@ -102,6 +102,22 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     add("tensor_add i32", f"2^{int(np.log2(n2))}", 12 * n2, n2, lambda: be.broadcast((ia, m2), (ib, m2), (io, m2), L.ADD))
     add("fill f32", f"2^{int(np.log2(n2))}", 4 * n2, n2, lambda: be.fill(x, 1.5, m2), note="pure-write probe")
     del ia, ib, io
+    # other element sizes through the same kernels (1-byte and 8-byte lanes of the 128-bit vectors)
+    nb = n2 * 4
+    ua = torch.randint(0, 255, (nb,), device=dev, generator=g, dtype=torch.uint8)
+    ub = torch.randint(0, 255, (nb,), device=dev, generator=g, dtype=torch.uint8)
+    uo = torch.empty_like(ua)
+    mb = Meta.contiguous((nb,))
+    add("tensor_add u8", f"2^{int(np.log2(nb))}", 3 * nb, nb, lambda: be.broadcast((ua, mb), (ub, mb), (uo, mb), L.ADD))
+    del ua, ub, uo
+    xd = torch.rand(n2 // 2, device=dev, generator=g, dtype=torch.float64)
+    md = Meta.contiguous((n2 // 2,))
+    add("scalar_mul f64 in place", f"2^{int(np.log2(n2 // 2))}", 16 * (n2 // 2), n2 // 2,
+        lambda: be.scalar_apply(xd, L.MUL, 1.0001, md))
+    rd = be.alloc(1, torch.float64)
+    add("sum (full) f64", f"2^{int(np.log2(n2 // 2))}", 8 * (n2 // 2) + 8, n2 // 2,
+        lambda: be.apply_reduce_contiguous_flat(xd, rd, 0, n2 // 2, L.SUM))
+    del xd
 
     # ---- config 3: strided / negative-step broadcast add -> (16,64,K,1024)
     K = 64 if quick else 1024

@@ -733,3 +733,44 @@ def test_sign_dense_reversed_view_is_walked_from_its_lowest_address():
     _b().scalar_apply(d, O.MUL, 2.0, _meta_pair(sub))
     want = x.copy(); want[:8] *= 2
     assert np.array_equal(_host(d), want)
+
+
+# ------------------------------------------------------------------------------------- beyond 2^31 elements
+def test_more_than_2_31_elements_u8_and_f32():
+    """64-bit indexing: the reference's flat reduce passes the count as `int`
+    (cuda/kernels/reduction/reduce.cu:239-274); here sizes past 2^31 elements are first-class."""
+    from rtensors_b200.meta import Meta
+    free, _ = torch.cuda.mem_get_info()
+    if free < 24 << 30:
+        pytest.skip("needs 24 GiB of free device memory")
+    n = (1 << 31) + 77
+    x = torch.full((n,), 3, dtype=torch.uint8, device="cuda")
+    x[-1] = 9
+    x[1 << 31] = 5
+    _b().scalar_apply(x, O.ADD, 250, Meta.contiguous((n,)))  # wraps: 3+250 = 253, 9+250 = 3, 5+250 = 255
+    assert int(x[0]) == 253 and int(x[-1]) == 3 and int(x[1 << 31]) == 255 and int(x[(1 << 31) - 1]) == 253
+    assert int((x == 253).sum()) == n - 2
+    # strided view past 2^31: every other element of the upper half, reversed
+    v = Meta.contiguous((n,)).slice(0, n - 1, 1 << 31, -2)
+    _b().scalar_apply(x, O.SUB, 3, v)
+    assert int(x[-1]) == 0 and int(x[-3]) == 250 and int(x[-2]) == 253
+    del x
+    torch.cuda.empty_cache()
+    m = (1 << 31) + 1029
+    y = torch.ones(m, dtype=torch.float32, device="cuda")
+    y[-1] = 1025.0
+    y[(1 << 31) + 3] = -7.0
+    out = _b().alloc(1, torch.float32)
+    _b().apply_reduce_contiguous_flat(y, out, 0, m, O.SUM)
+    want = float(m - 2) + 1025.0 - 7.0
+    assert abs(float(out.item()) - want) <= 1e-5 * 32 * want
+    _b().apply_reduce_contiguous_flat(y, out, 5, m - 5, O.MAX)
+    assert float(out.item()) == 1025.0
+    _b().apply_reduce_contiguous_flat(y, out, 0, m, O.MIN)
+    assert float(out.item()) == -7.0
+    # axis reduction whose total size exceeds 2^31: [2, 2^30 + 515 (rounded), 1]... rows of ~2^30
+    r = m // 2
+    red = _b().reduce_axis_ori(y, 0, 2, r, 1, O.SUM)
+    got = red.cpu().numpy()
+    assert abs(got[0] - float(r)) <= 1e-5 * 31 * r
+    assert abs(got[1] - (float(y[r:2 * r].sum(dtype=torch.float64)))) <= 1e-5 * 31 * r
