@@ -161,7 +161,8 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
             be.apply_reduce_contiguous_flat(src, r0, 0, per, L.SUM)
             dist.all_reduce(r0, op=dist.ReduceOp.SUM)
         add("sum (full) f32, per-GPU partial + NCCL allreduce", f"2^{int(np.log2(nflat))} over {world} GPUs",
-            4 * nflat + 4, nflat, sharded_sum, note="aggregate bytes over all GPUs / this rank's time")
+            4 * nflat + 4, nflat, sharded_sum, note=f"aggregate bytes over all GPUs / this rank's time; frac is of {world} x peak")
+        rows[-1]["frac"] = rows[-1]["gbs"] / (peak_gbs * world)
     nl = (1024 if quick else 4096) ** 2
     ta, tb = src[:nl], src[nl:2 * nl]
     add("mean_l1_loss f32", f"two ({int(nl ** 0.5)},{int(nl ** 0.5)})", 8 * nl + 4, nl,
@@ -184,6 +185,35 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     nw -= nw % 4
     w, gw = src[:nw], src[nw:2 * nw]
     add("sgd_update f32", f"{nw} params", 12 * nw, nw, lambda: be.sgd_update(w, gw, 0.0), flush=True)
+    # ---- multi-GPU (strong scaling of single ops): slab-sharded view broadcast with no collective,
+    # axis sum over the sharded dim with one all-reduce of the partial vector
+    if world > 1:
+        import torch.distributed as dist
+        from . import sharding
+
+        def add_sharded(name, shape, nbytes, elems, fn):
+            med, best = _time(fn)
+            t = torch.tensor([med], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)  # slowest rank
+            med = float(t.item())
+            gbs = nbytes / (med * 1e-3) / 1e9
+            rows.append({"op": name, "shape": shape, "ms": med, "ms_best": best, "gbs": gbs,
+                         "elements_per_s": elems / (med * 1e-3), "frac": gbs / (peak_gbs * world), "bytes": nbytes,
+                         "note": f"aggregate over {world} GPUs / slowest rank's time; frac is of {world} x peak"})
+        slab = sharding.binary_slab(Am, Bm, world, rank)
+        sdm = Meta.contiguous(slab.shape)
+        sout = out3[: sdm.size]
+        add_sharded("broadcast_add f32 permuted A, step -1 B, slab-sharded", f"{shape3} over {world} GPUs",
+                    4 * (dm3.size + K * 16 + 65536), dm3.size,
+                    lambda: be.broadcast((bufa, slab.left), (bufb, slab.right), (sout, sdm), L.ADD))
+        lo, hi = sharding.scalar_slab(S, world, rank)
+        part_rows = src[lo * S: hi * S]
+        add_sharded("sum_at(0) f32, rows sharded + all-reduce of the partial vector", f"({S},{S}) over {world} GPUs",
+                    4 * (S * S + S), S * S,
+                    lambda: sharding.sharded_reduce_axis(be, part_rows, 1, hi - lo, S, L.SUM, "r", S))
+        add_sharded("sum_at(1) f32, rows sharded, no collective", f"({S},{S}) over {world} GPUs", 4 * (S * S + S), S * S,
+                    lambda: sharding.sharded_reduce_axis(be, part_rows, hi - lo, S, 1, L.SUM, "outer", S))
+
     # ---- config 5 as a whole: one SGD step of the 784-1024-1024-10 MLP, global batch 4096 split
     # across the ranks (data parallel: loss all-reduce + one flat gradient bucket all-reduce)
     from .mlp import DenseMlp, synthetic_batch
