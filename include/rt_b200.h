@@ -184,6 +184,16 @@ int rtb_reduce_flat(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t 
 int rtb_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t offset, size_t outer, size_t r,
                     size_t inner, void *dst);
 
+/* ---- reduction over a VIEW (ReductionOp::*_at / TotalReductionOp on a non-contiguous tensor,
+ *      src/ops/reduction/mod.rs:351-360, where the reference first copies the view with
+ *      `contiguous()`).  axis < 0: full reduction into dst[0]; otherwise dst is row-major over the
+ *      view's shape with dim `axis` kept as 1.  Views that are [outer, R, inner] with a contiguous
+ *      inner run under arbitrary outer / R strides (slices, reversed or permuted outer dims,
+ *      transposed matrices) are reduced in place with no copy; any other view is materialised by
+ *      the strided copy kernel into a temporary from the context allocator first.  f32 / f64. ---- */
+int rtb_reduce_view(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
+                    const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst);
+
 /* ---- full reduction without any device allocation.  NO COUNTERPART IN THE REFERENCE (its flat
  *      reduction allocates and frees CUB scratch on every call, cuda/kernels/reduction/reduce.cu:
  *      239-274).  For hosts that must not, or cannot, call cudaMalloc: all device memory already

@@ -199,6 +199,22 @@ class CudaB200:
                                     C.c_size_t(sm.offset), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
                                     self._p(dst)))
 
+    def reduce_view(self, src: torch.Tensor, meta: Meta, axis: Optional[int], op: int) -> torch.Tensor:
+        """Reduction over an arbitrary view without requiring contiguity (rtb_reduce_view); axis
+        None = full reduction.  Returns the row-major result buffer (reduced dim kept as 1)."""
+        meta.check_extent(src.numel())
+        if axis is None:
+            n_out = 1
+        else:
+            n_out = 1
+            for k, s_ in enumerate(meta.shape):
+                n_out *= 1 if k == axis else s_
+        out = self.alloc(max(n_out, 1), src.dtype)
+        check(lib().rtb_reduce_view(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(meta.rank),
+                                    sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset),
+                                    C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
+        return out
+
     def reduce_axis_ori(self, src: torch.Tensor, offset: int, outer: int, r: int, inner: int, op: int):
         out = self.alloc(max(outer * inner, 1), src.dtype)
         check(lib().rtb_reduce_axis(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(offset),

@@ -169,6 +169,96 @@ RTB_API int rtb_reduce_axis(rtb_ctx *c, int dtype, int redop, const void *src, s
     return launch_reduce_axis(C(c), dtype, redop, (const char *)src + offset * es, outer, r, inner, dst);
 }
 
+namespace {
+
+// Collapses dims [lo, hi) of a view into one (extent, stride) if every neighbouring pair is walked
+// as one run; size-1 dims are ignored.  An empty / all-ones group collapses to (1, 0).
+bool collapse_group(const size_t *shape, const ptrdiff_t *strides, size_t lo, size_t hi, size_t *n, ptrdiff_t *st) {
+    size_t extent = 1;
+    ptrdiff_t stride = 0;
+    bool have = false;
+    for (size_t k = hi; k-- > lo;) {  // innermost first
+        if (shape[k] == 1) continue;
+        if (!have) {
+            extent = shape[k]; stride = strides[k]; have = true;
+        } else {
+            if (strides[k] != stride * (ptrdiff_t)extent) return false;
+            extent *= shape[k];
+        }
+    }
+    *n = extent; *st = have ? stride : 0;
+    return true;
+}
+
+}  // namespace
+
+RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
+                            const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst) {
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
+    if (rank && (!shape || !strides)) return fail(RTB_ERR_INVALID, "null shape or strides");
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    if (axis >= (ptrdiff_t)rank) return fail(RTB_ERR_DIM, "axis %td out of range for rank %zu", axis, rank);
+    const size_t es = dtype_size(dtype);
+    Ctx *ctx = C(c);
+    int rc = use_device(ctx);
+    if (rc) return rc;
+    size_t total = 1;
+    for (size_t k = 0; k < rank; ++k) total *= shape[k];
+    const char *base = (const char *)src;
+
+    if (axis < 0 || rank <= 1) {
+        // Full reduction.  One run (possibly walked backwards: the order of a max / min does not
+        // matter and sums are tree-ordered anyway) goes straight to the flat kernel.
+        size_t n = 1; ptrdiff_t st = 0;
+        if (collapse_group(shape, strides, 0, rank, &n, &st) && (n == 1 || st == 1 || st == -1)) {
+            ptrdiff_t first = (ptrdiff_t)offset + (st < 0 ? (ptrdiff_t)(n - 1) * st : 0);
+            return launch_reduce_flat(ctx, dtype, redop, base + first * (ptrdiff_t)es, n, dst);
+        }
+    } else {
+        if (total == 0) return RTB_OK;
+        size_t nA = 1, nB = 1;
+        ptrdiff_t sA = 0, sB = 0;
+        const size_t R = shape[axis];
+        const ptrdiff_t sR = strides[axis];
+        const bool okA = collapse_group(shape, strides, 0, (size_t)axis, &nA, &sA);
+        const bool okB = collapse_group(shape, strides, (size_t)axis + 1, rank, &nB, &sB);
+        const char *p0 = base + (ptrdiff_t)offset * (ptrdiff_t)es;
+        if (okA && okB) {
+            // output is row-major over (A, 1, B): dst[a*nB + b]
+            if (nB > 1 && sB == 1)  // B contiguous: [outer = A, R, inner = B]
+                return launch_reduce_axis_strided(ctx, dtype, redop, p0, nA, R, nB, sA, sR, dst);
+            if (nB == 1 && (sR == 1 || nA == 1 || sA != 1))  // rows of R (contiguous or strided), one per a
+                return launch_reduce_axis_strided(ctx, dtype, redop, p0, nA, R, 1, sA, sR, dst);
+            // B absent and A contiguous (a transposed matrix reduced along its strided dim): the
+            // roles swap -- [outer = 1, R, inner = A], dst[a]
+            if (nB == 1 && sA == 1) return launch_reduce_axis_strided(ctx, dtype, redop, p0, 1, R, nA, 0, sR, dst);
+        }
+    }
+    // General view: materialise it row-major (strided copy kernel), then reduce the copy -- what the
+    // reference always does for a non-contiguous tensor (src/ops/reduction/mod.rs:351-360).
+    if (total == 0) {
+        if (axis < 0 || rank <= 1) return launch_reduce_flat(ctx, dtype, redop, src, 0, dst);
+        return RTB_OK;
+    }
+    void *tmp = nullptr;
+    rc = rtb_alloc(c, total * es, &tmp);
+    if (rc != RTB_OK) return rc;
+    rc = rtb_copy_view(c, dtype, src, rank, shape, strides, offset, tmp);
+    if (rc == RTB_OK) {
+        if (axis < 0 || rank <= 1) {
+            rc = launch_reduce_flat(ctx, dtype, redop, tmp, total, dst);
+        } else {
+            size_t outer = 1, inner = 1;
+            for (size_t k = 0; k < (size_t)axis; ++k) outer *= shape[k];
+            for (size_t k = (size_t)axis + 1; k < rank; ++k) inner *= shape[k];
+            rc = launch_reduce_axis(ctx, dtype, redop, tmp, outer, shape[axis], inner, dst);
+        }
+    }
+    rtb_free(c, tmp);  // stream order keeps the block alive until the kernels above are done
+    return rc;
+}
+
 RTB_API int rtb_l1_loss(rtb_ctx *c, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss,
                         void *grad_map) {
     if (!c || !a || !b || !loss) return fail(RTB_ERR_INVALID, "null argument");

@@ -96,6 +96,9 @@ int run_elementwise(Ctx *ctx, const EwCall &call, size_t rank, const size_t *sha
 int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t len, void *dst);
 int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
                        void *dst);
+// same with explicit element strides: source element (o, k, i) at o*outer_stride + k*row_stride + i
+int launch_reduce_axis_strided(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
+                               ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst);
 int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap);
 int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n);
 int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n);

@@ -204,8 +204,8 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
 // GROUP threads cooperate on a row (32 = a warp, 256 = the CTA); split > 1 cuts R into `split`
 // chunks whose partial results go to dst[row * split + chunk] for a second pass.
 template <typename T, int OP, int GROUP>
-__global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t rows, size_t R, size_t split,
-                                                            T *dst, int mean, size_t count) {
+__global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t rows, size_t R, ptrdiff_t pitch,
+                                                            size_t split, T *dst, int mean, size_t count) {
     __shared__ T smem[kWarps];
     constexpr int N = VecOf<T>::N;
     constexpr int rows_per_block = kBlock / GROUP;
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t
         if (live) {
             const size_t row = item / split, chunk = item % split;
             const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
-            const T *p = src + row * R;
+            const T *p = src + (ptrdiff_t)row * pitch;  // pitch = elements between rows (R when dense)
             // vector body over the 16-byte aligned part of [k0, k1)
             size_t a0 = k0 + (((16u - (unsigned)((uintptr_t)(p + k0) & 15u)) & 15u) / sizeof(T));
             if (a0 > k1) a0 = k1;
@@ -272,14 +272,14 @@ __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t
 // finish (per-tile completion counter) folds the `split` partial rows in chunk order -- one launch,
 // and the fold order does not depend on which CTA came last.
 template <typename T, int OP, int VW, int TY>
-__device__ __forceinline__ void col_accumulate(const T *p, size_t row_stride, size_t k0, size_t k1, int ly, T acc[VW]) {
+__device__ __forceinline__ void col_accumulate(const T *p, ptrdiff_t row_stride, size_t k0, size_t k1, int ly, T acc[VW]) {
     constexpr int B = 8;  // rows in flight per thread
     size_t k = k0 + ly;
     if (VW > 1) {
         for (; k + (B - 1) * TY < k1; k += B * TY) {
             typename VecOf<T>::U v[B];
 #pragma unroll
-            for (int u = 0; u < B; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (k + TY * u) * row_stride);
+            for (int u = 0; u < B; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (ptrdiff_t)(k + TY * u) * row_stride);
 #pragma unroll
             for (int u = 0; u < B; ++u)
 #pragma unroll
@@ -287,7 +287,7 @@ __device__ __forceinline__ void col_accumulate(const T *p, size_t row_stride, si
         }
         for (; k < k1; k += TY) {
             typename VecOf<T>::U v;
-            v.q = *reinterpret_cast<const uint4 *>(p + k * row_stride);
+            v.q = *reinterpret_cast<const uint4 *>(p + (ptrdiff_t)k * row_stride);
 #pragma unroll
             for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
         }
@@ -295,11 +295,11 @@ __device__ __forceinline__ void col_accumulate(const T *p, size_t row_stride, si
         for (; k + (B - 1) * TY < k1; k += B * TY) {
             T v[B];
 #pragma unroll
-            for (int u = 0; u < B; ++u) v[u] = p[(k + TY * u) * row_stride];
+            for (int u = 0; u < B; ++u) v[u] = p[(ptrdiff_t)(k + TY * u) * row_stride];
 #pragma unroll
             for (int u = 0; u < B; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
         }
-        for (; k < k1; k += TY) acc[0] = Comb<T, OP>::apply(acc[0], p[k * row_stride]);
+        for (; k < k1; k += TY) acc[0] = Comb<T, OP>::apply(acc[0], p[(ptrdiff_t)k * row_stride]);
     }
 }
 
@@ -314,6 +314,7 @@ __device__ __forceinline__ T col_combine(const T (*smem)[TW + 1], int c) {
 
 template <typename T, int OP, int VW, int TX>
 __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t outer, size_t R, size_t inner,
+                                                            ptrdiff_t outer_stride, ptrdiff_t row_stride,
                                                             size_t split, size_t col_tiles, T *partial,
                                                             unsigned int *counters, T *dst, int mean, size_t count) {
     constexpr int TY = kBlock / TX;
@@ -335,7 +336,9 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
         T acc[VW];
 #pragma unroll
         for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-        if (col < inner && k0 < k1) col_accumulate<T, OP, VW, TY>(src + (o * R) * inner + col, inner, k0, k1, ly, acc);
+        // element (o, k, i) of the source sits at o*outer_stride + k*row_stride + i (dense: R*inner, inner)
+        if (col < inner && k0 < k1)
+            col_accumulate<T, OP, VW, TY>(src + (ptrdiff_t)o * outer_stride + (ptrdiff_t)col, row_stride, k0, k1, ly, acc);
 #pragma unroll
         for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
         __syncthreads();
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
         __threadfence();
 #pragma unroll
         for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-        if (col < inner) col_accumulate<T, OP, VW, TY>(partial + (o * split) * inner + col, inner, 0, split, ly, acc);
+        if (col < inner) col_accumulate<T, OP, VW, TY>(partial + (o * split) * inner + col, (ptrdiff_t)inner, 0, split, ly, acc);
 #pragma unroll
         for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
         __syncthreads();
@@ -462,7 +465,7 @@ int flat_by_op(Ctx *ctx, int redop, Src src, size_t n, T *out) {
 }
 
 template <typename T, int OP>
-int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean) {
+int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, ptrdiff_t pitch, T *dst, int mean) {
     // few long rows: cut each row into chunks so every SM has work, then fold the chunks
     size_t split = 1;
     const size_t min_items = (size_t)ctx->sm_count * 4;
@@ -486,15 +489,15 @@ int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, T *dst, int mean)
     // resident CTAs nothing hides that barrier.  The kernel still loops, so any grid size is legal.
     if (chunk_len >= 1024) {
         unsigned grid = grid_for(ctx, items, kAxisGridCap);
-        row_reduce_kernel<T, OP, kBlock><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+        row_reduce_kernel<T, OP, kBlock><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, pitch, split, target, mean, R);
     } else {
         unsigned grid = grid_for(ctx, (items + kWarps - 1) / kWarps, kAxisGridCap);
-        row_reduce_kernel<T, OP, 32><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, split, target, mean, R);
+        row_reduce_kernel<T, OP, 32><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, pitch, split, target, mean, R);
     }
     int rc = check_launch(ctx, "row_reduce_kernel");
     if (rc != RTB_OK || split == 1) return rc;
     unsigned fold_grid = grid_for(ctx, (rows + kWarps - 1) / kWarps, kAxisGridCap);
-    row_reduce_kernel<T, OP, 32><<<fold_grid, kBlock, 0, ctx->stream>>>(target, rows, split, 1, dst, mean, R);
+    row_reduce_kernel<T, OP, 32><<<fold_grid, kBlock, 0, ctx->stream>>>(target, rows, split, (ptrdiff_t)split, 1, dst, mean, R);
     return check_launch(ctx, "row_reduce_kernel(fold)");
 }
 
@@ -519,7 +522,8 @@ size_t resident_ctas(Ctx *ctx, K kernel) {
 }
 
 template <typename T, int OP, int VW, int TX>
-int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t outer_stride,
+                  ptrdiff_t row_stride, T *dst, int mean) {
     const size_t tile_cols = (size_t)TX * VW;
     const size_t col_tiles = (inner + tile_cols - 1) / tile_cols;
     const size_t base_ctas = outer * col_tiles;
@@ -535,37 +539,41 @@ int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, 
         partial = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     }
     const unsigned grid = grid_for(ctx, base_ctas * split, kAxisGridCap);  // one CTA per (tile, chunk)
-    col_reduce_kernel<T, OP, VW, TX><<<grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, split, col_tiles, partial,
-                                                                       counters, dst, mean, R);
+    col_reduce_kernel<T, OP, VW, TX><<<grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, outer_stride, row_stride, split,
+                                                                       col_tiles, partial, counters, dst, mean, R);
     return check_launch(ctx, "col_reduce_kernel");
 }
 
 template <typename T, int OP>
-int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
+int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t outer_stride,
+                ptrdiff_t row_stride, T *dst, int mean) {
     constexpr int N = VecOf<T>::N;
-    const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0);
+    // 128-bit loads need every (o, k) row start on a 16-byte boundary
+    const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0) && (outer_stride % N == 0) && (row_stride % N == 0);
     // TX = 32 (tile = 32 x 128-bit columns, 8 rows in flight per CTA).  A 256-lane tile (whole 4 KiB
     // row segments per CTA) was measured and is not faster: (64,4096,1024) axis 1 6.50 vs 6.5-6.7 TB/s,
     // (8192,8192) axis 0 4.72 vs 5.3-5.5 TB/s -- the fold of many chunk partials by one CTA per wide
     // tile costs more than the longer DRAM bursts gain.
-    if (vec) return cols_launch_t<T, OP, N, 32>(ctx, src, outer, R, inner, dst, mean);
-    return cols_launch_t<T, OP, 1, 32>(ctx, src, outer, R, inner, dst, mean);
+    if (vec) return cols_launch_t<T, OP, N, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean);
+    return cols_launch_t<T, OP, 1, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean);
 }
 
+// src element (o, k, i) at o*outer_stride + k*row_stride + i; dst[o*inner + i]
 template <typename T, int OP>
-int axis_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, T *dst, int mean) {
-    if (inner == 1) return rows_launch<T, OP>(ctx, src, outer, R, dst, mean);
-    return cols_launch<T, OP>(ctx, src, outer, R, inner, dst, mean);
+int axis_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t outer_stride,
+                ptrdiff_t row_stride, T *dst, int mean) {
+    if (inner == 1 && row_stride == 1) return rows_launch<T, OP>(ctx, src, outer, R, outer_stride, dst, mean);
+    return cols_launch<T, OP>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean);
 }
 
 template <typename T>
-int axis_by_op(Ctx *ctx, int redop, const T *src, size_t outer, size_t R, size_t inner, T *dst) {
+int axis_by_op(Ctx *ctx, int redop, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t so, ptrdiff_t sr, T *dst) {
     switch (redop) {
-        case RTB_SUM: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, dst, 0);
-        case RTB_MEAN: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, dst, 1);
-        case RTB_PROD: return axis_launch<T, RTB_PROD>(ctx, src, outer, R, inner, dst, 0);
-        case RTB_MAX: return axis_launch<T, RTB_MAX>(ctx, src, outer, R, inner, dst, 0);
-        case RTB_MIN: return axis_launch<T, RTB_MIN>(ctx, src, outer, R, inner, dst, 0);
+        case RTB_SUM: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, so, sr, dst, 0);
+        case RTB_MEAN: return axis_launch<T, RTB_SUM>(ctx, src, outer, R, inner, so, sr, dst, 1);
+        case RTB_PROD: return axis_launch<T, RTB_PROD>(ctx, src, outer, R, inner, so, sr, dst, 0);
+        case RTB_MAX: return axis_launch<T, RTB_MAX>(ctx, src, outer, R, inner, so, sr, dst, 0);
+        case RTB_MIN: return axis_launch<T, RTB_MIN>(ctx, src, outer, R, inner, so, sr, dst, 0);
     }
     return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
 }
@@ -581,9 +589,16 @@ int launch_reduce_flat(Ctx *ctx, int dtype, int redop, const void *src, size_t l
 
 int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
                        void *dst) {
+    return launch_reduce_axis_strided(ctx, dtype, redop, src, outer, r, inner, (ptrdiff_t)(r * inner), (ptrdiff_t)inner, dst);
+}
+
+int launch_reduce_axis_strided(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
+                               ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst) {
     std::lock_guard<std::mutex> lock(ctx->ws_mu);
-    if (dtype == RTB_F32) return axis_by_op<float>(ctx, redop, (const float *)src, outer, r, inner, (float *)dst);
-    if (dtype == RTB_F64) return axis_by_op<double>(ctx, redop, (const double *)src, outer, r, inner, (double *)dst);
+    if (dtype == RTB_F32)
+        return axis_by_op<float>(ctx, redop, (const float *)src, outer, r, inner, outer_stride, row_stride, (float *)dst);
+    if (dtype == RTB_F64)
+        return axis_by_op<double>(ctx, redop, (const double *)src, outer, r, inner, outer_stride, row_stride, (double *)dst);
     return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
 }
 

@@ -142,6 +142,19 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
         for axis in (0, 1):
             add(f"{opn}_at({axis}) f32", f"({S},{S})", 4 * (S * S + S), S * S,
                 (lambda op=op, axis=axis: be.apply_reduce((src, msq), r1, axis, op)), flush=S * S * 4 < (200 << 20))
+    # reductions over a strided view: an (S,S) window of an (S,2S) matrix, reduced in place, against
+    # the reference's recipe for non-contiguous tensors (copy the view contiguous, then reduce)
+    win = Meta.contiguous((S, 2 * S)).slice(1, S // 2, S // 2 + S, 1)
+    for axis in (0, 1):
+        add(f"sum_at({axis}) f32 over a strided window, no copy", f"({S},{S}) window of ({S},{2 * S})", 4 * (S * S + S), S * S,
+            (lambda axis=axis: be.reduce_view(src, win, axis, L.SUM)), flush=S * S * 4 < (200 << 20))
+
+    def copy_then_reduce():
+        tmp = be.contiguous(src, win)
+        be.apply_reduce((tmp, msq), r1, 1, L.SUM)
+    add("sum_at(1) f32 over the same window, copy first (reference recipe)", f"({S},{S}) window of ({S},{2 * S})",
+        4 * (S * S + S), S * S, copy_then_reduce, flush=S * S * 4 < (200 << 20),
+        note="algorithmic bytes of the reduction alone; the copy moves 2x more")
     d3 = (64, 512, 1024) if quick else (64, 4096, 1024)
     m3 = Meta.contiguous(d3)
     r3 = be.alloc(d3[0] * d3[2], f32)

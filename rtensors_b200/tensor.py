@@ -152,19 +152,15 @@ class Tensor:
 
     # ---- reductions -------------------------------------------------------------------------
     def _reduce(self, op: int, axis: Optional[int]) -> "Tensor":
-        t = self if self.is_contiguous() else self.contiguous()
-        b = t.backend
+        # The reference copies a non-contiguous view first (`contiguous()`); here the library reduces
+        # the view in place where its layout allows and copies only otherwise -- same result.
+        b = self.backend
         if axis is None:
-            out = b.alloc(1, t.buf.dtype)
-            b.apply_reduce_contiguous_flat(t.buf, out, t.offset, t.size, op)
-            return Tensor(b, out, Meta.contiguous(()))
-        if not 0 <= axis < t.rank:
-            raise L.RtbError(-5, f"axis {axis} out of range for rank {t.rank}")
-        om = Meta.contiguous(tuple(1 if k == axis else s for k, s in enumerate(t.shape)))
-        out = b.alloc(max(om.size, 1), t.buf.dtype)
-        if om.size:
-            b.apply_reduce((t.buf, t.meta), out, axis, op)
-        return Tensor(b, out, om)
+            return Tensor(b, b.reduce_view(self.buf, self.meta, None, op), Meta.contiguous(()))
+        if not 0 <= axis < self.rank:
+            raise L.RtbError(-5, f"axis {axis} out of range for rank {self.rank}")
+        om = Meta.contiguous(tuple(1 if k == axis else s for k, s in enumerate(self.shape)))
+        return Tensor(b, b.reduce_view(self.buf, self.meta, axis, op), om)
 
     def sum(self): return self._reduce(L.SUM, None)
     def mean(self): return self._reduce(L.MEAN, None)

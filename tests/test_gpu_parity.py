@@ -774,3 +774,68 @@ def test_more_than_2_31_elements_u8_and_f32():
     got = red.cpu().numpy()
     assert abs(got[0] - float(r)) <= 1e-5 * 31 * r
     assert abs(got[1] - (float(y[r:2 * r].sum(dtype=torch.float64)))) <= 1e-5 * 31 * r
+
+
+# ------------------------------------------------------------------------------------- reductions over views
+def test_reduce_view_matches_copy_then_reduce():
+    """rtb_reduce_view against the reference's recipe (copy the view contiguous, then reduce), on
+    views that reduce in place (contiguous inner run under strided / reversed / permuted outer dims,
+    transposed matrices) and on views that take the copy fallback."""
+    from rtensors_b200.meta import Meta
+    rng = np.random.default_rng(99)
+    base = O.Meta.contiguous((12, 40, 64))
+    x = rng.standard_normal(base.size).astype(np.float32)
+    d = _dev(x)
+    views = [
+        base,                                                     # dense
+        base.slice(0, 2, 11, 3),                                  # strided outer, dense rest
+        base.slice(0, None, None, -1),                            # reversed outer
+        base.slice(1, 5, 35, 2),                                  # strided middle
+        base.slice(1, None, None, -1).slice(0, 1, 9, 1),          # reversed middle
+        base.slice(2, 8, 40, 1),                                  # inner window (row pitch > row length)
+        base.slice(2, None, None, -1),                            # reversed inner -> copy fallback
+        base.slice(2, None, None, 2),                             # strided inner -> copy fallback / strided rows
+        base.permute((1, 0, 2)),                                  # permuted outer dims
+        base.permute((2, 1, 0)),                                  # fully transposed
+        base.index(0, 3).permute((1, 0)),                         # transposed matrix
+        base.index(2, 7),                                         # (12, 40) with strides (2560, 64)
+    ]
+    for m in views:
+        dense = gather_view(x, m)
+        dm = O.Meta.contiguous(m.shape)
+        for axis in [None] + list(range(len(m.shape))):
+            for op in (O.SUM, O.MAX, O.MEAN, O.MIN):
+                if axis is None:
+                    want = O.reduce_flat(dense, 0, dense.size, op)
+                    cnt = dense.size
+                    scale = np.array([np.abs(dense).sum(dtype=np.float64)])
+                else:
+                    want, _ = O.reduce_axis(dense, dm, axis, op)
+                    cnt = m.shape[axis]
+                    scale = np.abs(dense.reshape(m.shape)).sum(axis=axis, dtype=np.float64).reshape(-1)
+                got = _host(_b().reduce_view(d, _meta_pair(m), axis, op))[: want.size]
+                if op in (O.MAX, O.MIN):
+                    assert got.tobytes() == want.tobytes(), (m, axis, op)
+                else:
+                    s_ = scale if op == O.SUM else scale / cnt
+                    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+                    assert np.all(err <= _sum_tol(cnt) * s_ + 1e-30), (m, axis, op, err.max())
+
+
+def test_reduce_view_large_strided_outer_is_in_place():
+    """A (4096, 4096) window of a (4096, 8192) matrix and its transpose: reduced without a copy
+    (no allocation from the context allocator is needed for these layouts)."""
+    from rtensors_b200.meta import Meta
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    big = torch.randn(4096 * 8192, device="cuda", generator=g)
+    win = Meta.contiguous((4096, 8192)).slice(1, 1024, 5120, 1)
+    ref = big.view(4096, 8192)[:, 1024:5120]
+    got = _b().reduce_view(big, win, 1, O.SUM).view(4096)
+    assert torch.allclose(got, ref.sum(dim=1), rtol=1e-4, atol=1e-3)
+    got = _b().reduce_view(big, win, 0, O.MAX).view(4096)
+    assert torch.equal(got, ref.max(dim=0).values)
+    t = win.permute((1, 0))
+    got = _b().reduce_view(big, t, 1, O.MIN).view(4096)  # reduce along the strided dim of the transpose
+    assert torch.equal(got, ref.min(dim=0).values)
+    got = _b().reduce_view(big, t, 0, O.SUM).view(4096)
+    assert torch.allclose(got, ref.sum(dim=1), rtol=1e-4, atol=1e-3)
