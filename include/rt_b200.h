@@ -194,6 +194,16 @@ int rtb_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t 
 int rtb_reduce_view(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
                     const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst);
 
+/* ---- fused broadcast binary op + axis reduction: dst = reduce_axis(left (op) right) without writing
+ *      the broadcast result (the reference materialises it: Backend::broadcast into a fresh
+ *      tensor, then `*_at(axis)`, src/ops/broadcast/add.rs:441-477 + src/ops/reduction/mod.rs:351-360).
+ *      Both views carry the OUTPUT shape with stride 0 on broadcast dims; dst is row-major with
+ *      dim `axis` kept as 1.  f32 / f64.  Views whose dims before / after the axis do not each
+ *      collapse to one run fall back to materialise + reduce. ---------------------------------- */
+int rtb_broadcast_reduce(rtb_ctx *ctx, int dtype, int binop, int redop, const void *left, const ptrdiff_t *stride_l,
+                         size_t off_l, const void *right, const ptrdiff_t *stride_r, size_t off_r, size_t rank,
+                         const size_t *shape, size_t axis, void *dst);
+
 /* ---- full reduction without any device allocation.  NO COUNTERPART IN THE REFERENCE (its flat
  *      reduction allocates and frees CUB scratch on every call, cuda/kernels/reduction/reduce.cu:
  *      239-274).  For hosts that must not, or cannot, call cudaMalloc: all device memory already

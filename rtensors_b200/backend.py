@@ -215,6 +215,18 @@ class CudaB200:
                                     C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
         return out
 
+    def broadcast_reduce(self, a: torch.Tensor, am: Meta, b: torch.Tensor, bm: Meta, binop: int, axis: int, redop: int):
+        """`(a binop b).<redop>_at(axis)` in one kernel: the broadcast result is never written.
+        -> (result buffer, result Meta with dim `axis` = 1)"""
+        shape, sa, sb = broadcast_params(am, bm)
+        Meta(shape, sa, am.offset).check_extent(a.numel()); Meta(shape, sb, bm.offset).check_extent(b.numel())
+        om = Meta.contiguous(tuple(1 if k == axis else s_ for k, s_ in enumerate(shape)))
+        out = self.alloc(max(om.size, 1), a.dtype)
+        check(lib().rtb_broadcast_reduce(self._ctx, C.c_int(dtype_code(a)), C.c_int(binop), C.c_int(redop), self._p(a),
+                                         diffs(sa), C.c_size_t(am.offset), self._p(b), diffs(sb), C.c_size_t(bm.offset),
+                                         C.c_size_t(len(shape)), sizes(shape), C.c_size_t(axis), self._p(out)))
+        return out, om
+
     def reduce_axis_ori(self, src: torch.Tensor, offset: int, outer: int, r: int, inner: int, op: int):
         out = self.alloc(max(outer * inner, 1), src.dtype)
         check(lib().rtb_reduce_axis(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(offset),

@@ -259,6 +259,51 @@ RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, s
     return rc;
 }
 
+RTB_API int rtb_broadcast_reduce(rtb_ctx *c, int dtype, int binop, int redop, const void *left, const ptrdiff_t *sl,
+                                 size_t ol, const void *right, const ptrdiff_t *sr, size_t orr, size_t rank,
+                                 const size_t *shape, size_t axis, void *dst) {
+    if (!c || !left || !right || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    if (rank == 0 || rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu not in [1,%d]", rank, RTB_MAX_RANK);
+    if (!shape || !sl || !sr) return fail(RTB_ERR_INVALID, "null shape or strides");
+    if (axis >= rank) return fail(RTB_ERR_DIM, "axis %zu out of range for rank %zu", axis, rank);
+    if (binop < RTB_ADD || binop > RTB_DIV) return fail(RTB_ERR_INVALID, "unknown binary op %d", binop);
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    const size_t es = dtype_size(dtype);
+    Ctx *ctx = C(c);
+    int rc = use_device(ctx);
+    if (rc) return rc;
+    size_t total = 1;
+    for (size_t k = 0; k < rank; ++k) total *= shape[k];
+    if (total == 0) return RTB_OK;
+    // both operands must walk the dims before the axis, and the dims after it, as one run each
+    size_t nA = 1, nB = 1, nA2 = 1, nB2 = 1;
+    ptrdiff_t lA = 0, lB = 0, rA = 0, rB = 0;
+    const bool ok = collapse_group(shape, sl, 0, axis, &nA, &lA) && collapse_group(shape, sr, 0, axis, &nA2, &rA) &&
+                    collapse_group(shape, sl, axis + 1, rank, &nB, &lB) && collapse_group(shape, sr, axis + 1, rank, &nB2, &rB);
+    if (ok) {
+        const ptrdiff_t s_l[3] = {lA, sl[axis], lB}, s_r[3] = {rA, sr[axis], rB};
+        std::lock_guard<std::mutex> lock(ctx->ws_mu);
+        return launch_bcast_reduce(ctx, dtype, binop, redop, (const char *)left + (ptrdiff_t)ol * (ptrdiff_t)es, s_l,
+                                   (const char *)right + (ptrdiff_t)orr * (ptrdiff_t)es, s_r, nA, shape[axis], nB, dst);
+    }
+    // views that do not collapse: materialise the broadcast result, then reduce it
+    void *tmp = nullptr;
+    rc = rtb_alloc(c, total * es, &tmp);
+    if (rc != RTB_OK) return rc;
+    std::vector<ptrdiff_t> dense(rank);
+    rtb_meta_contiguous_strides(rank, shape, dense.data());
+    rc = rtb_broadcast(c, dtype, binop, left, sl, ol, right, sr, orr, tmp, dense.data(), 0, rank, shape);
+    if (rc == RTB_OK) {
+        size_t outer = 1, inner = 1;
+        for (size_t k = 0; k < axis; ++k) outer *= shape[k];
+        for (size_t k = axis + 1; k < rank; ++k) inner *= shape[k];
+        rc = rank == 1 ? launch_reduce_flat(ctx, dtype, redop, tmp, total, dst)
+                       : launch_reduce_axis(ctx, dtype, redop, tmp, outer, shape[axis], inner, dst);
+    }
+    rtb_free(c, tmp);
+    return rc;
+}
+
 RTB_API int rtb_l1_loss(rtb_ctx *c, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss,
                         void *grad_map) {
     if (!c || !a || !b || !loss) return fail(RTB_ERR_INVALID, "null argument");

@@ -379,6 +379,99 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
     }
 }
 
+// ---- fused broadcast + axis reduce: dst[a, b] = reduce_k f(l[a, k, b], r[a, k, b]) ------------------
+// The binary op is applied on the fly and never written out (config 1: (4096,1) + (1,4096) followed
+// by sum over axis 1 touches 48 KiB instead of a 64 MiB intermediate).  Each operand is addressed
+// as a*sa + k*sk + b*sb with its own strides (0 on broadcast dims).  Two layouts: lanes along b
+// when the output row is wide (coalesced in b), a warp per output with lanes along k otherwise.
+struct Strides3 {
+    ptrdiff_t a, k, b;
+};
+
+template <typename T> __device__ __forceinline__ T apply_binop(int op, T x, T y) {
+    switch (op) {
+        case RTB_ADD: return x + y;
+        case RTB_SUB: return x - y;
+        case RTB_MUL: return x * y;
+        default: return x / y;
+    }
+}
+
+template <typename T, int OP, bool WIDE>
+__global__ void __launch_bounds__(kBlock) bcast_reduce_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, int binop,
+                                                              size_t A, size_t R, size_t B, size_t split, T *dst, int mean) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (WIDE) {
+        // CTA = 32 outputs along b x 8 lanes along k, one CTA per (a, chunk of k, b tile); with
+        // split > 1, dst holds [A, split, B] partial results for a second pass
+        __shared__ T smem[kWarps][33];
+        const size_t b_tiles = (B + 31) / 32;
+        const size_t per = (R + split - 1) / split;
+        for (size_t item = blockIdx.x; item < A * split * b_tiles; item += gridDim.x) {
+            size_t q = item;
+            const size_t b = (q % b_tiles) * 32 + lane; q /= b_tiles;
+            const size_t chunk = q % split;
+            const size_t a = q / split;
+            const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+            T acc = Comb<T, OP>::identity();
+            if (b < B) {
+                const T *pl = l + (ptrdiff_t)a * sl.a + (ptrdiff_t)b * sl.b;
+                const T *pr = r + (ptrdiff_t)a * sr.a + (ptrdiff_t)b * sr.b;
+                size_t k = k0 + warp;
+                for (; k + 3 * kWarps < k1; k += 4 * kWarps) {
+                    T x[4], y[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        x[u] = pl[(ptrdiff_t)(k + u * kWarps) * sl.k];
+                        y[u] = pr[(ptrdiff_t)(k + u * kWarps) * sr.k];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc = Comb<T, OP>::apply(acc, apply_binop(binop, x[u], y[u]));
+                }
+                for (; k < k1; k += kWarps) acc = Comb<T, OP>::apply(acc, apply_binop(binop, pl[(ptrdiff_t)k * sl.k], pr[(ptrdiff_t)k * sr.k]));
+            }
+            smem[warp][lane] = acc;
+            __syncthreads();
+            if (warp == 0) {
+                T v = smem[0][lane];
+#pragma unroll
+                for (int y = 1; y < kWarps; ++y) v = Comb<T, OP>::apply(v, smem[y][lane]);
+                if (b < B) dst[(a * split + chunk) * B + b] = split == 1 ? finish(v, mean, R) : v;
+            }
+            __syncthreads();
+        }
+    } else {
+        // a warp per output element, lanes along k
+        const size_t outputs = A * B;
+        for (size_t o = (size_t)blockIdx.x * kWarps + warp; o < outputs; o += (size_t)gridDim.x * kWarps) {
+            const size_t a = o / B, b = o % B;
+            const T *pl = l + (ptrdiff_t)a * sl.a + (ptrdiff_t)b * sl.b;
+            const T *pr = r + (ptrdiff_t)a * sr.a + (ptrdiff_t)b * sr.b;
+            T acc[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::identity();
+            // cursors advance by a precomputed step, so the loop body has no 64-bit multiplies
+            const ptrdiff_t dl = sl.k * 32, dr = sr.k * 32;
+            const T *ql = pl + (ptrdiff_t)lane * sl.k, *qr = pr + (ptrdiff_t)lane * sr.k;
+            size_t k = lane;
+            for (; k + 96 < R; k += 128, ql += 4 * dl, qr += 4 * dr) {
+                T x[4], y[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    x[u] = ql[u * dl];
+                    y[u] = qr[u * dr];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] = Comb<T, OP>::apply(acc[u], apply_binop(binop, x[u], y[u]));
+            }
+            for (; k < R; k += 32, ql += dl, qr += dr) acc[0] = Comb<T, OP>::apply(acc[0], apply_binop(binop, *ql, *qr));
+            T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
+            v = warp_reduce<T, OP>(v);
+            if (lane == 0) dst[o] = finish(v, mean, R);
+        }
+    }
+}
+
 // ---- fused MLP pieces ----------------------------------------------------------------------------
 __global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask, size_t n) {
     const size_t nvec = n / 4;
@@ -523,7 +616,7 @@ size_t resident_ctas(Ctx *ctx, K kernel) {
 
 template <typename T, int OP, int VW, int TX>
 int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t outer_stride,
-                  ptrdiff_t row_stride, T *dst, int mean) {
+                  ptrdiff_t row_stride, T *dst, int mean, size_t count) {
     const size_t tile_cols = (size_t)TX * VW;
     const size_t col_tiles = (inner + tile_cols - 1) / tile_cols;
     const size_t base_ctas = outer * col_tiles;
@@ -540,13 +633,14 @@ int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, 
     }
     const unsigned grid = grid_for(ctx, base_ctas * split, kAxisGridCap);  // one CTA per (tile, chunk)
     col_reduce_kernel<T, OP, VW, TX><<<grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, outer_stride, row_stride, split,
-                                                                       col_tiles, partial, counters, dst, mean, R);
+                                                                       col_tiles, partial, counters, dst, mean, count);
     return check_launch(ctx, "col_reduce_kernel");
 }
 
 template <typename T, int OP>
 int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, ptrdiff_t outer_stride,
-                ptrdiff_t row_stride, T *dst, int mean) {
+                ptrdiff_t row_stride, T *dst, int mean, size_t count = 0) {
+    if (count == 0) count = R;  // the divisor of a mean; differs from R only when folding partial sums
     constexpr int N = VecOf<T>::N;
     // 128-bit loads need every (o, k) row start on a 16-byte boundary
     const bool vec = (inner % N == 0) && (((uintptr_t)src & 15u) == 0) && (outer_stride % N == 0) && (row_stride % N == 0);
@@ -554,8 +648,8 @@ int cols_launch(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, pt
     // row segments per CTA) was measured and is not faster: (64,4096,1024) axis 1 6.50 vs 6.5-6.7 TB/s,
     // (8192,8192) axis 0 4.72 vs 5.3-5.5 TB/s -- the fold of many chunk partials by one CTA per wide
     // tile costs more than the longer DRAM bursts gain.
-    if (vec) return cols_launch_t<T, OP, N, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean);
-    return cols_launch_t<T, OP, 1, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean);
+    if (vec) return cols_launch_t<T, OP, N, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean, count);
+    return cols_launch_t<T, OP, 1, 32>(ctx, src, outer, R, inner, outer_stride, row_stride, dst, mean, count);
 }
 
 // src element (o, k, i) at o*outer_stride + k*row_stride + i; dst[o*inner + i]
@@ -574,6 +668,54 @@ int axis_by_op(Ctx *ctx, int redop, const T *src, size_t outer, size_t R, size_t
         case RTB_PROD: return axis_launch<T, RTB_PROD>(ctx, src, outer, R, inner, so, sr, dst, 0);
         case RTB_MAX: return axis_launch<T, RTB_MAX>(ctx, src, outer, R, inner, so, sr, dst, 0);
         case RTB_MIN: return axis_launch<T, RTB_MIN>(ctx, src, outer, R, inner, so, sr, dst, 0);
+    }
+    return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+}
+
+template <typename T, int OP>
+int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 sr, int binop, size_t A, size_t R, size_t B,
+                        T *dst, int mean) {
+    if (B >= 32) {
+        const size_t base = A * ((B + 31) / 32);
+        // few output tiles: cut k into chunks so that every SM has work, then fold the partial rows
+        size_t split = 1;
+        const size_t want = (size_t)ctx->sm_count * 2;
+        if (base < want && R >= 128) {
+            split = (want + base - 1) / base;
+            if (split > R / 64) split = R / 64;
+            if (split < 1) split = 1;
+        }
+        T *target = dst;
+        if (split > 1) {
+            void *tmp = nullptr;  // not the reduction workspace: the fold below uses that
+            int rc = rtb_alloc(reinterpret_cast<rtb_ctx *>(ctx), A * split * B * sizeof(T), &tmp);
+            if (rc != RTB_OK) return rc;
+            target = static_cast<T *>(tmp);
+        }
+        bcast_reduce_kernel<T, OP, true><<<grid_for(ctx, base * split, kAxisGridCap), kBlock, 0, ctx->stream>>>(
+            l, sl, r, sr, binop, A, R, B, split, target, mean);
+        int rc = check_launch(ctx, "bcast_reduce_kernel");
+        if (split > 1) {
+            if (rc == RTB_OK) rc = cols_launch<T, OP>(ctx, target, A, split, B, (ptrdiff_t)(split * B), (ptrdiff_t)B, dst, mean, R);
+            rtb_free(reinterpret_cast<rtb_ctx *>(ctx), target);  // reuse is ordered by the stream
+        }
+        return rc;
+    }
+    size_t blocks = (A * B + kWarps - 1) / kWarps;
+    bcast_reduce_kernel<T, OP, false><<<grid_for(ctx, blocks, kAxisGridCap), kBlock, 0, ctx->stream>>>(l, sl, r, sr, binop, A, R, B, 1,
+                                                                                                dst, mean);
+    return check_launch(ctx, "bcast_reduce_kernel");
+}
+
+template <typename T>
+int bcast_reduce_by_op(Ctx *ctx, int redop, const T *l, Strides3 sl, const T *r, Strides3 sr, int binop, size_t A, size_t R,
+                       size_t B, T *dst) {
+    switch (redop) {
+        case RTB_SUM: return bcast_reduce_launch<T, RTB_SUM>(ctx, l, sl, r, sr, binop, A, R, B, dst, 0);
+        case RTB_MEAN: return bcast_reduce_launch<T, RTB_SUM>(ctx, l, sl, r, sr, binop, A, R, B, dst, 1);
+        case RTB_PROD: return bcast_reduce_launch<T, RTB_PROD>(ctx, l, sl, r, sr, binop, A, R, B, dst, 0);
+        case RTB_MAX: return bcast_reduce_launch<T, RTB_MAX>(ctx, l, sl, r, sr, binop, A, R, B, dst, 0);
+        case RTB_MIN: return bcast_reduce_launch<T, RTB_MIN>(ctx, l, sl, r, sr, binop, A, R, B, dst, 0);
     }
     return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
 }
@@ -637,4 +779,16 @@ int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_
     return check_launch(ctx, "u8_f32_kernel");
 }
 
+}  // namespace rtb
+
+namespace rtb {
+int launch_bcast_reduce(Ctx *ctx, int dtype, int binop, int redop, const void *l, const ptrdiff_t sl[3], const void *r,
+                        const ptrdiff_t sr[3], size_t A, size_t R, size_t B, void *dst) {
+    Strides3 a{sl[0], sl[1], sl[2]}, b{sr[0], sr[1], sr[2]};
+    if (dtype == RTB_F32)
+        return bcast_reduce_by_op<float>(ctx, redop, (const float *)l, a, (const float *)r, b, binop, A, R, B, (float *)dst);
+    if (dtype == RTB_F64)
+        return bcast_reduce_by_op<double>(ctx, redop, (const double *)l, a, (const double *)r, b, binop, A, R, B, (double *)dst);
+    return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+}
 }  // namespace rtb

@@ -89,6 +89,11 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     add("sum_at(1) f32", "(4096,4096)", 4 * (dm.size + 4096), dm.size,
         lambda: be.apply_reduce((out, dm), red, 1, L.SUM), flush=True)
     del out
+    add("broadcast_add + sum_at(1) fused f32 (no 64 MiB intermediate)", "(4096,1)+(1,4096) -> (4096,1)",
+        4 * (4096 + 4096 + 4096), 4096 * 4096, lambda: be.broadcast_reduce(A, am, B, bm, L.ADD, 1, L.SUM), flush=True,
+        note="bytes = the three small vectors actually touched; compare its time with the two rows above")
+    add("broadcast_add + sum_at(0) fused f32 (k cut into chunks, partial rows folded)", "(4096,1)+(1,4096) -> (1,4096)",
+        4 * (4096 + 4096 + 4096), 4096 * 4096, lambda: be.broadcast_reduce(A, am, B, bm, L.ADD, 0, L.SUM), flush=True)
 
     # ---- config 2 parts
     n2 = 1 << (24 if quick else 28)

@@ -839,3 +839,44 @@ def test_reduce_view_large_strided_outer_is_in_place():
     assert torch.equal(got, ref.min(dim=0).values)
     got = _b().reduce_view(big, t, 0, O.SUM).view(4096)
     assert torch.allclose(got, ref.sum(dim=1), rtol=1e-4, atol=1e-3)
+
+
+# ------------------------------------------------------------------------------------- fused broadcast + reduce
+def test_broadcast_reduce_matches_materialise_then_reduce():
+    rng = np.random.default_rng(5150)
+    cases = [((4096, 1), (1, 4096), 1), ((4096, 1), (1, 4096), 0), ((33, 1, 17), (1, 300, 17), 1), ((33, 1, 17), (1, 300, 1), 2),
+             ((8, 40, 64), (40, 64), 0), ((8, 40, 64), (8, 1, 64), 1), ((5, 6, 7, 8), (6, 1, 8), 2), ((1000,), (1000,), 0),
+             ((16, 512), (512,), 1), ((2, 1000, 40), (1000, 1), 1)]
+    for sha, shb, axis in cases:
+        a = rng.uniform(-1, 1, int(np.prod(sha))).astype(np.float32)
+        b = rng.uniform(0.5, 1.5, int(np.prod(shb))).astype(np.float32)
+        am, bm = O.Meta.contiguous(sha), O.Meta.contiguous(shb)
+        for binop in (O.ADD, O.MUL, O.SUB, O.DIV):
+            full, fm = O.binary(a, am, b, bm, binop)
+            for redop in (O.SUM, O.MAX, O.MEAN, O.MIN):
+                if fm.rank == 1:
+                    want = O.reduce_flat(full, 0, full.size, redop)
+                else:
+                    want, _ = O.reduce_axis(full, fm, axis, redop)
+                got, om = _b().broadcast_reduce(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), binop, axis, redop)
+                g = _host(got)[: want.size]
+                if redop in (O.MAX, O.MIN):
+                    assert g.tobytes() == want.tobytes(), (sha, shb, axis, binop, redop)
+                else:
+                    cnt = fm.shape[axis]
+                    scale = np.abs(full.reshape(fm.shape)).sum(axis=axis, dtype=np.float64).reshape(-1)
+                    if redop == O.MEAN:
+                        scale = scale / cnt
+                    err = np.abs(g.astype(np.float64) - want.astype(np.float64))
+                    assert np.all(err <= _sum_tol(cnt) * scale + 1e-30), (sha, shb, axis, binop, redop, err.max())
+    # strided / reversed operand views that collapse per group, and one that does not (fallback)
+    a = rng.uniform(-1, 1, 64 * 48).astype(np.float32)
+    b = rng.uniform(-1, 1, 48).astype(np.float32)
+    for am in (O.Meta.contiguous((64, 48)).slice(0, None, None, -2), O.Meta.contiguous((64, 48)).slice(1, None, None, -1),
+               O.Meta.contiguous((4, 16, 48)).slice(1, 0, 16, 3).slice(0, None, None, -1)):
+        bm = O.Meta.contiguous((48,))
+        full, fm = O.binary(a, am, b, bm, O.ADD)
+        for axis in range(fm.rank):
+            want, _ = O.reduce_axis(full, fm, axis, O.SUM)
+            got, _ = _b().broadcast_reduce(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), O.ADD, axis, O.SUM)
+            assert np.allclose(_host(got)[: want.size], want, rtol=1e-5, atol=1e-5)
