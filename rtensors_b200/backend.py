@@ -31,9 +31,9 @@ def dtype_code(t: torch.Tensor) -> int:
     return TORCH_TO_CODE[t.dtype]
 
 
-def _scalar_bytes(code: int, value):
-    np_dt = CODE_TO_NP[code]
-    return np.array([value], dtype=np_dt)
+def _scalar_bytes(code: int, value) -> bytes:
+    """The operand in the element type's own representation (ctypes passes bytes as a pointer)."""
+    return np.array(value, dtype=CODE_TO_NP[code]).tobytes()
 
 
 class CudaB200:
@@ -100,8 +100,8 @@ class CudaB200:
         code = dtype_code(buf) if dtype is None else dtype
         v = _scalar_bytes(code, value)
         meta.check_extent(buf.numel())
-        check(lib().rtb_scalar_op(self._ctx, C.c_int(code), C.c_int(op), self._p(buf), v.ctypes.data_as(C.c_void_p),
-                                  C.c_size_t(meta.rank), sizes(meta.shape), diffs(meta.strides),
+        check(lib().rtb_scalar_op(self._ctx, C.c_int(code), C.c_int(op), self._p(buf), v,
+                                  C.c_size_t(meta.rank), meta.c_shape, meta.c_strides,
                                   C.c_size_t(meta.offset)))
 
     def scalar_apply_add(self, buf, value, meta): self.scalar_apply(buf, L.ADD, value, meta)
@@ -112,7 +112,7 @@ class CudaB200:
     def apply_unary(self, buf: torch.Tensor, op: int, meta: Meta):
         meta.check_extent(buf.numel())
         check(lib().rtb_unary_op(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(meta.rank),
-                                 sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset)))
+                                 meta.c_shape, meta.c_strides, C.c_size_t(meta.offset)))
 
     def scalar_apply_log(self, buf, value, meta): self.scalar_apply(buf, L.LOG, value, meta)
     def scalar_apply_log1p(self, buf, value, meta): self.scalar_apply(buf, L.LOG1P, value, meta)
@@ -135,8 +135,8 @@ class CudaB200:
         code = dtype_code(buf)
         v = _scalar_bytes(code, value)
         meta.check_extent(buf.numel())
-        check(lib().rtb_fill(self._ctx, C.c_int(code), self._p(buf), v.ctypes.data_as(C.c_void_p),
-                             C.c_size_t(meta.rank), sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset)))
+        check(lib().rtb_fill(self._ctx, C.c_int(code), self._p(buf), v,
+                             C.c_size_t(meta.rank), meta.c_shape, meta.c_strides, C.c_size_t(meta.offset)))
 
     def contiguous(self, buf: torch.Tensor, meta: Meta) -> torch.Tensor:
         """Row-major copy of a view (view_to_contiguous, src/core/tensor.rs:299-325)."""
@@ -144,7 +144,7 @@ class CudaB200:
         if meta.size:
             meta.check_extent(buf.numel())
             check(lib().rtb_copy_view(self._ctx, C.c_int(dtype_code(buf)), self._p(buf), C.c_size_t(meta.rank),
-                                      sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset), self._p(out)))
+                                      meta.c_shape, meta.c_strides, C.c_size_t(meta.offset), self._p(out)))
         return out
 
     # -- broadcast ----------------------------------------------------------------------------
@@ -154,10 +154,10 @@ class CudaB200:
         (lb, lm), (rb, rm), (db, dm) = left, right, dst
         assert lm.shape == rm.shape == dm.shape
         lm.check_extent(lb.numel()); rm.check_extent(rb.numel()); dm.check_extent(db.numel())
-        check(lib().rtb_broadcast(self._ctx, C.c_int(dtype_code(db)), C.c_int(op), self._p(lb), diffs(lm.strides),
-                                  C.c_size_t(lm.offset), self._p(rb), diffs(rm.strides), C.c_size_t(rm.offset),
-                                  self._p(db), diffs(dm.strides), C.c_size_t(dm.offset), C.c_size_t(dm.rank),
-                                  sizes(dm.shape)))
+        check(lib().rtb_broadcast(self._ctx, C.c_int(dtype_code(db)), C.c_int(op), self._p(lb), lm.c_strides,
+                                  C.c_size_t(lm.offset), self._p(rb), rm.c_strides, C.c_size_t(rm.offset),
+                                  self._p(db), dm.c_strides, C.c_size_t(dm.offset), C.c_size_t(dm.rank),
+                                  dm.c_shape))
 
     def binary(self, a: torch.Tensor, am: Meta, b: torch.Tensor, bm: Meta, op: int):
         """`a op b` as the operator impls do it (src/ops/broadcast/add.rs:441-477), except that the
@@ -211,7 +211,7 @@ class CudaB200:
                 n_out *= 1 if k == axis else s_
         out = self.alloc(max(n_out, 1), src.dtype)
         check(lib().rtb_reduce_view(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(meta.rank),
-                                    sizes(meta.shape), diffs(meta.strides), C.c_size_t(meta.offset),
+                                    meta.c_shape, meta.c_strides, C.c_size_t(meta.offset),
                                     C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
         return out
 

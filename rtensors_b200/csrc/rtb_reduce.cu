@@ -472,6 +472,136 @@ __global__ void __launch_bounds__(kBlock) bcast_reduce_kernel(const T *l, Stride
     }
 }
 
+// Both operands either contiguous or invariant along k: a warp per output element, every lane
+// reading 128-bit vectors of consecutive k; an invariant operand is read once per output.
+template <typename T, int OP, int BINOP>
+__global__ void __launch_bounds__(kBlock) bcast_reduce_kvec_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, size_t A,
+                                                                   size_t R, size_t B, T *dst, int mean) {
+    constexpr int N = VecOf<T>::N;
+    using U = typename VecOf<T>::U;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t outputs = A * B, nvec = R / N;
+    for (size_t o = (size_t)blockIdx.x * kWarps + warp; o < outputs; o += (size_t)gridDim.x * kWarps) {
+        const size_t a = o / B, b = o % B;
+        const T *pl = l + (ptrdiff_t)a * sl.a + (ptrdiff_t)b * sl.b;
+        const T *pr = r + (ptrdiff_t)a * sr.a + (ptrdiff_t)b * sr.b;
+        U x[2], y[2];
+        if (sl.k == 0) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) x[0].e[e] = x[1].e[e] = pl[0];
+        }
+        if (sr.k == 0) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) y[0].e[e] = y[1].e[e] = pr[0];
+        }
+        T acc[2][N];
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[0][e] = acc[1][e] = Comb<T, OP>::identity();
+        size_t kv = lane;
+        for (; kv + 32 < nvec; kv += 64) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (sl.k) x[u].q = reinterpret_cast<const uint4 *>(pl)[kv + 32 * u];
+                if (sr.k) y[u].q = reinterpret_cast<const uint4 *>(pr)[kv + 32 * u];
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc[u][e] = Comb<T, OP>::apply(acc[u][e], apply_binop(BINOP, x[u].e[e], y[u].e[e]));
+        }
+        if (kv < nvec) {
+            if (sl.k) x[0].q = reinterpret_cast<const uint4 *>(pl)[kv];
+            if (sr.k) y[0].q = reinterpret_cast<const uint4 *>(pr)[kv];
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[0][e] = Comb<T, OP>::apply(acc[0][e], apply_binop(BINOP, x[0].e[e], y[0].e[e]));
+        }
+        T v = Comb<T, OP>::apply(acc[0][0], acc[1][0]);
+#pragma unroll
+        for (int e = 1; e < N; ++e) v = Comb<T, OP>::apply(v, Comb<T, OP>::apply(acc[0][e], acc[1][e]));
+        v = warp_reduce<T, OP>(v);
+        if (lane == 0) dst[o] = finish(v, mean, R);
+    }
+}
+
+// Both operands either contiguous or invariant along b: a CTA covers 32 x N consecutive outputs
+// (every lane one 128-bit vector of them) with its 8 warps along k; an operand that is also
+// invariant along k is read once.  With split > 1, dst holds [A, split, B] partial rows.
+template <typename T, int OP, int BINOP>
+__global__ void __launch_bounds__(kBlock) bcast_reduce_bvec_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, size_t A,
+                                                                   size_t R, size_t B, size_t split, T *dst, int mean) {
+    constexpr int N = VecOf<T>::N;
+    using U = typename VecOf<T>::U;
+    __shared__ uint4 smem[kWarps][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t bvecs = B / N, b_tiles = (bvecs + 31) / 32;
+    const size_t per = (R + split - 1) / split;
+    auto fetch = [&](U &v, const T *p, ptrdiff_t sb) {
+        if (sb) {
+            v.q = *reinterpret_cast<const uint4 *>(p);
+        } else {
+            const T s = *p;
+#pragma unroll
+            for (int e = 0; e < N; ++e) v.e[e] = s;
+        }
+    };
+    for (size_t item = blockIdx.x; item < A * split * b_tiles; item += gridDim.x) {
+        size_t q = item;
+        const size_t bv = (q % b_tiles) * 32 + lane; q /= b_tiles;
+        const size_t chunk = q % split;
+        const size_t a = q / split;
+        const size_t k0 = chunk * per, k1 = k0 + per < R ? k0 + per : R;
+        U acc;
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc.e[e] = Comb<T, OP>::identity();
+        if (bv < bvecs) {
+            const T *pl = l + (ptrdiff_t)a * sl.a + (ptrdiff_t)(bv * N) * sl.b;
+            const T *pr = r + (ptrdiff_t)a * sr.a + (ptrdiff_t)(bv * N) * sr.b;
+            U x[2], y[2];
+            if (sl.k == 0) { fetch(x[0], pl, sl.b); x[1] = x[0]; }
+            if (sr.k == 0) { fetch(y[0], pr, sr.b); y[1] = y[0]; }
+            size_t k = k0 + warp;
+            for (; k + kWarps < k1; k += 2 * kWarps) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (sl.k) fetch(x[u], pl + (ptrdiff_t)(k + u * kWarps) * sl.k, sl.b);
+                    if (sr.k) fetch(y[u], pr + (ptrdiff_t)(k + u * kWarps) * sr.k, sr.b);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int e = 0; e < N; ++e) acc.e[e] = Comb<T, OP>::apply(acc.e[e], apply_binop(BINOP, x[u].e[e], y[u].e[e]));
+            }
+            if (k < k1) {
+                if (sl.k) fetch(x[0], pl + (ptrdiff_t)k * sl.k, sl.b);
+                if (sr.k) fetch(y[0], pr + (ptrdiff_t)k * sr.k, sr.b);
+#pragma unroll
+                for (int e = 0; e < N; ++e) acc.e[e] = Comb<T, OP>::apply(acc.e[e], apply_binop(BINOP, x[0].e[e], y[0].e[e]));
+            }
+        }
+        smem[warp][lane] = acc.q;
+        __syncthreads();
+        if (warp == 0) {
+            U v;
+            v.q = smem[0][lane];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) {
+                U o;
+                o.q = smem[w][lane];
+#pragma unroll
+                for (int e = 0; e < N; ++e) v.e[e] = Comb<T, OP>::apply(v.e[e], o.e[e]);
+            }
+            if (bv < bvecs) {
+                if (split == 1) {
+#pragma unroll
+                    for (int e = 0; e < N; ++e) v.e[e] = finish(v.e[e], mean, R);
+                }
+                *reinterpret_cast<uint4 *>(dst + (a * split + chunk) * B + bv * N) = v.q;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- fused MLP pieces ----------------------------------------------------------------------------
 __global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask, size_t n) {
     const size_t nvec = n / 4;
@@ -676,7 +806,14 @@ template <typename T, int OP>
 int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 sr, int binop, size_t A, size_t R, size_t B,
                         T *dst, int mean) {
     if (B >= 32) {
-        const size_t base = A * ((B + 31) / 32);
+        constexpr size_t NB = VecOf<T>::N;
+        auto bvec_ok = [&](const T *p, const Strides3 &s) {
+            const bool al = reinterpret_cast<uintptr_t>(p) % 16 == 0 && (A == 1 || s.a % (ptrdiff_t)NB == 0) && s.k % (ptrdiff_t)NB == 0;
+            return s.b == 0 || (s.b == 1 && al);
+        };
+        const bool bvec = B % NB == 0 && B >= 32 * NB && bvec_ok(l, sl) && bvec_ok(r, sr) && binop >= RTB_ADD && binop <= RTB_DIV &&
+                          reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+        const size_t base = bvec ? A * ((B / NB + 31) / 32) : A * ((B + 31) / 32);
         // few output tiles: cut k into chunks so that every SM has work, then fold the partial rows
         size_t split = 1;
         const size_t want = (size_t)ctx->sm_count * 2;
@@ -692,8 +829,19 @@ int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 
             if (rc != RTB_OK) return rc;
             target = static_cast<T *>(tmp);
         }
-        bcast_reduce_kernel<T, OP, true><<<grid_for(ctx, base * split, kAxisGridCap), kBlock, 0, ctx->stream>>>(
-            l, sl, r, sr, binop, A, R, B, split, target, mean);
+        const unsigned wgrid = grid_for(ctx, base * split, kAxisGridCap);
+        if (bvec) {
+#define RTB_BVEC(BOP)                                                                                                          \
+    case BOP:                                                                                                                   \
+        bcast_reduce_bvec_kernel<T, OP, BOP><<<wgrid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, A, R, B, split, target, mean);    \
+        break;
+            switch (binop) {
+                RTB_BVEC(RTB_ADD) RTB_BVEC(RTB_SUB) RTB_BVEC(RTB_MUL) RTB_BVEC(RTB_DIV)
+            }
+#undef RTB_BVEC
+        } else {
+            bcast_reduce_kernel<T, OP, true><<<wgrid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, binop, A, R, B, split, target, mean);
+        }
         int rc = check_launch(ctx, "bcast_reduce_kernel");
         if (split > 1) {
             if (rc == RTB_OK) rc = cols_launch<T, OP>(ctx, target, A, split, B, (ptrdiff_t)(split * B), (ptrdiff_t)B, dst, mean, R);
@@ -702,6 +850,24 @@ int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 
         return rc;
     }
     size_t blocks = (A * B + kWarps - 1) / kWarps;
+    constexpr size_t N = VecOf<T>::N;
+    auto vec_ok = [&](const T *p, const Strides3 &s) {
+        if (s.k == 0) return true;
+        return s.k == 1 && reinterpret_cast<uintptr_t>(p) % 16 == 0 && (A == 1 || s.a % (ptrdiff_t)N == 0) &&
+               (B == 1 || s.b % (ptrdiff_t)N == 0);
+    };
+    if (R % N == 0 && R >= 32 * N && vec_ok(l, sl) && vec_ok(r, sr) && binop >= RTB_ADD && binop <= RTB_DIV) {
+        const unsigned grid = grid_for(ctx, blocks, kAxisGridCap);
+#define RTB_KVEC(BOP)                                                                                                 \
+    case BOP:                                                                                                          \
+        bcast_reduce_kvec_kernel<T, OP, BOP><<<grid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, A, R, B, dst, mean);      \
+        break;
+        switch (binop) {
+            RTB_KVEC(RTB_ADD) RTB_KVEC(RTB_SUB) RTB_KVEC(RTB_MUL) RTB_KVEC(RTB_DIV)
+        }
+#undef RTB_KVEC
+        return check_launch(ctx, "bcast_reduce_kvec_kernel");
+    }
     bcast_reduce_kernel<T, OP, false><<<grid_for(ctx, blocks, kAxisGridCap), kBlock, 0, ctx->stream>>>(l, sl, r, sr, binop, A, R, B, 1,
                                                                                                 dst, mean);
     return check_launch(ctx, "bcast_reduce_kernel");

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
+from functools import cached_property, lru_cache
 from typing import Optional, Sequence, Tuple
 
 from ._lib import Plan, check, diffs, lib, sizes
@@ -17,14 +18,20 @@ class Meta:
 
     @staticmethod
     def contiguous(shape: Sequence[int]) -> "Meta":
-        shape = tuple(int(s) for s in shape)
-        out = (C.c_ssize_t * max(len(shape), 1))()
-        lib().rtb_meta_contiguous_strides(C.c_size_t(len(shape)), sizes(shape), out)
-        return Meta(shape, tuple(out[: len(shape)]), 0)
+        return _contiguous(tuple(int(s) for s in shape))
 
     @property
     def rank(self) -> int:
         return len(self.shape)
+
+    # the ctypes arrays every launch passes; built once per Meta (instances are immutable)
+    @cached_property
+    def c_shape(self):
+        return sizes(self.shape)
+
+    @cached_property
+    def c_strides(self):
+        return diffs(self.strides)
 
     @property
     def size(self) -> int:
@@ -86,8 +93,20 @@ class Meta:
         return Meta(m.shape, m.strides, self.offset)
 
     def check_extent(self, buf_len: int) -> None:
-        check(lib().rtb_meta_check_extent(C.c_size_t(self.rank), sizes(self.shape), diffs(self.strides),
+        # a view that fits a buffer of n elements fits every longer one: remember the shortest seen
+        ok = self.__dict__.get("_fits")
+        if ok is not None and buf_len >= ok:
+            return
+        check(lib().rtb_meta_check_extent(C.c_size_t(self.rank), self.c_shape, self.c_strides,
                                           C.c_size_t(self.offset), C.c_size_t(buf_len)))
+        self.__dict__["_fits"] = buf_len if ok is None else min(ok, buf_len)
+
+
+@lru_cache(maxsize=4096)
+def _contiguous(shape: Tuple[int, ...]) -> Meta:
+    out = (C.c_ssize_t * max(len(shape), 1))()
+    lib().rtb_meta_contiguous_strides(C.c_size_t(len(shape)), sizes(shape), out)
+    return Meta(shape, tuple(out[: len(shape)]), 0)
 
 
 def broadcast_params(a: Meta, b: Meta):

@@ -3,7 +3,7 @@ of launches), so that an `ncu` capture ends by itself in a minute or two:
 
     python -m rtensors_b200.profile_cases c3 [K]   strided / negative-step broadcast add, K rows (default 64)
     python -m rtensors_b200.profile_cases red      axis sums of (8192,8192) and (16,4096,1024)
-    python -m rtensors_b200.profile_cases mid      mid-size ops with an L2 flush between them
+    python -m rtensors_b200.profile_cases mid      mid-size ops (and the fused broadcast+reduce) with an L2 flush between them
 """
 import sys
 
@@ -71,6 +71,10 @@ def main():
             flush.add_(1)
             red = be.alloc(4096, torch.float32)
             be.apply_reduce((src[:n], Meta.contiguous((4096,4096))), red, 1, L.SUM)
+            flush.add_(1)
+            be.broadcast_reduce(A, am, B, bm, L.ADD, 1, L.SUM)   # fused: no (4096,4096) intermediate
+            flush.add_(1)
+            be.broadcast_reduce(A, am, B, bm, L.ADD, 0, L.SUM)
         torch.cuda.synchronize()
         print('done mid')
 

@@ -869,6 +869,16 @@ def test_broadcast_reduce_matches_materialise_then_reduce():
                         scale = scale / cnt
                     err = np.abs(g.astype(np.float64) - want.astype(np.float64))
                     assert np.all(err <= _sum_tol(cnt) * scale + 1e-30), (sha, shb, axis, binop, redop, err.max())
+    # f64 through the same kernels (2-element vectors), k-contiguous and wide layouts
+    for sha, shb, axis in (((64, 1), (1, 1024), 1), ((64, 1), (1, 1024), 0), ((3, 256, 40), (256, 1), 1)):
+        a = rng.uniform(-1, 1, int(np.prod(sha)))
+        b = rng.uniform(0.5, 1.5, int(np.prod(shb)))
+        am, bm = O.Meta.contiguous(sha), O.Meta.contiguous(shb)
+        full, fm = O.binary(a, am, b, bm, O.MUL)
+        for redop in (O.SUM, O.MEAN, O.MAX):
+            want, _ = O.reduce_axis(full, fm, axis, redop)
+            got, _ = _b().broadcast_reduce(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), O.MUL, axis, redop)
+            assert np.allclose(_host(got)[: want.size], want, rtol=1e-12, atol=1e-12), (sha, shb, axis, redop)
     # strided / reversed operand views that collapse per group, and one that does not (fallback)
     a = rng.uniform(-1, 1, 64 * 48).astype(np.float32)
     b = rng.uniform(-1, 1, 48).astype(np.float32)
