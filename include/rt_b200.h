@@ -20,6 +20,7 @@
 #ifndef RT_B200_H
 #define RT_B200_H
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -53,7 +54,21 @@ typedef enum {
 } rtb_unop;
 
 /* reduction codes = ReductionOpCode (cuda/include/common.h:19-30) */
-typedef enum { RTB_SUM = 1, RTB_PROD = 2, RTB_MAX = 3, RTB_MIN = 4, RTB_MEAN = 5 } rtb_redop;
+typedef enum {
+    RTB_SUM = 1, RTB_PROD = 2, RTB_MAX = 3, RTB_MIN = 4, RTB_MEAN = 5,
+    /* accepted by the *_ex entry points only */
+    RTB_VARIANCE = 6, RTB_LOGSUMEXP = 7, RTB_NORM = 8, RTB_ARGMAX = 9, RTB_ARGMIN = 10
+} rtb_redop;
+
+/* = ReductionSettings (cuda/include/common.h:13-17), the record the reference front end fills for
+ * var / pop_var / std / norm (src/ops/reduction/mod.rs:413-510): variance and std divide by n-1
+ * when `unbiased`; `is_std` takes the square root; norm_type 1 = sum |x|, 2 = sqrt(sum x^2).
+ * A NULL settings pointer means {unbiased = true, is_std = false, norm_type = 2}. */
+typedef struct rtb_reduce_settings {
+    bool unbiased;
+    bool is_std;
+    int norm_type;
+} rtb_reduce_settings;
 
 /* status codes; rtb_last_error_string() gives the text for the calling thread's last failure */
 typedef enum {
@@ -193,6 +208,31 @@ int rtb_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t 
  *      the strided copy kernel into a temporary from the context allocator first.  f32 / f64. ---- */
 int rtb_reduce_view(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
                     const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst);
+
+/* ---- every reduction code, 1..10 (launch_flat_contiguous_reduce_*, launch_nd_reduce_contiguous_*,
+ *      launch_flat_contiguous_argmax_*, launch_nd_argmax_contiguous_*; cuda/kernels/reduction/
+ *      reduce.cu:992-1026).  Codes 1..5 behave as in the entry points above.  Codes 6..10 exist only
+ *      in the reference's CUDA backend -- its CPU backend panics for them
+ *      (src/ops/reduction/mod.rs:187-197, src/backend/cpu.rs:452-482):
+ *        VARIANCE   Welford states merged pairwise; m2 / (n-1) or m2 / n, denominator 1 when that
+ *                   would be <= 0 (so one element gives 0), square root when is_std;
+ *        LOGSUMEXP  max + log(sum exp(x - max)) in one pass.  The reference's FLAT launcher has no
+ *                   logsumexp case and leaves its output untouched (reduce.cu:795-843); here the
+ *                   flat form computes the same formula over the whole range;
+ *        NORM       type 1 or 2;
+ *        ARGMAX / ARGMIN  dst is uint64_t: the FIRST position along the reduced run of the largest
+ *                   / smallest value, 0 if no element compares above lowest() / below max() (the
+ *                   reference picks among equal values by thread order once the run is longer
+ *                   than its block size, reduce.cu:897-926).
+ *      f32 / f64.  The _view form follows rtb_reduce_view; argmax / argmin of a full reduction over
+ *      a view count positions in the view's row-major order. ---------------------------------- */
+int rtb_reduce_flat_ex(rtb_ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                       size_t start, size_t len, void *dst);
+int rtb_reduce_axis_ex(rtb_ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                       size_t offset, size_t outer, size_t r, size_t inner, void *dst);
+int rtb_reduce_view_ex(rtb_ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                       size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset, ptrdiff_t axis,
+                       void *dst);
 
 /* ---- fused broadcast binary op + axis reduction: dst = reduce_axis(left (op) right) without writing
  *      the broadcast result (the reference materialises it: Backend::broadcast into a fresh

@@ -12,10 +12,10 @@
  *
  * Covered: every scalar family (add sub mul div log log1p leaky_relu elu, scalar.h:9-96), every
  * unary family (negate relu, scalar.h:99-148; the 29 float-only ones, scalar.h:150-211), fill
- * (fill.h:9-12), broadcast (binary.h:8-20), flat / N-d reductions SUM PROD MAX MIN MEAN for
- * f32/f64 and the allocation flag (scalar.h:213-228).
- * Not provided (outside the path, and absent from the reference CPU backend that defines parity):
- * variance / norm / logsumexp / argmax reductions; integer matmul; buffer_equal.
+ * (fill.h:9-12), broadcast (binary.h:8-20), flat / N-d reductions for f32/f64 -- codes SUM PROD MAX
+ * MIN MEAN VARIANCE LOGSUMEXP NORM with their ReductionSettings, and the argmax / argmin launchers
+ * (scalar.h:213-228; cuda/kernels/reduction/reduce.cu:992-1026) -- and the allocation flag.
+ * Not provided (outside the path): integer matmul; buffer_equal.
  */
 #ifndef RT_B200_V1_H
 #define RT_B200_V1_H
@@ -67,6 +67,12 @@ typedef struct RtbV1ReductionSettings { bool unbiased; bool is_std; int norm_typ
     void launch_flat_contiguous_reduce_##S(const TYPE *data, TYPE *out, size_t start, size_t len, uint8_t code, \
                                            const RtbV1ReductionSettings *settings_HOST, unsigned int block_size); \
     void launch_nd_reduce_contiguous_##S(TYPE *data, TYPE *out, size_t offset, size_t outer, size_t r,          \
+                                         size_t inner, uint8_t code, const RtbV1ReductionSettings *settings_HOST, \
+                                         unsigned int block_size);                                              \
+    void launch_flat_contiguous_argmax_##S(const TYPE *data, uint64_t *out, size_t start, size_t len,           \
+                                           uint8_t code, const RtbV1ReductionSettings *settings_HOST,           \
+                                           unsigned int block_size);                                            \
+    void launch_nd_argmax_contiguous_##S(TYPE *data, uint64_t *out, size_t offset, size_t outer, size_t r,      \
                                          size_t inner, uint8_t code, const RtbV1ReductionSettings *settings_HOST, \
                                          unsigned int block_size);
 

@@ -22,6 +22,7 @@ ADD, SUB, MUL, DIV, LOG, LOG1P, LEAKY_RELU, ELU = range(8)
 (NEG, RELU, ABS, SIGN, SIGMOID, TANH, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, ASINH, ACOSH, ATANH, RSQRT,
  RECIPROCAL, SQUARE, CUBE, EXP, LN, LN1P, FLOOR, CEIL, ROUND, TRUNC, EXPM1, SILU) = range(31)
 SUM, PROD, MAX, MIN, MEAN = 1, 2, 3, 4, 5
+VARIANCE, LOGSUMEXP, NORM, ARGMAX, ARGMIN = 6, 7, 8, 9, 10   # ReductionOpTypes::get_code, ops/reduction/mod.rs:160-175
 
 NP_TO_CODE = {
     np.dtype(np.uint8): U8, np.dtype(np.int8): I8, np.dtype(np.uint16): U16, np.dtype(np.int16): I16,
@@ -243,6 +244,24 @@ def reduce_ori(src: np.ndarray, outer: int, r: int, inner: int, op: int, fast: b
     out = np.zeros(max(outer * inner, 1), dtype=src.dtype)
     _chk(lib(fast).orc_reduce_ori(C.c_int(_code(src)), _ptr(src), C.c_size_t(outer), C.c_size_t(r),
                                   C.c_size_t(inner), C.c_int(op), _ptr(out)))
+    return out
+
+
+def reduce_ext_ori(src: np.ndarray, outer: int, r: int, inner: int, op: int, unbiased: bool = True, is_std: bool = False,
+                   norm_type: int = 2, fast: bool = False):
+    """variance / std / norm / logsumexp of a contiguous (outer, R, inner) block over R; flat = (1, n, 1)."""
+    out = np.zeros(max(outer * inner, 1), dtype=src.dtype)
+    _chk(lib(fast).orc_reduce_ext_ori(C.c_int(_code(src)), _ptr(src), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
+                                      C.c_int(op), C.c_int(bool(unbiased)), C.c_int(bool(is_std)), C.c_int(norm_type),
+                                      _ptr(out)))
+    return out
+
+
+def argreduce_ori(src: np.ndarray, outer: int, r: int, inner: int, op: int, fast: bool = False):
+    """argmax / argmin positions (u64) along R of a contiguous (outer, R, inner) block."""
+    out = np.zeros(max(outer * inner, 1), dtype=np.uint64)
+    _chk(lib(fast).orc_argreduce_ori(C.c_int(_code(src)), _ptr(src), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
+                                     C.c_int(op), _ptr(out)))
     return out
 
 

@@ -573,6 +573,104 @@ ORC_API int orc_reduce_ori(int dtype, const void *src, size_t outer, size_t r, s
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Reductions that only the reference's CUDA backend implements: variance / standard deviation,
+ * L1 / L2 norm, logsumexp, argmax / argmin.  Its CPU backend has no accumulator for them
+ * (get_accumulator panics, ops/reduction/mod.rs:187-197; apply_argmax_* is todo!(),
+ * backend/cpu.rs:452-482), so this is a sequential restatement of the device algorithm in
+ * cuda/kernels/reduction/reduce.cu, element by element in increasing k:
+ *   variance  welford_update (reduce.cu:182-192); result m2 / (n-1) (unbiased) or m2 / n, with
+ *             a denominator of 1 when that would be <= 0, square-rooted for the std form
+ *             (reduce.cu:619-637; the flat form returns 0 for n <= 1, reduce.cu:344-357);
+ *   norm      type 1: acc + |x| (L1SumOp, reduce.cu:66-75); type 2: sqrt(sum x*x)
+ *             (SquareUnaryOp + PostSqrt, reduce.cu:77-86,143-152);
+ *   logsumexp lse_combine(state, {x, 1}) then m + log(s) (reduce.cu:641-716).  The reference's
+ *             FLAT dispatcher has no logsumexp case and leaves the output untouched
+ *             (reduce.cu:795-843); here the flat form is the same formula over one row;
+ *   argmax    strict `cur > best` from lowest() / `cur < best` from max(), so the FIRST index of
+ *             the extreme value (reduce.cu:897-905; the flat form is cub ArgMax / ArgMin, which
+ *             also returns the lowest index).  Indices are positions along the reduced axis.
+ * Pinned by the expected values of the reference's CUDA tests (backend/cuda.rs:2320-2590).
+ * ---------------------------------------------------------------------------------------- */
+enum { ORC_VARIANCE = 6, ORC_LOGSUMEXP = 7, ORC_NORM = 8, ORC_ARGMAX = 9, ORC_ARGMIN = 10 };
+
+#define DEF_REDUCE_EXT(S, T, TMIN, TMAX, SQRT, EXP, LOG, FABS)                               \
+    static T ext_one_##S(const T *p, size_t r, size_t stride, int op, int unbiased,          \
+                         int is_std, int norm_type) {                                        \
+        if (op == ORC_VARIANCE) {                                                            \
+            T mean = 0, m2 = 0; long count = 0;                                              \
+            for (size_t k = 0; k < r; ++k) {                                                 \
+                T x = p[k * stride];                                                         \
+                count += 1;                                                                  \
+                T delta = x - mean;                                                          \
+                mean += delta / (T)count;                                                    \
+                T delta2 = x - mean;                                                         \
+                m2 += delta * delta2;                                                        \
+            }                                                                                \
+            T denom = unbiased ? (count > 1 ? (T)(count - 1) : (T)1) : (count > 0 ? (T)count : (T)1); \
+            T v = m2 / denom;                                                                \
+            return is_std ? SQRT(v) : v;                                                     \
+        }                                                                                    \
+        if (op == ORC_NORM) {                                                                \
+            T acc = 0;                                                                       \
+            if (norm_type == 1) { for (size_t k = 0; k < r; ++k) acc = acc + FABS(p[k * stride]); return acc; } \
+            for (size_t k = 0; k < r; ++k) { T x = p[k * stride]; acc = acc + x * x; }       \
+            return SQRT(acc);                                                                \
+        }                                                                                    \
+        /* logsumexp */                                                                      \
+        T m = -(T)INFINITY, s = 0;                                                           \
+        for (size_t k = 0; k < r; ++k) {                                                     \
+            T x = p[k * stride];                                                             \
+            if (s == (T)0) { m = x; s = (T)1; continue; }                                    \
+            T mm = m > x ? m : x;                                                            \
+            s = s * EXP(m - mm) + (T)1 * EXP(x - mm);                                        \
+            m = mm;                                                                          \
+        }                                                                                    \
+        return r == 0 ? -(T)INFINITY : m + LOG(s);                                           \
+    }                                                                                        \
+    static uint64_t arg_one_##S(const T *p, size_t r, size_t stride, int op) {               \
+        T best = op == ORC_ARGMAX ? (T)TMIN : (T)TMAX;                                       \
+        uint64_t idx = 0;                                                                    \
+        for (size_t k = 0; k < r; ++k) {                                                     \
+            T x = p[k * stride];                                                             \
+            if (op == ORC_ARGMAX ? x > best : x < best) { best = x; idx = (uint64_t)k; }     \
+        }                                                                                    \
+        return idx;                                                                          \
+    }
+DEF_REDUCE_EXT(f32, float, -FLT_MAX, FLT_MAX, sqrtf, expf, logf, fabsf)
+DEF_REDUCE_EXT(f64, double, -DBL_MAX, DBL_MAX, sqrt, exp, log, fabs)
+
+/* (outer, R, inner) form of launch_nd_reduce_contiguous_* for codes 6..8; flat = (1, len, 1). */
+ORC_API int orc_reduce_ext_ori(int dtype, const void *src, size_t outer, size_t r, size_t inner, int op,
+                               int unbiased, int is_std, int norm_type, void *dst) {
+    if (op < ORC_VARIANCE || op > ORC_NORM) return ORC_ERR_OP;
+    if (op == ORC_NORM && norm_type != 1 && norm_type != 2) return ORC_ERR_OP;
+    if (dtype != ORC_F32 && dtype != ORC_F64) return ORC_ERR_DTYPE;
+    for (size_t o = 0; o < outer; ++o)
+        for (size_t i = 0; i < inner; ++i) {
+            size_t base = o * r * inner + i;
+            if (dtype == ORC_F32)
+                ((float *)dst)[o * inner + i] = ext_one_f32((const float *)src + base, r, inner, op, unbiased, is_std, norm_type);
+            else
+                ((double *)dst)[o * inner + i] = ext_one_f64((const double *)src + base, r, inner, op, unbiased, is_std, norm_type);
+        }
+    return ORC_OK;
+}
+
+/* launch_nd_argmax_contiguous_* / launch_flat_contiguous_argmax_*: u64 positions along the axis */
+ORC_API int orc_argreduce_ori(int dtype, const void *src, size_t outer, size_t r, size_t inner, int op,
+                              uint64_t *dst) {
+    if (op != ORC_ARGMAX && op != ORC_ARGMIN) return ORC_ERR_OP;
+    if (dtype != ORC_F32 && dtype != ORC_F64) return ORC_ERR_DTYPE;
+    for (size_t o = 0; o < outer; ++o)
+        for (size_t i = 0; i < inner; ++i) {
+            size_t base = o * r * inner + i;
+            dst[o * inner + i] = dtype == ORC_F32 ? arg_one_f32((const float *)src + base, r, inner, op)
+                                                  : arg_one_f64((const double *)src + base, r, inner, op);
+        }
+    return ORC_OK;
+}
+
+/* ------------------------------------------------------------------------------------------
  * L1 loss on two same-shape contiguous tensors: L1::l1 + attach_l1_grad,
  * ops/broadcast/l1.rs:16-77.  diff = a - b; g = sign(diff); diff = |diff|;
  * reduction 0 = mean (sum / from_usize(n)), 1 = sum.  grad_map (optional) = sign(g), divided

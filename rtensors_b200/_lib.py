@@ -14,6 +14,7 @@ ADD, SUB, MUL, DIV, LOG, LOG1P, LEAKY_RELU, ELU = range(8)
 (NEG, RELU, ABS, SIGN, SIGMOID, TANH, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, SINH, COSH, ASINH, ACOSH, ATANH, RSQRT,
  RECIPROCAL, SQUARE, CUBE, EXP, LN, LN1P, FLOOR, CEIL, ROUND, TRUNC, EXPM1, SILU) = range(31)
 SUM, PROD, MAX, MIN, MEAN = 1, 2, 3, 4, 5
+VARIANCE, LOGSUMEXP, NORM, ARGMAX, ARGMIN = 6, 7, 8, 9, 10
 OK = 0
 
 
@@ -23,6 +24,11 @@ class RtbError(RuntimeError):
     def __init__(self, code: int, text: str):
         super().__init__(f"rtb status {code}: {text}")
         self.code = code
+
+
+class ReduceSettings(C.Structure):
+    """rtb_reduce_settings = the reference's ReductionSettings (cuda/include/common.h:13-17)."""
+    _fields_ = [("unbiased", C.c_bool), ("is_std", C.c_bool), ("norm_type", C.c_int)]
 
 
 class Plan(C.Structure):

@@ -215,6 +215,44 @@ class CudaB200:
                                     C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
         return out
 
+    def reduce_view_ex(self, src: torch.Tensor, meta: Meta, axis: Optional[int], op: int, unbiased: bool = True,
+                       is_std: bool = False, norm_type: int = 2) -> torch.Tensor:
+        """Any reduction code over a view (rtb_reduce_view_ex): also variance / std, logsumexp, norms and
+        argmax / argmin (whose result buffer is int64 holding the u64 positions)."""
+        meta.check_extent(src.numel())
+        n_out = 1
+        if axis is not None:
+            for k, s_ in enumerate(meta.shape):
+                n_out *= 1 if k == axis else s_
+        out = self.alloc(max(n_out, 1), torch.int64 if op in (L.ARGMAX, L.ARGMIN) else src.dtype)
+        st = L.ReduceSettings(bool(unbiased), bool(is_std), int(norm_type))
+        check(lib().rtb_reduce_view_ex(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), C.byref(st), self._p(src),
+                                       C.c_size_t(meta.rank), meta.c_shape, meta.c_strides, C.c_size_t(meta.offset),
+                                       C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
+        return out
+
+    def apply_reduce_ex(self, src: Tuple[torch.Tensor, Meta], dst: torch.Tensor, dim: int, op: int, unbiased: bool = True,
+                        is_std: bool = False, norm_type: int = 2):
+        """Backend::apply_reduce / apply_argmax with the op's settings (src/backend/mod.rs:375-465): contiguous
+        input; rank 1 goes to the flat launcher; dst is int64 (u64 positions) for ARGMAX / ARGMIN."""
+        sb, sm = src
+        if not sm.is_contiguous():
+            raise L.RtbError(-7, "Reduction over non-contiguous tensors is not implemented yet.")
+        st = L.ReduceSettings(bool(unbiased), bool(is_std), int(norm_type))
+        if sm.rank == 1:
+            if sm.offset + sm.size > sb.numel():
+                raise L.RtbError(-4, "flat reduction range exceeds the buffer")
+            return check(lib().rtb_reduce_flat_ex(self._ctx, C.c_int(dtype_code(sb)), C.c_int(op), C.byref(st), self._p(sb),
+                                                  C.c_size_t(sm.offset), C.c_size_t(sm.size), self._p(dst)))
+        outer = int(np.prod(sm.shape[:dim], dtype=np.int64)) if dim > 0 else 1
+        inner = max(int(np.prod(sm.shape[dim + 1:], dtype=np.int64)), 1)
+        r = sm.shape[dim]
+        if sm.offset + outer * r * inner > sb.numel():
+            raise L.RtbError(-4, "axis reduction range exceeds the buffer")
+        check(lib().rtb_reduce_axis_ex(self._ctx, C.c_int(dtype_code(sb)), C.c_int(op), C.byref(st), self._p(sb),
+                                       C.c_size_t(sm.offset), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
+                                       self._p(dst)))
+
     def broadcast_reduce(self, a: torch.Tensor, am: Meta, b: torch.Tensor, bm: Meta, binop: int, axis: int, redop: int):
         """`(a binop b).<redop>_at(axis)` in one kernel: the broadcast result is never written.
         -> (result buffer, result Meta with dim `axis` = 1)"""

@@ -74,17 +74,49 @@ void broadcast_v1(int dtype, const void *l, const void *r, void *d, size_t loff,
     note(run_elementwise(ctx, call, rank, shape.data(), sd.data(), doff, sl.data(), loff, sr.data(), roff));
 }
 
-void reduce_flat_v1(int dtype, const void *data, void *out, size_t start, size_t len, uint8_t code) {
+rtb_reduce_settings settings_of(const RtbV1ReductionSettings *s) {
+    rtb_reduce_settings r{true, false, 2};
+    if (s) { r.unbiased = s->unbiased; r.is_std = s->is_std; r.norm_type = s->norm_type; }
+    return r;
+}
+
+// codes 1..5 and, for the flat form, 6 (variance) and 8 (norm) as dispatch_flat_contiguous_reduce
+// has them (cuda/kernels/reduction/reduce.cu:795-843); code 7 (logsumexp) is computed too, where
+// the reference's flat dispatcher silently leaves `out` untouched.
+void reduce_flat_v1(int dtype, const void *data, void *out, size_t start, size_t len, uint8_t code,
+                    const RtbV1ReductionSettings *settings) {
     Ctx *ctx = default_ctx();
     if (!ctx) return;
-    note(launch_reduce_flat(ctx, dtype, code, (const char *)data + start * dtype_size(dtype), len, out));
+    const char *p = (const char *)data + start * dtype_size(dtype);
+    if (code >= RTB_VARIANCE && code <= RTB_NORM) {
+        rtb_reduce_settings st = settings_of(settings);
+        note(launch_reduce_ext(ctx, dtype, code, &st, p, 1, len, 1, 0, 1, out));
+        return;
+    }
+    note(launch_reduce_flat(ctx, dtype, code, p, len, out));
 }
 
 void reduce_nd_v1(int dtype, const void *data, void *out, size_t offset, size_t outer, size_t r, size_t inner,
+                  uint8_t code, const RtbV1ReductionSettings *settings) {
+    Ctx *ctx = default_ctx();
+    if (!ctx || outer == 0 || inner == 0) return;
+    const char *p = (const char *)data + offset * dtype_size(dtype);
+    if (code >= RTB_VARIANCE && code <= RTB_NORM) {
+        rtb_reduce_settings st = settings_of(settings);
+        note(launch_reduce_ext(ctx, dtype, code, &st, p, outer, r, inner, (ptrdiff_t)(r * inner), (ptrdiff_t)inner, out));
+        return;
+    }
+    note(launch_reduce_axis(ctx, dtype, code, p, outer, r, inner, out));
+}
+
+// launch_flat_contiguous_argmax_* / launch_nd_argmax_contiguous_* (reduce.cu:992-1008): codes 9, 10
+void argreduce_v1(int dtype, const void *data, uint64_t *out, size_t offset, size_t outer, size_t r, size_t inner,
                   uint8_t code) {
     Ctx *ctx = default_ctx();
     if (!ctx || outer == 0 || inner == 0) return;
-    note(launch_reduce_axis(ctx, dtype, code, (const char *)data + offset * dtype_size(dtype), outer, r, inner, out));
+    if (code != RTB_ARGMAX && code != RTB_ARGMIN) return;  // the reference launches nothing for other codes
+    note(launch_reduce_ext(ctx, dtype, code, nullptr, (const char *)data + offset * dtype_size(dtype), outer, r, inner,
+                           (ptrdiff_t)(r * inner), (ptrdiff_t)inner, out));
 }
 
 }  // namespace
@@ -189,13 +221,22 @@ V1_SCALAR_IMPL(elu, RTB_ELU, float, f32, RTB_F32) V1_SCALAR_IMPL(elu, RTB_ELU, d
 
 #define V1_REDUCE_IMPL(TYPE, S, DT)                                                                               \
     RTB_API void launch_flat_contiguous_reduce_##S(const TYPE *data, TYPE *out, size_t start, size_t len,         \
-                                                   uint8_t code, const RtbV1ReductionSettings *, unsigned int) {  \
-        reduce_flat_v1(DT, data, out, start, len, code);                                                          \
+                                                   uint8_t code, const RtbV1ReductionSettings *st, unsigned int) { \
+        reduce_flat_v1(DT, data, out, start, len, code, st);                                                      \
     }                                                                                                             \
     RTB_API void launch_nd_reduce_contiguous_##S(TYPE *data, TYPE *out, size_t offset, size_t outer, size_t r,    \
+                                                 size_t inner, uint8_t code, const RtbV1ReductionSettings *st,    \
+                                                 unsigned int) {                                                  \
+        reduce_nd_v1(DT, data, out, offset, outer, r, inner, code, st);                                           \
+    }                                                                                                             \
+    RTB_API void launch_flat_contiguous_argmax_##S(const TYPE *data, uint64_t *out, size_t start, size_t len,     \
+                                                   uint8_t code, const RtbV1ReductionSettings *, unsigned int) {  \
+        argreduce_v1(DT, data, out, start, 1, len, 1, code);                                                      \
+    }                                                                                                             \
+    RTB_API void launch_nd_argmax_contiguous_##S(TYPE *data, uint64_t *out, size_t offset, size_t outer, size_t r, \
                                                  size_t inner, uint8_t code, const RtbV1ReductionSettings *,      \
                                                  unsigned int) {                                                  \
-        reduce_nd_v1(DT, data, out, offset, outer, r, inner, code);                                               \
+        argreduce_v1(DT, data, out, offset, outer, r, inner, code);                                               \
     }
 V1_REDUCE_IMPL(float, f32, RTB_F32)
 V1_REDUCE_IMPL(double, f64, RTB_F64)

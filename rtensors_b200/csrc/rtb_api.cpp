@@ -192,8 +192,24 @@ bool collapse_group(const size_t *shape, const ptrdiff_t *strides, size_t lo, si
 
 }  // namespace
 
-RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
-                            const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst) {
+namespace {
+
+inline bool is_ext(int redop) { return redop >= RTB_VARIANCE && redop <= RTB_ARGMIN; }
+inline bool is_arg(int redop) { return redop == RTB_ARGMAX || redop == RTB_ARGMIN; }
+
+// flat and [outer, R, inner] launches for any reduction code
+int any_flat(Ctx *ctx, int dtype, int redop, const rtb_reduce_settings *set, const void *p, size_t n, void *dst) {
+    if (is_ext(redop)) return launch_reduce_ext(ctx, dtype, redop, set, p, 1, n, 1, 0, 1, dst);
+    return launch_reduce_flat(ctx, dtype, redop, p, n, dst);
+}
+int any_axis(Ctx *ctx, int dtype, int redop, const rtb_reduce_settings *set, const void *p, size_t outer, size_t r,
+             size_t inner, ptrdiff_t so, ptrdiff_t sr, void *dst) {
+    if (is_ext(redop)) return launch_reduce_ext(ctx, dtype, redop, set, p, outer, r, inner, so, sr, dst);
+    return launch_reduce_axis_strided(ctx, dtype, redop, p, outer, r, inner, so, sr, dst);
+}
+
+int reduce_view_impl(rtb_ctx *c, int dtype, int redop, const rtb_reduce_settings *set, const void *src, size_t rank,
+                     const size_t *shape, const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst) {
     if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
     if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
     if (rank && (!shape || !strides)) return fail(RTB_ERR_INVALID, "null shape or strides");
@@ -209,11 +225,12 @@ RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, s
 
     if (axis < 0 || rank <= 1) {
         // Full reduction.  One run (possibly walked backwards: the order of a max / min does not
-        // matter and sums are tree-ordered anyway) goes straight to the flat kernel.
+        // matter and sums are tree-ordered anyway) goes straight to the flat kernel; a position
+        // (argmax / argmin) is only meaningful walking forwards.
         size_t n = 1; ptrdiff_t st = 0;
-        if (collapse_group(shape, strides, 0, rank, &n, &st) && (n == 1 || st == 1 || st == -1)) {
+        if (collapse_group(shape, strides, 0, rank, &n, &st) && (n == 1 || st == 1 || (st == -1 && !is_arg(redop)))) {
             ptrdiff_t first = (ptrdiff_t)offset + (st < 0 ? (ptrdiff_t)(n - 1) * st : 0);
-            return launch_reduce_flat(ctx, dtype, redop, base + first * (ptrdiff_t)es, n, dst);
+            return any_flat(ctx, dtype, redop, set, base + first * (ptrdiff_t)es, n, dst);
         }
     } else {
         if (total == 0) return RTB_OK;
@@ -227,18 +244,18 @@ RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, s
         if (okA && okB) {
             // output is row-major over (A, 1, B): dst[a*nB + b]
             if (nB > 1 && sB == 1)  // B contiguous: [outer = A, R, inner = B]
-                return launch_reduce_axis_strided(ctx, dtype, redop, p0, nA, R, nB, sA, sR, dst);
+                return any_axis(ctx, dtype, redop, set, p0, nA, R, nB, sA, sR, dst);
             if (nB == 1 && (sR == 1 || nA == 1 || sA != 1))  // rows of R (contiguous or strided), one per a
-                return launch_reduce_axis_strided(ctx, dtype, redop, p0, nA, R, 1, sA, sR, dst);
+                return any_axis(ctx, dtype, redop, set, p0, nA, R, 1, sA, sR, dst);
             // B absent and A contiguous (a transposed matrix reduced along its strided dim): the
             // roles swap -- [outer = 1, R, inner = A], dst[a]
-            if (nB == 1 && sA == 1) return launch_reduce_axis_strided(ctx, dtype, redop, p0, 1, R, nA, 0, sR, dst);
+            if (nB == 1 && sA == 1) return any_axis(ctx, dtype, redop, set, p0, 1, R, nA, 0, sR, dst);
         }
     }
     // General view: materialise it row-major (strided copy kernel), then reduce the copy -- what the
     // reference always does for a non-contiguous tensor (src/ops/reduction/mod.rs:351-360).
     if (total == 0) {
-        if (axis < 0 || rank <= 1) return launch_reduce_flat(ctx, dtype, redop, src, 0, dst);
+        if (axis < 0 || rank <= 1) return any_flat(ctx, dtype, redop, set, src, 0, dst);
         return RTB_OK;
     }
     void *tmp = nullptr;
@@ -247,16 +264,53 @@ RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, s
     rc = rtb_copy_view(c, dtype, src, rank, shape, strides, offset, tmp);
     if (rc == RTB_OK) {
         if (axis < 0 || rank <= 1) {
-            rc = launch_reduce_flat(ctx, dtype, redop, tmp, total, dst);
+            rc = any_flat(ctx, dtype, redop, set, tmp, total, dst);
         } else {
             size_t outer = 1, inner = 1;
             for (size_t k = 0; k < (size_t)axis; ++k) outer *= shape[k];
             for (size_t k = (size_t)axis + 1; k < rank; ++k) inner *= shape[k];
-            rc = launch_reduce_axis(ctx, dtype, redop, tmp, outer, shape[axis], inner, dst);
+            rc = any_axis(ctx, dtype, redop, set, tmp, outer, shape[axis], inner, (ptrdiff_t)(shape[axis] * inner), (ptrdiff_t)inner, dst);
         }
     }
     rtb_free(c, tmp);  // stream order keeps the block alive until the kernels above are done
     return rc;
+}
+
+}  // namespace
+
+RTB_API int rtb_reduce_view(rtb_ctx *c, int dtype, int redop, const void *src, size_t rank, const size_t *shape,
+                            const ptrdiff_t *strides, size_t offset, ptrdiff_t axis, void *dst) {
+    if (redop < RTB_SUM || redop > RTB_MEAN) return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+    return reduce_view_impl(c, dtype, redop, nullptr, src, rank, shape, strides, offset, axis, dst);
+}
+
+RTB_API int rtb_reduce_view_ex(rtb_ctx *c, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                               size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset, ptrdiff_t axis,
+                               void *dst) {
+    if (redop < RTB_SUM || redop > RTB_ARGMIN) return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+    return reduce_view_impl(c, dtype, redop, settings, src, rank, shape, strides, offset, axis, dst);
+}
+
+RTB_API int rtb_reduce_flat_ex(rtb_ctx *c, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                               size_t start, size_t len, void *dst) {
+    if (!is_ext(redop)) return rtb_reduce_flat(c, dtype, redop, src, start, len, dst);
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_reduce_ext(C(c), dtype, redop, settings, (const char *)src + start * dtype_size(dtype), 1, len, 1, 0, 1, dst);
+}
+
+RTB_API int rtb_reduce_axis_ex(rtb_ctx *c, int dtype, int redop, const rtb_reduce_settings *settings, const void *src,
+                               size_t offset, size_t outer, size_t r, size_t inner, void *dst) {
+    if (!is_ext(redop)) return rtb_reduce_axis(c, dtype, redop, src, offset, outer, r, inner, dst);
+    if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    if (dtype != RTB_F32 && dtype != RTB_F64) return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+    if (outer == 0 || inner == 0) return RTB_OK;  // no outputs: nothing to launch
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_reduce_ext(C(c), dtype, redop, settings, (const char *)src + offset * dtype_size(dtype), outer, r, inner,
+                             (ptrdiff_t)(r * inner), (ptrdiff_t)inner, dst);
 }
 
 RTB_API int rtb_broadcast_reduce(rtb_ctx *c, int dtype, int binop, int redop, const void *left, const ptrdiff_t *sl,

@@ -99,6 +99,9 @@ int launch_reduce_axis(Ctx *ctx, int dtype, int redop, const void *src, size_t o
 // same with explicit element strides: source element (o, k, i) at o*outer_stride + k*row_stride + i
 int launch_reduce_axis_strided(Ctx *ctx, int dtype, int redop, const void *src, size_t outer, size_t r, size_t inner,
                                ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst);
+// codes RTB_VARIANCE .. RTB_ARGMIN over the same addressing; dst holds uint64_t for the arg codes
+int launch_reduce_ext(Ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src, size_t outer,
+                      size_t r, size_t inner, ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst);
 // fused broadcast binary op + axis reduce: operands addressed as a*s[0] + k*s[1] + b*s[2]
 int launch_bcast_reduce(Ctx *ctx, int dtype, int binop, int redop, const void *l, const ptrdiff_t sl[3], const void *r,
                         const ptrdiff_t sr[3], size_t A, size_t R, size_t B, void *dst);

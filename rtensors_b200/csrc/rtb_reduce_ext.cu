@@ -1,0 +1,444 @@
+// Reductions whose running value is a small state rather than one number: variance / standard
+// deviation (Welford states merged with Chan's formula), logsumexp (running max + rescaled sum),
+// L1 / L2 norm, argmax / argmin (value + position).  The reference implements them only in its CUDA
+// backend (cuda/kernels/reduction/reduce.cu:166-240, 324-420, 560-716, 845-990); semantics kept:
+// variance of n <= 1 elements is 0, denominators n-1 / n, argmax / argmin return the first
+// position of the extreme value (0 when nothing compares above lowest() / below max()).
+//
+// Layout handled: source element (o, k, i) at o*outer_stride + k*row_stride + i, reduced over k,
+// output row-major over (o, i).  inner == 1 with row_stride == 1 runs one CTA (or warp) per row
+// reading 128-bit vectors; everything else runs tiles of 32 x VW columns with the 8 warps of a
+// CTA along k.  When there are too few outputs to fill the GPU, k is cut into chunks whose partial
+// states go to the context workspace and a second small kernel merges them.
+#include "rtb_internal.h"
+
+#include <cfloat>
+#include <cmath>
+
+namespace rtb {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kWarps = kBlock / 32;
+constexpr size_t kWorkspaceHeader = 65536;  // bytes of completion counters in front of the scratch
+constexpr unsigned kGridCap = 1u << 22;
+
+struct ExtSettings {
+    int unbiased;
+    int is_std;
+};
+
+__device__ __forceinline__ float t_exp(float x) { return expf(x); }
+__device__ __forceinline__ double t_exp(double x) { return exp(x); }
+__device__ __forceinline__ float t_log(float x) { return logf(x); }
+__device__ __forceinline__ double t_log(double x) { return log(x); }
+__device__ __forceinline__ float t_sqrt(float x) { return sqrtf(x); }
+__device__ __forceinline__ double t_sqrt(double x) { return sqrt(x); }
+__device__ __forceinline__ float t_abs(float x) { return fabsf(x); }
+__device__ __forceinline__ double t_abs(double x) { return fabs(x); }
+template <typename T> __device__ __forceinline__ T t_lowest();
+template <> __device__ __forceinline__ float t_lowest<float>() { return -FLT_MAX; }
+template <> __device__ __forceinline__ double t_lowest<double>() { return -DBL_MAX; }
+template <typename T> __device__ __forceinline__ T t_ninf();
+template <> __device__ __forceinline__ float t_ninf<float>() { return -INFINITY; }
+template <> __device__ __forceinline__ double t_ninf<double>() { return -(double)INFINITY; }
+
+template <typename V> __device__ __forceinline__ V shfl_down_any(V v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+
+// ---- reducers ----------------------------------------------------------------------------------
+// State identity(); add_one(state, x, k); add_batch<NB>(state, x[NB], k0, kstep) for NB values at
+// positions k0 + e*kstep; merge(a, b); shfl(state, delta); Out finish(state, settings).
+
+template <typename T> struct RedVar {
+    using Out = T;
+    static constexpr bool kPositional = false;
+    struct State {
+        T mean, m2;
+        unsigned long long n;
+    };
+    __device__ static State identity() { return State{(T)0, (T)0, 0ull}; }
+    __device__ static State merge(const State &a, const State &b) {
+        if (b.n == 0) return a;
+        if (a.n == 0) return b;
+        const T na = (T)a.n, nb = (T)b.n;
+        const T w = nb / (na + nb);
+        const T delta = b.mean - a.mean;
+        State r;
+        r.mean = a.mean + delta * w;
+        r.m2 = a.m2 + b.m2 + (delta * delta) * (na * w);
+        r.n = a.n + b.n;
+        return r;
+    }
+    // a batch becomes one state (its own mean and squared deviations), merged with one division
+    template <int NB> __device__ static void add_batch(State &s, const T (&x)[NB], unsigned long long, unsigned long long) {
+        T sum = x[0];
+#pragma unroll
+        for (int e = 1; e < NB; ++e) sum += x[e];
+        const T bm = sum * ((T)1 / (T)NB);
+        T m2 = (T)0;
+#pragma unroll
+        for (int e = 0; e < NB; ++e) {
+            const T d = x[e] - bm;
+            m2 += d * d;
+        }
+        s = merge(s, State{bm, m2, (unsigned long long)NB});
+    }
+    __device__ static void add_one(State &s, T x, unsigned long long) { s = merge(s, State{x, (T)0, 1ull}); }
+    __device__ static State shfl(const State &s, int d) {
+        return State{shfl_down_any(s.mean, d), shfl_down_any(s.m2, d), shfl_down_any(s.n, d)};
+    }
+    __device__ static Out finish(const State &s, ExtSettings st) {
+        const unsigned long long den = st.unbiased ? (s.n > 1 ? s.n - 1 : 1ull) : (s.n > 0 ? s.n : 1ull);
+        const T v = s.m2 / (T)den;
+        return st.is_std ? t_sqrt(v) : v;
+    }
+};
+
+template <typename T> struct RedLse {
+    using Out = T;
+    static constexpr bool kPositional = false;
+    struct State {
+        T m, s;  // running max, sum of exp(x - m); s == 0 marks "empty"
+    };
+    __device__ static State identity() { return State{t_ninf<T>(), (T)0}; }
+    __device__ static State merge(const State &a, const State &b) {
+        if (b.s == (T)0) return a;
+        if (a.s == (T)0) return b;
+        const T m = a.m > b.m ? a.m : b.m;
+        return State{m, a.s * t_exp(a.m - m) + b.s * t_exp(b.m - m)};
+    }
+    template <int NB> __device__ static void add_batch(State &s, const T (&x)[NB], unsigned long long, unsigned long long) {
+        T vm = x[0];
+#pragma unroll
+        for (int e = 1; e < NB; ++e) vm = x[e] > vm ? x[e] : vm;
+        T vs = (T)0;
+#pragma unroll
+        for (int e = 0; e < NB; ++e) vs += t_exp(x[e] - vm);
+        // one more exponential rescales whichever side has the smaller max
+        if (s.s == (T)0) {
+            s = State{vm, vs};
+        } else if (vm <= s.m) {
+            s.s += vs * t_exp(vm - s.m);
+        } else {
+            s.s = s.s * t_exp(s.m - vm) + vs;
+            s.m = vm;
+        }
+    }
+    __device__ static void add_one(State &s, T x, unsigned long long) { s = merge(s, State{x, (T)1}); }
+    __device__ static State shfl(const State &s, int d) { return State{shfl_down_any(s.m, d), shfl_down_any(s.s, d)}; }
+    __device__ static Out finish(const State &s, ExtSettings) { return s.m + t_log(s.s); }
+};
+
+template <typename T, int P> struct RedNorm {
+    using Out = T;
+    static constexpr bool kPositional = false;
+    struct State {
+        T v;
+    };
+    __device__ static State identity() { return State{(T)0}; }
+    __device__ static State merge(const State &a, const State &b) { return State{a.v + b.v}; }
+    __device__ static T term(T x) { return P == 1 ? t_abs(x) : x * x; }
+    template <int NB> __device__ static void add_batch(State &s, const T (&x)[NB], unsigned long long, unsigned long long) {
+        T acc = term(x[0]);
+#pragma unroll
+        for (int e = 1; e < NB; ++e) acc += term(x[e]);
+        s.v += acc;
+    }
+    __device__ static void add_one(State &s, T x, unsigned long long) { s.v += term(x); }
+    __device__ static State shfl(const State &s, int d) { return State{shfl_down_any(s.v, d)}; }
+    __device__ static Out finish(const State &s, ExtSettings) { return P == 2 ? t_sqrt(s.v) : s.v; }
+};
+
+template <typename T, bool MAXI> struct RedArg {
+    using Out = unsigned long long;
+    static constexpr bool kPositional = true;
+    static constexpr unsigned long long kNone = ~0ull;
+    struct State {
+        T v;
+        unsigned long long k;
+    };
+    __device__ static State identity() { return State{MAXI ? t_lowest<T>() : -t_lowest<T>(), kNone}; }
+    __device__ static bool better(T x, T best) { return MAXI ? x > best : x < best; }
+    __device__ static State merge(const State &a, const State &b) {
+        return (better(b.v, a.v) || (b.v == a.v && b.k < a.k)) ? b : a;
+    }
+    __device__ static void add_one(State &s, T x, unsigned long long k) {
+        if (better(x, s.v)) { s.v = x; s.k = k; }  // positions arrive in increasing order: strict keeps the first
+    }
+    template <int NB> __device__ static void add_batch(State &s, const T (&x)[NB], unsigned long long k0, unsigned long long kstep) {
+#pragma unroll
+        for (int e = 0; e < NB; ++e) add_one(s, x[e], k0 + (unsigned long long)e * kstep);
+    }
+    __device__ static State shfl(const State &s, int d) { return State{shfl_down_any(s.v, d), shfl_down_any(s.k, d)}; }
+    __device__ static Out finish(const State &s, ExtSettings) { return s.k == kNone ? 0ull : s.k; }
+};
+
+template <typename T> struct Vec128 {
+    static constexpr int N = 16 / (int)sizeof(T);
+    union U {
+        uint4 q;
+        T e[N];
+    };
+};
+
+template <typename R> __device__ __forceinline__ typename R::State warp_merge(typename R::State s) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s = R::merge(s, R::shfl(s, d));
+    return s;
+}
+
+// ---- inner == 1: one CTA (GROUP == kBlock) or one warp (GROUP == 32) per (row, chunk) -----------
+template <typename T, typename R, int GROUP>
+__global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ src, size_t rows, size_t len, ptrdiff_t pitch,
+                                                          size_t split, typename R::State *partial, typename R::Out *dst,
+                                                          ExtSettings st) {
+    using State = typename R::State;
+    using V = Vec128<T>;
+    constexpr int N = V::N;
+    constexpr int U = 4;  // vectors in flight per thread
+    __shared__ State smem[kWarps];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = GROUP == kBlock ? (int)threadIdx.x : lane;
+    const size_t items = rows * split;
+    const size_t per = (len + split - 1) / split;
+    const size_t first = GROUP == kBlock ? blockIdx.x : (size_t)blockIdx.x * kWarps + warp;
+    const size_t step = GROUP == kBlock ? gridDim.x : (size_t)gridDim.x * kWarps;
+    // every thread of a CTA runs the same number of iterations when GROUP == kBlock (block barriers)
+    for (size_t item = first; item < items; item += step) {
+        const size_t row = item / split, chunk = item % split;
+        const size_t k0 = chunk * per < len ? chunk * per : len;
+        const size_t k1 = k0 + per < len ? k0 + per : len;
+        const T *p = src + (ptrdiff_t)row * pitch;
+        State s = R::identity();
+        if (k0 < k1) {
+            const size_t mis = (reinterpret_cast<uintptr_t>(p + k0) / sizeof(T)) % N;
+            size_t head = mis ? N - mis : 0;
+            if (head > k1 - k0) head = k1 - k0;
+            if ((size_t)tid < head) R::add_one(s, p[k0 + tid], k0 + tid);
+            const size_t kb = k0 + head;
+            const size_t nvec = (k1 - kb) / N;
+            const uint4 *pv = reinterpret_cast<const uint4 *>(p + kb);
+            size_t v = tid;
+            for (; v + (U - 1) * GROUP < nvec; v += U * GROUP) {
+                typename V::U x[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) x[u].q = pv[v + u * GROUP];
+                if (!R::kPositional) {
+                    T flat[U * N];
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int e = 0; e < N; ++e) flat[u * N + e] = x[u].e[e];
+                    R::template add_batch<U * N>(s, flat, 0ull, 0ull);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) R::template add_batch<N>(s, x[u].e, kb + (v + u * GROUP) * N, 1ull);
+                }
+            }
+            for (; v < nvec; v += GROUP) {
+                typename V::U x;
+                x.q = pv[v];
+                R::template add_batch<N>(s, x.e, kb + v * N, 1ull);
+            }
+            const size_t kt = kb + nvec * N;
+            if (kt + tid < k1) R::add_one(s, p[kt + tid], kt + tid);
+        }
+        s = warp_merge<R>(s);
+        if (GROUP == kBlock) {
+            if (lane == 0) smem[warp] = s;
+            __syncthreads();
+            if (warp == 0) {
+                s = lane < kWarps ? smem[lane] : R::identity();
+#pragma unroll
+                for (int d = kWarps / 2; d > 0; d >>= 1) s = R::merge(s, R::shfl(s, d));
+            }
+            __syncthreads();
+            if (threadIdx.x != 0) continue;
+        } else if (lane != 0) {
+            continue;
+        }
+        if (split == 1) dst[row] = R::finish(s, st);
+        else partial[row * split + chunk] = s;
+    }
+}
+
+// ---- inner > 1 (or strided rows): tiles of 32 x VW columns, the 8 warps of a CTA along k --------
+template <typename T, typename R, int VW>
+__global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ src, size_t outer, size_t len, size_t inner,
+                                                          ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t split,
+                                                          typename R::State *partial, typename R::Out *dst, ExtSettings st) {
+    using State = typename R::State;
+    constexpr int U = 4;  // rows in flight per thread
+    __shared__ State smem[kWarps][32][VW];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t col_tiles = (inner + 32 * VW - 1) / (32 * VW);
+    const size_t per = (len + split - 1) / split;
+    const size_t items = outer * split * col_tiles;
+    for (size_t item = blockIdx.x; item < items; item += gridDim.x) {
+        size_t q = item;
+        const size_t col = ((q % col_tiles) * 32 + lane) * VW; q /= col_tiles;
+        const size_t chunk = q % split;
+        const size_t o = q / split;
+        const size_t k0 = chunk * per < len ? chunk * per : len;
+        const size_t k1 = k0 + per < len ? k0 + per : len;
+        State s[VW];
+#pragma unroll
+        for (int c = 0; c < VW; ++c) s[c] = R::identity();
+        if (col < inner) {
+            const T *p = src + (ptrdiff_t)o * outer_stride + (ptrdiff_t)col;
+            size_t k = k0 + warp;
+            for (; k + (U - 1) * kWarps < k1; k += U * kWarps) {
+                T x[U][VW];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const T *pr = p + (ptrdiff_t)(k + u * kWarps) * row_stride;
+                    if (VW > 1) {
+                        typename Vec128<T>::U t;
+                        t.q = *reinterpret_cast<const uint4 *>(pr);
+#pragma unroll
+                        for (int c = 0; c < VW; ++c) x[u][c] = t.e[c];
+                    } else {
+                        x[u][0] = *pr;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < VW; ++c) {
+                    T colv[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) colv[u] = x[u][c];
+                    R::template add_batch<U>(s[c], colv, k, (unsigned long long)kWarps);
+                }
+            }
+            for (; k < k1; k += kWarps) {
+                const T *pr = p + (ptrdiff_t)k * row_stride;
+                if (VW > 1) {
+                    typename Vec128<T>::U t;
+                    t.q = *reinterpret_cast<const uint4 *>(pr);
+#pragma unroll
+                    for (int c = 0; c < VW; ++c) R::add_one(s[c], t.e[c], k);
+                } else {
+                    R::add_one(s[0], *pr, k);
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < VW; ++c) smem[warp][lane][c] = s[c];
+        __syncthreads();
+        if (warp == 0 && col < inner) {
+#pragma unroll
+            for (int c = 0; c < VW; ++c) {
+                State t = smem[0][lane][c];
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) t = R::merge(t, smem[w][lane][c]);
+                if (split == 1) dst[o * inner + col + c] = R::finish(t, st);
+                else partial[(o * split + chunk) * inner + col + c] = t;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- second pass: a warp per output merges the chunk states -------------------------------------
+template <typename R>
+__global__ void __launch_bounds__(kBlock) ext_finish_kernel(const typename R::State *partial, size_t outer, size_t split,
+                                                            size_t inner, typename R::Out *dst, ExtSettings st) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t outputs = outer * inner;
+    for (size_t idx = (size_t)blockIdx.x * kWarps + warp; idx < outputs; idx += (size_t)gridDim.x * kWarps) {
+        const size_t o = idx / inner, i = idx % inner;
+        typename R::State s = R::identity();
+        for (size_t c = lane; c < split; c += 32) s = R::merge(s, partial[(o * split + c) * inner + i]);
+        s = warp_merge<R>(s);
+        if (lane == 0) dst[idx] = R::finish(s, st);
+    }
+}
+
+unsigned grid_of(size_t items) { return (unsigned)(items < kGridCap ? (items ? items : 1) : kGridCap); }
+
+template <typename T, typename R>
+int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, ptrdiff_t outer_stride, ptrdiff_t row_stride,
+               void *dst_raw, ExtSettings st) {
+    using State = typename R::State;
+    using Out = typename R::Out;
+    constexpr size_t N = Vec128<T>::N;
+    Out *dst = static_cast<Out *>(dst_raw);
+    if (outer == 0 || inner == 0) return RTB_OK;
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
+    const size_t want = (size_t)ctx->sm_count * 4;  // work items that fill the GPU
+    State *partial = nullptr;
+    size_t split = 1;
+    auto get_partial = [&](size_t states) {
+        void *ws = nullptr;
+        int rc = workspace(ctx, states * sizeof(State), &ws);
+        if (rc == RTB_OK) partial = reinterpret_cast<State *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
+        return rc;
+    };
+    int rc = RTB_OK;
+    if (inner == 1 && row_stride == 1) {
+        if (outer < want && len >= 8192) {
+            split = (want + outer - 1) / outer;
+            if (split > len / 4096) split = len / 4096;
+        }
+        if (split > 1 && (rc = get_partial(outer * split)) != RTB_OK) return rc;
+        const size_t items = outer * split;
+        if ((len + split - 1) / split >= 1024)
+            ext_rows_kernel<T, R, kBlock><<<grid_of(items), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split, partial, dst, st);
+        else
+            ext_rows_kernel<T, R, 32><<<grid_of((items + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split,
+                                                                                                 partial, dst, st);
+        rc = check_launch(ctx, "ext_rows_kernel");
+    } else {
+        const bool vec = inner % N == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && outer_stride % (ptrdiff_t)N == 0 &&
+                         row_stride % (ptrdiff_t)N == 0;
+        const size_t cols_per_tile = 32 * (vec ? N : 1);
+        const size_t base = outer * ((inner + cols_per_tile - 1) / cols_per_tile);
+        if (base < want && len >= 128) {
+            split = (want + base - 1) / base;
+            if (split > len / 32) split = len / 32;
+        }
+        if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
+        const unsigned grid = grid_of(base * split);
+        if (vec)
+            ext_cols_kernel<T, R, (int)N><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
+                                                                            dst, st);
+        else
+            ext_cols_kernel<T, R, 1><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial, dst,
+                                                                       st);
+        rc = check_launch(ctx, "ext_cols_kernel");
+    }
+    if (rc != RTB_OK || split == 1) return rc;
+    ext_finish_kernel<R><<<grid_of((outer * inner + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(partial, outer, split, inner, dst, st);
+    return check_launch(ctx, "ext_finish_kernel");
+}
+
+template <typename T>
+int ext_by_op(Ctx *ctx, int redop, const rtb_reduce_settings *set, const T *src, size_t outer, size_t len, size_t inner,
+              ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst) {
+    ExtSettings st{set ? (int)set->unbiased : 1, set ? (int)set->is_std : 0};
+    switch (redop) {
+        case RTB_VARIANCE: return ext_launch<T, RedVar<T>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+        case RTB_LOGSUMEXP: return ext_launch<T, RedLse<T>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+        case RTB_NORM: {
+            const int p = set ? set->norm_type : 2;
+            if (p == 1) return ext_launch<T, RedNorm<T, 1>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+            if (p == 2) return ext_launch<T, RedNorm<T, 2>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+            return fail(RTB_ERR_INVALID, "norm type %d is not 1 or 2", p);
+        }
+        case RTB_ARGMAX: return ext_launch<T, RedArg<T, true>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+        case RTB_ARGMIN: return ext_launch<T, RedArg<T, false>>(ctx, src, outer, len, inner, outer_stride, row_stride, dst, st);
+    }
+    return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
+}
+
+}  // namespace
+
+int launch_reduce_ext(Ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src, size_t outer, size_t r,
+                      size_t inner, ptrdiff_t outer_stride, ptrdiff_t row_stride, void *dst) {
+    if (dtype == RTB_F32)
+        return ext_by_op<float>(ctx, redop, settings, (const float *)src, outer, r, inner, outer_stride, row_stride, dst);
+    if (dtype == RTB_F64)
+        return ext_by_op<double>(ctx, redop, settings, (const double *)src, outer, r, inner, outer_stride, row_stride, dst);
+    return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
+}
+
+}  // namespace rtb

@@ -173,6 +173,34 @@ class Tensor:
     def min_at(self, axis): return self._reduce(L.MIN, axis)
     def prod_at(self, axis): return self._reduce(L.PROD, axis)
 
+    # The reductions only the reference's CUDA backend implements (ReductionOp, src/ops/reduction/mod.rs:413-510).
+    def _reduce_ex(self, op: int, axis: Optional[int], unbiased=True, is_std=False, norm_type=2) -> "Tensor":
+        b = self.backend
+        if axis is not None and not 0 <= axis < self.rank:
+            raise ValueError(f"axis {axis} out of range for rank {self.rank}")
+        out = b.reduce_view_ex(self.buf, self.meta, axis, op, unbiased, is_std, norm_type)
+        shape = () if axis is None else tuple(1 if k == axis else s for k, s in enumerate(self.shape))
+        return Tensor(b, out, Meta.contiguous(shape))
+
+    def var_at(self, axis): return self._reduce_ex(L.VARIANCE, axis, True)
+    def pop_var_at(self, axis): return self._reduce_ex(L.VARIANCE, axis, False)
+    def std_at(self, axis, unbiased=True): return self._reduce_ex(L.VARIANCE, axis, unbiased, True)
+    def norm_at(self, axis, norm_type=2): return self._reduce_ex(L.NORM, axis, norm_type=norm_type)
+    def l1_norm_at(self, axis): return self.norm_at(axis, 1)
+    def l2_norm_at(self, axis): return self.norm_at(axis, 2)
+    def logsumexp_at(self, axis): return self._reduce_ex(L.LOGSUMEXP, axis)
+    def argmax_at(self, axis): return self._reduce_ex(L.ARGMAX, axis)
+    def argmin_at(self, axis): return self._reduce_ex(L.ARGMIN, axis)
+    def var(self): return self.var_at(None)
+    def pop_var(self): return self.pop_var_at(None)
+    def std(self, unbiased=True): return self.std_at(None, unbiased)
+    def norm(self, norm_type=2): return self.norm_at(None, norm_type)
+    def l1_norm(self): return self.norm_at(None, 1)
+    def l2_norm(self): return self.norm_at(None, 2)
+    def logsumexp(self): return self.logsumexp_at(None)
+    def argmax(self): return self.argmax_at(None)
+    def argmin(self): return self.argmin_at(None)
+
 
 def mean_l1_loss(a: Tensor, b: Tensor, with_grad: bool = False):
     """mean(|a - b|) as a rank-0 tensor (src/ops/broadcast/l1.rs:79-84); with_grad also returns the

@@ -67,6 +67,22 @@ class CudaEngine:
         self.b.apply_reduce_contiguous_flat(d, out, am.offset, am.size, op)
         return to_host(out)[0]
 
+    def reduce_ext(self, a, am, axis, code, unbiased, is_std, norm_type):
+        import torch
+        d = to_dev(a)
+        if axis is None:
+            # Idx::Item goes to the flat launcher over [offset, offset + size) (ops/reduction/mod.rs:262-279)
+            flat = self.Meta.contiguous((am.size,))
+            flat = type(flat)(flat.shape, flat.strides, am.offset)
+            shape, src = (), (d, flat)
+        else:
+            shape, src = tuple(1 if k == axis else s for k, s in enumerate(am.shape)), (d, am)
+        n = max(int(np.prod(shape)), 1)
+        out = self.b.alloc(n, torch.int64 if code >= 9 else d.dtype)
+        self.b.apply_reduce_ex(src, out, 0 if axis is None else axis, code, unbiased, is_std, norm_type)
+        h = to_host(out)
+        return (h.view(np.uint64) if code >= 9 else h), shape
+
     def reduce_axis(self, a, am, axis, op):
         d = to_dev(a)
         oshape = tuple(1 if k == axis else s for k, s in enumerate(am.shape))

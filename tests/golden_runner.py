@@ -24,6 +24,11 @@ TRUTH = {
     "cube": lambda x: x * x * x, "exp": np.exp,
 }
 RED = {"sum": 1, "prod": 2, "max": 3, "min": 4, "mean": 5}
+# name -> (code, unbiased, is_std, norm_type): the ReductionSettings the reference front end sends
+# (ops/reduction/mod.rs:413-510)
+RED_EXT = {"var": (6, True, False, 2), "pop_var": (6, False, False, 2), "std": (6, True, True, 2),
+           "pop_std": (6, False, True, 2), "logsumexp": (7, True, False, 2), "l1": (8, True, False, 1),
+           "l2": (8, True, False, 2), "argmax": (9, True, False, 2), "argmin": (10, True, False, 2)}
 
 
 def build_tensor(spec, dtype, engine):
@@ -121,6 +126,19 @@ def run_case(case, engine):
         a, am = build_tensor(case["a"], case["dtype"], engine)
         out, shape = engine.reduce_axis(a, am, case["axis"], RED[case["op"]])
         check_values(case, out, shape)
+    elif kind == "reduce_ext":
+        a, am = build_tensor(case["a"], case["dtype"], engine)
+        code, unbiased, is_std, norm_type = RED_EXT[case["op"]]
+        out, shape = engine.reduce_ext(a, am, case["axis"], code, unbiased, is_std, norm_type)
+        assert list(shape) == list(case["shape"]), (case["name"], shape)
+        out = np.asarray(out)[: len(case["values"])]
+        if code >= 9:
+            assert out.dtype == np.uint64 and out.tolist() == case["values"], (case["name"], out)
+        else:
+            exp = np.array(case["values"], dtype=a.dtype)
+            # a device engine merges partial states in tree order: a few ulps from the listed values
+            ulps = 8 if getattr(engine, "tree_sums", False) else 0
+            assert np.all(np.abs(out - exp) <= ulps * np.spacing(np.abs(exp))), (case["name"], out, exp)
     elif kind == "unary_fixture":
         dt = NP[case["dtype"]]
         d = np.array(case["definition"], dtype=dt)
@@ -202,3 +220,16 @@ class OracleEngine:
     def reduce_axis(self, a, am, axis, op):
         out, om = self.o.reduce_axis(a, am, axis, op, self.fast)
         return out, om.shape
+
+    def reduce_ext(self, a, am, axis, code, unbiased, is_std, norm_type):
+        assert am.is_contiguous()
+        if axis is None:
+            outer, r, inner, shape = 1, am.size, 1, ()
+        else:
+            outer = int(np.prod(am.shape[:axis], dtype=np.int64))
+            r, inner = am.shape[axis], int(np.prod(am.shape[axis + 1:], dtype=np.int64))
+            shape = tuple(1 if k == axis else s for k, s in enumerate(am.shape))
+        src = a[am.offset:]
+        if code >= 9:
+            return self.o.argreduce_ori(src, outer, r, inner, code, self.fast), shape
+        return self.o.reduce_ext_ori(src, outer, r, inner, code, unbiased, is_std, norm_type, self.fast), shape

@@ -890,3 +890,144 @@ def test_broadcast_reduce_matches_materialise_then_reduce():
             want, _ = O.reduce_axis(full, fm, axis, O.SUM)
             got, _ = _b().broadcast_reduce(_dev(a), _meta_pair(am), _dev(b), _meta_pair(bm), O.ADD, axis, O.SUM)
             assert np.allclose(_host(got)[: want.size], want, rtol=1e-5, atol=1e-5)
+
+
+# ------------------------------------------------------------------------------------- variance / std / norm / logsumexp / argmax
+_EXT_LAYOUTS = [(1, 1, 1), (2, 1, 50), (1, 1000003, 1), (7, 5000, 1), (300, 37, 1), (64, 9000, 1), (5, 333, 64), (3, 1000, 33),
+                (1, 4096, 256), (40, 10, 1), (1, 70000, 8)]
+
+
+def _ext_truth(x64, code, unbiased, is_std, norm_type):
+    """f64 ground truth over axis 1 of a (outer, R, inner) array."""
+    if code == O.VARIANCE:
+        n = x64.shape[1]
+        ddof = 1 if unbiased else 0
+        v = x64.var(axis=1, ddof=ddof) if n - ddof > 0 else np.zeros((x64.shape[0], x64.shape[2]))
+        return np.sqrt(v) if is_std else v
+    if code == O.NORM:
+        return np.abs(x64).sum(axis=1) if norm_type == 1 else np.sqrt((x64 * x64).sum(axis=1))
+    m = x64.max(axis=1, keepdims=True)
+    return (m + np.log(np.exp(x64 - m).sum(axis=1, keepdims=True)))[:, 0, :]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64], ids=["f32", "f64"])
+@pytest.mark.parametrize("outer,r,inner", _EXT_LAYOUTS)
+def test_ext_reductions_match_oracle_and_f64_truth(dt, outer, r, inner):
+    rng = np.random.default_rng(outer * 1315423911 % (1 << 31) + r * 7 + inner)
+    off = 3  # an odd start: rows are not 16-byte aligned
+    n = outer * r * inner
+    buf = (rng.standard_normal(n + off) * 1.5 + 0.5).astype(dt)
+    x = buf[off:]
+    x64 = x.astype(np.float64).reshape(outer, r, inner)
+    d = _dev(buf)
+    from rtensors_b200.meta import Meta
+    meta = Meta((outer, r, inner), (r * inner, inner, 1), off)
+    eps = 1e-5 if dt == np.float32 else 1e-13
+    tol = eps * max(math.log2(max(r, 2)), 1.0)
+    for code, unbiased, is_std, norm_type in [(O.VARIANCE, True, False, 2), (O.VARIANCE, False, False, 2),
+                                              (O.VARIANCE, True, True, 2), (O.VARIANCE, False, True, 2),
+                                              (O.LOGSUMEXP, True, False, 2), (O.NORM, True, False, 1), (O.NORM, True, False, 2)]:
+        out = _b().alloc(outer * inner, d.dtype)
+        _b().apply_reduce_ex((d, meta), out, 1, code, unbiased, is_std, norm_type)
+        got = _host(out).astype(np.float64).reshape(outer, inner)
+        truth = _ext_truth(x64, code, unbiased, is_std, norm_type)
+        scale = np.maximum(np.abs(truth), 1e-30)
+        assert np.all(np.abs(got - truth) <= tol * scale + 1e-300), (code, unbiased, is_std, norm_type,
+                                                                     float(np.max(np.abs(got - truth) / scale)))
+        if r <= 70000:  # the sequential oracle itself drifts from the truth on longer runs
+            want = O.reduce_ext_ori(x, outer, r, inner, code, unbiased, is_std, norm_type).astype(np.float64).reshape(outer, inner)
+            otol = tol if dt == np.float64 or r <= 10000 else 20 * tol
+            assert np.all(np.abs(got - want) <= otol * scale + 1e-300), (code, unbiased, is_std, norm_type)
+    # positions: exact, also with many equal values (first position wins)
+    for data in (buf, np.round(buf * 2).astype(dt)):
+        dd = _dev(data)
+        for code in (O.ARGMAX, O.ARGMIN):
+            out = _b().alloc(outer * inner, torch.int64)
+            _b().apply_reduce_ex((dd, meta), out, 1, code)
+            want = O.argreduce_ori(data[off:], outer, r, inner, code)
+            assert np.array_equal(_host(out).view(np.uint64), want), (code,)
+
+
+def test_ext_reductions_flat_rank1_and_edge_values():
+    from rtensors_b200.meta import Meta
+    b = _b()
+    x = np.array([3.0, -1.0, 3.0, 7.5, 7.5, -2.0], dtype=np.float32)
+    d = _dev(x)
+    m = Meta((6,), (1,), 0)
+    for code, args, want in [(O.VARIANCE, (True, False, 2), np.var(x.astype(np.float64), ddof=1)),
+                             (O.NORM, (True, False, 1), 24.0), (O.LOGSUMEXP, (True, False, 2), None)]:
+        out = b.alloc(1, torch.float32)
+        b.apply_reduce_ex((d, m), out, 0, code, *args)
+        ref = O.reduce_ext_ori(x, 1, 6, 1, code, *args)[0]
+        assert abs(float(_host(out)[0]) - float(ref)) <= 1e-6 * abs(float(ref))
+        if want is not None:
+            assert abs(float(_host(out)[0]) - want) <= 1e-6 * abs(want)
+    for code, want in ((O.ARGMAX, 3), (O.ARGMIN, 5)):
+        out = b.alloc(1, torch.int64)
+        b.apply_reduce_ex((d, m), out, 0, code)
+        assert int(_host(out)[0]) == want
+    # one element: variance 0 (both denominators), std 0; logsumexp = the element; argmax 0
+    one = _dev(np.array([4.25], dtype=np.float64))
+    m1 = Meta((1,), (1,), 0)
+    for args in ((True, False, 2), (False, False, 2), (True, True, 2)):
+        out = b.alloc(1, torch.float64)
+        b.apply_reduce_ex((one, m1), out, 0, O.VARIANCE, *args)
+        assert float(_host(out)[0]) == 0.0
+    out = b.alloc(1, torch.float64)
+    b.apply_reduce_ex((one, m1), out, 0, O.LOGSUMEXP)
+    assert float(_host(out)[0]) == 4.25
+    # nothing compares above lowest(): position 0, as in the reference kernel
+    ninf = _dev(np.full(70, -np.inf, dtype=np.float32))
+    out = b.alloc(1, torch.int64)
+    b.apply_reduce_ex((ninf, Meta((70,), (1,), 0)), out, 0, O.ARGMAX)
+    assert int(_host(out)[0]) == 0
+    # unknown norm type and unknown code are refused
+    out = b.alloc(1, torch.float32)
+    with pytest.raises(Exception):
+        b.apply_reduce_ex((d, m), out, 0, O.NORM, True, False, 3)
+    with pytest.raises(Exception):
+        b.apply_reduce_ex((d, m), out, 0, 11)
+
+
+def test_ext_reductions_over_views_and_tensor_api():
+    import rtensors_b200 as rt
+    from rtensors_b200.meta import Meta
+    rng = np.random.default_rng(77)
+    S = 96
+    buf = rng.standard_normal(S * S).astype(np.float32)
+    d = _dev(buf)
+    full = O.Meta.contiguous((S, S))
+    views = [full.slice(1, 8, 72, 1),                      # window: rows with a pitch
+             full.permute((1, 0)),                         # transposed
+             full.slice(0, None, None, -1),                # rows reversed
+             full.slice(1, None, None, 2),                 # strided inner: copy fallback
+             O.Meta.contiguous((S * S,)).slice(0, None, None, -1)]  # reversed flat run
+    for vm in views:
+        dense = gather_view(buf, vm).reshape(vm.shape)
+        for axis in [None] + list(range(len(vm.shape))):
+            for code, args in [(O.VARIANCE, (True, True, 2)), (O.LOGSUMEXP, (True, False, 2)), (O.NORM, (True, False, 2)),
+                               (O.ARGMAX, (True, False, 2)), (O.ARGMIN, (True, False, 2))]:
+                got = _host(_b().reduce_view_ex(d, _meta_pair(vm), axis, code, *args))
+                if axis is None:
+                    outer, r, inner = 1, dense.size, 1
+                else:
+                    outer = int(np.prod(dense.shape[:axis], dtype=np.int64))
+                    r, inner = dense.shape[axis], int(np.prod(dense.shape[axis + 1:], dtype=np.int64))
+                flat = np.ascontiguousarray(dense).reshape(-1)
+                if code >= O.ARGMAX:
+                    want = O.argreduce_ori(flat, outer, r, inner, code)
+                    assert np.array_equal(got.view(np.uint64)[: want.size], want), (vm, axis, code)
+                else:
+                    want = O.reduce_ext_ori(flat, outer, r, inner, code, *args)
+                    assert np.allclose(got[: want.size], want, rtol=2e-4, atol=1e-6), (vm, axis, code)
+    # Tensor front end: names and result shapes of ReductionOp / TotalReductionOp
+    t = rt.Tensor.from_buf([1., 2., 3., 4., 5., 6., 7., 8.], (4, 2), np.float64, _b())
+    assert t.var_at(0).shape == (1, 2) and np.allclose(t.var_at(0).cpu().reshape(-1), [6.666666666666667] * 2)
+    assert np.allclose(t.pop_var_at(0).cpu().reshape(-1), [5., 5.])
+    assert np.allclose(t.std_at(0, False).cpu().reshape(-1), [2.23606797749979] * 2)
+    assert np.allclose(t.logsumexp_at(0).cpu().reshape(-1), [7.145077938960783, 8.145077938960782])
+    assert np.allclose(t.l1_norm_at(0).cpu().reshape(-1), [16., 20.])
+    assert np.allclose(t.l2_norm_at(1).cpu().reshape(-1), np.sqrt([5., 25., 61., 113.]))
+    assert float(t.var().cpu().reshape(-1)[0]) == 6.0 and abs(float(t.std(False).cpu().reshape(-1)[0]) - 2.29128784747792) < 1e-14
+    assert int(t.argmax().cpu().reshape(-1)[0]) == 7 and int(t.argmin().cpu().reshape(-1)[0]) == 0
+    assert t.argmax_at(1).shape == (4, 1) and t.argmax_at(1).cpu().reshape(-1).tolist() == [1, 1, 1, 1]
