@@ -28,7 +28,8 @@ struct ExtSettings {
     int is_std;
 };
 
-__device__ __forceinline__ float t_exp(float x) { return expf(x); }
+// f32 logsumexp terms use the hardware exponential (2 ulp), as the reference's fast-math build does
+__device__ __forceinline__ float t_exp(float x) { return __expf(x); }
 __device__ __forceinline__ double t_exp(double x) { return exp(x); }
 __device__ __forceinline__ float t_log(float x) { return logf(x); }
 __device__ __forceinline__ double t_log(double x) { return log(x); }
@@ -36,6 +37,13 @@ __device__ __forceinline__ float t_sqrt(float x) { return sqrtf(x); }
 __device__ __forceinline__ double t_sqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float t_abs(float x) { return fabsf(x); }
 __device__ __forceinline__ double t_abs(double x) { return fabs(x); }
+// The library is built without FMA contraction so that single operations round as on the CPU; these
+// reductions are tolerance-checked (the reference's own build contracts them), so they fuse by hand.
+__device__ __forceinline__ float t_fma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ double t_fma(double a, double b, double c) { return fma(a, b, c); }
+// weight nb / (na + nb) of a state merge: a 2-ulp quotient is ample for f32 weights
+__device__ __forceinline__ float t_ratio(float a, float b) { return __fdividef(a, b); }
+__device__ __forceinline__ double t_ratio(double a, double b) { return a / b; }
 template <typename T> __device__ __forceinline__ T t_lowest();
 template <> __device__ __forceinline__ float t_lowest<float>() { return -FLT_MAX; }
 template <> __device__ __forceinline__ double t_lowest<double>() { return -DBL_MAX; }
@@ -61,11 +69,11 @@ template <typename T> struct RedVar {
         if (b.n == 0) return a;
         if (a.n == 0) return b;
         const T na = (T)a.n, nb = (T)b.n;
-        const T w = nb / (na + nb);
+        const T w = t_ratio(nb, na + nb);
         const T delta = b.mean - a.mean;
         State r;
-        r.mean = a.mean + delta * w;
-        r.m2 = a.m2 + b.m2 + (delta * delta) * (na * w);
+        r.mean = t_fma(delta, w, a.mean);
+        r.m2 = t_fma(delta * delta, na * w, a.m2 + b.m2);
         r.n = a.n + b.n;
         return r;
     }
@@ -79,7 +87,7 @@ template <typename T> struct RedVar {
 #pragma unroll
         for (int e = 0; e < NB; ++e) {
             const T d = x[e] - bm;
-            m2 += d * d;
+            m2 = t_fma(d, d, m2);
         }
         s = merge(s, State{bm, m2, (unsigned long long)NB});
     }
@@ -137,14 +145,14 @@ template <typename T, int P> struct RedNorm {
     };
     __device__ static State identity() { return State{(T)0}; }
     __device__ static State merge(const State &a, const State &b) { return State{a.v + b.v}; }
-    __device__ static T term(T x) { return P == 1 ? t_abs(x) : x * x; }
+    __device__ static T accum(T acc, T x) { return P == 1 ? acc + t_abs(x) : t_fma(x, x, acc); }
     template <int NB> __device__ static void add_batch(State &s, const T (&x)[NB], unsigned long long, unsigned long long) {
-        T acc = term(x[0]);
+        T acc = accum((T)0, x[0]);
 #pragma unroll
-        for (int e = 1; e < NB; ++e) acc += term(x[e]);
+        for (int e = 1; e < NB; ++e) acc = accum(acc, x[e]);
         s.v += acc;
     }
-    __device__ static void add_one(State &s, T x, unsigned long long) { s.v += term(x); }
+    __device__ static void add_one(State &s, T x, unsigned long long) { s.v = accum(s.v, x); }
     __device__ static State shfl(const State &s, int d) { return State{shfl_down_any(s.v, d)}; }
     __device__ static Out finish(const State &s, ExtSettings) { return P == 2 ? t_sqrt(s.v) : s.v; }
 };
@@ -268,7 +276,7 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                                                           ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t split,
                                                           typename R::State *partial, typename R::Out *dst, ExtSettings st) {
     using State = typename R::State;
-    constexpr int U = 4;  // rows in flight per thread
+    constexpr int U = 8;  // rows in flight per thread
     __shared__ State smem[kWarps][32][VW];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t col_tiles = (inner + 32 * VW - 1) / (32 * VW);
@@ -353,6 +361,13 @@ __global__ void __launch_bounds__(kBlock) ext_finish_kernel(const typename R::St
     }
 }
 
+// CTAs of `kernel` that are resident at once on the whole GPU
+template <typename K> size_t resident_ctas(Ctx *ctx, K kernel) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    return (size_t)ctx->sm_count * (size_t)per_sm;
+}
+
 unsigned grid_of(size_t items) { return (unsigned)(items < kGridCap ? (items ? items : 1) : kGridCap); }
 
 template <typename T, typename R>
@@ -392,10 +407,12 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
                          row_stride % (ptrdiff_t)N == 0;
         const size_t cols_per_tile = 32 * (vec ? N : 1);
         const size_t base = outer * ((inner + cols_per_tile - 1) / cols_per_tile);
-        if (base < want && len >= 128) {
-            split = (want + base - 1) / base;
-            if (split > len / 32) split = len / 32;
-        }
+        // CTAs do equal work, so the launch is fastest as ONE wave of resident CTAs: as many chunks
+        // of k per tile as fit, each at least 64 rows
+        const size_t resident = vec ? resident_ctas(ctx, ext_cols_kernel<T, R, (int)N>) : resident_ctas(ctx, ext_cols_kernel<T, R, 1>);
+        split = resident / base;
+        if (split > len / 64) split = len / 64;
+        if (split < 1) split = 1;
         if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
         const unsigned grid = grid_of(base * split);
         if (vec)

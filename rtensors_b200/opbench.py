@@ -166,6 +166,22 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     for opn, op in (("sum", L.SUM), ("mean", L.MEAN), ("max", L.MAX), ("min", L.MIN)):
         add(f"{opn}_at(1) f32", str(d3), 4 * (m3.size + d3[0] * d3[2]), m3.size,
             (lambda op=op: be.apply_reduce((src, m3), r3, 1, op)))
+    # state-merging reductions (variance / std, logsumexp, L2 norm, argmax) on the same tensors
+    ri = be.alloc(max(S, d3[0] * d3[2]), torch.int64)
+    ext = (("var", L.VARIANCE, (True, False, 2), r1, r3), ("std", L.VARIANCE, (True, True, 2), r1, r3),
+           ("logsumexp", L.LOGSUMEXP, (True, False, 2), r1, r3), ("l2_norm", L.NORM, (True, False, 2), r1, r3),
+           ("argmax", L.ARGMAX, (True, False, 2), ri, ri))
+    for opn, op, args, o1, o3 in ext:
+        for axis in (0, 1):
+            add(f"{opn}_at({axis}) f32", f"({S},{S})", 4 * (S * S + S), S * S,
+                (lambda op=op, axis=axis, args=args, o1=o1: be.apply_reduce_ex((src, msq), o1, axis, op, *args)),
+                flush=S * S * 4 < (200 << 20))
+        add(f"{opn}_at(1) f32", str(d3), 4 * (m3.size + d3[0] * d3[2]), m3.size,
+            (lambda op=op, args=args, o3=o3: be.apply_reduce_ex((src, m3), o3, 1, op, *args)))
+    mflat = Meta.contiguous((n4,))
+    for opn, op, args, o1, o3 in ext:
+        add(f"{opn} (full) f32", f"2^{int(np.log2(n4))}", 4 * n4 + 4, n4,
+            (lambda op=op, args=args, o1=o1: be.apply_reduce_ex((src, mflat), o1, 0, op, *args)))
     r0 = be.alloc(1, f32)
     nflat = n4
     if world == 1:
