@@ -39,7 +39,9 @@ RTB200_DT(unsigned __int128, RTB_U128) RTB200_DT(__int128, RTB_I128)
 #undef RTB200_DT
 
 enum class BinaryOpType { Add = 0, Sub = 1, Mul = 2, Div = 3 };
-enum class ReductionOpTypes { Sum = 1, Prod = 2, Max = 3, Min = 4, Mean = 5 };
+// codes of ReductionOpTypes::get_code (src/ops/reduction/mod.rs:160-175); Variance also covers Stdev
+enum class ReductionOpTypes { Sum = 1, Prod = 2, Max = 3, Min = 4, Mean = 5, Variance = 6, LogSumExp = 7, Norm = 8, ArgMax = 9, ArgMin = 10 };
+enum class NormType { L1 = 1, L2 = 2 };
 
 struct Slice {
     std::optional<size_t> start, end;
@@ -194,6 +196,16 @@ class Cuda {
         for (size_t k = dim + 1; k < sm.rank(); ++k) inner *= sm.shape[k];
         check(rtb_reduce_axis(ctx_, DTypeOf<T>::value, (int)op, src.ptr, sm.offset, outer, sm.shape[dim], inner, dst.ptr));
     }
+    // any reduction code over a view, the op's settings alongside (variance / std / norm); Out is T,
+    // or uint64_t for ArgMax / ArgMin.  axis < 0 reduces everything.
+    template <typename T, typename Out>
+    void reduce_view(const Buf<T> &src, const MetaTensor &m, ptrdiff_t axis, ReductionOpTypes op, Buf<Out> &dst, bool unbiased = true,
+                     bool is_std = false, NormType norm = NormType::L2) const {
+        check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, src.len));
+        rtb_reduce_settings st{unbiased, is_std, (int)norm};
+        check(rtb_reduce_view_ex(ctx_, DTypeOf<T>::value, (int)op, &st, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset,
+                                 axis, dst.ptr));
+    }
     template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
         check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
     }
@@ -346,6 +358,38 @@ template <typename T> class TensorBase {
     TensorBase max_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Max); }
     TensorBase min_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Min); }
     TensorBase prod_at(size_t a) const { return reduce_at(a, ReductionOpTypes::Prod); }
+
+    // The reductions only the reference's CUDA backend implements (ReductionOp / TotalReductionOp,
+    // src/ops/reduction/mod.rs:199-250, 413-510); any view, no copy where its layout allows.
+    template <typename Out>
+    TensorBase<Out> reduce_ex(ptrdiff_t axis, ReductionOpTypes op, bool unbiased = true, bool is_std = false,
+                              NormType norm = NormType::L2) const {
+        if (axis >= (ptrdiff_t)meta.rank()) throw TensorError(RTB_ERR_DIM, "axis out of range");
+        std::vector<size_t> os;
+        if (axis >= 0) { os = meta.shape; os[axis] = 1; }
+        MetaTensor om = MetaTensor::contiguous(os);
+        TensorBase<Out> out{backend, backend->template alloc<Out>(om.size() ? om.size() : 1), om};
+        if (om.size()) backend->reduce_view(*buf, meta, axis, op, *out.buf, unbiased, is_std, norm);
+        return out;
+    }
+    TensorBase var_at(size_t a) const { return reduce_ex<T>((ptrdiff_t)a, ReductionOpTypes::Variance, true); }
+    TensorBase pop_var_at(size_t a) const { return reduce_ex<T>((ptrdiff_t)a, ReductionOpTypes::Variance, false); }
+    TensorBase std_at(size_t a, bool unbiased) const { return reduce_ex<T>((ptrdiff_t)a, ReductionOpTypes::Variance, unbiased, true); }
+    TensorBase norm_at(size_t a, NormType n) const { return reduce_ex<T>((ptrdiff_t)a, ReductionOpTypes::Norm, true, false, n); }
+    TensorBase l1_norm_at(size_t a) const { return norm_at(a, NormType::L1); }
+    TensorBase l2_norm_at(size_t a) const { return norm_at(a, NormType::L2); }
+    TensorBase logsumexp_at(size_t a) const { return reduce_ex<T>((ptrdiff_t)a, ReductionOpTypes::LogSumExp); }
+    TensorBase<uint64_t> argmax_at(size_t a) const { return reduce_ex<uint64_t>((ptrdiff_t)a, ReductionOpTypes::ArgMax); }
+    TensorBase<uint64_t> argmin_at(size_t a) const { return reduce_ex<uint64_t>((ptrdiff_t)a, ReductionOpTypes::ArgMin); }
+    TensorBase var() const { return reduce_ex<T>(-1, ReductionOpTypes::Variance, true); }
+    TensorBase pop_var() const { return reduce_ex<T>(-1, ReductionOpTypes::Variance, false); }
+    TensorBase std(bool unbiased) const { return reduce_ex<T>(-1, ReductionOpTypes::Variance, unbiased, true); }
+    TensorBase norm(NormType n) const { return reduce_ex<T>(-1, ReductionOpTypes::Norm, true, false, n); }
+    TensorBase l1_norm() const { return norm(NormType::L1); }
+    TensorBase l2_norm() const { return norm(NormType::L2); }
+    TensorBase logsumexp() const { return reduce_ex<T>(-1, ReductionOpTypes::LogSumExp); }
+    TensorBase<uint64_t> argmax() const { return reduce_ex<uint64_t>(-1, ReductionOpTypes::ArgMax); }
+    TensorBase<uint64_t> argmin() const { return reduce_ex<uint64_t>(-1, ReductionOpTypes::ArgMin); }
 };
 
 // mean(|input - target|) as a rank-0 tensor (src/ops/broadcast/l1.rs:79-84), fused

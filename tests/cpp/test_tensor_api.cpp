@@ -125,6 +125,33 @@ int main() {
         ASSERT_EQ(m.mean_at(1).cpu(), (std::vector<double>{1.5, 3.5, 5.5, 7.5}));
         ASSERT_EQ(m.mean_at(1).shape(), (std::vector<size_t>{4, 1}));
     }
+    {  // backend/cuda.rs:2320-2590: the reductions only the reference's CUDA backend has
+        auto near = [](double a, double b) { return std::fabs(a - b) <= 1e-14 * std::fabs(b); };
+        auto m = Tensor<double>::from_buf(cuda, {1, 2, 3, 4, 5, 6, 7, 8}, {4, 2});
+        ASSERT_EQ(m.var().item(), 6.0);
+        ASSERT_EQ(m.pop_var().item(), 5.25);
+        ASSERT_TRUE(near(m.std(true).item(), 2.449489742783178));
+        ASSERT_TRUE(near(m.std(false).item(), 2.29128784747792));
+        ASSERT_EQ(m.l1_norm().item(), 36.0);
+        ASSERT_TRUE(near(m.l2_norm().item(), 14.2828568570857));
+        ASSERT_EQ(m.pop_var_at(0).cpu(), (std::vector<double>{5, 5}));
+        ASSERT_EQ(m.var_at(0).shape(), (std::vector<size_t>{1, 2}));
+        ASSERT_TRUE(near(m.var_at(0).cpu()[1], 6.666666666666667));
+        ASSERT_TRUE(near(m.std_at(0, true).cpu()[0], 2.581988897471611));
+        ASSERT_TRUE(near(m.logsumexp_at(0).cpu()[0], 7.145077938960783));
+        ASSERT_TRUE(near(m.logsumexp_at(0).cpu()[1], 8.145077938960782));
+        ASSERT_EQ(m.l1_norm_at(0).cpu(), (std::vector<double>{16, 20}));
+        ASSERT_TRUE(near(m.l2_norm_at(0).cpu()[0], 9.16515138991168));
+        auto am = Tensor<double>::from_buf(cuda, {1, 4, 3, 2, 9, 6, 7, 1}, {4, 2});
+        ASSERT_EQ(am.argmax_at(0).cpu(), (std::vector<uint64_t>{2, 2}));
+        auto an = Tensor<double>::from_buf(cuda, {1, -4, 3, 2, 9, 6, -7, 1}, {4, 2});
+        ASSERT_EQ(an.argmin_at(0).cpu(), (std::vector<uint64_t>{3, 0}));
+        auto t = Tensor<double>::from_buf(cuda, {0.2, 0.3, 0.1, 0.7, 0.3, -0.1, -0.3, 0.3}, {4, 2});
+        ASSERT_EQ(t.argmax().item(), (uint64_t)3);
+        ASSERT_EQ(t.argmin().item(), (uint64_t)6);
+        // a transposed view reduces without a copy and counts positions in the view's own order
+        ASSERT_EQ(am.permute({1, 0}).argmax_at(1).cpu(), (std::vector<uint64_t>{2, 2}));
+    }
     {  // ops/unary/mod.rs:442-451 relu on the N-d strided fixture (testing/mod.rs:159-195)
         std::vector<double> def = {-1.0, 1.0, 0.0, 2.0, 1.0, 2.3, -0.3, 0.4, 0.0, -0.3, 0.4, 0.5, -0.2, 0.1, 0.2, -0.5};
         auto t = Tensor<double>::from_buf(cuda, def, {4, 4, 1});
