@@ -271,7 +271,14 @@ __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t
 // `split` cuts R into chunks, one CTA each.  With split > 1 every CTA stores its partial row, and the last CTA of a column tile to
 // finish (per-tile completion counter) folds the `split` partial rows in chunk order -- one launch,
 // and the fold order does not depend on which CTA came last.
-template <typename T, int OP, int VW, int TY>
+template <bool CG, typename T> __device__ __forceinline__ uint4 ld128(const T *p) {
+    return CG ? __ldcg(reinterpret_cast<const uint4 *>(p)) : *reinterpret_cast<const uint4 *>(p);
+}
+template <bool CG, typename T> __device__ __forceinline__ T ld1(const T *p) { return CG ? __ldcg(p) : *p; }
+
+// CG: read through L2 only (__ldcg) -- used when the rows are chunk partials that other CTAs of
+// this launch have just written, which an L1 line fetched earlier on this SM could hide
+template <typename T, int OP, int VW, int TY, bool CG = false>
 __device__ __forceinline__ void col_accumulate(const T *p, ptrdiff_t row_stride, size_t k0, size_t k1, int ly, T acc[VW]) {
     constexpr int B = 8;  // rows in flight per thread
     size_t k = k0 + ly;
@@ -279,7 +286,7 @@ __device__ __forceinline__ void col_accumulate(const T *p, ptrdiff_t row_stride,
         for (; k + (B - 1) * TY < k1; k += B * TY) {
             typename VecOf<T>::U v[B];
 #pragma unroll
-            for (int u = 0; u < B; ++u) v[u].q = *reinterpret_cast<const uint4 *>(p + (ptrdiff_t)(k + TY * u) * row_stride);
+            for (int u = 0; u < B; ++u) v[u].q = ld128<CG>(p + (ptrdiff_t)(k + TY * u) * row_stride);
 #pragma unroll
             for (int u = 0; u < B; ++u)
 #pragma unroll
@@ -287,7 +294,7 @@ __device__ __forceinline__ void col_accumulate(const T *p, ptrdiff_t row_stride,
         }
         for (; k < k1; k += TY) {
             typename VecOf<T>::U v;
-            v.q = *reinterpret_cast<const uint4 *>(p + (ptrdiff_t)k * row_stride);
+            v.q = ld128<CG>(p + (ptrdiff_t)k * row_stride);
 #pragma unroll
             for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::apply(acc[j], v.e[j]);
         }
@@ -295,11 +302,11 @@ __device__ __forceinline__ void col_accumulate(const T *p, ptrdiff_t row_stride,
         for (; k + (B - 1) * TY < k1; k += B * TY) {
             T v[B];
 #pragma unroll
-            for (int u = 0; u < B; ++u) v[u] = p[(ptrdiff_t)(k + TY * u) * row_stride];
+            for (int u = 0; u < B; ++u) v[u] = ld1<CG>(p + (ptrdiff_t)(k + TY * u) * row_stride);
 #pragma unroll
             for (int u = 0; u < B; ++u) acc[0] = Comb<T, OP>::apply(acc[0], v[u]);
         }
-        for (; k < k1; k += TY) acc[0] = Comb<T, OP>::apply(acc[0], p[(ptrdiff_t)k * row_stride]);
+        for (; k < k1; k += TY) acc[0] = Comb<T, OP>::apply(acc[0], ld1<CG>(p + (ptrdiff_t)k * row_stride));
     }
 }
 
@@ -365,7 +372,7 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
         __threadfence();
 #pragma unroll
         for (int j = 0; j < VW; ++j) acc[j] = Comb<T, OP>::identity();
-        if (col < inner) col_accumulate<T, OP, VW, TY>(partial + (o * split) * inner + col, (ptrdiff_t)inner, 0, split, ly, acc);
+        if (col < inner) col_accumulate<T, OP, VW, TY, true>(partial + (o * split) * inner + col, (ptrdiff_t)inner, 0, split, ly, acc);
 #pragma unroll
         for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
         __syncthreads();

@@ -9,7 +9,8 @@
 // output row-major over (o, i).  inner == 1 with row_stride == 1 runs one CTA (or warp) per row
 // reading 128-bit vectors; everything else runs tiles of 32 x VW columns with the 8 warps of a
 // CTA along k.  When there are too few outputs to fill the GPU, k is cut into chunks whose partial
-// states go to the context workspace and a second small kernel merges them.
+// states go to the context workspace; the CTA that finishes a row / column tile last (a completion
+// counter in the workspace header, left at zero again) merges them -- one launch.
 #include "rtb_internal.h"
 
 #include <cfloat>
@@ -22,6 +23,11 @@ constexpr int kBlock = 256;
 constexpr int kWarps = kBlock / 32;
 constexpr size_t kWorkspaceHeader = 65536;  // bytes of completion counters in front of the scratch
 constexpr unsigned kGridCap = 1u << 22;
+// completion counters in the workspace header: [0, 64) belong to the flat sum kernel, the rest to
+// per-row / per-tile counters of the chunked axis kernels (shared with the plain reductions; every
+// kernel leaves them at zero and launches on one context are ordered)
+constexpr size_t kTileCounterOffset = 64;
+constexpr size_t kMaxTileCounters = 16384 - 64;
 
 struct ExtSettings {
     int unbiased;
@@ -189,22 +195,51 @@ template <typename T> struct Vec128 {
     };
 };
 
+// A chunk state written by another CTA of this launch: read word by word through L2 (__ldcg), so
+// that an L1 line fetched earlier on this SM cannot hide it.
+template <typename S> __device__ __forceinline__ S load_state_cg(const S *p) {
+    static_assert(sizeof(S) % 4 == 0, "states are made of 4-byte words");
+    union {
+        S s;
+        unsigned int w[sizeof(S) / 4];
+    } u;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(S) / 4); ++i) u.w[i] = __ldcg(reinterpret_cast<const unsigned int *>(p) + i);
+    return u.s;
+}
+
 template <typename R> __device__ __forceinline__ typename R::State warp_merge(typename R::State s) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) s = R::merge(s, R::shfl(s, d));
     return s;
 }
 
+// all threads call; the merged state is valid in thread 0
+template <typename R> __device__ __forceinline__ typename R::State block_merge(typename R::State s, typename R::State *smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    s = warp_merge<R>(s);
+    if (lane == 0) smem[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+        s = lane < kWarps ? smem[lane] : R::identity();
+#pragma unroll
+        for (int d = kWarps / 2; d > 0; d >>= 1) s = R::merge(s, R::shfl(s, d));
+    }
+    __syncthreads();
+    return s;
+}
+
 // ---- inner == 1: one CTA (GROUP == kBlock) or one warp (GROUP == 32) per (row, chunk) -----------
 template <typename T, typename R, int GROUP>
 __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ src, size_t rows, size_t len, ptrdiff_t pitch,
-                                                          size_t split, typename R::State *partial, typename R::Out *dst,
-                                                          ExtSettings st) {
+                                                          size_t split, typename R::State *partial, unsigned int *counters,
+                                                          typename R::Out *dst, ExtSettings st) {
     using State = typename R::State;
     using V = Vec128<T>;
     constexpr int N = V::N;
     constexpr int U = 4;  // vectors in flight per thread
     __shared__ State smem[kWarps];
+    __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tid = GROUP == kBlock ? (int)threadIdx.x : lane;
     const size_t items = rows * split;
@@ -251,22 +286,31 @@ __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ 
             const size_t kt = kb + nvec * N;
             if (kt + tid < k1) R::add_one(s, p[kt + tid], kt + tid);
         }
-        s = warp_merge<R>(s);
-        if (GROUP == kBlock) {
-            if (lane == 0) smem[warp] = s;
-            __syncthreads();
-            if (warp == 0) {
-                s = lane < kWarps ? smem[lane] : R::identity();
-#pragma unroll
-                for (int d = kWarps / 2; d > 0; d >>= 1) s = R::merge(s, R::shfl(s, d));
-            }
-            __syncthreads();
-            if (threadIdx.x != 0) continue;
-        } else if (lane != 0) {
+        if (GROUP != kBlock) {  // warp per row; rows this short are never chunked
+            s = warp_merge<R>(s);
+            if (lane == 0) dst[row] = R::finish(s, st);
             continue;
         }
-        if (split == 1) dst[row] = R::finish(s, st);
-        else partial[row * split + chunk] = s;
+        s = block_merge<R>(s, smem);
+        if (split == 1) {
+            if (threadIdx.x == 0) dst[row] = R::finish(s, st);
+            continue;
+        }
+        if (threadIdx.x == 0) {
+            partial[row * split + chunk] = s;
+            __threadfence();
+            is_last = atomicAdd(counters + row, 1u) == (unsigned int)split - 1u;
+        }
+        __syncthreads();
+        if (!is_last) continue;  // uniform per CTA
+        __threadfence();
+        s = R::identity();
+        for (size_t c = threadIdx.x; c < split; c += kBlock) s = R::merge(s, load_state_cg(partial + row * split + c));
+        s = block_merge<R>(s, smem);
+        if (threadIdx.x == 0) {
+            dst[row] = R::finish(s, st);
+            counters[row] = 0;  // ready for the next launch
+        }
     }
 }
 
@@ -274,10 +318,12 @@ __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ 
 template <typename T, typename R, int VW>
 __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ src, size_t outer, size_t len, size_t inner,
                                                           ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t split,
-                                                          typename R::State *partial, typename R::Out *dst, ExtSettings st) {
+                                                          typename R::State *partial, unsigned int *counters,
+                                                          typename R::Out *dst, ExtSettings st) {
     using State = typename R::State;
     constexpr int U = 8;  // rows in flight per thread
     __shared__ State smem[kWarps][32][VW];
+    __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t col_tiles = (inner + 32 * VW - 1) / (32 * VW);
     const size_t per = (len + split - 1) / split;
@@ -329,35 +375,41 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                 }
             }
         }
+        // merge the 8 warps of the CTA: warp 0 ends with the state of (o, chunk, col + c)
+        auto across_warps = [&](bool last_pass) {
 #pragma unroll
-        for (int c = 0; c < VW; ++c) smem[warp][lane][c] = s[c];
-        __syncthreads();
-        if (warp == 0 && col < inner) {
+            for (int c = 0; c < VW; ++c) smem[warp][lane][c] = s[c];
+            __syncthreads();
+            if (warp == 0 && col < inner) {
 #pragma unroll
-            for (int c = 0; c < VW; ++c) {
-                State t = smem[0][lane][c];
+                for (int c = 0; c < VW; ++c) {
+                    State t = smem[0][lane][c];
 #pragma unroll
-                for (int w = 1; w < kWarps; ++w) t = R::merge(t, smem[w][lane][c]);
-                if (split == 1) dst[o * inner + col + c] = R::finish(t, st);
-                else partial[(o * split + chunk) * inner + col + c] = t;
+                    for (int w = 1; w < kWarps; ++w) t = R::merge(t, smem[w][lane][c]);
+                    if (last_pass) dst[o * inner + col + c] = R::finish(t, st);
+                    else partial[(o * split + chunk) * inner + col + c] = t;
+                }
+                if (!last_pass) __threadfence();  // chunk states visible device-wide before the counter moves
             }
+            __syncthreads();
+        };
+        across_warps(split == 1);
+        if (split == 1) continue;
+        if (threadIdx.x == 0) {
+            __threadfence();
+            is_last = atomicAdd(counters + o * col_tiles + (item % col_tiles), 1u) == (unsigned int)split - 1u;
         }
         __syncthreads();
-    }
-}
-
-// ---- second pass: a warp per output merges the chunk states -------------------------------------
-template <typename R>
-__global__ void __launch_bounds__(kBlock) ext_finish_kernel(const typename R::State *partial, size_t outer, size_t split,
-                                                            size_t inner, typename R::Out *dst, ExtSettings st) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const size_t outputs = outer * inner;
-    for (size_t idx = (size_t)blockIdx.x * kWarps + warp; idx < outputs; idx += (size_t)gridDim.x * kWarps) {
-        const size_t o = idx / inner, i = idx % inner;
-        typename R::State s = R::identity();
-        for (size_t c = lane; c < split; c += 32) s = R::merge(s, partial[(o * split + c) * inner + i]);
-        s = warp_merge<R>(s);
-        if (lane == 0) dst[idx] = R::finish(s, st);
+        if (!is_last) continue;  // uniform per CTA
+        __threadfence();
+#pragma unroll
+        for (int c = 0; c < VW; ++c) s[c] = R::identity();
+        if (col < inner)
+            for (size_t ch = warp; ch < split; ch += kWarps)
+#pragma unroll
+                for (int c = 0; c < VW; ++c) s[c] = R::merge(s[c], load_state_cg(partial + (o * split + ch) * inner + col + c));
+        across_warps(true);
+        if (threadIdx.x == 0) counters[o * col_tiles + (item % col_tiles)] = 0;  // ready for the next launch
     }
 }
 
@@ -381,51 +433,51 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
     std::lock_guard<std::mutex> lock(ctx->ws_mu);
     const size_t want = (size_t)ctx->sm_count * 4;  // work items that fill the GPU
     State *partial = nullptr;
+    unsigned int *counters = nullptr;
     size_t split = 1;
     auto get_partial = [&](size_t states) {
         void *ws = nullptr;
         int rc = workspace(ctx, states * sizeof(State), &ws);
-        if (rc == RTB_OK) partial = reinterpret_cast<State *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
+        if (rc != RTB_OK) return rc;
+        partial = reinterpret_cast<State *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
+        counters = reinterpret_cast<unsigned int *>(ws) + kTileCounterOffset;
         return rc;
     };
     int rc = RTB_OK;
     if (inner == 1 && row_stride == 1) {
-        if (outer < want && len >= 8192) {
+        if (outer < want && outer <= kMaxTileCounters && len >= 8192) {
             split = (want + outer - 1) / outer;
-            if (split > len / 4096) split = len / 4096;
+            if (split > len / 4096) split = len / 4096;  // chunks stay >= 4096 elements: always the CTA form
         }
         if (split > 1 && (rc = get_partial(outer * split)) != RTB_OK) return rc;
         const size_t items = outer * split;
         if ((len + split - 1) / split >= 1024)
-            ext_rows_kernel<T, R, kBlock><<<grid_of(items), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split, partial, dst, st);
+            ext_rows_kernel<T, R, kBlock><<<grid_of(items), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split, partial, counters,
+                                                                                     dst, st);
         else
-            ext_rows_kernel<T, R, 32><<<grid_of((items + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split,
-                                                                                                 partial, dst, st);
-        rc = check_launch(ctx, "ext_rows_kernel");
-    } else {
-        const bool vec = inner % N == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && outer_stride % (ptrdiff_t)N == 0 &&
-                         row_stride % (ptrdiff_t)N == 0;
-        const size_t cols_per_tile = 32 * (vec ? N : 1);
-        const size_t base = outer * ((inner + cols_per_tile - 1) / cols_per_tile);
-        // CTAs do equal work, so the launch is fastest as ONE wave of resident CTAs: as many chunks
-        // of k per tile as fit, each at least 64 rows
-        const size_t resident = vec ? resident_ctas(ctx, ext_cols_kernel<T, R, (int)N>) : resident_ctas(ctx, ext_cols_kernel<T, R, 1>);
-        split = resident / base;
-        if (split > len / 64) split = len / 64;
-        if (split < 1) split = 1;
-        if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
-        const unsigned grid = grid_of(base * split);
-        if (vec)
-            ext_cols_kernel<T, R, (int)N><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
-                                                                            dst, st);
-        else
-            ext_cols_kernel<T, R, 1><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial, dst,
-                                                                       st);
-        rc = check_launch(ctx, "ext_cols_kernel");
+            ext_rows_kernel<T, R, 32><<<grid_of((items + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, 1,
+                                                                                                 nullptr, nullptr, dst, st);
+        return check_launch(ctx, "ext_rows_kernel");
     }
-    if (rc != RTB_OK || split == 1) return rc;
-    ext_finish_kernel<R><<<grid_of((outer * inner + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(partial, outer, split, inner, dst, st);
-    return check_launch(ctx, "ext_finish_kernel");
+    const bool vec = inner % N == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && outer_stride % (ptrdiff_t)N == 0 &&
+                     row_stride % (ptrdiff_t)N == 0;
+    const size_t cols_per_tile = 32 * (vec ? N : 1);
+    const size_t base = outer * ((inner + cols_per_tile - 1) / cols_per_tile);
+    // CTAs do equal work, so the launch is fastest as ONE wave of resident CTAs: as many chunks of k
+    // per tile as fit, each at least 64 rows
+    const size_t resident = vec ? resident_ctas(ctx, ext_cols_kernel<T, R, (int)N>) : resident_ctas(ctx, ext_cols_kernel<T, R, 1>);
+    split = base <= kMaxTileCounters ? resident / base : 1;  // one completion counter per tile
+    if (split > len / 64) split = len / 64;
+    if (split < 1) split = 1;
+    if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
+    const unsigned grid = grid_of(base * split);
+    if (vec)
+        ext_cols_kernel<T, R, (int)N><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
+                                                                        counters, dst, st);
+    else
+        ext_cols_kernel<T, R, 1><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
+                                                                   counters, dst, st);
+    return check_launch(ctx, "ext_cols_kernel");
 }
 
 template <typename T>

@@ -3,6 +3,7 @@ of launches), so that an `ncu` capture ends by itself in a minute or two:
 
     python -m rtensors_b200.profile_cases c3 [K]   strided / negative-step broadcast add, K rows (default 64)
     python -m rtensors_b200.profile_cases red      axis sums of (8192,8192) and (16,4096,1024)
+    python -m rtensors_b200.profile_cases ext      variance / logsumexp / L2 norm / argmax of (8192,8192) over both axes
     python -m rtensors_b200.profile_cases mid      mid-size ops (and the fused broadcast+reduce) with an L2 flush between them
 """
 import sys
@@ -42,6 +43,17 @@ def main():
         r3 = be.alloc(16*1024, torch.float32)
         for _ in range(3):
             be.apply_reduce((src,m3), r3, 1, L.SUM)
+    elif which == 'ext':
+        S = 8192
+        src = torch.randn(S*S, device=dev)
+        m = Meta.contiguous((S,S))
+        r1 = be.alloc(S, torch.float32)
+        ri = be.alloc(S, torch.int64)
+        for op, args, out in ((L.VARIANCE, (True, False, 2), r1), (L.LOGSUMEXP, (True, False, 2), r1),
+                              (L.NORM, (True, False, 2), r1), (L.ARGMAX, (True, False, 2), ri)):
+            for axis in (0, 1):
+                for _ in range(2):
+                    be.apply_reduce_ex((src, m), out, axis, op, *args)
     torch.cuda.synchronize()
     print('done')
     if which == 'mid':
