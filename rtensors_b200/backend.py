@@ -271,6 +271,15 @@ class CudaB200:
                                     C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner), self._p(out)))
         return out
 
+    def reduce_ext_ori(self, src: torch.Tensor, offset: int, outer: int, r: int, inner: int, op: int, unbiased: bool = True,
+                       is_std: bool = False, norm_type: int = 2):
+        """Codes 6..10 over a contiguous (outer, r, inner) block (rtb_reduce_axis_ex); int64 output for positions."""
+        out = self.alloc(max(outer * inner, 1), torch.int64 if op in (L.ARGMAX, L.ARGMIN) else src.dtype)
+        st = L.ReduceSettings(bool(unbiased), bool(is_std), int(norm_type))
+        check(lib().rtb_reduce_axis_ex(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), C.byref(st), self._p(src),
+                                       C.c_size_t(offset), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner), self._p(out)))
+        return out
+
     def l1_loss(self, a: torch.Tensor, b: torch.Tensor, reduction: int = 0, with_grad: bool = False):
         assert a.numel() == b.numel() and a.dtype == b.dtype
         loss = self.alloc(1, a.dtype)

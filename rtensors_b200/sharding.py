@@ -126,6 +126,63 @@ def sharded_reduce_axis(engine, local, outer: int, r: int, inner: int, op: int, 
     return finish_mean(part, global_r) if op == L.MEAN else part
 
 
+def _all_gather(t: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """[world, *t.shape]: every rank's copy of a small partial tensor."""
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous(), group=group)
+    return torch.stack(parts)
+
+
+def sharded_reduce_ex(engine, local, outer: int, r: int, inner: int, op: int, sharded: str, global_r: int, r_begin: int = 0,
+                      unbiased: bool = True, is_std: bool = False, norm_type: int = 2, group=None):
+    """variance / std, norm, logsumexp, argmax / argmin of the local [outer, r, inner] block over r.
+    sharded = "outer": disjoint outputs, no communication.  sharded = "r": this rank holds rows
+    [r_begin, r_begin + r) of global_r; every rank reduces its slab with the library and the small
+    per-rank results (outer*inner values each) are combined after ONE all-gather (norms: one
+    all-reduce): variance from (n, mean, M2) per rank with Chan's formula, logsumexp as the
+    logsumexp of the per-rank values, argmax / argmin as the best (value, global position) with
+    ties to the lower position."""
+    world, _ = world_info()
+
+    def run(code, *args):
+        return _as_torch(engine.reduce_ext_ori(local, 0, outer, r, inner, code, *args))
+
+    if sharded == "outer" or world == 1:
+        return run(op, unbiased, is_std, norm_type)
+    if op == L.NORM:
+        part = run(op, True, False, norm_type)
+        if norm_type == 2:
+            part = part * part
+        _all_reduce(part, "sum", group)
+        return torch.sqrt(part) if norm_type == 2 else part
+    if op == L.LOGSUMEXP:
+        g = _all_gather(run(op, True, False, 2), world, group)
+        m = g.max(dim=0).values
+        return m + torch.log(torch.exp(g - m).sum(dim=0))
+    if op == L.VARIANCE:
+        mean = _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, L.MEAN)).double()
+        m2 = run(op, False, False, 2).double() * r                 # population variance * n = M2
+        n = torch.full_like(mean, float(r))
+        g = _all_gather(torch.stack([n, mean, m2]), world, group)  # [world, 3, outputs]
+        ns, means, m2s = g[:, 0], g[:, 1], g[:, 2]
+        total = ns.sum(dim=0)
+        gmean = (ns * means).sum(dim=0) / total
+        gm2 = m2s.sum(dim=0) + (ns * (means - gmean) ** 2).sum(dim=0)
+        den = torch.clamp(total - 1, min=1) if unbiased else torch.clamp(total, min=1)
+        v = gm2 / den
+        dt = _as_torch(local).dtype
+        return (torch.sqrt(v) if is_std else v).to(dt)
+    if op in (L.ARGMAX, L.ARGMIN):
+        vals = _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, L.MAX if op == L.ARGMAX else L.MIN))
+        pos = run(op, True, False, 2).to(torch.int64) + int(r_begin)
+        gv = _all_gather(vals, world, group)
+        gp = _all_gather(pos, world, group)
+        best = gv.max(dim=0).values if op == L.ARGMAX else gv.min(dim=0).values
+        cand = torch.where(gv == best, gp, torch.full_like(gp, torch.iinfo(torch.int64).max))
+        return cand.min(dim=0).values
+    raise ValueError(f"unsupported reduction code {op}")
+
+
 def sharded_mean_l1_loss(engine, a_local, b_local, global_n: int, group=None):
     """mean(|a-b|) over tensors split across ranks: local sum of |a-b| -> all-reduce -> / (T)(float)N."""
     world, _ = world_info()

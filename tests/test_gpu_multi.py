@@ -52,6 +52,18 @@ def _worker(rank, world, port, out_dir):
                 assert got == want
             else:
                 assert abs(got - want) <= 1e-5 * 20 * float(np.abs(x).sum()) / (x.size if op == L.MEAN else 1)
+        # state-merging reductions with the reduced dim split across the two GPUs
+        z = (rng.standard_normal((5, 600, 64)) * 2 + 1).astype(np.float32)
+        z[2, 11, 9] = z[2, 500, 9] = 99.0
+        lo, hi = sharding.scalar_slab(600, world, rank)
+        zl = be.alloc_from_slice(np.ascontiguousarray(z[:, lo:hi, :]).reshape(-1))
+        for op, args in ((L.VARIANCE, (True, False, 2)), (L.VARIANCE, (False, True, 2)), (L.NORM, (True, False, 2)),
+                         (L.LOGSUMEXP, (True, False, 2))):
+            got = sharding.sharded_reduce_ex(be, zl, 5, hi - lo, 64, op, "r", 600, lo, *args).cpu().numpy()
+            want = O.reduce_ext_ori(z.reshape(-1), 5, 600, 64, op, *args)
+            assert np.allclose(got, want, rtol=1e-4, atol=1e-6), (op, args)
+        got = sharding.sharded_reduce_ex(be, zl, 5, hi - lo, 64, L.ARGMAX, "r", 600, lo).cpu().numpy()
+        assert np.array_equal(got, O.argreduce_ori(z.reshape(-1), 5, 600, 64, O.ARGMAX).astype(np.int64))
         torch.cuda.synchronize()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:

@@ -40,6 +40,12 @@ class OracleBackendMirror:
     def l1_loss(self, a, b, reduction, with_grad):
         return O.l1_loss(a, b, reduction, with_grad)
 
+    def reduce_ext_ori(self, src, offset, outer, r, inner, op, unbiased=True, is_std=False, norm_type=2):
+        blk = np.ascontiguousarray(src[offset:offset + outer * r * inner])
+        if op in (O.ARGMAX, O.ARGMIN):
+            return O.argreduce_ori(blk, outer, r, inner, op).astype(np.int64)
+        return O.reduce_ext_ori(blk, outer, r, inner, op, unbiased, is_std, norm_type)
+
 
 def _free_port():
     s = socket.socket()
@@ -100,6 +106,22 @@ def _worker(rank, world, port, out_dir):
         got = sharding.sharded_reduce_axis(eng, local, hi - lo, 50, 8, L.SUM, "outer", 50).numpy()
         want = O.reduce_ori(y.reshape(-1), 3, 50, 8, O.SUM).reshape(3, 8)[lo:hi].reshape(-1)
         assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
+        # 4b. variance / std / norm / logsumexp / argmax with the reduced dim sharded: per-rank results
+        # combined after one all-gather; ties in argmax resolve to the lowest GLOBAL position
+        z = (rng.standard_normal((3, 50, 8)) * 2 + 1).astype(np.float32)
+        z[1, 7, 3] = z[1, 40, 3] = 99.0   # the same maximum in both ranks' slabs
+        lo, hi = sharding.scalar_slab(50, world, rank)
+        local = np.ascontiguousarray(z[:, lo:hi, :]).reshape(-1)
+        for op, args in ((L.VARIANCE, (True, False, 2)), (L.VARIANCE, (False, True, 2)), (L.NORM, (True, False, 1)),
+                         (L.NORM, (True, False, 2)), (L.LOGSUMEXP, (True, False, 2))):
+            got = sharding.sharded_reduce_ex(eng, local, 3, hi - lo, 8, op, "r", 50, lo, *args).numpy()
+            want = O.reduce_ext_ori(z.reshape(-1), 3, 50, 8, op, *args)
+            assert np.allclose(got, want, rtol=2e-5, atol=1e-6), (op, args)
+        for op in (L.ARGMAX, L.ARGMIN):
+            got = sharding.sharded_reduce_ex(eng, local, 3, hi - lo, 8, op, "r", 50, lo).numpy()
+            want = O.argreduce_ori(z.reshape(-1), 3, 50, 8, op).astype(np.int64)
+            assert np.array_equal(got, want), (op, got, want)
+        assert sharding.sharded_reduce_ex(eng, local, 3, hi - lo, 8, L.ARGMAX, "r", 50, lo).numpy().reshape(3, 8)[1, 3] == 7
         # 5. mean_l1_loss over sharded tensors
         p, q = rng.standard_normal(4000).astype(np.float32), rng.standard_normal(4000).astype(np.float32)
         lo, hi = sharding.scalar_slab(4000, world, rank)
