@@ -66,6 +66,7 @@ template <typename V> __device__ __forceinline__ V shfl_down_any(V v, int d) { r
 template <typename T> struct RedVar {
     using Out = T;
     static constexpr bool kPositional = false;
+    static constexpr bool kHeavyMerge = true;  // merging two states costs tens of instructions
     struct State {
         T mean, m2;
         unsigned long long n;
@@ -111,6 +112,7 @@ template <typename T> struct RedVar {
 template <typename T> struct RedLse {
     using Out = T;
     static constexpr bool kPositional = false;
+    static constexpr bool kHeavyMerge = true;
     struct State {
         T m, s;  // running max, sum of exp(x - m); s == 0 marks "empty"
     };
@@ -146,6 +148,7 @@ template <typename T> struct RedLse {
 template <typename T, int P> struct RedNorm {
     using Out = T;
     static constexpr bool kPositional = false;
+    static constexpr bool kHeavyMerge = false;
     struct State {
         T v;
     };
@@ -166,6 +169,7 @@ template <typename T, int P> struct RedNorm {
 template <typename T, bool MAXI> struct RedArg {
     using Out = unsigned long long;
     static constexpr bool kPositional = true;
+    static constexpr bool kHeavyMerge = true;
     static constexpr unsigned long long kNone = ~0ull;
     struct State {
         T v;
@@ -321,7 +325,7 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                                                           typename R::State *partial, unsigned int *counters,
                                                           typename R::Out *dst, ExtSettings st) {
     using State = typename R::State;
-    constexpr int U = 8;  // rows in flight per thread
+    constexpr int U = 8;  // rows in flight per thread (4 measured slower, also for the heavy states)
     __shared__ State smem[kWarps][32][VW];
     __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -451,7 +455,10 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
         }
         if (split > 1 && (rc = get_partial(outer * split)) != RTB_OK) return rc;
         const size_t items = outer * split;
-        if ((len + split - 1) / split >= 1024)
+        // A block-wide merge of heavy states costs more than reducing a few thousand elements, so such
+        // rows up to 16384 elements go to one warp each when there are enough rows to fill the GPU.
+        const bool warp_rows = len < 1024 || (R::kHeavyMerge && split == 1 && len <= 16384 && outer >= (size_t)ctx->sm_count * 32);
+        if (!warp_rows)
             ext_rows_kernel<T, R, kBlock><<<grid_of(items), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split, partial, counters,
                                                                                      dst, st);
         else
