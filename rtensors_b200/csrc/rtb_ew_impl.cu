@@ -407,6 +407,86 @@ __global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) r
     }
 }
 
+// Lean form of the row kernel for the binary broadcast hot path: FAST conditions, four columns per
+// thread and an inner extent that is a whole number of column tiles, so there are no per-column
+// predicates; column offsets are 32-bit; a broadcast operand (LB / RB) is ONE scalar per row that
+// feeds the functor directly.  Counters of the general kernel on the strided / negative-step
+// broadcast showed ~50 warp instructions per 512-byte store, most of them predicates, scalar
+// splats and 64-bit column arithmetic; this loop needs ~8.
+template <typename F, bool LB, bool RB>
+__global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kernel(T *d, const T *l, const T *r,
+                                                                                 const __grid_constant__ RowParams p, F f) {
+    constexpr int UX = 4;
+    const uint32_t chunk = blockIdx.x % p.n_col_chunks;
+    const uint32_t row_block = blockIdx.x / p.n_col_chunks;
+    const uint32_t tx = threadIdx.x & ((1u << p.tx_log2) - 1u);
+    const uint32_t ty = threadIdx.x >> p.tx_log2;
+    const uint32_t tile_y = kBlock >> p.tx_log2;
+    const int last = p.rank - 2;
+    const int64_t step_d = last >= 0 ? (int64_t)tile_y * p.sd[last] : 0;
+    const int64_t step_l = last >= 0 ? (int64_t)tile_y * p.sl[last] : 0;
+    const int64_t step_r = last >= 0 ? (int64_t)tile_y * p.sr[last] : 0;
+    const uint32_t ustride = (uint32_t)VEC << p.tx_log2;                   // elements between a thread's columns
+    const uint32_t col0 = ((chunk * UX) << p.tx_log2) * VEC + tx * VEC;     // < 2^31 (FAST)
+    const bool lrev = p.mode_l == kRevVec, rrev = p.mode_r == kRevVec;
+
+    RowCursor<2> cur;
+    const uint64_t first = (uint64_t)row_block * tile_y * (uint32_t)p.iters + ty;
+    if (first >= p.n_rows) return;
+    cur.row = (uint32_t)first;
+    cur.decode(p, d, l, r);
+    // column u of a forward operand sits at base + u*ustride, of a reversed one at base - u*ustride
+    auto place = [&](const T *row, bool bcast, bool rev) {
+        return bcast ? row : rev ? row - (int64_t)col0 - (VEC - 1) : row + col0;
+    };
+    auto fetch = [&](const T *q, bool rev, Vec (&v)[UX]) {
+#pragma unroll
+        for (int u = 0; u < UX; ++u) {
+            Vec t;
+            t.q = *reinterpret_cast<const uint4 *>(rev ? q - (int64_t)(u * ustride) : q + u * ustride);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[u].e[j] = rev ? t.e[VEC - 1 - j] : t.e[j];
+        }
+    };
+    T *pd = cur.pd + col0;
+    const T *pl = place(cur.pl, LB, lrev);
+    const T *pr = place(cur.pr, RB, rrev);
+    Vec a[UX], b[UX];  // unused (and removed by the compiler) for a broadcast operand
+    T as = T(), bs = T();
+    bool fresh = true;
+#pragma unroll 1
+    for (int it = 0; it < p.iters; ++it) {
+        if (fresh || step_l != 0) {
+            if constexpr (LB) as = *pl;
+            else fetch(pl, lrev, a);
+        }
+        if (fresh || step_r != 0) {
+            if constexpr (RB) bs = *pr;
+            else fetch(pr, rrev, b);
+        }
+#pragma unroll
+        for (int u = 0; u < UX; ++u) {
+            Vec o;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o.e[j] = f(LB ? as : a[u].e[j], RB ? bs : b[u].e[j]);
+            *reinterpret_cast<uint4 *>(pd + u * ustride) = o.q;
+        }
+        cur.row += tile_y;
+        cur.c_last += tile_y;
+        if (cur.row >= p.n_rows) break;
+        if (cur.c_last < p.n_last) {
+            pd += step_d; pl += step_l; pr += step_r;
+            fresh = false;
+        } else {
+            cur.decode(p, d, l, r);
+            pd = cur.pd + col0;
+            pl = place(cur.pl, LB, lrev);
+            pr = place(cur.pr, RB, rrev);
+            fresh = true;
+        }
+    }
+}
+
 // ---- host launch -------------------------------------------------------------------------------
 FastDiv make_fastdiv(uint32_t d) {
     FastDiv f;
@@ -463,6 +543,17 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     p.iters = (int)iters;
     const uint64_t grid = ((row_tiles + iters - 1) / iters) * chunks;
     if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
+    if constexpr (NIN == 2) {
+        const uint64_t inner_vecs = plan.shape[R - 1] / VEC;
+        if (fast && ux == 4 && inner_vecs % ((uint64_t)plan.tile_x * 4) == 0) {
+            const bool lb = plan.mode_l == kBroadcast, rb = plan.mode_r == kBroadcast;
+            if (lb && rb) rows_lean_kernel<F, true, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else if (lb) rows_lean_kernel<F, true, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else if (rb) rows_lean_kernel<F, false, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else rows_lean_kernel<F, false, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            return check_launch(ctx, "rows_lean_kernel");
+        }
+    }
     if (fast && ux == 4)
         rows_kernel<F, NIN, true, 4><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
     else if (fast)
