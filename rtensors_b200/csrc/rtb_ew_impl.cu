@@ -407,13 +407,13 @@ __global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) r
     }
 }
 
-// Lean form of the row kernel for the binary broadcast hot path: FAST conditions, four columns per
+// Lean form of the row kernel (any operand count; the binary broadcast hot path first of all): FAST conditions, four columns per
 // thread and an inner extent that is a whole number of column tiles, so there are no per-column
 // predicates; column offsets are 32-bit; a broadcast operand (LB / RB) is ONE scalar per row that
 // feeds the functor directly.  Counters of the general kernel on the strided / negative-step
 // broadcast showed ~50 warp instructions per 512-byte store, most of them predicates, scalar
 // splats and 64-bit column arithmetic; this loop needs ~8.
-template <typename F, bool LB, bool RB>
+template <typename F, int NIN, bool LB, bool RB>
 __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kernel(T *d, const T *l, const T *r,
                                                                                  const __grid_constant__ RowParams p, F f) {
     constexpr int UX = 4;
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
     const uint32_t col0 = ((chunk * UX) << p.tx_log2) * VEC + tx * VEC;     // < 2^31 (FAST)
     const bool lrev = p.mode_l == kRevVec, rrev = p.mode_r == kRevVec;
 
-    RowCursor<2> cur;
+    RowCursor<NIN> cur;
     const uint64_t first = (uint64_t)row_block * tile_y * (uint32_t)p.iters + ty;
     if (first >= p.n_rows) return;
     cur.row = (uint32_t)first;
@@ -456,11 +456,11 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
     bool fresh = true;
 #pragma unroll 1
     for (int it = 0; it < p.iters; ++it) {
-        if (fresh || step_l != 0) {
+        if (NIN >= 1 && (fresh || step_l != 0)) {
             if constexpr (LB) as = *pl;
             else fetch(pl, lrev, a);
         }
-        if (fresh || step_r != 0) {
+        if (NIN >= 2 && (fresh || step_r != 0)) {
             if constexpr (RB) bs = *pr;
             else fetch(pr, rrev, b);
         }
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
         for (int u = 0; u < UX; ++u) {
             Vec o;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) o.e[j] = f(LB ? as : a[u].e[j], RB ? bs : b[u].e[j]);
+            for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? (LB ? as : a[u].e[j]) : T(), NIN >= 2 ? (RB ? bs : b[u].e[j]) : T());
             *reinterpret_cast<uint4 *>(pd + u * ustride) = o.q;
         }
         cur.row += tile_y;
@@ -543,16 +543,21 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     p.iters = (int)iters;
     const uint64_t grid = ((row_tiles + iters - 1) / iters) * chunks;
     if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
-    if constexpr (NIN == 2) {
-        const uint64_t inner_vecs = plan.shape[R - 1] / VEC;
-        if (fast && ux == 4 && inner_vecs % ((uint64_t)plan.tile_x * 4) == 0) {
-            const bool lb = plan.mode_l == kBroadcast, rb = plan.mode_r == kBroadcast;
-            if (lb && rb) rows_lean_kernel<F, true, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else if (lb) rows_lean_kernel<F, true, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else if (rb) rows_lean_kernel<F, false, true><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else rows_lean_kernel<F, false, false><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            return check_launch(ctx, "rows_lean_kernel");
+    if (fast && ux == 4 && (plan.shape[R - 1] / VEC) % ((uint64_t)plan.tile_x * 4) == 0) {
+        const bool lb = NIN >= 1 && plan.mode_l == kBroadcast, rb = NIN >= 2 && plan.mode_r == kBroadcast;
+        const unsigned g = (unsigned)grid;
+        if constexpr (NIN == 2) {
+            if (lb && rb) rows_lean_kernel<F, 2, true, true><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else if (lb) rows_lean_kernel<F, 2, true, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else if (rb) rows_lean_kernel<F, 2, false, true><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else rows_lean_kernel<F, 2, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        } else if constexpr (NIN == 1) {
+            if (lb) rows_lean_kernel<F, 1, true, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            else rows_lean_kernel<F, 1, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        } else {
+            rows_lean_kernel<F, 0, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
         }
+        return check_launch(ctx, "rows_lean_kernel");
     }
     if (fast && ux == 4)
         rows_kernel<F, NIN, true, 4><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);

@@ -154,6 +154,13 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
         add(f"sum_at({axis}) f32 over a strided window, no copy", f"({S},{S}) window of ({S},{2 * S})", 4 * (S * S + S), S * S,
             (lambda axis=axis: be.reduce_view(src, win, axis, L.SUM)), flush=S * S * 4 < (200 << 20))
 
+    # elementwise ops in place on the same window (rows of S elements with a pitch of 2S)
+    add("scalar_add f32 in place on a strided window", f"({S},{S}) window of ({S},{2 * S})", 8 * S * S, S * S,
+        lambda: be.scalar_apply(src, L.ADD, 1.0, win), flush=S * S * 8 < (200 << 20))
+    add("fill f32 on a strided window", f"({S},{S}) window of ({S},{2 * S})", 4 * S * S, S * S,
+        lambda: be.fill(src, 0.25, win), flush=S * S * 4 < (200 << 20))
+    src.normal_(generator=g)
+
     def copy_then_reduce():
         tmp = be.contiguous(src, win)
         be.apply_reduce((tmp, msq), r1, 1, L.SUM)
