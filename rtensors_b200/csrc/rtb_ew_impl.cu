@@ -534,12 +534,15 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     const int ux = plan.ux;
     const uint64_t chunks = plan.n_col_chunks;
     p.n_col_chunks = (uint32_t)chunks;
-    // a CTA walks `iters` consecutive row tiles: the row decode and any broadcast operand held in
-    // registers are paid once per CTA, while the grid stays at >= 8 CTAs per SM
+    // A CTA walks `iters` consecutive row tiles, so the row decode and any broadcast operand held in
+    // registers are paid once per CTA.  Small CTAs balance better than long loops: measured on B200
+    // with the (16,64,1024,1024) strided / negative-step broadcast add, at most 1 / 2 / 3 / 4 / 8 / 64
+    // tiles per CTA give 5.26 / 6.84 / 7.43 / 7.41 / 7.29 / 6.84 TB/s.  So: up to 4 tiles, fewer when
+    // that would leave under 8 CTAs per SM.
     const uint64_t row_tiles = (plan.n_rows + (uint64_t)plan.tile_y - 1) / (uint64_t)plan.tile_y;
     uint64_t iters = (row_tiles * chunks) / ((uint64_t)ctx->sm_count * 8);
     if (iters < 1) iters = 1;
-    if (iters > 64) iters = 64;
+    if (iters > 4) iters = 4;
     p.iters = (int)iters;
     const uint64_t grid = ((row_tiles + iters - 1) / iters) * chunks;
     if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
