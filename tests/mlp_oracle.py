@@ -1,6 +1,6 @@
 """The dense-MLP SGD step composed from the CPU oracle's pieces (test infrastructure).  GEMMs use
 the oracle's f64-accumulating GEMM in place of OpenBLAS; everything else is the restated CPU
-backend.  Data flow and quirks: see rtensors_b200/mlp.py and DESIGN.md."""
+backend.  Data flow and quirks: the docstring of rtensors_b200/mlp.py."""
 import numpy as np
 
 import oracle as O
