@@ -34,6 +34,10 @@ class CudaEngine:
     def broadcast_params(self, a, b):
         return broadcast_params(a, b)
 
+    @staticmethod
+    def error_kind(e):
+        return {-4: "bounds", -6: "shape", -5: "dim"}.get(getattr(e, "code", None))
+
     def scalar_assign(self, buf, meta, op, value):
         d = to_dev(buf)
         self.b.scalar_apply(d, op, value, meta)
@@ -43,6 +47,14 @@ class CudaEngine:
         d = to_dev(buf)
         self.b.apply_unary(d, op, meta)
         return to_host(d)
+
+    def fill(self, buf, meta, value):
+        d = to_dev(buf)
+        self.b.fill(d, value, meta)
+        return to_host(d)
+
+    def owned(self, buf, meta):
+        return to_host(self.b.contiguous(to_dev(buf), meta))
 
     def scalar_out(self, buf, meta, op, value):
         d = to_dev(buf)

@@ -10,7 +10,14 @@ import numpy as np
 
 NP = {"f32": np.float32, "f64": np.float64, "i8": np.int8, "i16": np.int16, "i32": np.int32, "i64": np.int64,
       "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "bool": np.bool_}
-BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3, "log": 4, "log1p": 5, "leaky_relu": 6, "elu": 7}
+# truth closures of ops/scalar/mod.rs, evaluated in the tensor's own dtype (x, operand) -> value
+SCALAR_TRUTH = {
+    "log_base": lambda x, v: (np.log(x) / np.log(x.dtype.type(v))).astype(x.dtype),
+    "log1p_base": lambda x, v: (np.log1p(x) / np.log(x.dtype.type(v))).astype(x.dtype),
+    "leaky": lambda x, v: np.where(x > 0, x, x * x.dtype.type(v)).astype(x.dtype),
+    "elu": lambda x, v: np.where(x >= 0, x, np.expm1(np.minimum(x, 0)) * x.dtype.type(v)).astype(x.dtype),
+}
 UN = {n: i for i, n in enumerate(
     ["neg", "relu", "abs", "sign", "sigmoid", "tanh", "sqrt", "sin", "cos", "tan", "asin", "acos", "atan", "sinh", "cosh",
      "asinh", "acosh", "atanh", "rsqrt", "reciprocal", "square", "cube", "exp", "ln", "ln1p", "floor", "ceil", "round",
@@ -21,7 +28,8 @@ TRUTH = {
     "sqrt": np.sqrt, "ln": np.log, "sin": np.sin, "cos": np.cos, "tan": np.tan, "asin": np.arcsin, "acos": np.arccos,
     "atan": np.arctan, "sinh": np.sinh, "cosh": np.cosh, "asinh": np.arcsinh, "acosh": np.arccosh, "atanh": np.arctanh,
     "rsqrt": lambda x: 1.0 / np.sqrt(x), "reciprocal": lambda x: 1.0 / x, "square": lambda x: x * x,
-    "cube": lambda x: x * x * x, "exp": np.exp,
+    "cube": lambda x: x * x * x, "exp": np.exp, "expm1": np.expm1, "ln1p": np.log1p, "floor": np.floor, "ceil": np.ceil,
+    "trunc": np.trunc, "round": lambda x: np.trunc(x + np.copysign(0.5, x)),  # Rust f.round(): halves away from zero
 }
 RED = {"sum": 1, "prod": 2, "max": 3, "min": 4, "mean": 5}
 # name -> (code, unbiased, is_std, norm_type): the ReductionSettings the reference front end sends
@@ -46,7 +54,11 @@ def build_tensor(spec, dtype, engine):
     meta = engine.Meta.contiguous(shape)
     for coord, value in spec.get("set", []):
         buf[sum(c * s for c, s in zip(coord, meta.strides))] = value
-    for v in spec.get("view", []):
+    return buf, apply_view(meta, spec.get("view", []))
+
+
+def apply_view(meta, ops):
+    for v in ops:
         if v[0] == "slice":
             meta = meta.slice(v[1], v[2], v[3], v[4])
         elif v[0] == "index":
@@ -55,7 +67,7 @@ def build_tensor(spec, dtype, engine):
             meta = meta.permute(v[1])
         else:
             raise ValueError(v)
-    return buf, meta
+    return meta
 
 
 def check_values(case, out, shape):
@@ -86,7 +98,78 @@ def run_case(case, engine):
             assert meta.offset == em["offset"] and meta.is_contiguous() == em["contiguous"]
         for op, value in case["ops"]:
             buf = engine.scalar_assign(buf, meta, BIN[op], value)
+        if "buf" in case:
+            assert np.array_equal(buf, np.array(case["buf"], dtype=buf.dtype)), (case["name"], buf)
+        if "buf_close" in case:
+            exp, eps = case["buf_close"]
+            assert np.all(np.abs(buf.astype(np.float64) - np.array(exp, dtype=buf.dtype).astype(np.float64)) < eps), (case["name"], buf)
+        for idx, v in case.get("buf_at", []):
+            assert buf[idx] == v, (case["name"], idx, buf[idx])
+    elif kind == "program":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        for step in case["steps"]:
+            m = apply_view(meta, step[1])
+            if step[0] == "assign":
+                buf = engine.scalar_assign(buf, m, BIN[step[2]], step[3])
+            else:
+                before = buf.copy()
+                out, _ = engine.scalar_out(buf, m, BIN[step[2]], step[3])
+                assert np.asarray(out)[: len(step[4])].tolist() == step[4], (case["name"], step, out)
+                assert np.array_equal(buf, before), case["name"]
         assert np.array_equal(buf, np.array(case["buf"], dtype=buf.dtype)), (case["name"], buf)
+    elif kind == "fill":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        base = engine.Meta.contiguous(case["a"]["shape"])
+        buf = engine.fill(buf, meta, case["value"])
+        if "buf" in case:
+            assert np.array_equal(buf, np.array(case["buf"], dtype=buf.dtype)), (case["name"], buf)
+        for coord, v in case.get("base_spots", []):
+            assert buf[sum(c * s for c, s in zip(coord, base.strides))] == v, (case["name"], coord)
+    elif kind == "owned":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        if "view_contiguous" in case:
+            assert meta.is_contiguous() == case["view_contiguous"], case["name"]
+        out = engine.owned(buf, meta)
+        assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
+        assert np.asarray(out)[: len(case["values"])].tolist() == case["values"], (case["name"], out)
+    elif kind == "view_check":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
+        if "strides" in case:
+            assert list(meta.strides) == list(case["strides"]), (case["name"], meta.strides)
+        for coord, v in case["spots"]:
+            got = buf[meta.offset + sum(c * s for c, s in zip(coord, meta.strides))]
+            assert got == v, (case["name"], coord, got, v)
+    elif kind == "view_set":
+        buf, base = build_tensor(case["a"], case["dtype"], engine)
+        meta = apply_view(base, case["view"])
+        assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
+        for coord, v in case["sets"]:
+            buf[meta.offset + sum(c * s for c, s in zip(coord, meta.strides))] = v
+        for coord, v in case["base_spots"]:
+            assert buf[base.offset + sum(c * s for c, s in zip(coord, base.strides))] == v, (case["name"], coord)
+    elif kind == "slice_error":
+        m = engine.Meta.contiguous(case["a_shape"])
+        dim, start, end, step = case["slice"]
+        try:
+            m.slice(dim, start, end, step)
+        except Exception as e:
+            assert engine.error_kind(e) == case["error"], (case["name"], e)
+            return
+        raise AssertionError(f"{case['name']}: slice should be refused")
+    elif kind == "permute_error":
+        m = engine.Meta.contiguous(case["a_shape"])
+        try:
+            m.permute(case["dims"])
+        except Exception as e:
+            assert engine.error_kind(e) == "dim", (case["name"], e)
+            return
+        raise AssertionError(f"{case['name']}: permute should be refused")
+    elif kind == "view_values":
+        buf, meta = build_tensor(case["a"], case["dtype"], engine)
+        assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
+        got = gather_view(buf, meta)
+        assert np.asarray(got).reshape(-1).tolist() == case["values"], (case["name"], got)
     elif kind == "scalar":
         buf, meta = build_tensor(case["a"], case["dtype"], engine)
         before = buf.copy()
@@ -139,6 +222,25 @@ def run_case(case, engine):
             # a device engine merges partial states in tree order: a few ulps from the listed values
             ulps = 8 if getattr(engine, "tree_sums", False) else 0
             assert np.all(np.abs(out - exp) <= ulps * np.spacing(np.abs(exp))), (case["name"], out, exp)
+    elif kind == "scalar_fixture":
+        dt = NP[case["dtype"]]
+        d = np.array(case["definition"], dtype=dt)
+        if case["layout"] == "contiguous":
+            meta = engine.Meta.contiguous((2, 1))
+        elif case["layout"] == "1d":
+            meta = engine.Meta.contiguous((3, 1)).slice(0, None, None, 2)
+        else:
+            meta = engine.Meta.contiguous((4, 4, 1)).slice(0, None, None, 2).slice(1, None, None, 2)
+        by = [s * d.itemsize for s in meta.strides]
+        view = np.lib.stride_tricks.as_strided(d[meta.offset:], shape=meta.shape, strides=by)
+        exp = d.copy()
+        expv = np.lib.stride_tricks.as_strided(exp[meta.offset:], shape=meta.shape, strides=by)
+        expv[...] = SCALAR_TRUTH[case["truth"]](view, case["value"])
+        got = engine.scalar_assign(d.copy(), meta, BIN[case["op"]], case["value"])
+        if np.dtype(dt).kind == "f":  # eps_eq of the reference: |a - b| < tolerance
+            assert np.all(np.abs(got - exp) < case["tol"]), (case["name"], got, exp)
+        else:
+            assert np.array_equal(got, exp), (case["name"], got, exp)
     elif kind == "unary_fixture":
         dt = NP[case["dtype"]]
         d = np.array(case["definition"], dtype=dt)
@@ -196,6 +298,14 @@ class OracleEngine:
         self.o.unary_op(buf, op, meta, self.fast)
         return buf
 
+    def fill(self, buf, meta, value):
+        self.o.fill(buf, value, meta, self.fast)
+        return buf
+
+    def owned(self, buf, meta):
+        # view_to_contiguous, core/tensor.rs:299-325: element by element in row-major order
+        return gather_view(buf, meta).reshape(-1)
+
     def scalar_out(self, buf, meta, op, value):
         # out-of-place scalar op = owned() copy, then in place (ops/scalar/add.rs:93-97)
         out = gather_view(buf, meta)
@@ -220,6 +330,10 @@ class OracleEngine:
     def reduce_axis(self, a, am, axis, op):
         out, om = self.o.reduce_axis(a, am, axis, op, self.fast)
         return out, om.shape
+
+    @staticmethod
+    def error_kind(e):
+        return {-2: "bounds", -3: "shape", -1: "dim"}.get(getattr(e, "code", None))
 
     def reduce_ext(self, a, am, axis, code, unbiased, is_std, norm_type):
         assert am.is_contiguous()

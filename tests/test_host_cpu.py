@@ -227,3 +227,31 @@ def test_no_device_compute_fails_loudly_without_gpu():
     assert rc != 0
     with pytest.raises(RuntimeError):
         rt.CudaB200(0)
+
+
+# ---- the reference's view-arithmetic tests, replayed on the library's host-side planner (no GPU)
+_HOST_KINDS = ("view_check", "view_set", "view_values", "slice_error", "permute_error", "broadcast_error", "assign_shape_error")
+
+
+class _HostEngine:
+    """The part of the engine interface that needs no device: view metadata from the library."""
+    Meta = Meta
+
+    @staticmethod
+    def broadcast_params(a, b):
+        return broadcast_params(a, b)
+
+    @staticmethod
+    def error_kind(e):
+        return {-4: "bounds", -6: "shape", -5: "dim"}.get(getattr(e, "code", None))
+
+
+def _host_cases():
+    from golden.reference_cases import CASES
+    return [c for c in CASES if c["kind"] in _HOST_KINDS]
+
+
+@pytest.mark.parametrize("case", _host_cases(), ids=[c["name"] for c in _host_cases()])
+def test_reference_view_case_on_host_planner(case):
+    from golden_runner import run_case
+    run_case(case, _HostEngine())
