@@ -743,3 +743,40 @@ CASES += [
          a=dict(buf=list(range(1, 25)), shape=[2, 3, 4]), view=[(S, 0, 1, 2, 1), (P, [2, 0, 1])], shape=[4, 1, 3],
          sets=[((0, 0, 0), 1300), ((3, 0, 2), 2400)], base_spots=[((1, 0, 0), 1300), ((1, 2, 3), 2400), ((0, 0, 0), 1)]),
 ]
+
+
+# core/mod.rs: unsqueeze / unsqueeze_at / squeeze / squeeze_at (a sample: plain tensors, after slices,
+# over negative strides).  View ops ("unsqueeze", dim) and ("squeeze", dim | None).
+U, Q = "unsqueeze", "squeeze"
+CASES += [
+    _vc("unsqueeze_scalar", "2492-2503", [42], [], [(U, 0)], [1], [((0,), 42)], strides=[1]),
+    _vc("unsqueeze_1d", "2506-2523", [1, 2, 3, 4, 5], [5], [(U, 0)], [1, 5], [((0, k), k + 1) for k in range(5)], strides=[5, 1]),
+    _vc("unsqueeze_2d", "2526-2544", _M23, [2, 3], [(U, 0)], [1, 2, 3],
+        [((0, 0, 0), 1), ((0, 0, 1), 2), ((0, 0, 2), 3), ((0, 1, 0), 4), ((0, 1, 1), 5), ((0, 1, 2), 6)], strides=[6, 3, 1]),
+    _vc("double_unsqueeze", "2547-2564", [1, 2, 3], [3], [(U, 0), (U, 0)], [1, 1, 3], [((0, 0, 0), 1), ((0, 0, 1), 2), ((0, 0, 2), 3)],
+        strides=[3, 3, 1]),
+    _vc("unsqueeze_after_slice", "2567-2585", _M23, [2, 3], [(I, 0, 0), (U, 0)], [1, 3], [((0, 0), 1), ((0, 1), 2), ((0, 2), 3)],
+        strides=[3, 1]),
+    _vc("unsqueeze_after_column_slice", "2588-2606", _M23, [2, 3], [(I, 1, 0), (U, 0)], [1, 2], [((0, 0), 1), ((0, 1), 4)],
+        strides=[6, 3]),
+    _vc("unsqueeze_at_beginning", "2794-2805", _M23, [2, 3], [(U, 0)], [1, 2, 3],
+        [((0, 0, 0), 1), ((0, 0, 2), 3), ((0, 1, 0), 4), ((0, 1, 2), 6)], strides=[6, 3, 1]),
+    _vc("unsqueeze_at_middle", "2808-2819", _M23, [2, 3], [(U, 1)], [2, 1, 3],
+        [((0, 0, 0), 1), ((0, 0, 2), 3), ((1, 0, 0), 4), ((1, 0, 2), 6)], strides=[3, 3, 1]),
+    _vc("unsqueeze_at_end", "2822-2833", _M23, [2, 3], [(U, 2)], [2, 3, 1],
+        [((0, 0, 0), 1), ((0, 2, 0), 3), ((1, 0, 0), 4), ((1, 2, 0), 6)], strides=[3, 1, 1]),
+    _vc("unsqueeze_at_with_negative_stride", "3199-3214", _R8, [8], [(S, 0, None, None, -1), (U, 0)], [1, 8],
+        [((0, 0), 8), ((0, 7), 1)], strides=[-8, -1]),
+    _vc("unsqueeze_at_negative_stride_2d", "3217-3236", list(range(1, 13)), [3, 4], [(S, 0, None, None, -1), (U, 1)], [3, 1, 4],
+        [((0, 0, 0), 9), ((0, 0, 3), 12), ((2, 0, 0), 1)], strides=[-4, 4, 1]),
+    _vc("squeeze_basic_2d", "3501-3513", [1, 2, 3], [1, 3], [(Q, None)], [3], [((0,), 1), ((1,), 2), ((2,), 3)], strides=[1]),
+    _vc("squeeze_basic_3d", "3516-3527", _M23, [1, 2, 1, 3], [(Q, None)], [2, 3], [((0, 0), 1), ((0, 2), 3), ((1, 0), 4), ((1, 2), 6)],
+        strides=[3, 1]),
+    _vc("squeeze_all_dimensions", "3530-3538", [42], [1, 1, 1], [(Q, None)], [], [((), 42)], strides=[]),
+    _vc("squeeze_no_size_one_dims", "3541-3550", _M23, [2, 3], [(Q, None)], [2, 3], [((0, 0), 1), ((1, 2), 6)], strides=[3, 1]),
+    _vc("squeeze_at_specific_dim", "3553-3562", _M23, [1, 2, 3], [(Q, 0)], [2, 3], [((0, 0), 1), ((1, 2), 6)], strides=[3, 1]),
+    _vc("squeeze_at_middle_dim", "3565-3574", _M23, [2, 1, 3], [(Q, 1)], [2, 3], [((0, 0), 1), ((1, 2), 6)], strides=[3, 1]),
+    _vc("squeeze_at_end_dim", "3577-3586", _M23, [2, 3, 1], [(Q, 2)], [2, 3], [((0, 0), 1), ((1, 2), 6)], strides=[3, 1]),
+    _vc("squeeze_after_slice", "3589-3603", _M23, [2, 3], [(I, 0, 0), (U, 0), (Q, None)], [3], [((0,), 1), ((2,), 3)]),
+    _vc("squeeze_after_column_slice", "3606-3624", _M23, [2, 3], [(I, 1, 1), (U, 1), (Q, None)], [2], [((0,), 2), ((1,), 5)]),
+]

@@ -65,6 +65,10 @@ def apply_view(meta, ops):
             meta = meta.index(v[1], v[2])
         elif v[0] == "permute":
             meta = meta.permute(v[1])
+        elif v[0] == "unsqueeze":
+            meta = meta.unsqueeze(v[1])
+        elif v[0] == "squeeze":
+            meta = meta.squeeze(v[1])
         else:
             raise ValueError(v)
     return meta
