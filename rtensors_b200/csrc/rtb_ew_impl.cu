@@ -206,6 +206,7 @@ template <> struct FlatShape<2> { static constexpr int kThreads = 1024, kVecs = 
 
 template <typename F, int NIN>
 __global__ void __launch_bounds__(FlatShape<NIN>::kThreads) flat_kernel(T *d, const T *l, const T *r, size_t n, F f) {
+    grid_dep_sync();
     constexpr int BS = FlatShape<NIN>::kThreads, U = FlatShape<NIN>::kVecs;
     // head = elements before the first 16-byte boundary of d (l and r share d's phase)
     size_t head = ((16u - (unsigned)((uintptr_t)d & 15u)) & 15u) / sizeof(T);
@@ -351,6 +352,7 @@ struct RowCursor {
 // dim: a broadcast row or column) stay in registers until that dim wraps.
 template <typename F, int NIN, bool FAST, int UX>
 __global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) rows_kernel(T *d, const T *l, const T *r, const __grid_constant__ RowParams p, F f) {
+    grid_dep_sync();
     const uint32_t chunk = blockIdx.x % p.n_col_chunks;
     const uint32_t row_block = blockIdx.x / p.n_col_chunks;
     const uint32_t tx = threadIdx.x & ((1u << p.tx_log2) - 1u);
@@ -425,6 +427,7 @@ __global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) r
 template <typename F, int NIN, bool LB, bool RB>
 __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kernel(T *d, const T *l, const T *r,
                                                                                  const __grid_constant__ RowParams p, F f) {
+    grid_dep_sync();
     constexpr int UX = 4;
     const uint32_t chunk = blockIdx.x % p.n_col_chunks;
     const uint32_t row_block = blockIdx.x / p.n_col_chunks;
@@ -524,7 +527,7 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         constexpr size_t per_cta = (size_t)FlatShape<NIN>::kThreads * FlatShape<NIN>::kVecs;
         size_t blocks = (nvec + per_cta - 1) / per_cta;
         if (blocks >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "flat launch too large");
-        flat_kernel<F, NIN><<<(unsigned)blocks, FlatShape<NIN>::kThreads, 0, ctx->stream>>>(d, l, r, n, f);
+        launch_dep(ctx, (unsigned)blocks, FlatShape<NIN>::kThreads, flat_kernel<F, NIN>, d, l, r, n, f);
         return check_launch(ctx, "flat_kernel");
     }
     RowParams p;
@@ -560,24 +563,24 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         const bool lb = NIN >= 1 && plan.mode_l == kBroadcast, rb = NIN >= 2 && plan.mode_r == kBroadcast;
         const unsigned g = (unsigned)grid;
         if constexpr (NIN == 2) {
-            if (lb && rb) rows_lean_kernel<F, 2, true, true><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else if (lb) rows_lean_kernel<F, 2, true, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else if (rb) rows_lean_kernel<F, 2, false, true><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else rows_lean_kernel<F, 2, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            if (lb && rb) launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 2, true, true>, d, l, r, p, f);
+            else if (lb) launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 2, true, false>, d, l, r, p, f);
+            else if (rb) launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 2, false, true>, d, l, r, p, f);
+            else launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 2, false, false>, d, l, r, p, f);
         } else if constexpr (NIN == 1) {
-            if (lb) rows_lean_kernel<F, 1, true, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
-            else rows_lean_kernel<F, 1, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            if (lb) launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 1, true, false>, d, l, r, p, f);
+            else launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 1, false, false>, d, l, r, p, f);
         } else {
-            rows_lean_kernel<F, 0, false, false><<<g, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+            launch_dep(ctx, g, kBlock, rows_lean_kernel<F, 0, false, false>, d, l, r, p, f);
         }
         return check_launch(ctx, "rows_lean_kernel");
     }
     if (fast && ux == 4)
-        rows_kernel<F, NIN, true, 4><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, true, 4>, d, l, r, p, f);
     else if (fast)
-        rows_kernel<F, NIN, true, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, true, 1>, d, l, r, p, f);
     else
-        rows_kernel<F, NIN, false, 1><<<(unsigned)grid, kBlock, 0, ctx->stream>>>(d, l, r, p, f);
+        launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, false, 1>, d, l, r, p, f);
     return check_launch(ctx, "rows_kernel");
 }
 

@@ -7,6 +7,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include <cuda_runtime.h>
@@ -57,6 +58,44 @@ Ctx *default_ctx();  // ctx on the current device bound to the legacy default st
 
 inline void count_launch(Ctx *ctx) { ctx->launches.fetch_add(1, std::memory_order_relaxed); }
 int check_launch(Ctx *ctx, const char *what);
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Every kernel of the library is launched with the "programmatic stream serialization" attribute and
+// begins with grid_dep_sync().  A kernel that follows another kernel of the library on the same
+// stream is then scheduled while its predecessor's last wave is still running -- its CTAs become
+// resident as SMs free up -- and only blocks (griddepcontrol.wait) until the predecessor has
+// completed and its writes are visible.  Nothing before that wait touches global memory, so stream
+// order is kept exactly; what is saved is the launch gap and the drain of the tail, measured at
+// 2.0 - 2.7 us per kernel boundary on B200 (a 64 MiB read-modify-write: 14.4 -> 11.7 us each when
+// run back to back).  After a kernel that does not cooperate (a copy, another library's kernel)
+// the launch behaves like a plain one.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Kernels of many short CTAs release their dependents at once: that only takes effect when the
+// LAST CTA has started.  Kernels whose CTAs are all resident from the start and run long (the
+// one-wave reductions) release them after their main loop instead -- CTAs of the next kernel
+// that sit waiting next to a 600 us streaming loop were measured to slow it by up to 10 %.
+__device__ __forceinline__ void grid_dep_sync() {
+    grid_dep_launch();
+    grid_dep_wait();
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_dep(Ctx *ctx, unsigned grid, unsigned block, void (*kernel)(KArgs...), Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // the caller reads the error with check_launch()
+}
+#endif
 
 // ---- planner (host) ----------------------------------------------------------------------------
 constexpr int kMaxPlanRank = 8;

@@ -141,6 +141,7 @@ template <typename T> struct SrcL1 {
 template <typename T, int OP, typename Src>
 __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, T *partials, unsigned int *counter,
                                                              T *out, int mean) {
+    grid_dep_wait();
     __shared__ T smem[kWarps];
     __shared__ bool is_last;
     constexpr int N = VecOf<T>::N;
@@ -180,6 +181,7 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
     for (size_t k = tail0 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride)
         acc[2] = Comb<T, OP>::apply(acc[2], src.scalar(k));
 
+    grid_dep_launch();  // streaming done: the next kernel of the stream may start to move in
     T v = Comb<T, OP>::apply(Comb<T, OP>::apply(acc[0], acc[1]), Comb<T, OP>::apply(acc[2], acc[3]));
     v = block_reduce<T, OP>(v, smem);
     if (threadIdx.x == 0) {
@@ -206,6 +208,7 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
 template <typename T, int OP, int GROUP>
 __global__ void __launch_bounds__(kBlock) row_reduce_kernel(const T *src, size_t rows, size_t R, ptrdiff_t pitch,
                                                             size_t split, T *dst, int mean, size_t count) {
+    grid_dep_sync();
     __shared__ T smem[kWarps];
     constexpr int N = VecOf<T>::N;
     constexpr int rows_per_block = kBlock / GROUP;
@@ -324,6 +327,7 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
                                                             ptrdiff_t outer_stride, ptrdiff_t row_stride,
                                                             size_t split, size_t col_tiles, T *partial,
                                                             unsigned int *counters, T *dst, int mean, size_t count) {
+    grid_dep_wait();
     constexpr int TY = kBlock / TX;
     constexpr int TW = TX * VW;  // columns per tile
     __shared__ T smem[TY][TW + 1];
@@ -346,6 +350,7 @@ __global__ void __launch_bounds__(kBlock) col_reduce_kernel(const T *src, size_t
         // element (o, k, i) of the source sits at o*outer_stride + k*row_stride + i (dense: R*inner, inner)
         if (col < inner && k0 < k1)
             col_accumulate<T, OP, VW, TY>(src + (ptrdiff_t)o * outer_stride + (ptrdiff_t)col, row_stride, k0, k1, ly, acc);
+        grid_dep_launch();
 #pragma unroll
         for (int j = 0; j < VW; ++j) smem[ly][lx * VW + j] = acc[j];
         __syncthreads();
@@ -407,6 +412,7 @@ template <typename T> __device__ __forceinline__ T apply_binop(int op, T x, T y)
 template <typename T, int OP, bool WIDE>
 __global__ void __launch_bounds__(kBlock) bcast_reduce_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, int binop,
                                                               size_t A, size_t R, size_t B, size_t split, T *dst, int mean) {
+    grid_dep_sync();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (WIDE) {
         // CTA = 32 outputs along b x 8 lanes along k, one CTA per (a, chunk of k, b tile); with
@@ -484,6 +490,7 @@ __global__ void __launch_bounds__(kBlock) bcast_reduce_kernel(const T *l, Stride
 template <typename T, int OP, int BINOP>
 __global__ void __launch_bounds__(kBlock) bcast_reduce_kvec_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, size_t A,
                                                                    size_t R, size_t B, T *dst, int mean) {
+    grid_dep_sync();
     constexpr int N = VecOf<T>::N;
     using U = typename VecOf<T>::U;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -536,6 +543,7 @@ __global__ void __launch_bounds__(kBlock) bcast_reduce_kvec_kernel(const T *l, S
 template <typename T, int OP, int BINOP>
 __global__ void __launch_bounds__(kBlock) bcast_reduce_bvec_kernel(const T *l, Strides3 sl, const T *r, Strides3 sr, size_t A,
                                                                    size_t R, size_t B, size_t split, T *dst, int mean) {
+    grid_dep_sync();
     constexpr int N = VecOf<T>::N;
     using U = typename VecOf<T>::U;
     __shared__ uint4 smem[kWarps][32];
@@ -611,6 +619,7 @@ __global__ void __launch_bounds__(kBlock) bcast_reduce_bvec_kernel(const T *l, S
 
 // ---- fused MLP pieces ----------------------------------------------------------------------------
 __global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask, size_t n) {
+    grid_dep_sync();
     const size_t nvec = n / 4;
     const size_t stride = (size_t)gridDim.x * kBlock;
     for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
@@ -631,6 +640,7 @@ __global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask
 }
 
 __global__ void __launch_bounds__(kBlock) sgd_kernel(float *p, const float *g, float lr, size_t n) {
+    grid_dep_sync();
     const size_t nvec = n / 4;
     const size_t stride = (size_t)gridDim.x * kBlock;
     for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
@@ -646,6 +656,7 @@ __global__ void __launch_bounds__(kBlock) sgd_kernel(float *p, const float *g, f
 }
 
 __global__ void __launch_bounds__(kBlock) u8_f32_kernel(const uint8_t *src, float *dst, float divisor, size_t n) {
+    grid_dep_sync();
     const size_t nvec = n / 4;
     const size_t stride = (size_t)gridDim.x * kBlock;
     for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
@@ -678,7 +689,7 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
     if (rc != RTB_OK) return rc;
     unsigned int *counter = reinterpret_cast<unsigned int *>(ws);
     T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
-    flat_reduce_kernel<T, OP, Src><<<grid, kBlock, 0, ctx->stream>>>(src, n, partials, counter, out, mean);
+    launch_dep(ctx, grid, kBlock, flat_reduce_kernel<T, OP, Src>, src, n, partials, counter, out, mean);
     return check_launch(ctx, "flat_reduce_kernel");
 }
 
@@ -719,15 +730,15 @@ int rows_launch(Ctx *ctx, const T *src, size_t rows, size_t R, ptrdiff_t pitch, 
     // resident CTAs nothing hides that barrier.  The kernel still loops, so any grid size is legal.
     if (chunk_len >= 1024) {
         unsigned grid = grid_for(ctx, items, kAxisGridCap);
-        row_reduce_kernel<T, OP, kBlock><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, pitch, split, target, mean, R);
+        launch_dep(ctx, grid, kBlock, row_reduce_kernel<T, OP, kBlock>, src, rows, R, pitch, split, target, mean, R);
     } else {
         unsigned grid = grid_for(ctx, (items + kWarps - 1) / kWarps, kAxisGridCap);
-        row_reduce_kernel<T, OP, 32><<<grid, kBlock, 0, ctx->stream>>>(src, rows, R, pitch, split, target, mean, R);
+        launch_dep(ctx, grid, kBlock, row_reduce_kernel<T, OP, 32>, src, rows, R, pitch, split, target, mean, R);
     }
     int rc = check_launch(ctx, "row_reduce_kernel");
     if (rc != RTB_OK || split == 1) return rc;
     unsigned fold_grid = grid_for(ctx, (rows + kWarps - 1) / kWarps, kAxisGridCap);
-    row_reduce_kernel<T, OP, 32><<<fold_grid, kBlock, 0, ctx->stream>>>(target, rows, split, (ptrdiff_t)split, 1, dst, mean, R);
+    launch_dep(ctx, fold_grid, kBlock, row_reduce_kernel<T, OP, 32>, target, rows, split, (ptrdiff_t)split, 1, dst, mean, R);
     return check_launch(ctx, "row_reduce_kernel(fold)");
 }
 
@@ -769,7 +780,7 @@ int cols_launch_t(Ctx *ctx, const T *src, size_t outer, size_t R, size_t inner, 
         partial = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
     }
     const unsigned grid = grid_for(ctx, base_ctas * split, kAxisGridCap);  // one CTA per (tile, chunk)
-    col_reduce_kernel<T, OP, VW, TX><<<grid, kBlock, 0, ctx->stream>>>(src, outer, R, inner, outer_stride, row_stride, split,
+    launch_dep(ctx, grid, kBlock, col_reduce_kernel<T, OP, VW, TX>, src, outer, R, inner, outer_stride, row_stride, split,
                                                                        col_tiles, partial, counters, dst, mean, count);
     return check_launch(ctx, "col_reduce_kernel");
 }
@@ -840,14 +851,14 @@ int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 
         if (bvec) {
 #define RTB_BVEC(BOP)                                                                                                          \
     case BOP:                                                                                                                   \
-        bcast_reduce_bvec_kernel<T, OP, BOP><<<wgrid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, A, R, B, split, target, mean);    \
+        launch_dep(ctx, wgrid, kBlock, bcast_reduce_bvec_kernel<T, OP, BOP>, l, sl, r, sr, A, R, B, split, target, mean);    \
         break;
             switch (binop) {
                 RTB_BVEC(RTB_ADD) RTB_BVEC(RTB_SUB) RTB_BVEC(RTB_MUL) RTB_BVEC(RTB_DIV)
             }
 #undef RTB_BVEC
         } else {
-            bcast_reduce_kernel<T, OP, true><<<wgrid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, binop, A, R, B, split, target, mean);
+            launch_dep(ctx, wgrid, kBlock, bcast_reduce_kernel<T, OP, true>, l, sl, r, sr, binop, A, R, B, split, target, mean);
         }
         int rc = check_launch(ctx, "bcast_reduce_kernel");
         if (split > 1) {
@@ -867,7 +878,7 @@ int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 
         const unsigned grid = grid_for(ctx, blocks, kAxisGridCap);
 #define RTB_KVEC(BOP)                                                                                                 \
     case BOP:                                                                                                          \
-        bcast_reduce_kvec_kernel<T, OP, BOP><<<grid, kBlock, 0, ctx->stream>>>(l, sl, r, sr, A, R, B, dst, mean);      \
+        launch_dep(ctx, grid, kBlock, bcast_reduce_kvec_kernel<T, OP, BOP>, l, sl, r, sr, A, R, B, dst, mean);      \
         break;
         switch (binop) {
             RTB_KVEC(RTB_ADD) RTB_KVEC(RTB_SUB) RTB_KVEC(RTB_MUL) RTB_KVEC(RTB_DIV)
@@ -875,7 +886,7 @@ int bcast_reduce_launch(Ctx *ctx, const T *l, Strides3 sl, const T *r, Strides3 
 #undef RTB_KVEC
         return check_launch(ctx, "bcast_reduce_kvec_kernel");
     }
-    bcast_reduce_kernel<T, OP, false><<<grid_for(ctx, blocks, kAxisGridCap), kBlock, 0, ctx->stream>>>(l, sl, r, sr, binop, A, R, B, 1,
+    launch_dep(ctx, grid_for(ctx, blocks, kAxisGridCap), kBlock, bcast_reduce_kernel<T, OP, false>, l, sl, r, sr, binop, A, R, B, 1,
                                                                                                 dst, mean);
     return check_launch(ctx, "bcast_reduce_kernel");
 }
@@ -934,21 +945,21 @@ int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int r
 int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n) {
     if ((((uintptr_t)x | (uintptr_t)mask) & 15u) != 0) return fail(RTB_ERR_INVALID, "relu_mask needs 16-byte aligned buffers");
     unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
-    relu_mask_kernel<<<grid, kBlock, 0, ctx->stream>>>(x, mask, n);
+    launch_dep(ctx, grid, kBlock, relu_mask_kernel, x, mask, n);
     return check_launch(ctx, "relu_mask_kernel");
 }
 
 int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n) {
     if ((((uintptr_t)p | (uintptr_t)g) & 15u) != 0) return fail(RTB_ERR_INVALID, "sgd_update needs 16-byte aligned buffers");
     unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
-    sgd_kernel<<<grid, kBlock, 0, ctx->stream>>>(p, g, lr, n);
+    launch_dep(ctx, grid, kBlock, sgd_kernel, p, g, lr, n);
     return check_launch(ctx, "sgd_kernel");
 }
 
 int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n) {
     if (((uintptr_t)src & 3u) != 0 || ((uintptr_t)dst & 15u) != 0) return fail(RTB_ERR_INVALID, "u8_to_f32 needs aligned buffers");
     unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
-    u8_f32_kernel<<<grid, kBlock, 0, ctx->stream>>>(src, dst, divisor, n);
+    launch_dep(ctx, grid, kBlock, u8_f32_kernel, src, dst, divisor, n);
     return check_launch(ctx, "u8_f32_kernel");
 }
 

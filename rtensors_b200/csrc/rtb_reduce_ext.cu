@@ -238,6 +238,7 @@ template <typename T, typename R, int GROUP>
 __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ src, size_t rows, size_t len, ptrdiff_t pitch,
                                                           size_t split, typename R::State *partial, unsigned int *counters,
                                                           typename R::Out *dst, ExtSettings st) {
+    grid_dep_wait();
     using State = typename R::State;
     using V = Vec128<T>;
     constexpr int N = V::N;
@@ -290,6 +291,7 @@ __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ 
             const size_t kt = kb + nvec * N;
             if (kt + tid < k1) R::add_one(s, p[kt + tid], kt + tid);
         }
+        grid_dep_launch();
         if (GROUP != kBlock) {  // warp per row; rows this short are never chunked
             s = warp_merge<R>(s);
             if (lane == 0) dst[row] = R::finish(s, st);
@@ -324,6 +326,7 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                                                           ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t split,
                                                           typename R::State *partial, unsigned int *counters,
                                                           typename R::Out *dst, ExtSettings st) {
+    grid_dep_wait();
     using State = typename R::State;
     constexpr int U = 8;  // rows in flight per thread (4 measured slower, also for the heavy states)
     __shared__ State smem[kWarps][32][VW];
@@ -379,6 +382,7 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                 }
             }
         }
+        grid_dep_launch();
         // merge the 8 warps of the CTA: warp 0 ends with the state of (o, chunk, col + c)
         auto across_warps = [&](bool last_pass) {
 #pragma unroll
@@ -459,10 +463,10 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
         // rows up to 16384 elements go to one warp each when there are enough rows to fill the GPU.
         const bool warp_rows = len < 1024 || (R::kHeavyMerge && split == 1 && len <= 16384 && outer >= (size_t)ctx->sm_count * 32);
         if (!warp_rows)
-            ext_rows_kernel<T, R, kBlock><<<grid_of(items), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, split, partial, counters,
+            launch_dep(ctx, grid_of(items), kBlock, ext_rows_kernel<T, R, kBlock>, src, outer, len, outer_stride, split, partial, counters,
                                                                                      dst, st);
         else
-            ext_rows_kernel<T, R, 32><<<grid_of((items + kWarps - 1) / kWarps), kBlock, 0, ctx->stream>>>(src, outer, len, outer_stride, 1,
+            launch_dep(ctx, grid_of((items + kWarps - 1) / kWarps), kBlock, ext_rows_kernel<T, R, 32>, src, outer, len, outer_stride, 1,
                                                                                                  nullptr, nullptr, dst, st);
         return check_launch(ctx, "ext_rows_kernel");
     }
@@ -479,10 +483,10 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
     if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
     const unsigned grid = grid_of(base * split);
     if (vec)
-        ext_cols_kernel<T, R, (int)N><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
+        launch_dep(ctx, grid, kBlock, ext_cols_kernel<T, R, (int)N>, src, outer, len, inner, outer_stride, row_stride, split, partial,
                                                                         counters, dst, st);
     else
-        ext_cols_kernel<T, R, 1><<<grid, kBlock, 0, ctx->stream>>>(src, outer, len, inner, outer_stride, row_stride, split, partial,
+        launch_dep(ctx, grid, kBlock, ext_cols_kernel<T, R, 1>, src, outer, len, inner, outer_stride, row_stride, split, partial,
                                                                    counters, dst, st);
     return check_launch(ctx, "ext_cols_kernel");
 }
