@@ -418,12 +418,12 @@ __global__ void __launch_bounds__(kBlock, (UX == 4 && sizeof(T) == 4) ? 4 : 1) r
     }
 }
 
-// Lean form of the row kernel (any operand count; the binary broadcast hot path first of all): FAST conditions, four columns per
-// thread and an inner extent that is a whole number of column tiles, so there are no per-column
-// predicates; column offsets are 32-bit; a broadcast operand (LB / RB) is ONE scalar per row that
-// feeds the functor directly.  Counters of the general kernel on the strided / negative-step
-// broadcast showed ~50 warp instructions per 512-byte store, most of them predicates, scalar
-// splats and 64-bit column arithmetic; this loop needs ~8.
+// Lean form of the row kernel for the FAST conditions with four columns per thread (any operand
+// count; the binary broadcast path first of all).  Column offsets are 32-bit, a ragged last column
+// tile costs one loop-invariant compare per column, and a broadcast operand (LB / RB) is ONE
+// scalar per row that feeds the functor directly.  Counters of the general kernel on the strided /
+// negative-step broadcast showed ~50 warp instructions per 512-byte store, most of them
+// predicates, scalar splats and 64-bit column arithmetic; this loop needs ~8.
 template <typename F, int NIN, bool LB, bool RB>
 __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kernel(T *d, const T *l, const T *r,
                                                                                  const __grid_constant__ RowParams p, F f) {
@@ -441,6 +441,13 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
     const uint32_t ustride = (uint32_t)VEC << p.tx_log2;                   // elements between a thread's columns
     const uint32_t col0 = ((chunk * UX) << p.tx_log2) * VEC + tx * VEC;     // < 2^31 (FAST)
     const bool lrev = p.mode_l == kRevVec, rrev = p.mode_r == kRevVec;
+    // columns of this thread inside the row (all four except in a ragged last column tile); they
+    // are a prefix, so one loop-invariant compare per column is all the predication there is
+    int nu = 0;
+#pragma unroll
+    for (int u = 0; u < UX; ++u)
+        if ((uint64_t)col0 + (uint64_t)u * ustride < p.inner) nu = u + 1;
+    if (nu == 0) return;
 
     RowCursor<NIN> cur;
     const uint64_t first = (uint64_t)row_block * tile_y * (uint32_t)p.iters + ty;
@@ -454,6 +461,7 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
     auto fetch = [&](const T *q, bool rev, Vec (&v)[UX]) {
 #pragma unroll
         for (int u = 0; u < UX; ++u) {
+            if (u >= nu) continue;
             Vec t;
             t.q = *reinterpret_cast<const uint4 *>(rev ? q - (int64_t)(u * ustride) : q + u * ustride);
 #pragma unroll
@@ -478,6 +486,7 @@ __global__ void __launch_bounds__(kBlock, sizeof(T) == 4 ? 4 : 1) rows_lean_kern
         }
 #pragma unroll
         for (int u = 0; u < UX; ++u) {
+            if (u >= nu) continue;
             Vec o;
 #pragma unroll
             for (int j = 0; j < VEC; ++j) o.e[j] = f(NIN >= 1 ? (LB ? as : a[u].e[j]) : T(), NIN >= 2 ? (RB ? bs : b[u].e[j]) : T());
@@ -559,7 +568,7 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     p.iters = (int)iters;
     const uint64_t grid = ((row_tiles + iters - 1) / iters) * chunks;
     if (grid >= (1ull << 31)) return fail(RTB_ERR_TOO_LARGE, "grid too large for one launch");
-    if (fast && ux == 4 && (plan.shape[R - 1] / VEC) % ((uint64_t)plan.tile_x * 4) == 0) {
+    if (fast && ux == 4) {
         const bool lb = NIN >= 1 && plan.mode_l == kBroadcast, rb = NIN >= 2 && plan.mode_r == kBroadcast;
         const unsigned g = (unsigned)grid;
         if constexpr (NIN == 2) {
@@ -575,9 +584,7 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         }
         return check_launch(ctx, "rows_lean_kernel");
     }
-    if (fast && ux == 4)
-        launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, true, 4>, d, l, r, p, f);
-    else if (fast)
+    if (fast)
         launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, true, 1>, d, l, r, p, f);
     else
         launch_dep(ctx, (unsigned)grid, kBlock, rows_kernel<F, NIN, false, 1>, d, l, r, p, f);

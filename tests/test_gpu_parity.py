@@ -218,6 +218,36 @@ def test_random_broadcast_views(dt):
         _check_binary(a, am, b, bm, int(rng.choice(ops)))
 
 
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.int32, np.uint8], ids=lambda d: np.dtype(d).name)
+def test_long_rows_with_ragged_column_tiles(dt):
+    """Rows of at least 128 vectors whose length is not a whole number of column tiles, with forward,
+    reversed and broadcast operands, in and out of place."""
+    rng = np.random.default_rng(4242)
+    per = 16 // np.dtype(dt).itemsize
+    for rows, inner in ((37, 250 * per), (5, 129 * per), (3, 1027 * per), (64, 513 * per)):
+        a = _rand(rng, rows * inner, dt)
+        b = _rand(rng, inner, dt)
+        c = _rand(rng, rows, dt)
+        am = O.Meta.contiguous((rows, inner))
+        _check_binary(a, am, b, O.Meta.contiguous((inner,)), O.ADD)                                   # row-invariant right operand
+        _check_binary(a, am, b, O.Meta.contiguous((inner,)).slice(0, None, None, -1), O.SUB)          # reversed
+        _check_binary(c, O.Meta.contiguous((rows, 1)), b, O.Meta.contiguous((1, inner)), O.MUL)      # scalar per row x vector
+        _check_binary(a, am.slice(1, None, None, -1), c, O.Meta.contiguous((rows, 1)), O.ADD)       # reversed left, scalar right
+        # one-operand forms on a window of a wider buffer (pitch != row length)
+        wide = _rand(rng, rows * (inner + 4 * per), dt)
+        wm = O.Meta.contiguous((rows, inner + 4 * per)).slice(1, 0, inner, 1)
+        ref = wide.copy()
+        O.scalar_op(ref, O.ADD, 3, wm)
+        d = _dev(wide)
+        _b().scalar_apply(d, O.ADD, 3, _meta_pair(wm))
+        assert _host(d).tobytes() == ref.tobytes(), (dt, rows, inner)
+        ref2 = wide.copy()
+        O.fill(ref2, 1, wm)
+        d = _dev(wide)
+        _b().fill(d, 1, _meta_pair(wm))
+        assert _host(d).tobytes() == ref2.tobytes(), (dt, rows, inner)
+
+
 def test_broadcast_in_place_forms():
     rng = np.random.default_rng(3)
     from rtensors_b200.meta import Meta
