@@ -1061,3 +1061,71 @@ def test_ext_reductions_over_views_and_tensor_api():
     assert float(t.var().cpu().reshape(-1)[0]) == 6.0 and abs(float(t.std(False).cpu().reshape(-1)[0]) - 2.29128784747792) < 1e-14
     assert int(t.argmax().cpu().reshape(-1)[0]) == 7 and int(t.argmin().cpu().reshape(-1)[0]) == 0
     assert t.argmax_at(1).shape == (4, 1) and t.argmax_at(1).cpu().reshape(-1).tolist() == [1, 1, 1, 1]
+
+
+# ------------------------------------------------------------------------------------- CUDA graphs
+def test_a_chain_of_library_calls_replays_from_a_cuda_graph():
+    """After one eager pass (workspace and allocator blocks exist), a chain of calls -- broadcast add,
+    in-place scalar op and relu, axis sum over a view, variance, fused broadcast+reduce -- is captured
+    into a CUDA graph on a side stream and replayed on new input values; results equal the eager ones
+    bit for bit (the kernels, their order and their partial-sum trees are the same)."""
+    from rtensors_b200 import _lib as L
+    from rtensors_b200._lib import check, lib
+    from rtensors_b200.meta import Meta, broadcast_params
+    be = _b()
+    rng = np.random.default_rng(31337)
+    rows, cols = 512, 1024
+    am, bm = Meta.contiguous((rows, 1)), Meta.contiguous((1, cols))
+    shape, sa, sb = broadcast_params(am, bm)
+    dm = Meta.contiguous(shape)
+    a = _dev(rng.uniform(-1, 1, rows).astype(np.float32))
+    b = _dev(rng.uniform(-1, 1, cols).astype(np.float32))
+    out = be.alloc(rows * cols, torch.float32)
+    colsum = be.alloc(cols, torch.float32)
+    rowvar = be.alloc(rows, torch.float32)
+    fused = be.alloc(rows, torch.float32)
+    win = dm.slice(1, 128, 896, 1)          # a strided window of the result
+    winsum = be.alloc(rows, torch.float32)
+
+    def chain():
+        be.broadcast((a, Meta(shape, sa, 0)), (b, Meta(shape, sb, 0)), (out, dm), L.ADD)
+        be.scalar_apply(out, L.MUL, 1.5, dm)
+        be.apply_unary(out, L.RELU, dm)
+        be.apply_reduce((out, dm), colsum, 0, L.SUM)
+        be.apply_reduce_ex((out, dm), rowvar, 1, L.VARIANCE)
+        check(lib().rtb_reduce_view(be._ctx, C.c_int(L.F32), C.c_int(L.SUM), be._p(out), C.c_size_t(win.rank), win.c_shape,
+                                    win.c_strides, C.c_size_t(win.offset), C.c_ssize_t(1), be._p(winsum)))
+        check(lib().rtb_broadcast_reduce(be._ctx, C.c_int(L.F32), C.c_int(L.ADD), C.c_int(L.SUM), be._p(a), L.diffs(sa), C.c_size_t(0),
+                                         be._p(b), L.diffs(sb), C.c_size_t(0), C.c_size_t(2), L.sizes(shape), C.c_size_t(1),
+                                         be._p(fused)))
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        be.sync_stream()
+        chain()                               # eager pass: sizes the workspace, fills the allocator cache
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            be.sync_stream()
+            chain()
+        # new inputs, replay, then the same chain eagerly on the same inputs
+        a.copy_(torch.from_numpy(rng.uniform(-1, 1, rows).astype(np.float32)))
+        b.copy_(torch.from_numpy(rng.uniform(-1, 1, cols).astype(np.float32)))
+        side.synchronize()
+        launches_before = be.launches
+        graph.replay()
+        side.synchronize()
+        assert be.launches == launches_before   # a replay goes through no library entry point
+        replayed = [t.clone() for t in (out, colsum, rowvar, winsum, fused)]
+        be.sync_stream()
+        chain()
+        side.synchronize()
+        for r, e in zip(replayed, (out, colsum, rowvar, winsum, fused)):
+            assert _host(r).tobytes() == _host(e).tobytes()
+    torch.cuda.current_stream().wait_stream(side)
+    be.sync_stream()
+    # and the values are right
+    want = np.maximum((_host(a)[:, None] + _host(b)[None, :]) * np.float32(1.5), 0).astype(np.float32)
+    assert _host(out).tobytes() == want.reshape(-1).tobytes()
+    assert np.allclose(_host(fused), (_host(a)[:, None] + _host(b)[None, :]).sum(axis=1), rtol=1e-5, atol=1e-4)
