@@ -305,5 +305,11 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
                  "shape": f"global batch 4096, {local_b} per GPU x {world}", "ms": med, "ms_best": best,
                  "samples_per_s": 4096 / (med * 1e-3), "gemm_tflops": gemm_flops / (med * 1e-3) / 1e12,
                  "note": "whole step incl. cuBLAS GEMMs and, at N>1, two NCCL all-reduces (loss, 7.45 MB gradient bucket)"})
+    if world == 1:
+        model.step_graphed(img, tgt, 4096)  # eager step + capture
+        med_g, best_g = _time(lambda: model.step_graphed(img, tgt, 4096), reps=5, rounds=5)
+        rows.append({"op": "MLP SGD step, replayed from a CUDA graph", "shape": "global batch 4096, 1 GPU", "ms": med_g,
+                     "ms_best": best_g, "samples_per_s": 4096 / (med_g * 1e-3), "gemm_tflops": gemm_flops / (med_g * 1e-3) / 1e12,
+                     "note": "same kernels as the row above, one graph launch per step"})
     torch.cuda.synchronize()
     return rows

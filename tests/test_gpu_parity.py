@@ -532,6 +532,20 @@ def test_mlp_loss_decreases_over_steps():
     assert losses[-1] < losses[0]  # the reference's own autograd tests assert exactly this
 
 
+def test_mlp_step_replayed_from_a_graph_equals_the_eager_step():
+    """Two models with the same seed: one steps eagerly, the other through step_graphed (first call
+    eager + capture, then replays) on a sequence of different batches; parameters stay bit-identical."""
+    from rtensors_b200.mlp import DenseMlp, synthetic_batch
+    eager = DenseMlp(_b(), (784, 128, 64, 10), lr=0.1)
+    graphed = DenseMlp(_b(), (784, 128, 64, 10), lr=0.1)
+    for k in range(5):
+        img, tgt, _, _ = synthetic_batch(256, "cuda:0", seed=1000 + k)
+        le = eager.step(img, tgt)
+        lg = graphed.step_graphed(img, tgt)
+        assert _host(le).tobytes() == _host(lg).tobytes(), k
+        assert _host(eager.params).tobytes() == _host(graphed.params).tobytes(), k
+
+
 # ------------------------------------------------------------------------------------- context / allocator
 def test_context_allocator_and_copies():
     import rtensors_b200 as rt
