@@ -1143,3 +1143,70 @@ def test_a_chain_of_library_calls_replays_from_a_cuda_graph():
     want = np.maximum((_host(a)[:, None] + _host(b)[None, :]) * np.float32(1.5), 0).astype(np.float32)
     assert _host(out).tobytes() == want.reshape(-1).tobytes()
     assert np.allclose(_host(fused), (_host(a)[:, None] + _host(b)[None, :]).sum(axis=1), rtol=1e-5, atol=1e-4)
+
+
+# ------------------------------------------------------------------------------------- config 4 at full size
+def test_config4_reductions_at_full_size():
+    """normal(0,1) data at the benchmark's own sizes: (8192,8192) x {sum, mean, max, min} x axis {0,1},
+    (64,4096,1024) x 4 ops x axis 1, the flat sum of 2^30 and mean_l1_loss of two (4096,4096), each
+    against the CPU oracle on the same values (the device draws them, the host gets a copy), plus the
+    size-independent properties: max / min of the axis results equal the full max / min exactly, and
+    the axis sums add up to the full sum."""
+    b = _b()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0x5EED + 4)
+    big = torch.randn(1 << 30, device="cuda", generator=g)
+    host = big.cpu().numpy()
+
+    def check_axis(outer, r, inner, axes_label):
+        n = outer * r * inner
+        x = host[:n]
+        absum = np.abs(x.reshape(outer, r, inner)).sum(axis=1, dtype=np.float64).reshape(-1)
+        res = {}
+        for op in (O.SUM, O.MEAN, O.MAX, O.MIN):
+            want = O.reduce_ori(x, outer, r, inner, op, fast=True)
+            got = _host(b.reduce_axis_ori(big, 0, outer, r, inner, op))[: outer * inner]
+            res[op] = got
+            if op in (O.MAX, O.MIN):
+                assert got.tobytes() == want.tobytes(), (axes_label, op)
+            else:
+                scale = absum if op == O.SUM else absum / r
+                err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+                assert np.all(err <= _sum_tol(r) * scale + 1e-30), (axes_label, op, err.max())
+        return res
+
+    S = 8192
+    r0 = check_axis(1, S, S, "8192^2 axis 0")
+    r1 = check_axis(S, S, 1, "8192^2 axis 1")
+    x2 = host[: S * S]
+    assert r0[O.MAX].max() == r1[O.MAX].max() == x2.max() and r0[O.MIN].min() == r1[O.MIN].min() == x2.min()
+    total64 = float(x2.sum(dtype=np.float64))
+    tol = _sum_tol(S * S) * float(np.abs(x2).sum(dtype=np.float64))
+    assert abs(float(r0[O.SUM].sum(dtype=np.float64)) - total64) <= tol and abs(float(r1[O.SUM].sum(dtype=np.float64)) - total64) <= tol
+    check_axis(64, 4096, 1024, "(64,4096,1024) axis 1")
+
+    # flat sum of 2^30: against the oracle's sequential f32 accumulator (backward-error bound) and the f64 truth
+    out = b.alloc(1, torch.float32)
+    b.apply_reduce_contiguous_flat(big, out, 0, 1 << 30, O.SUM)
+    got = float(_host(out)[0])
+    want = float(O.reduce_flat(host, 0, 1 << 30, O.SUM, fast=True)[0])
+    abs_total = float(np.abs(host).sum(dtype=np.float64))
+    truth = float(host.sum(dtype=np.float64))
+    assert abs(got - want) <= _sum_tol(1 << 30) * abs_total
+    assert abs(got - truth) <= abs(want - truth) + 1e-6 * abs_total  # the tree sum is at least as close to the truth
+    for op in (O.MAX, O.MIN):
+        b.apply_reduce_contiguous_flat(big, out, 0, 1 << 30, op)
+        assert _host(out).tobytes() == O.reduce_flat(host, 0, 1 << 30, op, fast=True).tobytes()
+
+    # mean_l1_loss of two (4096,4096)
+    n = 4096 * 4096
+    loss, gmap = b.l1_loss(big[:n], big[n: 2 * n], 0, True)
+    wl, wg = O.l1_loss(host[:n], host[n: 2 * n], 0, True, fast=True)
+    # 2^24 positive terms of about 1.1: the CPU backend's single f32 accumulator stalls once the sum
+    # passes 2^24 (its result here is about 2 % low), so the bound is taken against the f64 truth and
+    # the oracle value only has to be no closer to it than the device value
+    truth = float(np.abs(host[:n].astype(np.float64) - host[n: 2 * n].astype(np.float64)).sum()) / n
+    got = float(_host(loss)[0])
+    assert abs(got - truth) <= _sum_tol(n) * truth
+    assert abs(got - truth) <= abs(float(wl[0]) - truth) + 1e-7
+    assert _host(gmap).tobytes() == wg.tobytes()
