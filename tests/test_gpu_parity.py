@@ -1210,3 +1210,41 @@ def test_config4_reductions_at_full_size():
     assert abs(got - truth) <= _sum_tol(n) * truth
     assert abs(got - truth) <= abs(float(wl[0]) - truth) + 1e-7
     assert _host(gmap).tobytes() == wg.tobytes()
+
+
+L_MUL, L_SUB = O.MUL, O.SUB  # the library's op codes are the oracle's
+
+
+def test_long_chain_of_dependent_small_kernels_keeps_stream_order():
+    """300 kernels back to back, each consuming what the previous one wrote (scalar ops on the whole
+    buffer and on strided windows, a broadcast add of a reduced vector, reductions into a vector
+    that is read again): with dependent launches every kernel starts before its predecessor has
+    finished, so any access ahead of the wait would show up as a wrong value here."""
+    from rtensors_b200.meta import Meta
+    be = _b()
+    rng = np.random.default_rng(2024)
+    rows, cols = 96, 512
+    x = rng.uniform(0.5, 1.5, rows * cols).astype(np.float32)
+    ref = x.copy()
+    d = _dev(x)
+    full = Meta.contiguous((rows, cols))
+    win = full.slice(0, None, None, 2).slice(1, 64, 448, 1)
+    owin = O.Meta.contiguous((rows, cols)).slice(0, None, None, 2).slice(1, 64, 448, 1)
+    ofull = O.Meta.contiguous((rows, cols))
+    colmax = be.alloc(cols, torch.float32)
+    for it in range(60):
+        be.scalar_apply(d, L_MUL, 1.01, full)
+        O.scalar_op(ref, O.MUL, 1.01, ofull)
+        be.scalar_apply(d, L_SUB, 0.005, win)
+        O.scalar_op(ref, O.SUB, 0.005, owin)
+        be.apply_reduce((d, full), colmax, 0, O.MAX)
+        cm, _ = O.reduce_axis(ref, ofull, 0, O.MAX)
+        # x -= 0.01 * colmax, broadcast over the rows
+        be.scalar_apply(colmax, L_MUL, 0.01, Meta.contiguous((cols,)))
+        cm = cm.copy()
+        O.scalar_op(cm, O.MUL, 0.01, O.Meta.contiguous((cols,)))
+        be.binary_assign(d, full, colmax, Meta.contiguous((1, cols)), L_SUB)
+        sh, sa, sb = O.broadcast_params(ofull, O.Meta.contiguous((1, cols)))
+        O.broadcast(ref, O.Meta(sh, sa, 0), cm, O.Meta(sh, sb, 0), ref, O.Meta(sh, sa, 0), O.SUB)
+    assert _host(d).tobytes() == ref.tobytes()
+
