@@ -780,3 +780,24 @@ CASES += [
     _vc("squeeze_after_slice", "3589-3603", _M23, [2, 3], [(I, 0, 0), (U, 0), (Q, None)], [3], [((0,), 1), ((2,), 3)]),
     _vc("squeeze_after_column_slice", "3606-3624", _M23, [2, 3], [(I, 1, 1), (U, 1), (Q, None)], [2], [((0,), 2), ((1,), 5)]),
 ]
+
+
+# core/mod.rs: view_as (relabel a contiguous view, offset kept) and shape_to_stride.
+# View op ("view_as", shape); kind "strides_of": row-major strides of a shape.
+V = "view_as"
+CASES += [
+    _vc("view_as_owned_success", "927-943", _M23, [2, 3], [(V, [3, 2])], [3, 2],
+        [((0, 0), 1), ((0, 1), 2), ((1, 0), 3), ((1, 1), 4), ((2, 0), 5), ((2, 1), 6)], strides=[2, 1]),
+    dict(name="view_as_owned_error", cite="core/mod.rs:945-951", kind="view_as_error", a_shape=[2, 3], new_shape=[4, 2]),
+    _vc("view_as_slice_success", "954-973", _M23, [2, 3], [(I, 0, 1), (V, [1, 3])], [1, 3], [((0, 0), 4), ((0, 1), 5), ((0, 2), 6)],
+        strides=[3, 1]),
+    _vc("view_as_mut_view_modify", "975-988", [1, 2, 40, 4], [2, 2], [(V, [4])], [4], [((2,), 40)], strides=[1]),
+    _vc("view_as_scalar_1", "990-1000", [99], [], [(V, [1])], [1], [((0,), 99)], strides=[1]),
+    _vc("view_as_scalar_2", "1002-1003", [99], [], [(V, [1]), (V, [1, 1, 1])], [1, 1, 1], [((0, 0, 0), 99)]),
+    dict(name="shape_to_stride", cite="core/mod.rs:1023-1028", kind="strides_of", shape=[2, 2, 3], strides=[6, 3, 1]),
+    dict(name="shape_to_stride_single_dim", cite="core/mod.rs:1031-1036", kind="strides_of", shape=[4], strides=[1]),
+    dict(name="shape_to_stride_empty", cite="core/mod.rs:1039-1044", kind="strides_of", shape=[], strides=[]),
+    dict(name="shape_to_stride_ones", cite="core/mod.rs:1047-1052", kind="strides_of", shape=[1, 1, 1], strides=[1, 1, 1]),
+    dict(name="shape_to_stride_mixed", cite="core/mod.rs:1055-1060", kind="strides_of", shape=[5, 1, 2], strides=[2, 2, 1]),
+    dict(name="shape_to_stride_larger", cite="core/mod.rs:1063-1068", kind="strides_of", shape=[3, 4, 5], strides=[20, 5, 1]),
+]

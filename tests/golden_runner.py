@@ -69,6 +69,8 @@ def apply_view(meta, ops):
             meta = meta.unsqueeze(v[1])
         elif v[0] == "squeeze":
             meta = meta.squeeze(v[1])
+        elif v[0] == "view_as":
+            meta = meta.view_as(v[1])
         else:
             raise ValueError(v)
     return meta
@@ -161,6 +163,15 @@ def run_case(case, engine):
             assert engine.error_kind(e) == case["error"], (case["name"], e)
             return
         raise AssertionError(f"{case['name']}: slice should be refused")
+    elif kind == "view_as_error":
+        m = engine.Meta.contiguous(case["a_shape"])
+        try:
+            m.view_as(case["new_shape"])
+        except Exception:
+            return
+        raise AssertionError(f"{case['name']}: view_as should be refused")
+    elif kind == "strides_of":
+        assert list(engine.Meta.contiguous(case["shape"]).strides) == list(case["strides"]), case["name"]
     elif kind == "permute_error":
         m = engine.Meta.contiguous(case["a_shape"])
         try:
