@@ -801,3 +801,45 @@ CASES += [
     dict(name="shape_to_stride_mixed", cite="core/mod.rs:1055-1060", kind="strides_of", shape=[5, 1, 2], strides=[2, 2, 1]),
     dict(name="shape_to_stride_larger", cite="core/mod.rs:1063-1068", kind="strides_of", shape=[3, 4, 5], strides=[20, 5, 1]),
 ]
+
+
+# core/mod.rs: index slices (`slice(dim, i..i)` removes the dim) of matrices and cubes.
+_CUBE = [1, 2, 4, 5, 6, 7, 8, 9]
+CASES += [
+    _vc("slice_matrix_row", "26-41", _M23, [2, 3], [(I, 0, 0)], [3], [((0,), 1), ((1,), 2), ((2,), 3)], strides=[1]),
+    _vc("slice_matrix_column", "43-49", _M23, [2, 3], [(I, 1, 0)], [2], [((0,), 1), ((1,), 4)], strides=[3]),
+    _vc("slice_cube_depth0", "52-64", _CUBE, [2, 2, 2], [(I, 0, 0)], [2, 2], [((0, 0), 1), ((0, 1), 2), ((1, 0), 4), ((1, 1), 5)],
+        strides=[2, 1]),
+    _vc("slice_cube_depth1", "66-74", _CUBE, [2, 2, 2], [(I, 0, 1)], [2, 2], [((0, 0), 6), ((0, 1), 7), ((1, 0), 8), ((1, 1), 9)],
+        strides=[2, 1]),
+    _vc("slice_cube_row", "76-84", _CUBE, [2, 2, 2], [(I, 1, 0)], [2, 2], [((0, 0), 1), ((0, 1), 2), ((1, 0), 6), ((1, 1), 7)],
+        strides=[4, 1]),
+    _vc("slice_cube_column", "86-94", _CUBE, [2, 2, 2], [(I, 2, 0)], [2, 2], [((0, 0), 1), ((0, 1), 4), ((1, 0), 6), ((1, 1), 8)],
+        strides=[4, 2]),
+    _vc("slice_of_slice_1", "96-106", _M23, [2, 3], [(I, 0, 1)], [3], [((0,), 4), ((1,), 5), ((2,), 6)]),
+    _vc("slice_of_slice_2", "108-111", _M23, [2, 3], [(I, 0, 1), (I, 0, 2)], [], [((), 6)]),
+]
+
+
+# core/mod.rs: offsets, sizes and contiguity of views.  kind "meta_check": offset / size / contiguous
+# of the view (keys present are checked); "a_meta" builds a MetaTensor directly from (shape, strides).
+CASES += [
+    dict(name="meta_size_scalar", cite="core/mod.rs:1370-1373", kind="meta_check", a=dict(buf=[42], shape=[]), size=1),
+    dict(name="meta_size_vector", cite="core/mod.rs:1375-1376", kind="meta_check", a=dict(buf=[1, 2, 3, 4], shape=[4]), size=4),
+    dict(name="meta_size_matrix", cite="core/mod.rs:1378-1379", kind="meta_check", a=dict(buf=_M23, shape=[2, 3]), size=6),
+    dict(name="meta_offsets_on_slices_1", cite="core/mod.rs:1382-1388", kind="meta_check",
+         a=dict(buf=[1, 2, 3, 4], shape=[2, 2], view=[(I, 0, 1)]), offset=2),
+    dict(name="meta_offsets_on_slices_2", cite="core/mod.rs:1390-1394", kind="meta_check",
+         a=dict(buf=list(range(1, 9)), shape=[2, 2, 2], view=[(I, 0, 1)]), offset=4),
+    dict(name="meta_offsets_on_slices_3", cite="core/mod.rs:1396-1397", kind="meta_check",
+         a=dict(buf=list(range(1, 9)), shape=[2, 2, 2], view=[(I, 0, 1), (I, 1, 1)]), offset=5),
+    dict(name="is_contiguous_owned", cite="core/mod.rs:1401-1404", kind="meta_check", a=dict(buf=_M23, shape=[2, 3]), contiguous=True),
+    dict(name="is_contiguous_row_slice", cite="core/mod.rs:1406-1408", kind="meta_check",
+         a=dict(buf=_M23, shape=[2, 3], view=[(I, 0, 1)]), contiguous=True),
+    dict(name="is_contiguous_column_slice", cite="core/mod.rs:1410-1412", kind="meta_check",
+         a=dict(buf=_M23, shape=[2, 3], view=[(I, 1, 0)]), contiguous=False),
+    dict(name="tensor_meta_direct_contiguous", cite="core/mod.rs:1437-1454", kind="meta_check", a_meta=([2, 3], [3, 1], 0), size=6,
+         offset=0, contiguous=True),
+    dict(name="tensor_meta_direct_noncontiguous", cite="core/mod.rs:1456-1460", kind="meta_check", a_meta=([2], [3], 0), size=2,
+         contiguous=False),
+]

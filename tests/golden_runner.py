@@ -163,6 +163,18 @@ def run_case(case, engine):
             assert engine.error_kind(e) == case["error"], (case["name"], e)
             return
         raise AssertionError(f"{case['name']}: slice should be refused")
+    elif kind == "meta_check":
+        if "a_meta" in case:
+            shape, strides, offset = case["a_meta"]
+            meta = engine.Meta(tuple(shape), tuple(strides), offset)
+        else:
+            _, meta = build_tensor(case["a"], "i32", engine)
+        if "size" in case:
+            assert meta.size == case["size"], case["name"]
+        if "offset" in case:
+            assert meta.offset == case["offset"], case["name"]
+        if "contiguous" in case:
+            assert meta.is_contiguous() == case["contiguous"], case["name"]
     elif kind == "view_as_error":
         m = engine.Meta.contiguous(case["a_shape"])
         try:

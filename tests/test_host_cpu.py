@@ -230,7 +230,7 @@ def test_no_device_compute_fails_loudly_without_gpu():
 
 
 # ---- the reference's view-arithmetic tests, replayed on the library's host-side planner (no GPU)
-_HOST_KINDS = ("view_check", "view_set", "view_values", "slice_error", "permute_error", "view_as_error", "strides_of", "broadcast_error", "assign_shape_error")
+_HOST_KINDS = ("view_check", "view_set", "view_values", "slice_error", "permute_error", "view_as_error", "strides_of", "meta_check", "broadcast_error", "assign_shape_error")
 
 
 class _HostEngine:
