@@ -843,3 +843,58 @@ CASES += [
     dict(name="tensor_meta_direct_noncontiguous", cite="core/mod.rs:1456-1460", kind="meta_check", a_meta=([2], [3], 0), size=2,
          contiguous=False),
 ]
+
+
+# core/mod.rs: writes through custom-step slices, read back through the base tensor
+def _vs(name, cite, buf, shape, view, vshape, sets, base_spots):
+    return dict(name=name, cite=f"core/mod.rs:{cite}", kind="view_set", dtype="i32", a=dict(buf=buf, shape=shape), view=view,
+                shape=vshape, sets=sets, base_spots=base_spots)
+
+
+CASES += [
+    _vs("custom_positive_step_mut", "692-716", _R16, [16], [(S, 0, None, None, 2)], [8], [((0,), 100), ((1,), 102), ((7,), 114)],
+        [((0,), 100), ((1,), 1), ((2,), 102), ((3,), 3), ((14,), 114), ((15,), 15)]),
+    _vs("custom_positive_step_mut_with_range", "719-741", _R16, [16], [(S, 0, 1, 10, 3)], [3], [((0,), 101), ((1,), 104), ((2,), 107)],
+        [((0,), 0), ((1,), 101), ((4,), 104), ((7,), 107), ((8,), 8)]),
+    _vs("custom_negative_step_mut", "744-766", _R16, [16], [(S, 0, None, None, -2)], [8], [((0,), 115), ((1,), 113), ((7,), 101)],
+        [((1,), 101), ((2,), 2), ((13,), 113), ((14,), 14), ((15,), 115)]),
+    _vs("custom_negative_step_mut_with_range", "769-791", _R16, [16], [(S, 0, 12, 3, -3)], [3], [((0,), 212), ((1,), 209), ((2,), 206)],
+        [((6,), 206), ((7,), 7), ((9,), 209), ((10,), 10), ((12,), 212)]),
+]
+
+
+# core/mod.rs: the range syntaxes (written out as the Slice each converts to), read and written through
+_T8 = [10, 20, 30, 40, 50, 60, 70, 80]
+_T10 = _T8 + [90, 100]
+
+
+def _rw(name, cite, buf, shape, view, vshape, reads, sets, base_spots):
+    return [_vc(name + "_read", cite, buf, shape, view, vshape, reads),
+            _vs(name + "_write", cite, buf, shape, view, vshape, sets, base_spots)]
+
+
+CASES += _rw("range_to_syntax", "1585-1614", _T8, [8], [(S, 0, None, 5, 1)], [5], [((k,), 10 * (k + 1)) for k in range(5)],
+             [((0,), 11), ((2,), 33), ((4,), 55)], [((0,), 11), ((2,), 33), ((4,), 55), ((5,), 60)])
+CASES += _rw("range_from_syntax", "1617-1643", _T8, [8], [(S, 0, 2, None, 1)], [6], [((0,), 30), ((1,), 40), ((5,), 80)],
+             [((0,), 333), ((5,), 888)], [((2,), 333), ((7,), 888), ((0,), 10), ((1,), 20)])
+CASES += _rw("range_full_syntax", "1646-1671", [10, 20, 30, 40], [4], [(S, 0, None, None, 1)], [4],
+             [((0,), 10), ((1,), 20), ((2,), 30), ((3,), 40)], [((0,), 100), ((3,), 400)], [((0,), 100), ((3,), 400)])
+CASES += _rw("inclusive_range_syntax", "1674-1701", _T8, [8], [(S, 0, 2, 6, 1)], [4], [((0,), 30), ((1,), 40), ((2,), 50), ((3,), 60)],
+             [((0,), 333), ((3,), 666)], [((2,), 333), ((5,), 666), ((1,), 20), ((6,), 70)])
+CASES += _rw("inclusive_range_zero_end", "1704-1726", [10, 20, 30, 40, 50], [5], [(S, 0, 0, 3, 1)], [3],
+             [((0,), 10), ((1,), 20), ((2,), 30)], [((1,), 222)], [((1,), 222)])
+CASES += _rw("single_index_syntax", "1729-1754", [10, 20, 30, 40, 50, 60], [2, 3], [(I, 1, 1)], [2], [((0,), 20), ((1,), 50)],
+             [((0,), 222), ((1,), 555)], [((0, 1), 222), ((1, 1), 555), ((0, 0), 10), ((0, 2), 30)])
+CASES += _rw("reverse_range_exclusive_with_values", "1757-1783", _T8, [8], [(S, 0, 5, 2, -1)], [3],
+             [((0,), 60), ((1,), 50), ((2,), 40)], [((0,), 666), ((2,), 444)], [((5,), 666), ((3,), 444), ((2,), 30), ((6,), 70)])
+CASES += _rw("slice_from_with_step", "1786-1811", _T10, [10], [(S, 0, 8, None, -1)], [9], [((0,), 90), ((1,), 80), ((8,), 10)],
+             [((0,), 999), ((8,), 111)], [((8,), 999), ((0,), 111), ((9,), 100)])
+CASES += _rw("slice_to_with_step", "1814-1841", _T8, [8], [(S, 0, None, 5, -1)], [2], [((0,), 80), ((1,), 70)],
+             [((0,), 888), ((1,), 777)], [((7,), 888), ((6,), 777), ((5,), 60), ((4,), 50)])
+CASES += _rw("reverse_first_n_elements", "1844-1871", _T8, [8], [(S, 0, 4, None, -1)], [5],
+             [((0,), 50), ((1,), 40), ((2,), 30), ((3,), 20), ((4,), 10)], [((0,), 555), ((4,), 111)], [((4,), 555), ((0,), 111)])
+CASES += _rw("manual_slice_construction_values", "1874-1899", _T10, [10], [(S, 0, 8, 2, -2)], [3],
+             [((0,), 90), ((1,), 70), ((2,), 50)], [((0,), 999), ((2,), 555)], [((8,), 999), ((4,), 555), ((6,), 70)])
+CASES += [_vc("empty_slice_same_indices", "1902-1911", [10, 20, 30, 40, 50, 60], [6], [(S, 0, 5, 5, 1)], [], [])]
+CASES += _rw("matrix_column_slice_with_mutation", "1914-1943", list(range(1, 13)), [3, 4], [(S, 1, 2, 3, 1)], [3, 1],
+             [((0, 0), 3), ((1, 0), 7), ((2, 0), 11)], [((0, 0), 33), ((2, 0), 111)], [((0, 2), 33), ((2, 2), 111), ((1, 2), 7)])
