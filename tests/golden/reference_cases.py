@@ -898,3 +898,13 @@ CASES += _rw("manual_slice_construction_values", "1874-1899", _T10, [10], [(S, 0
 CASES += [_vc("empty_slice_same_indices", "1902-1911", [10, 20, 30, 40, 50, 60], [6], [(S, 0, 5, 5, 1)], [], [])]
 CASES += _rw("matrix_column_slice_with_mutation", "1914-1943", list(range(1, 13)), [3, 4], [(S, 1, 2, 3, 1)], [3, 1],
              [((0, 0), 3), ((1, 0), 7), ((2, 0), 11)], [((0, 0), 33), ((2, 0), 111)], [((0, 2), 33), ((2, 2), 111), ((1, 2), 7)])
+
+
+# backend/cuda_tests.rs repeats the slicing / fill tests of core/mod.rs on the CUDA backend with the
+# same tensors; the two it adds: a float fill, and a 10-million-element upload read at both ends.
+CASES += [
+    dict(name="cuda_fill_f32", cite="backend/cuda_tests.rs:602-614", kind="fill", dtype="f32",
+         a=dict(buf=[0., 1., 2., 3., 4., 5.], shape=[2, 3]), value=3.14, buf=[3.14] * 6),
+    dict(name="rediculously_large_cuda_tensor", cite="backend/cuda_tests.rs:363-370", kind="owned", dtype="u8",
+         a=dict(ones=[10_000_000]), shape=[10_000_000], ends=(1, 1)),
+]

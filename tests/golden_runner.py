@@ -137,7 +137,11 @@ def run_case(case, engine):
             assert meta.is_contiguous() == case["view_contiguous"], case["name"]
         out = engine.owned(buf, meta)
         assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
-        assert np.asarray(out)[: len(case["values"])].tolist() == case["values"], (case["name"], out)
+        if "values" in case:
+            assert np.asarray(out)[: len(case["values"])].tolist() == case["values"], (case["name"], out)
+        if "ends" in case:
+            n = int(np.prod(case["shape"], dtype=np.int64))
+            assert (np.asarray(out)[0], np.asarray(out)[n - 1]) == case["ends"], case["name"]
     elif kind == "view_check":
         buf, meta = build_tensor(case["a"], case["dtype"], engine)
         assert list(meta.shape) == list(case["shape"]), (case["name"], meta.shape)
