@@ -908,3 +908,30 @@ CASES += [
     dict(name="rediculously_large_cuda_tensor", cite="backend/cuda_tests.rs:363-370", kind="owned", dtype="u8",
          a=dict(ones=[10_000_000]), shape=[10_000_000], ends=(1, 1)),
 ]
+
+
+# core/mod.rs: more unsqueeze / unsqueeze_at (writes through, indexing, 1-D / 3-D / sequential)
+_T12 = [10 * k for k in range(1, 13)]
+_R24 = list(range(1, 25))
+CASES += [
+    _vc("unsqueeze_mut_basic", "2620-2638", [1, 2, 3, 4], [2, 2], [(U, 0)], [1, 2, 2], [((0, 0, 0), 1), ((0, 1, 1), 4)], strides=[4, 2, 1]),
+    _vs("unsqueeze_mut_with_write", "2641-2665", _M23, [2, 3], [(U, 0)], [1, 2, 3], [((0, 0, 0), 100), ((0, 1, 2), 600)],
+        [((0, 0), 100), ((1, 2), 600), ((0, 1), 2), ((1, 0), 4)]),
+    _vs("unsqueeze_mut_after_slice", "2668-2694", _R8, [2, 4], [(I, 0, 1), (U, 0)], [1, 4], [((0, 0), 500), ((0, 3), 800)],
+        [((1, 0), 500), ((1, 3), 800), ((0, 0), 1), ((0, 3), 4)]),
+    _vs("unsqueeze_scalar_mut", "2697-2717", [99], [], [(U, 0)], [1], [((0,), 77)], [((), 77)]),
+    _vc("unsqueeze_indexing_comprehensive", "2720-2756", _T12, [3, 4], [(U, 0)], [1, 3, 4],
+        [((0, r, c), _T12[4 * r + c]) for r in range(3) for c in range(4)], strides=[12, 4, 1]),
+    _vc("unsqueeze_3d_indexing", "2759-2791", _R24, [2, 3, 4], [(U, 0)], [1, 2, 3, 4],
+        [((0, 0, 0, 0), 1), ((0, 0, 0, 3), 4), ((0, 0, 2, 3), 12), ((0, 1, 0, 0), 13), ((0, 1, 2, 3), 24)], strides=[24, 12, 4, 1]),
+    _vc("unsqueeze_at_1d_tensor_front", "2848-2853", [1, 2, 3, 4], [4], [(U, 0)], [1, 4], [], strides=[4, 1]),
+    _vc("unsqueeze_at_1d_tensor_back", "2855-2861", [1, 2, 3, 4], [4], [(U, 1)], [4, 1], [], strides=[1, 1]),
+    _vc("unsqueeze_at_3d_tensor_0", "2864-2873", _R24, [2, 3, 4], [(U, 0)], [1, 2, 3, 4], [], strides=[24, 12, 4, 1]),
+    _vc("unsqueeze_at_3d_tensor_1", "2875-2878", _R24, [2, 3, 4], [(U, 1)], [2, 1, 3, 4], [], strides=[12, 12, 4, 1]),
+    _vc("unsqueeze_at_3d_tensor_2", "2880-2883", _R24, [2, 3, 4], [(U, 2)], [2, 3, 1, 4], [], strides=[12, 4, 4, 1]),
+    _vc("unsqueeze_at_3d_tensor_3", "2885-2890", _R24, [2, 3, 4], [(U, 3)], [2, 3, 4, 1], [], strides=[12, 4, 1, 1]),
+    _vc("unsqueeze_at_multiple_sequential", "2893-2912", [1, 2, 3, 4], [2, 2], [(U, 0), (U, 1), (U, 2)], [1, 1, 1, 2, 2],
+        [((0, 0, 0, 0, 0), 1), ((0, 0, 0, 1, 1), 4)]),
+    _vc("unsqueeze_at_multiple_different_positions", "2915-2940", _M23, [2, 3], [(U, 2), (U, 0), (U, 2)], [1, 2, 1, 3, 1],
+        [((0, 0, 0, 0, 0), 1), ((0, 0, 0, 2, 0), 3), ((0, 1, 0, 0, 0), 4), ((0, 1, 0, 2, 0), 6)]),
+]
