@@ -935,3 +935,24 @@ CASES += [
     _vc("unsqueeze_at_multiple_different_positions", "2915-2940", _M23, [2, 3], [(U, 2), (U, 0), (U, 2)], [1, 2, 1, 3, 1],
         [((0, 0, 0, 0, 0), 1), ((0, 0, 0, 2, 0), 3), ((0, 1, 0, 0, 0), 4), ((0, 1, 0, 2, 0), 6)]),
 ]
+
+
+# core/mod.rs: more squeeze cases (after 3-D slices, writes through, chained with slices, over a
+# negative stride, several size-1 dims)
+CASES += [
+    _vc("squeeze_after_3d_slice", "3628-3648", _R24, [2, 3, 4], [(I, 0, 1), (U, 0), (Q, None)], [3, 4], [((0, 0), 13), ((2, 3), 24)]),
+    _vs("squeeze_mut_basic", "3651-3664", [1, 2, 3], [1, 3], [(Q, None)], [3], [((1,), 20)], [((0, 1), 20)]),
+    _vs("squeeze_mut_after_modifications", "3667-3687", _M23, [1, 2, 3], [(Q, None)], [2, 3],
+        [((0, 0), 10), ((0, 2), 30), ((1, 1), 50)], [((0, 0, 0), 10), ((0, 0, 2), 30), ((0, 1, 1), 50), ((0, 0, 1), 2), ((0, 1, 0), 4)]),
+    _vs("squeeze_at_mut_basic", "3690-3703", _M23, [2, 1, 3], [(Q, 1)], [2, 3], [((0, 0), 10), ((1, 2), 60)],
+        [((0, 0, 0), 10), ((1, 0, 2), 60)]),
+    _vs("squeeze_mut_after_slice", "3706-3731", list(range(1, 13)), [3, 4], [(I, 0, 1), (U, 0), (Q, None)], [4],
+        [((0,), 50), ((3,), 80)], [((1, 0), 50), ((1, 3), 80)]),
+    _vs("squeeze_mut_after_column_slice", "3734-3763", list(range(1, 10)), [3, 3], [(I, 1, 1), (U, 1), (Q, None)], [3],
+        [((0,), 20), ((2,), 80)], [((0, 1), 20), ((1, 1), 5), ((2, 1), 80)]),
+    _vc("squeeze_chained_with_slices", "3766-3795", _R24, [2, 3, 4], [(I, 0, 0), (U, 1), (I, 2, 2), (U, 0), (Q, None)], [3],
+        [((0,), 3), ((1,), 7), ((2,), 11)]),
+    _vc("squeeze_preserves_data_after_negative_stride", "3798-3814", _M23, [6], [(S, 0, None, None, -1), (U, 0), (Q, None)], [6],
+        [((0,), 6), ((5,), 1)]),
+    _vc("squeeze_multiple_dims_2d", "3817-3828", _M23, [1, 6, 1], [(Q, None)], [6], [((k,), k + 1) for k in range(6)], strides=[1]),
+]
