@@ -1,19 +1,23 @@
 // Elementwise engine for ONE dtype: compiled once per dtype with -DRTB_EW_DTYPE=<rtb_dtype code>.
 //
-// Two kernels serve every elementwise family (broadcast binary, scalar op, unary op, fill, copy):
+// Three kernels serve every elementwise family (broadcast binary, scalar op, unary op, fill, copy):
 //
-//   flat_kernel  one contiguous run per operand, all operands in the same 16-byte phase.
-//                A scalar head brings the pointers to a 16-byte boundary, the body moves 128-bit
-//                vectors (four independent loads in flight per thread before the first store),
-//                a scalar tail finishes.  HBM-bound: 2*s bytes per element in place, 3*s for a
-//                same-shape binary op.
-//   rows_kernel  everything else, after the planner collapsed the view to <= 8 dims.  A CTA owns
-//                a tile of (rows x 128-bit columns) and walks several row tiles: the row index is
-//                decoded once per CTA with multiply-shift division and then advanced by adds,
-//                never per element.  Each operand's walk along the inner dim is one of:
-//                contiguous (vector or scalar), reversed (vector load at the mirrored address +
-//                lane reversal), broadcast (one load, splat) or strided.  A lean instantiation
-//                serves the all-vector case (no per-element paths).
+//   flat_kernel       one contiguous run per operand, all operands in the same 16-byte phase.
+//                     A scalar head brings the pointers to a 16-byte boundary, the body moves
+//                     128-bit vectors (every thread issues all its loads before its first store),
+//                     a scalar tail finishes.  HBM-bound: 2*s bytes per element in place, 3*s for
+//                     a same-shape binary op.
+//   rows_lean_kernel  views (after the planner collapsed them to <= 8 dims) whose inner dim every
+//                     operand walks as whole aligned vectors, reversed vectors or one broadcast
+//                     scalar, with rows of at least 128 vectors.  A CTA owns a tile of (rows x
+//                     4 x 128-bit columns per thread) and walks up to four row tiles: the row index
+//                     is decoded once per CTA with multiply-shift division and then advanced by
+//                     adds, never per element; operands that do not move from row to row stay in
+//                     registers.
+//   rows_kernel       every other view: each operand's walk along the inner dim is one of
+//                     contiguous (vector or scalar), reversed (vector load at the mirrored address
+//                     + lane reversal), broadcast (one load, splat) or strided, with partial
+//                     vectors at the row ends.
 //
 // Arithmetic follows the reference CPU backend (src/backend/cpu.rs:549-557, 632-657, 679-696;
 // src/ops/base.rs:29-36; src/core/value.rs:515-548, 708-764): integers wrap, boolean + - * are
