@@ -171,6 +171,7 @@ def main():
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--e2e-chunk-log2", type=int, default=23, help="elements per chunk of the host pipeline")
     ap.add_argument("--elems-log2", type=int, default=28, help="per-GPU slab size (for small profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -280,7 +281,7 @@ def main():
         esteps = max(1, min(args.steps, 5))
 
         from rtensors_b200.host import HostPipeline
-        pipe = HostPipeline(be, chunk_elems=1 << 24)
+        pipe = HostPipeline(be, chunk_elems=1 << args.e2e_chunk_log2)
 
         def chunk_compute(v, length):
             mc = Meta.contiguous((length,))
@@ -307,7 +308,7 @@ def main():
         e_ms = float(tt.item()) / esteps
         e2e = {"value": world * step_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e_ms,
                "h2d_bytes_per_step": 3 * 4 * n, "d2h_bytes_per_step": 2 * 4 * n, "steps": esteps,
-               "how": "HostPipeline: 2^24-element chunks, H2D / kernels / D2H on three streams, pinned host buffers"}
+               "how": f"HostPipeline: 2^{args.e2e_chunk_log2}-element chunks, H2D / kernels / D2H on three streams, pinned host buffers"}
         del ha, hia, hib, ra, ri
 
     ops = None
