@@ -13,7 +13,11 @@
  * Conventions (both layers): every data pointer is a DEVICE pointer owned by the caller; the
  * library never frees or retains it.  Offsets, shapes and strides are in ELEMENTS; strides may
  * be zero (broadcast) or negative (reversed slice).  Work is enqueued on a stream and returns
- * before completion; the caller synchronises before reading results on the host.  Citations
+ * before completion; the caller synchronises before reading results on the host.  Kernels are
+ * launched with programmatic stream serialization and wait for their predecessor on the stream
+ * before touching memory: stream order is exactly that of plain launches, consecutive library
+ * kernels merely overlap their launch gaps.  After a first eager pass (workspace and allocator
+ * blocks in place) a sequence of calls can be captured into a CUDA graph.  Citations
  * give the reference interface each entry point replaces (paths relative to libs/rtensors/ of
  * aheschl1/rtensors).
  */
