@@ -289,6 +289,16 @@ int rtb_sgd_update_f32(rtb_ctx *ctx, float *p, const float *g, float lr, size_t 
 /* Backend::convert u8 -> f32 followed by `/ divisor` (src/backend/cuda.rs:790-812,
  * examples/mnist/src/main.rs:108-111) */
 int rtb_u8_to_f32_div(rtb_ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n);
+/* Backend::convert (src/backend/mod.rs:234; CPU loop src/backend/cpu.rs:221-233; the reference's
+ * CUDA form is one host read + one host write per element, src/backend/cuda.rs:682-703): dst[i] =
+ * src[i] converted by the rules of DTypeConversion (src/core/value.rs:270-290, 333-460, 770-822),
+ * i.e. Rust `as` casts: float -> integer rounds half away from zero and saturates (NaN -> 0),
+ * integer -> integer truncates, integer -> float and f64 -> f32 round to nearest even, anything
+ * -> boolean is `!= 0`, boolean -> anything is 0 or 1.  Any pair of the 13 dtypes, equal ones
+ * included.  Both buffers hold n elements, must not overlap, and must be aligned to their element
+ * type (16 bytes for the 128-bit integers).  TensorBase::into_dtype (src/core/primitives.rs:527-538)
+ * is alloc + this call. */
+int rtb_convert(rtb_ctx *ctx, int src_dtype, int dst_dtype, const void *src, void *dst, size_t n);
 
 /* ---- multi-GPU sharding (new; the reference is single-device).  Host-only arithmetic: rank
  *      `part` of `parts` gets the half-open slab [*begin, *end) of an extent, earlier ranks

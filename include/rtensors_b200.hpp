@@ -83,6 +83,19 @@ struct MetaTensor {
         check(rtb_meta_permute(rank(), shape.data(), strides.data(), dims.size(), dims.data(), o.shape.data(), o.strides.data()));
         return o;
     }
+    // view_as_inner (src/core/tensor.rs:328-355): contiguous views only, equal element count
+    MetaTensor view_as(std::vector<size_t> new_shape) const {
+        MetaTensor o = MetaTensor::contiguous(std::move(new_shape));
+        if (!is_contiguous()) throw TensorError(RTB_ERR_NONCONTIG, "Cannot view_as non contiguous tensor");
+        if (o.size() != size()) throw TensorError(RTB_ERR_SHAPE, "Invalid size for initial shape");
+        o.offset = offset;
+        return o;
+    }
+    MetaTensor transpose() const {
+        std::vector<size_t> dims(rank());
+        for (size_t k = 0; k < rank(); ++k) dims[k] = rank() - 1 - k;
+        return permute(dims);
+    }
     MetaTensor unsqueeze(size_t dim) const {
         MetaTensor o;
         o.offset = offset; o.shape.resize(rank() + 1); o.strides.resize(rank() + 1);
@@ -206,6 +219,11 @@ class Cuda {
         check(rtb_reduce_view_ex(ctx_, DTypeOf<T>::value, (int)op, &st, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset,
                                  axis, dst.ptr));
     }
+    // Backend::convert (src/backend/mod.rs:234): dst[i] = src[i] as N, both buffers of equal length
+    template <typename T, typename N> void convert(const Buf<T> &src, Buf<N> &dst) const {
+        if (src.len != dst.len) throw TensorError(RTB_ERR_SHAPE, "Buffer size mismatch in convert");
+        check(rtb_convert(ctx_, DTypeOf<T>::value, DTypeOf<N>::value, src.ptr, dst.ptr, src.len));
+    }
     template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
         check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
     }
@@ -245,6 +263,8 @@ template <typename T> class TensorBase {
     static TensorBase zeros(const Cuda &b, std::vector<size_t> shape) { return full(b, std::move(shape), T(0)); }
     static TensorBase ones(const Cuda &b, std::vector<size_t> shape) { return full(b, std::move(shape), T(1)); }
     static TensorBase scalar(const Cuda &b, T v) { return from_buf(b, {v}, {}); }
+    static TensorBase column(const Cuda &b, const std::vector<T> &v) { return from_buf(b, v, {v.size()}); }
+    static TensorBase row(const Cuda &b, const std::vector<T> &v) { return from_buf(b, v, {1, v.size()}); }
 
     const std::vector<size_t> &shape() const { return meta.shape; }
     const std::vector<ptrdiff_t> &strides() const { return meta.strides; }
@@ -265,6 +285,21 @@ template <typename T> class TensorBase {
         return t;
     }
     TensorBase owned() const { return contiguous(); }
+    TensorBase view_as(std::vector<size_t> shape) const { return view_of(meta.view_as(std::move(shape))); }
+    TensorBase transpose() const { return view_of(meta.transpose()); }
+    // contiguous() then view_as: always a fresh buffer (src/core/tensor.rs:238-243)
+    TensorBase reshape(std::vector<size_t> shape) const {
+        TensorBase c = contiguous();
+        c.meta = c.meta.view_as(std::move(shape));
+        return c;
+    }
+    void fill(T v) { backend->fill(*buf, v, meta); }
+    // alloc + convert of the whole buffer, meta cloned (src/core/primitives.rs:527-538)
+    template <typename N> TensorBase<N> into_dtype() const {
+        TensorBase<N> t{backend, backend->template alloc<N>(buf->len), meta};
+        backend->convert(*buf, *t.buf);
+        return t;
+    }
     std::vector<T> cpu() const {
         TensorBase c = contiguous();
         std::vector<T> all = backend->dump(*c.buf);

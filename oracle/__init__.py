@@ -303,6 +303,24 @@ def u8_to_f32_div(src: np.ndarray, divisor: float = 255.0) -> np.ndarray:
     return out
 
 
+DTYPE_SIZE = {U8: 1, I8: 1, U16: 2, I16: 2, U32: 4, U128: 16, I32: 4, U64: 8, I64: 8, I128: 16, F32: 4, F64: 8, BOOL: 1}
+
+
+def convert(src_bytes: bytes, src_dtype: int, dst_dtype: int, fast: bool = False) -> bytes:
+    """Backend::convert over raw little-endian element bytes (so that the 128-bit types, which numpy
+    lacks, go through the same door).  Returns the destination buffer's bytes."""
+    if src_dtype not in DTYPE_SIZE or dst_dtype not in DTYPE_SIZE:
+        raise OracleError(-5)
+    n, rem = divmod(len(src_bytes), DTYPE_SIZE[src_dtype])
+    assert rem == 0
+    src = np.frombuffer(bytes(src_bytes), dtype=np.uint8).copy() if n else np.zeros(1, np.uint8)
+    out = np.zeros(max(n * DTYPE_SIZE[dst_dtype], 1), dtype=np.uint8)
+    rc = lib(fast).orc_convert(C.c_int(src_dtype), C.c_int(dst_dtype), _ptr(src), _ptr(out), C.c_size_t(n))
+    if rc != 0:
+        raise OracleError(rc)
+    return out[: n * DTYPE_SIZE[dst_dtype]].tobytes()
+
+
 def gemm(a: np.ndarray, b: np.ndarray, m: int, k: int, n: int, ta: bool = False, tb: bool = False) -> np.ndarray:
     c = np.zeros(m * n, dtype=np.float32)
     lib(True).orc_gemm_f32(_ptr(a), _ptr(b), _ptr(c), C.c_size_t(m), C.c_size_t(k), C.c_size_t(n),

@@ -759,6 +759,95 @@ ORC_API void orc_u8_to_f32_div(const uint8_t *src, float *dst, float divisor, si
     for (size_t i = 0; i < n; ++i) dst[i] = (float)src[i] / divisor;
 }
 
+/* ------------------------------------------------------------------------------------------
+ * dtype conversion: Backend::convert (backend/cpu.rs:221-233) applies DTypeConversion::convert
+ * (core/value.rs:270-290) per element.  The per-type rules (core/value.rs:333-395 floats,
+ * 402-460 integers, 770-822 boolean) are Rust `as` casts:
+ *   float -> int   : round() (half away from zero) then a saturating cast, NaN -> 0
+ *   float -> float : nearest-even (f64 -> f32 may overflow to inf)
+ *   int   -> int   : two's-complement truncation / sign extension
+ *   int   -> float : nearest-even of the exact value
+ *   any   -> bool  : value != 0 (NaN is true);  bool -> any : 0 or 1
+ * Every source value is widened exactly (integers to 128 bits, f32 to f64) and cast from there,
+ * which gives the same result as the direct cast.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct { int kind; /* 0 unsigned, 1 signed, 2 float */ u128_t u; i128_t s; double f; } wide_t;
+
+static wide_t cv_load(int dtype, const void *p, size_t i) {
+    wide_t w = {0, 0, 0, 0.0};
+    switch (dtype) {
+        case ORC_U8: w.u = ((const uint8_t *)p)[i]; break;
+        case ORC_U16: w.u = ((const uint16_t *)p)[i]; break;
+        case ORC_U32: w.u = ((const uint32_t *)p)[i]; break;
+        case ORC_U64: w.u = ((const uint64_t *)p)[i]; break;
+        case ORC_U128: w.u = ((const u128_t *)p)[i]; break;
+        case ORC_BOOL: w.u = ((const uint8_t *)p)[i] ? 1 : 0; break;
+        case ORC_I8: w.kind = 1; w.s = ((const int8_t *)p)[i]; break;
+        case ORC_I16: w.kind = 1; w.s = ((const int16_t *)p)[i]; break;
+        case ORC_I32: w.kind = 1; w.s = ((const int32_t *)p)[i]; break;
+        case ORC_I64: w.kind = 1; w.s = ((const int64_t *)p)[i]; break;
+        case ORC_I128: w.kind = 1; w.s = ((const i128_t *)p)[i]; break;
+        case ORC_F32: w.kind = 2; w.f = (double)((const float *)p)[i]; break;
+        default: w.kind = 2; w.f = ((const double *)p)[i]; break;
+    }
+    return w;
+}
+
+/* saturating float -> integer of `bits` bits; the value is already integral */
+static u128_t cv_sat_unsigned(double r, int bits) {
+    if (!(r > 0.0)) return 0; /* negative, zero and NaN */
+    if (r >= ldexp(1.0, bits)) return bits == 128 ? ~(u128_t)0 : (((u128_t)1 << bits) - 1);
+    return (u128_t)r;
+}
+static i128_t cv_sat_signed(double r, int bits) {
+    if (r != r) return 0;
+    i128_t lo = -((i128_t)1 << (bits - 2)) * 2, hi = -(lo + 1);
+    if (r >= ldexp(1.0, bits - 1)) return hi;
+    if (r <= -ldexp(1.0, bits - 1)) return lo;
+    return (i128_t)r;
+}
+
+#define CV_INT_DST(T, BITS, SIGNED)                                                          \
+    {                                                                                        \
+        T v;                                                                                 \
+        if (w.kind == 0) v = (T)w.u;                                                         \
+        else if (w.kind == 1) v = (T)w.s;                                                    \
+        else if (SIGNED) v = (T)cv_sat_signed(round(w.f), BITS);                             \
+        else v = (T)cv_sat_unsigned(round(w.f), BITS);                                       \
+        ((T *)dst)[i] = v;                                                                   \
+    }                                                                                        \
+    break
+
+ORC_API int orc_convert(int src_dtype, int dst_dtype, const void *src, void *dst, size_t n) {
+    if (src_dtype < 0 || src_dtype > ORC_BOOL || dst_dtype < 0 || dst_dtype > ORC_BOOL) return ORC_ERR_DTYPE;
+    for (size_t i = 0; i < n; ++i) {
+        wide_t w = cv_load(src_dtype, src, i);
+        switch (dst_dtype) {
+            case ORC_U8: CV_INT_DST(uint8_t, 8, 0);
+            case ORC_U16: CV_INT_DST(uint16_t, 16, 0);
+            case ORC_U32: CV_INT_DST(uint32_t, 32, 0);
+            case ORC_U64: CV_INT_DST(uint64_t, 64, 0);
+            case ORC_U128: CV_INT_DST(u128_t, 128, 0);
+            case ORC_I8: CV_INT_DST(int8_t, 8, 1);
+            case ORC_I16: CV_INT_DST(int16_t, 16, 1);
+            case ORC_I32: CV_INT_DST(int32_t, 32, 1);
+            case ORC_I64: CV_INT_DST(int64_t, 64, 1);
+            case ORC_I128: CV_INT_DST(i128_t, 128, 1);
+            case ORC_F32:
+                /* an f32 source round-trips through f64 unchanged */
+                ((float *)dst)[i] = w.kind == 0 ? (float)w.u : (w.kind == 1 ? (float)w.s : (float)w.f);
+                break;
+            case ORC_F64:
+                ((double *)dst)[i] = w.kind == 0 ? (double)w.u : (w.kind == 1 ? (double)w.s : w.f);
+                break;
+            default:
+                ((uint8_t *)dst)[i] = w.kind == 0 ? (w.u != 0) : (w.kind == 1 ? (w.s != 0) : (w.f != 0.0));
+                break;
+        }
+    }
+    return ORC_OK;
+}
+
 /* Plain row-major GEMM with f64 accumulation, C[m,n] = A[m,k] * B[k,n]; ta/tb read the operand
  * transposed.  Stands in for OpenBLAS sgemm in the oracle's MLP step; tolerance-checked only. */
 ORC_API void orc_gemm_f32(const float *a, const float *b, float *c, size_t m, size_t k, size_t n,

@@ -308,6 +308,24 @@ class CudaB200:
     def sgd_update(self, p: torch.Tensor, g: torch.Tensor, lr: float):
         check(lib().rtb_sgd_update_f32(self._ctx, self._p(p), self._p(g), C.c_float(lr), C.c_size_t(p.numel())))
 
+    def convert(self, src: torch.Tensor, dst_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`convert::<T, N>` (src/backend/mod.rs:234) into `out`, or into a fresh buffer: every element
+        cast by the reference's DTypeConversion rules (src/core/value.rs:270-290)."""
+        if out is None:
+            out = self.alloc(max(src.numel(), 1), dst_dtype)
+        elif out.dtype != dst_dtype or out.numel() < src.numel():
+            raise ValueError("Buffer size mismatch in convert")
+        check(lib().rtb_convert(self._ctx, C.c_int(dtype_code(src)), C.c_int(TORCH_TO_CODE[dst_dtype]), self._p(src),
+                                self._p(out), C.c_size_t(src.numel())))
+        return out
+
+    def convert_raw(self, src: torch.Tensor, src_code: int, dst_code: int) -> torch.Tensor:
+        """convert over raw byte buffers (torch.uint8), for the 128-bit integer types torch lacks."""
+        n = src.numel() // L.DTYPE_SIZE[src_code]
+        out = self.alloc(max(n, 1) * L.DTYPE_SIZE[dst_code], torch.uint8)
+        check(lib().rtb_convert(self._ctx, C.c_int(src_code), C.c_int(dst_code), self._p(src), self._p(out), C.c_size_t(n)))
+        return out
+
     def u8_to_f32_div(self, src: torch.Tensor, divisor: float = 255.0) -> torch.Tensor:
         out = self.alloc(src.numel(), torch.float32)
         check(lib().rtb_u8_to_f32_div(self._ctx, self._p(src), self._p(out), C.c_float(divisor),

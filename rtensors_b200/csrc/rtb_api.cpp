@@ -431,6 +431,17 @@ RTB_API int rtb_sgd_update_f32(rtb_ctx *c, float *p, const float *g, float lr, s
     return launch_sgd(C(c), p, g, lr, n);
 }
 
+RTB_API int rtb_convert(rtb_ctx *c, int src_dtype, int dst_dtype, const void *src, void *dst, size_t n) {
+    if (!c) return fail(RTB_ERR_INVALID, "null context");
+    if (src_dtype < 0 || src_dtype > RTB_BOOL || dst_dtype < 0 || dst_dtype > RTB_BOOL)
+        return fail(RTB_ERR_DTYPE, "convert: unknown dtype");
+    if (n == 0) return RTB_OK;
+    if (!src || !dst) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_convert(C(c), src_dtype, dst_dtype, src, dst, n);
+}
+
 RTB_API int rtb_u8_to_f32_div(rtb_ctx *c, const uint8_t *src, float *dst, float divisor, size_t n) {
     if (!c || !src || !dst) return fail(RTB_ERR_INVALID, "null argument");
     int rc = use_device(C(c));

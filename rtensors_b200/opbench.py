@@ -123,6 +123,14 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     add("sum (full) f64", f"2^{int(np.log2(n2 // 2))}", 8 * (n2 // 2) + 8, n2 // 2,
         lambda: be.apply_reduce_contiguous_flat(xd, rd, 0, n2 // 2, L.SUM))
     del xd
+    # dtype conversion (Backend::convert): one streaming kernel per type pair
+    for dt, label in ((torch.float64, "f64"), (torch.int32, "i32"), (torch.uint8, "u8")):
+        co = be.alloc(n2, dt)
+        add(f"convert f32 -> {label}", f"2^{int(np.log2(n2))}", (4 + co.element_size()) * n2, n2,
+            lambda co=co, dt=dt: be.convert(x, dt, out=co))
+        if dt is torch.uint8:
+            add("convert u8 -> f32", f"2^{int(np.log2(n2))}", 5 * n2, n2, lambda co=co: be.convert(co, f32, out=x))
+        del co
 
     # ---- config 3: strided / negative-step broadcast add -> (16,64,K,1024)
     K = 64 if quick else 1024

@@ -64,6 +64,14 @@ class Tensor:
     @staticmethod
     def scalar(value, dtype=np.float32, backend=None): return Tensor.from_buf([value], (), dtype, backend)
 
+    @staticmethod
+    def column(values, dtype=np.float32, backend=None):  # shape (n,), src/core/primitives.rs:428-432
+        return Tensor.from_buf(values, (len(values),), dtype, backend)
+
+    @staticmethod
+    def row(values, dtype=np.float32, backend=None):  # shape (1, n), src/core/primitives.rs:440-444
+        return Tensor.from_buf(values, (1, len(values)), dtype, backend)
+
     # ---- meta -------------------------------------------------------------------------------
     @property
     def shape(self): return self.meta.shape
@@ -91,6 +99,17 @@ class Tensor:
         return Tensor(self.backend, self.backend.contiguous(self.buf, self.meta), Meta.contiguous(self.shape))
 
     owned = contiguous
+
+    def reshape(self, shape) -> "Tensor":
+        """contiguous() then view_as: always a fresh buffer (src/core/tensor.rs:238-243)."""
+        c = self.contiguous()
+        return Tensor(c.backend, c.buf, c.meta.view_as(shape))
+
+    def into_dtype(self, dtype) -> "Tensor":
+        """A tensor of the same meta over a converted copy of the whole buffer
+        (src/core/primitives.rs:527-538: alloc + Backend::convert, meta cloned)."""
+        out = self.backend.convert(self.buf, _NP_TO_TORCH[np.dtype(dtype)])
+        return Tensor(self.backend, out, self.meta)
 
     # ---- host access ------------------------------------------------------------------------
     def cpu(self) -> np.ndarray:

@@ -170,6 +170,29 @@ int main() {
         auto b = Tensor<float>::from_buf(cuda, {2, 2, 1, 8}, {2, 2});
         ASSERT_EQ(mean_l1_loss(a, b).item(), 1.75f);
     }
+    {  // into_dtype (core/primitives.rs:527-538; values of backend/remote/remote_tests.rs:816-825),
+       // row / column (core/primitives.rs:428-444), view_as / reshape / transpose (core/tensor.rs:238-243,328-355)
+        auto t = Tensor<float>::from_buf(cuda, {1.7f, -2.2f, 3.0f}, {3});
+        ASSERT_EQ(t.into_dtype<int64_t>().cpu(), (std::vector<int64_t>{2, -2, 3}));
+        ASSERT_EQ(t.into_dtype<uint8_t>().cpu(), (std::vector<uint8_t>{2, 0, 3}));
+        ASSERT_EQ(t.into_dtype<double>().cpu(), (std::vector<double>{(double)1.7f, (double)-2.2f, 3.0}));
+        auto r = Tensor<int32_t>::row(cuda, {1, 2, 3, 4, 5, 6});
+        ASSERT_EQ(r.shape(), (std::vector<size_t>{1, 6}));
+        ASSERT_EQ(Tensor<int32_t>::column(cuda, {1, 2, 3}).shape(), (std::vector<size_t>{3}));
+        auto m = r.view_as({2, 3});
+        ASSERT_EQ(m.transpose().shape(), (std::vector<size_t>{3, 2}));
+        ASSERT_EQ(m.transpose().cpu(), (std::vector<int32_t>{1, 4, 2, 5, 3, 6}));
+        bool threw = false;
+        try { m.transpose().view_as({6}); } catch (const TensorError &) { threw = true; }
+        ASSERT_TRUE(threw);
+        auto flat = m.transpose().reshape({6});
+        ASSERT_EQ(flat.cpu(), (std::vector<int32_t>{1, 4, 2, 5, 3, 6}));
+        ASSERT_TRUE(flat.buf.get() != m.buf.get());
+        auto f = m.slice(1, Slice::full().step(2));
+        f.fill(9);
+        ASSERT_EQ(r.cpu(), (std::vector<int32_t>{9, 2, 9, 9, 5, 9}));
+        ASSERT_EQ(f.into_dtype<float>().cpu(), (std::vector<float>{9, 9, 9, 9}));
+    }
     std::printf("ok: %d checks\n", g_checks);
     return 0;
 }

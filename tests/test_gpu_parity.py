@@ -1248,3 +1248,70 @@ def test_long_chain_of_dependent_small_kernels_keeps_stream_order():
         O.broadcast(ref, O.Meta(sh, sa, 0), cm, O.Meta(sh, sb, 0), ref, O.Meta(sh, sa, 0), O.SUB)
     assert _host(d).tobytes() == ref.tobytes()
 
+
+
+# ------------------------------------------------------------------------------------- dtype conversion
+@pytest.mark.parametrize("src", list(range(13)), ids=lambda c: __import__("convert_cases").NAMES[c])
+def test_convert_all_pairs_edge_values(src):
+    """Every (src, dst) pair on edge values + seeded random ones, bit-exact with the oracle (any NaN
+    matches any NaN).  Element counts are not a multiple of the per-thread pack, so the tail runs too."""
+    from convert_cases import ALL_CODES, NAMES, decode, encode, same, samples
+    rng = np.random.default_rng(2000 + src)
+    raw = encode(src, samples(src, rng))
+    d = _dev(np.frombuffer(raw, dtype=np.uint8).copy())
+    for dst in ALL_CODES:
+        got = _host(_b().convert_raw(d, src, dst)).tobytes()[: (len(raw) // O.DTYPE_SIZE[src]) * O.DTYPE_SIZE[dst]]
+        want = O.convert(raw, src, dst)
+        assert same(dst, decode(dst, got), decode(dst, want)), (NAMES[src], NAMES[dst])
+
+
+@pytest.mark.parametrize("src,dst", [(np.float32, np.int32), (np.float32, np.float64), (np.uint8, np.float32),
+                                     (np.float64, np.float32), (np.int64, np.float32), (np.float32, np.uint8),
+                                     (np.int32, np.int8), (np.float32, np.bool_), (np.bool_, np.float64)])
+@pytest.mark.parametrize("n", [1, 17, 4096, (1 << 20) + 13])
+def test_convert_bulk_matches_oracle(src, dst, n):
+    rng = np.random.default_rng(n + np.dtype(src).itemsize)
+    if np.dtype(src).kind == "f":
+        a = (rng.standard_normal(n) * 10.0 ** rng.integers(-2, 12, n)).astype(src)
+    else:
+        a = _rand(rng, n, src)
+    got = _host(_b().convert(_dev(a), _b_torch(dst)))[:n]
+    want = np.frombuffer(O.convert(a.tobytes(), O.NP_TO_CODE[np.dtype(src)], O.NP_TO_CODE[np.dtype(dst)]), dtype=dst)
+    assert got.tobytes() == want.tobytes()
+
+
+def _b_torch(npdt):
+    from rtensors_b200.tensor import _NP_TO_TORCH
+    return _NP_TO_TORCH[np.dtype(npdt)]
+
+
+def test_convert_unaligned_views_and_errors():
+    """Buffers that are element-aligned but not pack-aligned take the per-element path; a buffer
+    that is not element-aligned, or an unknown dtype, is refused."""
+    import rtensors_b200 as rt
+    lib, ctx = rt.lib(), _b()._ctx
+    rng = np.random.default_rng(77)
+    a = (rng.standard_normal(1001) * 1000).astype(np.float32)
+    d = _dev(np.concatenate([np.zeros(1, np.float32), a]))
+    out = _b().alloc(1003, torch.int16)
+    rc = lib.rtb_convert(ctx, C.c_int(O.F32), C.c_int(O.I16), C.c_void_p(d.data_ptr() + 4), C.c_void_p(out.data_ptr() + 2),
+                         C.c_size_t(1001))
+    assert rc == 0
+    want = np.frombuffer(O.convert(a.tobytes(), O.F32, O.I16), dtype=np.int16)
+    assert _host(out)[1:1002].tobytes() == want.tobytes()
+    assert lib.rtb_convert(ctx, C.c_int(O.F32), C.c_int(O.I16), C.c_void_p(d.data_ptr() + 2), C.c_void_p(out.data_ptr()),
+                           C.c_size_t(8)) != 0
+    assert lib.rtb_convert(ctx, C.c_int(13), C.c_int(O.I16), C.c_void_p(d.data_ptr()), C.c_void_p(out.data_ptr()),
+                           C.c_size_t(8)) != 0
+    assert lib.rtb_convert(ctx, C.c_int(O.F32), C.c_int(O.I16), None, None, C.c_size_t(0)) == 0
+
+
+def test_tensor_into_dtype_keeps_the_view():
+    """into_dtype converts the whole buffer and clones the meta (core/primitives.rs:527-538), so a
+    strided view stays the same view of the converted buffer."""
+    from rtensors_b200.tensor import Tensor
+    t = Tensor.from_buf([1.7, -2.2, 3.0, 2.5, -0.4, 300.2], (2, 3), np.float32, _b())
+    assert t.into_dtype(np.int64).cpu().tolist() == [[2, -2, 3], [3, 0, 300]]
+    assert t.into_dtype(np.bool_).cpu().tolist() == [[True, True, True], [True, True, True]]
+    v = t.permute((1, 0)).slice(0, None, None, -1)
+    assert v.into_dtype(np.uint8).cpu().tolist() == [[3, 255], [0, 0], [2, 3]]
