@@ -4,6 +4,7 @@ of launches), so that an `ncu` capture ends by itself in a minute or two:
     python -m rtensors_b200.profile_cases c3 [K]   strided / negative-step broadcast add, K rows (default 64)
     python -m rtensors_b200.profile_cases red      axis sums of (8192,8192) and (16,4096,1024)
     python -m rtensors_b200.profile_cases ext      variance / logsumexp / L2 norm / argmax of (8192,8192) over both axes
+    python -m rtensors_b200.profile_cases convert  dtype conversion of 2^26 elements: f32->f64, f32->i32, u8->f32, f32->u8 (twice each)
     python -m rtensors_b200.profile_cases mid      mid-size ops (and the fused broadcast+reduce) with an L2 flush between them
 """
 import sys
@@ -89,6 +90,18 @@ def main():
             be.broadcast_reduce(A, am, B, bm, L.ADD, 0, L.SUM)
         torch.cuda.synchronize()
         print('done mid')
+    elif which == 'convert':
+        n = 1 << 26
+        x = torch.randn(n, device=dev) * 100
+        u = torch.randint(0, 255, (n,), device=dev, dtype=torch.uint8)
+        o64, o32, o8 = be.alloc(n, torch.float64), be.alloc(n, torch.int32), be.alloc(n, torch.uint8)
+        for _ in range(2):
+            be.convert(x, torch.float64, out=o64)
+            be.convert(x, torch.int32, out=o32)
+            be.convert(u, torch.float32, out=x)
+            be.convert(x, torch.uint8, out=o8)
+        torch.cuda.synchronize()
+        print('done convert')
 
 
 if __name__ == "__main__":
