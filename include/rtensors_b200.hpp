@@ -148,12 +148,26 @@ class Cuda {
         if (b.len) check(rtb_d2h(ctx_, out.data(), b.ptr, b.len * sizeof(T)));
         return out;
     }
+    template <typename T> size_t len(const Buf<T> &b) const { return b.len; }
+    // Backend::copy_from_slice / copy_range_within (src/backend/mod.rs:227-228; checks as in src/backend/cpu.rs:151-183)
+    template <typename T> void copy_from_slice(Buf<T> &dst, const std::vector<T> &src) const {
+        if (dst.len != src.size()) throw TensorError(RTB_ERR_SHAPE, "Buffer size mismatch in copy_from_slice");
+        if (!src.empty()) check(rtb_h2d(ctx_, dst.ptr, src.data(), src.size() * sizeof(T)));
+        sync();
+    }
+    template <typename T> void copy_range_within(Buf<T> &dst, const Buf<T> &src, size_t dst_offset, size_t src_offset, size_t n) const {
+        if (dst_offset + n > dst.len || src_offset + n > src.len)
+            throw TensorError(RTB_ERR_BOUNDS, "Index out of bounds in copy_range_within");
+        if (n) check(rtb_d2d(ctx_, dst.ptr + dst_offset, src.ptr + src_offset, n * sizeof(T)));
+    }
     template <typename T> T read(const Buf<T> &b, size_t offset) const {
+        if (offset >= b.len) throw TensorError(RTB_ERR_BOUNDS, "Index out of bounds for buffer");
         T v;
         check(rtb_d2h(ctx_, &v, b.ptr + offset, sizeof(T)));
         return v;
     }
     template <typename T> void write(Buf<T> &b, size_t offset, T v) const {
+        if (offset >= b.len) throw TensorError(RTB_ERR_BOUNDS, "Index out of bounds for buffer");
         check(rtb_h2d(ctx_, b.ptr + offset, &v, sizeof(T)));
         sync();
     }

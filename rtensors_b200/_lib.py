@@ -18,6 +18,10 @@ VARIANCE, LOGSUMEXP, NORM, ARGMAX, ARGMIN = 6, 7, 8, 9, 10
 OK = 0
 
 
+# rtb_status codes used by host-side checks (include/rt_b200.h)
+ERR_INVALID, ERR_DTYPE, ERR_BROADCAST, ERR_BOUNDS, ERR_DIM, ERR_SHAPE, ERR_NONCONTIG = -1, -2, -3, -4, -5, -6, -7
+
+
 class RtbError(RuntimeError):
     """A non-zero rtb_status; `.code` is the status, the text comes from rtb_last_error_string()."""
 

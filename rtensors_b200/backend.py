@@ -91,6 +91,48 @@ class CudaB200:
     def dump(self, buf: torch.Tensor) -> np.ndarray:
         return buf.detach().cpu().numpy()
 
+    # buffer-level methods of the trait (src/backend/mod.rs:227-233), checks as in src/backend/cpu.rs:151-207
+    def len(self, buf: torch.Tensor) -> int:
+        return buf.numel()
+
+    def copy(self, buf: torch.Tensor) -> torch.Tensor:
+        out = self.alloc(max(buf.numel(), 1), buf.dtype)
+        if buf.numel():
+            check(lib().rtb_d2d(self._ctx, self._p(out), self._p(buf), C.c_size_t(buf.numel() * buf.element_size())))
+        return out[: buf.numel()]
+
+    def copy_from_slice(self, dst: torch.Tensor, src: np.ndarray):
+        src = np.ascontiguousarray(src).reshape(-1)
+        if dst.numel() != src.size:
+            raise L.RtbError(L.ERR_SHAPE, f"Buffer size mismatch in copy_from_slice: dst size {dst.numel()}, src size {src.size}")
+        if src.size:
+            check(lib().rtb_h2d(self._ctx, self._p(dst), src.ctypes.data_as(C.c_void_p), C.c_size_t(src.nbytes)))
+            self.sync()  # the host array may go away
+
+    def copy_range_within(self, dst: torch.Tensor, src: torch.Tensor, dst_offset: int, src_offset: int, n: int):
+        if dst_offset + n > dst.numel() or src_offset + n > src.numel():
+            raise L.RtbError(L.ERR_BOUNDS, "Index out of bounds in copy_range_within")
+        if n:
+            es = dst.element_size()
+            check(lib().rtb_d2d(self._ctx, C.c_void_p(dst.data_ptr() + dst_offset * es),
+                                C.c_void_p(src.data_ptr() + src_offset * es), C.c_size_t(n * es)))
+
+    def read(self, buf: torch.Tensor, offset: int):
+        if not 0 <= offset < buf.numel():
+            raise L.RtbError(L.ERR_BOUNDS, f"Index {offset} out of bounds for buffer of length {buf.numel()}")
+        host = np.empty(1, dtype=CODE_TO_NP[dtype_code(buf)])
+        check(lib().rtb_d2h(self._ctx, host.ctypes.data_as(C.c_void_p),
+                            C.c_void_p(buf.data_ptr() + offset * buf.element_size()), C.c_size_t(host.nbytes)))
+        return host[0]
+
+    def write(self, buf: torch.Tensor, offset: int, value):
+        if not 0 <= offset < buf.numel():
+            raise L.RtbError(L.ERR_BOUNDS, f"Index {offset} out of bounds for buffer of length {buf.numel()}")
+        host = np.array([value], dtype=CODE_TO_NP[dtype_code(buf)])
+        check(lib().rtb_h2d(self._ctx, C.c_void_p(buf.data_ptr() + offset * buf.element_size()),
+                            host.ctypes.data_as(C.c_void_p), C.c_size_t(host.nbytes)))
+        self.sync()
+
     @staticmethod
     def _p(t: Optional[torch.Tensor]):
         return C.c_void_p(0 if t is None else t.data_ptr())

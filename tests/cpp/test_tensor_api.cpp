@@ -193,6 +193,23 @@ int main() {
         ASSERT_EQ(r.cpu(), (std::vector<int32_t>{9, 2, 9, 9, 5, 9}));
         ASSERT_EQ(f.into_dtype<float>().cpu(), (std::vector<float>{9, 9, 9, 9}));
     }
+    {  // buffer-level trait methods (backend/mod.rs:227-233) with the CPU backend's checks (backend/cpu.rs:151-207)
+        auto a = cuda.alloc_from_slice<int32_t>({1, 2, 3, 4, 5, 6});
+        auto b = cuda.alloc<int32_t>(6);
+        cuda.copy_from_slice(*b, std::vector<int32_t>{10, 20, 30, 40, 50, 60});
+        cuda.copy_range_within(*b, *a, 1, 3, 2);
+        ASSERT_EQ(cuda.dump(*b), (std::vector<int32_t>{10, 4, 5, 40, 50, 60}));
+        ASSERT_EQ(cuda.len(*b), (size_t)6);
+        ASSERT_EQ(cuda.read(*b, 2), 5);
+        cuda.write(*b, 5, 7);
+        ASSERT_EQ(cuda.read(*b, 5), 7);
+        int errors = 0;
+        try { cuda.read(*b, 6); } catch (const TensorError &e) { errors += e.code == RTB_ERR_BOUNDS; }
+        try { cuda.write(*b, 6, 1); } catch (const TensorError &e) { errors += e.code == RTB_ERR_BOUNDS; }
+        try { cuda.copy_range_within(*b, *a, 5, 0, 2); } catch (const TensorError &e) { errors += e.code == RTB_ERR_BOUNDS; }
+        try { cuda.copy_from_slice(*b, std::vector<int32_t>{1}); } catch (const TensorError &e) { errors += e.code == RTB_ERR_SHAPE; }
+        ASSERT_EQ(errors, 4);
+    }
     std::printf("ok: %d checks\n", g_checks);
     return 0;
 }

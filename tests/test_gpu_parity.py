@@ -1315,3 +1315,27 @@ def test_tensor_into_dtype_keeps_the_view():
     assert t.into_dtype(np.bool_).cpu().tolist() == [[True, True, True], [True, True, True]]
     v = t.permute((1, 0)).slice(0, None, None, -1)
     assert v.into_dtype(np.uint8).cpu().tolist() == [[3, 255], [0, 0], [2, 3]]
+
+
+def test_buffer_level_trait_methods():
+    """copy / copy_from_slice / copy_range_within / read / write / len with the CPU backend's checks
+    (backend/cpu.rs:151-207)."""
+    import rtensors_b200._lib as L
+    be = _b()
+    a = _dev(np.arange(1, 7, dtype=np.int32))
+    b = be.alloc(6, torch.int32)
+    be.copy_from_slice(b, np.array([10, 20, 30, 40, 50, 60], dtype=np.int32))
+    be.copy_range_within(b, a, 1, 3, 2)
+    assert _host(b).tolist() == [10, 4, 5, 40, 50, 60]
+    assert be.len(b) == 6 and be.read(b, 2) == 5
+    be.write(b, 5, 7)
+    assert be.read(b, 5) == 7
+    c = be.copy(b)
+    be.write(b, 0, -1)
+    assert _host(c).tolist() == [10, 4, 5, 40, 50, 7]
+    for bad, code in ((lambda: be.read(b, 6), L.ERR_BOUNDS), (lambda: be.write(b, 6, 1), L.ERR_BOUNDS),
+                      (lambda: be.copy_range_within(b, a, 5, 0, 2), L.ERR_BOUNDS),
+                      (lambda: be.copy_from_slice(b, np.zeros(1, np.int32)), L.ERR_SHAPE)):
+        with pytest.raises(L.RtbError) as e:
+            bad()
+        assert e.value.code == code
