@@ -1339,3 +1339,58 @@ def test_buffer_level_trait_methods():
         with pytest.raises(L.RtbError) as e:
             bad()
         assert e.value.code == code
+
+
+def test_one_context_called_from_several_host_threads():
+    """The reference's `Cuda` is Send + Sync and its launchers are called from any host thread
+    (backend/cuda.rs:38-60).  Four threads share one context (one stream, one reduction workspace)
+    and interleave elementwise ops, plain and extended reductions and the fused broadcast+reduce on
+    buffers of their own; every result must equal what the same calls give alone."""
+    import threading
+    from rtensors_b200.meta import Meta
+    be = _b()
+    rng = np.random.default_rng(4242)
+    rows, cols = 300, 1030
+    data = [rng.standard_normal(rows * cols).astype(np.float32) for _ in range(4)]
+    m = Meta.contiguous((rows, cols))
+
+    def work(a, rounds):
+        outs = []
+        for _ in range(rounds):
+            d = _dev(a)
+            be.scalar_apply(d, L_MUL, 1.5, m)
+            be.apply_unary(d, L_RELU, m)
+            outs.append(_host(be.reduce_view(d, m, 0, L_SUM)).copy())
+            outs.append(_host(be.reduce_view(d, m, 1, L_MAX)).copy())
+            outs.append(_host(be.reduce_view(d, m, None, L_SUM)).copy())
+            outs.append(_host(be.reduce_view_ex(d, m, 0, L_VAR)).copy())
+            outs.append(_host(be.reduce_view_ex(d, m, 1, L_ARGMAX)).copy())
+            col = _dev(a[:rows].copy())
+            row = _dev(a[:cols].copy())
+            outs.append(_host(be.broadcast_reduce(col, Meta.contiguous((rows, 1)), row, Meta.contiguous((1, cols)), 0, 0, L_SUM)[0]).copy())
+        return outs
+
+    alone = [work(a, 1) for a in data]
+    got = [None] * 4
+    errs = []
+
+    def run(k):
+        try:
+            got[k] = work(data[k], 6)
+        except Exception as e:  # pragma: no cover
+            errs.append(e)
+
+    ts = [threading.Thread(target=run, args=(k,)) for k in range(4)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert not errs, errs
+    for k in range(4):
+        n = len(alone[k])
+        for j, o in enumerate(got[k]):
+            assert o.tobytes() == alone[k][j % n].tobytes(), (k, j)
+
+
+import rtensors_b200._lib as _L  # noqa: E402
+L_MUL, L_RELU, L_SUM, L_MAX, L_VAR, L_ARGMAX = _L.MUL, _L.RELU, _L.SUM, _L.MAX, _L.VARIANCE, _L.ARGMAX
