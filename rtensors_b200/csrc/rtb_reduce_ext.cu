@@ -67,6 +67,7 @@ template <typename T> struct RedVar {
     using Out = T;
     static constexpr bool kPositional = false;
     static constexpr bool kHeavyMerge = true;  // merging two states costs tens of instructions
+    static constexpr bool kPipelineCols = true;  // column kernel: prefetch the next batch while merging
     struct State {
         T mean, m2;
         unsigned long long n;
@@ -113,6 +114,7 @@ template <typename T> struct RedLse {
     using Out = T;
     static constexpr bool kPositional = false;
     static constexpr bool kHeavyMerge = true;
+    static constexpr bool kPipelineCols = false;  // column kernel: prefetch the next batch while merging
     struct State {
         T m, s;  // running max, sum of exp(x - m); s == 0 marks "empty"
     };
@@ -149,6 +151,7 @@ template <typename T, int P> struct RedNorm {
     using Out = T;
     static constexpr bool kPositional = false;
     static constexpr bool kHeavyMerge = false;
+    static constexpr bool kPipelineCols = false;  // column kernel: prefetch the next batch while merging
     struct State {
         T v;
     };
@@ -170,6 +173,7 @@ template <typename T, bool MAXI> struct RedArg {
     using Out = unsigned long long;
     static constexpr bool kPositional = true;
     static constexpr bool kHeavyMerge = true;
+    static constexpr bool kPipelineCols = true;  // column kernel: prefetch the next batch while merging
     static constexpr unsigned long long kNone = ~0ull;
     struct State {
         T v;
@@ -321,7 +325,7 @@ __global__ void __launch_bounds__(kBlock) ext_rows_kernel(const T *__restrict__ 
 }
 
 // ---- inner > 1 (or strided rows): tiles of 32 x VW columns, the 8 warps of a CTA along k --------
-template <typename T, typename R, int VW>
+template <typename T, typename R, int VW, bool PIPE = false>
 __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ src, size_t outer, size_t len, size_t inner,
                                                           ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t split,
                                                           typename R::State *partial, unsigned int *counters,
@@ -329,6 +333,7 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
     grid_dep_wait();
     using State = typename R::State;
     constexpr int U = 8;  // rows in flight per thread (4 measured slower, also for the heavy states)
+    constexpr bool kPipelined = PIPE;
     __shared__ State smem[kWarps][32][VW];
     __shared__ bool is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -348,11 +353,10 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
         if (col < inner) {
             const T *p = src + (ptrdiff_t)o * outer_stride + (ptrdiff_t)col;
             size_t k = k0 + warp;
-            for (; k + (U - 1) * kWarps < k1; k += U * kWarps) {
-                T x[U][VW];
+            auto fetch = [&](T (&x)[U][VW], size_t kk) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const T *pr = p + (ptrdiff_t)(k + u * kWarps) * row_stride;
+                    const T *pr = p + (ptrdiff_t)(kk + u * kWarps) * row_stride;
                     if (VW > 1) {
                         typename Vec128<T>::U t;
                         t.q = *reinterpret_cast<const uint4 *>(pr);
@@ -362,12 +366,42 @@ __global__ void __launch_bounds__(kBlock) ext_cols_kernel(const T *__restrict__ 
                         x[u][0] = *pr;
                     }
                 }
+            };
+            auto absorb = [&](const T (&x)[U][VW], size_t kk) {
 #pragma unroll
                 for (int c = 0; c < VW; ++c) {
                     T colv[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u) colv[u] = x[u][c];
-                    R::template add_batch<U>(s[c], colv, k, (unsigned long long)kWarps);
+                    R::template add_batch<U>(s[c], colv, kk, (unsigned long long)kWarps);
+                }
+            };
+            if (kPipelined) {
+                // the next batch's loads are issued before this batch is absorbed, so the merge
+                // arithmetic (a division per column for Welford) runs under the load latency
+                T x[U][VW];
+                bool have = k + (U - 1) * kWarps < k1;
+                if (have) fetch(x, k);
+                while (have) {
+                    const size_t kn = k + U * kWarps;
+                    const bool next = kn + (U - 1) * kWarps < k1;
+                    T y[U][VW];
+                    if (next) fetch(y, kn);
+                    absorb(x, k);
+                    if (next) {
+#pragma unroll
+                        for (int u = 0; u < U; ++u)
+#pragma unroll
+                            for (int c = 0; c < VW; ++c) x[u][c] = y[u][c];
+                    }
+                    k = kn;
+                    have = next;
+                }
+            } else {
+                for (; k + (U - 1) * kWarps < k1; k += U * kWarps) {
+                    T x[U][VW];
+                    fetch(x, k);
+                    absorb(x, k);
                 }
             }
             for (; k < k1; k += kWarps) {
@@ -476,13 +510,24 @@ int ext_launch(Ctx *ctx, const T *src, size_t outer, size_t len, size_t inner, p
     const size_t base = outer * ((inner + cols_per_tile - 1) / cols_per_tile);
     // CTAs do equal work, so the launch is fastest as ONE wave of resident CTAs: as many chunks of k
     // per tile as fit, each at least 64 rows
-    const size_t resident = vec ? resident_ctas(ctx, ext_cols_kernel<T, R, (int)N>) : resident_ctas(ctx, ext_cols_kernel<T, R, 1>);
+    // Few column tiles (the chunked one-wave regime) and a reducer whose merge is long: the
+    // software-pipelined instantiation (next batch loaded before this one is absorbed; twice the
+    // registers, half the resident CTAs).  Measured on (8192,8192) axis 0: variance 59 -> 53 us,
+    // argmax 56 -> 52 us; with many tiles and long loops it is 3-5 % slower, and logsumexp (121
+    // registers) loses a third, so those stay on the plain loop.
+    const bool pipe = vec && R::kPipelineCols && base < (size_t)ctx->sm_count * 2;
+    const size_t resident = !vec ? resident_ctas(ctx, ext_cols_kernel<T, R, 1>)
+                                 : (pipe ? resident_ctas(ctx, ext_cols_kernel<T, R, (int)N, R::kPipelineCols>)
+                                         : resident_ctas(ctx, ext_cols_kernel<T, R, (int)N>));
     split = base <= kMaxTileCounters ? resident / base : 1;  // one completion counter per tile
     if (split > len / 64) split = len / 64;
     if (split < 1) split = 1;
     if (split > 1 && (rc = get_partial(outer * split * inner)) != RTB_OK) return rc;
     const unsigned grid = grid_of(base * split);
-    if (vec)
+    if (pipe)
+        launch_dep(ctx, grid, kBlock, ext_cols_kernel<T, R, (int)N, R::kPipelineCols>, src, outer, len, inner, outer_stride,
+                   row_stride, split, partial, counters, dst, st);
+    else if (vec)
         launch_dep(ctx, grid, kBlock, ext_cols_kernel<T, R, (int)N>, src, outer, len, inner, outer_stride, row_stride, split, partial,
                                                                         counters, dst, st);
     else
