@@ -52,7 +52,7 @@ def _newest_header() -> float:
 
 def _compile(unit, verbose):
     src, obj, extra = unit
-    cmd = [NVCC, *ARCH, *COMMON, *extra, "-x", "cu", "-dc" if False else "-c", src, "-o", obj]
+    cmd = [NVCC, *ARCH, *COMMON, *extra, "-x", "cu", "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     p = subprocess.run(cmd, capture_output=True, text=True)
