@@ -238,6 +238,11 @@ class Cuda {
         if (src.len != dst.len) throw TensorError(RTB_ERR_SHAPE, "Buffer size mismatch in convert");
         check(rtb_convert(ctx_, DTypeOf<T>::value, DTypeOf<N>::value, src.ptr, dst.ptr, src.len));
     }
+    // dense relu / abs gradient map of a view (src/ops/unary/mod.rs:213-252), kind = RTB_MASK_RELU / RTB_MASK_ABS
+    template <typename T> void grad_mask(const Buf<T> &src, const MetaTensor &m, int kind, Buf<T> &dst) const {
+        check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, src.len));
+        check(rtb_grad_mask(ctx_, DTypeOf<T>::value, kind, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
+    }
     template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
         check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
     }
@@ -379,6 +384,14 @@ template <typename T> class TensorBase {
     TensorBase abs() const { TensorBase t = owned(); t.abs_inplace(); return t; }
     TensorBase sign() const { TensorBase t = owned(); t.sign_inplace(); return t; }
     TensorBase neg() const { TensorBase t = owned(); t.neg_inplace(); return t; }
+    TensorBase grad_map(int kind) const {
+        MetaTensor m = MetaTensor::contiguous(meta.shape);
+        TensorBase t{backend, backend->template alloc<T>(m.size()), m};
+        if (m.size()) backend->grad_mask(*buf, meta, kind, *t.buf);
+        return t;
+    }
+    TensorBase relu_grad_map() const { return grad_map(RTB_MASK_RELU); }
+    TensorBase abs_grad_map() const { return grad_map(RTB_MASK_ABS); }
 
     // reductions: a non-contiguous view is copied first; `_at` keeps the reduced dim as size 1
     TensorBase reduce(ReductionOpTypes op) const {

@@ -190,6 +190,18 @@ def elementwise(buf: np.ndarray, kind: int, op: int, value, meta: Meta, fast: bo
                                    C.c_size_t(meta.offset)))
 
 
+MASK_RELU, MASK_ABS = 1, 2
+
+
+def grad_mask(buf: np.ndarray, kind: int, meta: Meta, fast: bool = False) -> np.ndarray:
+    """The relu / abs gradient map of the view `meta` of `buf` as a dense array (ops/unary/mod.rs:213-252)."""
+    assert buf.flags.c_contiguous and buf.ndim == 1
+    out = np.zeros(max(meta.size, 1), dtype=buf.dtype)
+    _chk(lib(fast).orc_grad_mask(C.c_int(_code(buf)), C.c_int(kind), _ptr(buf), C.c_size_t(meta.rank), _sizes(meta.shape),
+                                 _diffs(meta.strides), C.c_size_t(meta.offset), _ptr(out)))
+    return out[: meta.size]
+
+
 def scalar_op(buf, op, value, meta, fast=False):
     elementwise(buf, 0, op, value, meta, fast)
 

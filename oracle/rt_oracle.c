@@ -760,6 +760,42 @@ ORC_API void orc_u8_to_f32_div(const uint8_t *src, float *dst, float divisor, si
 }
 
 /* ------------------------------------------------------------------------------------------
+ * Gradient maps of relu and abs, ops/unary/mod.rs:213-252: a zeros tensor of the input's shape,
+ * then for every coordinate (row-major) map = input > 0 ? 1 : 0 (relu) or input > 0 ? 1 : -1 (abs).
+ * kind 1 = relu, 2 = abs.
+ * ---------------------------------------------------------------------------------------- */
+#define DEF_GRAD_MASK(S, T, CODE)                                                            \
+    static void mask_##S(int kind, const T *src, size_t rank, const size_t *shape,           \
+                         const ptrdiff_t *strides, size_t offset, T *dst) {                  \
+        if (meta_size(rank, shape) == 0) return;                                             \
+        off_iter it;                                                                         \
+        it_init(&it, rank, shape, strides, offset);                                          \
+        size_t i = 0;                                                                        \
+        while (!it.done) {                                                                   \
+            T v = src[it.off];                                                               \
+            dst[i++] = v > (T)0 ? (T)1 : (kind == 1 ? (T)0 : (T)-1);                         \
+            it_next(&it);                                                                    \
+        }                                                                                    \
+    }
+FOR_ALL_TYPES(DEF_GRAD_MASK)
+
+ORC_API int orc_grad_mask(int dtype, int kind, const void *src, size_t rank, const size_t *shape,
+                          const ptrdiff_t *strides, size_t offset, void *dst) {
+    if (rank > ORC_MAX_RANK) return ORC_ERR_DIM;
+    if (kind != 1 && kind != 2) return ORC_ERR_OP;
+    /* -T::ONE needs a signed type */
+    if (kind == 2 && (dtype == ORC_U8 || dtype == ORC_U16 || dtype == ORC_U32 || dtype == ORC_U64 ||
+                      dtype == ORC_U128 || dtype == ORC_BOOL))
+        return ORC_ERR_DTYPE;
+    switch (dtype) {
+#define CASE_MASK(S, T, CODE)                                                                \
+    case CODE: mask_##S(kind, (const T *)src, rank, shape, strides, offset, (T *)dst); return ORC_OK;
+        FOR_ALL_TYPES(CASE_MASK)
+    }
+    return ORC_ERR_DTYPE;
+}
+
+/* ------------------------------------------------------------------------------------------
  * dtype conversion: Backend::convert (backend/cpu.rs:221-233) applies DTypeConversion::convert
  * (core/value.rs:270-290) per element.  The per-type rules (core/value.rs:333-395 floats,
  * 402-460 integers, 770-822 boolean) are Rust `as` casts:

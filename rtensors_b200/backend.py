@@ -189,6 +189,16 @@ class CudaB200:
                                       meta.c_shape, meta.c_strides, C.c_size_t(meta.offset), self._p(out)))
         return out
 
+    def grad_mask(self, buf: torch.Tensor, meta: Meta, kind: int) -> torch.Tensor:
+        """Dense relu (L.MASK_RELU) or abs (L.MASK_ABS) gradient map of a view, one kernel instead of the
+        reference's per-element get / set loop (src/ops/unary/mod.rs:213-252)."""
+        out = self.alloc(max(meta.size, 1), buf.dtype)
+        if meta.size:
+            meta.check_extent(buf.numel())
+            check(lib().rtb_grad_mask(self._ctx, C.c_int(dtype_code(buf)), C.c_int(kind), self._p(buf), C.c_size_t(meta.rank),
+                                      meta.c_shape, meta.c_strides, C.c_size_t(meta.offset), self._p(out)))
+        return out
+
     # -- broadcast ----------------------------------------------------------------------------
     def broadcast(self, left: Tuple[torch.Tensor, Meta], right: Tuple[torch.Tensor, Meta],
                   dst: Tuple[torch.Tensor, Meta], op: int):

@@ -133,6 +133,21 @@ RTB_API int rtb_copy_view(rtb_ctx *c, int dtype, const void *src, size_t rank, c
     return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
 }
 
+RTB_API int rtb_grad_mask(rtb_ctx *c, int dtype, int kind, const void *src, size_t rank, const size_t *shape,
+                          const ptrdiff_t *strides, size_t offset, void *dst) {
+    int rc = check_view_args(c, src, rank, shape, strides);
+    if (rc) return rc;
+    if (!dst) return fail(RTB_ERR_INVALID, "null destination");
+    if (kind != RTB_MASK_RELU && kind != RTB_MASK_ABS) return fail(RTB_ERR_INVALID, "unknown gradient map kind %d", kind);
+    if ((rc = use_device(C(c)))) return rc;
+    std::vector<ptrdiff_t> dense(rank ? rank : 1);
+    rtb_meta_contiguous_strides(rank, shape, dense.data());
+    EwCall call{};
+    call.dtype = dtype; call.family = kFamCopy; call.op = kind;
+    call.d = dst; call.l = src; call.r = nullptr;
+    return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
+}
+
 RTB_API int rtb_broadcast(rtb_ctx *c, int dtype, int binop, const void *left, const ptrdiff_t *sl, size_t ol,
                           const void *right, const ptrdiff_t *sr, size_t orr, void *dst, const ptrdiff_t *sd,
                           size_t od, size_t rank, const size_t *shape) {

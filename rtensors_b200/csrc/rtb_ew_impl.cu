@@ -139,6 +139,13 @@ template <int OP> struct FScalar { T v; __device__ __forceinline__ T operator()(
 template <int OP> struct FUnary { __device__ __forceinline__ T operator()(T a, T) const { return una<OP>(a); } };
 struct FFill { T v; __device__ __forceinline__ T operator()(T, T) const { return v; } };
 struct FCopy { __device__ __forceinline__ T operator()(T a, T) const { return a; } };
+// Gradient maps the reference builds with one host get + one host set per element
+// (src/ops/unary/mod.rs:213-252): relu -> (x > 0 ? 1 : 0); abs -> (x > 0 ? 1 : -1), so 0 and NaN map
+// to -1 exactly as the `if val > T::ZERO` there does.  Out of place: src view -> dense map.
+struct FMaskRelu { __device__ __forceinline__ T operator()(T a, T) const { return a > (T)0 ? (T)1 : (T)0; } };
+#if RTB_KIND == 1 || RTB_KIND == 2
+struct FMaskAbs { __device__ __forceinline__ T operator()(T a, T) const { return a > (T)0 ? (T)1 : (T)-1; } };
+#endif
 
 // Extended families with a run-time op code (one instantiation each; the switch is noise next to
 // the transcendental it selects).  Formulas are the reference CPU backend's, not libm shortcuts
@@ -677,7 +684,13 @@ int RTB_CAT(ew_dispatch_, RTB_SUFFIX)(Ctx *ctx, const EwCall &c, const rtb_plan 
         case kFamScalar: return launch_scalar(ctx, c, plan, v);
         case kFamUnary: return launch_unary(ctx, c, plan);
         case kFamFill: return launch<FFill, 0>(ctx, c, plan, FFill{v});
-        case kFamCopy: return launch<FCopy, 1>(ctx, c, plan, FCopy{});
+        case kFamCopy:
+            if (c.op == 0) return launch<FCopy, 1>(ctx, c, plan, FCopy{});
+            if (c.op == 1) return launch<FMaskRelu, 1>(ctx, c, plan, FMaskRelu{});
+#if RTB_KIND == 1 || RTB_KIND == 2
+            if (c.op == 2) return launch<FMaskAbs, 1>(ctx, c, plan, FMaskAbs{});
+#endif
+            return fail(RTB_ERR_DTYPE, "abs gradient map needs a signed element type");
     }
     return fail(RTB_ERR_INVALID, "unknown elementwise family %d", c.family);
 }

@@ -169,6 +169,13 @@ class Tensor:
     def neg(self): return self.owned().neg_inplace()
     def __neg__(self): return self.neg()
 
+    # gradient maps the reference's autograd stores for relu and abs (src/ops/unary/mod.rs:213-252)
+    def relu_grad_map(self) -> "Tensor":
+        return Tensor(self.backend, self.backend.grad_mask(self.buf, self.meta, L.MASK_RELU), Meta.contiguous(self.shape))
+
+    def abs_grad_map(self) -> "Tensor":
+        return Tensor(self.backend, self.backend.grad_mask(self.buf, self.meta, L.MASK_ABS), Meta.contiguous(self.shape))
+
     # ---- reductions -------------------------------------------------------------------------
     def _reduce(self, op: int, axis: Optional[int]) -> "Tensor":
         # The reference copies a non-contiguous view first (`contiguous()`); here the library reduces

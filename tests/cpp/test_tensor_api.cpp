@@ -210,6 +210,17 @@ int main() {
         try { cuda.copy_from_slice(*b, std::vector<int32_t>{1}); } catch (const TensorError &e) { errors += e.code == RTB_ERR_SHAPE; }
         ASSERT_EQ(errors, 4);
     }
+    {  // gradient maps of relu and abs (ops/unary/mod.rs:213-252): > 0 -> 1, else 0 / -1
+        auto t = Tensor<float>::from_buf(cuda, {-1.0f, 0.0f, 2.0f, 3.0f, -0.5f, 0.25f}, {2, 3});
+        ASSERT_EQ(t.relu_grad_map().cpu(), (std::vector<float>{0, 0, 1, 1, 0, 1}));
+        ASSERT_EQ(t.abs_grad_map().cpu(), (std::vector<float>{-1, -1, 1, 1, -1, 1}));
+        ASSERT_EQ(t.transpose().relu_grad_map().cpu(), (std::vector<float>{0, 1, 0, 0, 1, 1}));
+        auto u = Tensor<uint8_t>::from_buf(cuda, {0, 5}, {2});
+        ASSERT_EQ(u.relu_grad_map().cpu(), (std::vector<uint8_t>{0, 1}));
+        bool threw = false;
+        try { u.abs_grad_map(); } catch (const TensorError &e) { threw = e.code == RTB_ERR_DTYPE; }
+        ASSERT_TRUE(threw);
+    }
     std::printf("ok: %d checks\n", g_checks);
     return 0;
 }

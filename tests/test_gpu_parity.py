@@ -1394,3 +1394,38 @@ def test_one_context_called_from_several_host_threads():
 
 import rtensors_b200._lib as _L  # noqa: E402
 L_MUL, L_RELU, L_SUM, L_MAX, L_VAR, L_ARGMAX = _L.MUL, _L.RELU, _L.SUM, _L.MAX, _L.VARIANCE, _L.ARGMAX
+
+
+@pytest.mark.parametrize("dt", NP_DTYPES, ids=lambda d: np.dtype(d).name)
+def test_relu_and_abs_gradient_maps_on_views(dt):
+    """rtb_grad_mask against the oracle on a contiguous tensor, a strided / reversed window and a
+    permuted view, every dtype; abs needs a signed type and is refused otherwise."""
+    import rtensors_b200._lib as L
+    rng = np.random.default_rng(31 + np.dtype(dt).itemsize)
+    buf = _rand(rng, 6 * 40 * 50 + 7, dt)
+    if np.dtype(dt).kind == "f":
+        buf[::11] = 0
+        buf[5] = np.nan
+    base = O.Meta.contiguous((6, 40, 50))
+    views = [base, O.Meta((6, 40, 50), base.strides, 7), base.slice(1, 3, 37, 2).slice(2, None, None, -1),
+             base.permute((2, 0, 1)), base.slice(0, 1, 2, 1).squeeze()]
+    d = _dev(buf)
+    signed = np.dtype(dt).kind in "fi"
+    for m in views:
+        for kind in (L.MASK_RELU, L.MASK_ABS):
+            if kind == L.MASK_ABS and not signed:
+                with pytest.raises(L.RtbError):
+                    _b().grad_mask(d, _meta_pair(m), kind)
+                with pytest.raises(O.OracleError):
+                    O.grad_mask(buf, kind, m)
+                continue
+            got = _host(_b().grad_mask(d, _meta_pair(m), kind))[: m.size]
+            assert got.tobytes() == O.grad_mask(buf, kind, m).tobytes(), (m, kind)
+
+
+def test_tensor_gradient_maps():
+    from rtensors_b200.tensor import Tensor
+    t = Tensor.from_buf([-1.0, 0.0, 2.0, 3.0, -0.5, 0.25], (2, 3), np.float32, _b())
+    assert t.relu_grad_map().cpu().tolist() == [[0, 0, 1], [1, 0, 1]]
+    assert t.abs_grad_map().cpu().tolist() == [[-1, -1, 1], [1, -1, 1]]
+    assert t.transpose().relu_grad_map().cpu().tolist() == [[0, 1], [0, 0], [1, 1]]
