@@ -284,14 +284,20 @@ int rtb_reduce_to_shape(rtb_ctx *ctx, int dtype, const void *upstream, size_t ra
  * relu with its gradient mask in one pass (relu_inplace + the per-element mask loop of
  * src/ops/unary/mod.rs:213-252): x = x>0 ? x : 0, mask = x>0 ? 1 : 0 */
 int rtb_relu_mask_f32(rtb_ctx *ctx, float *x, float *mask, size_t n);
-/* The gradient map of relu / abs as a kernel (the reference fills it with one host get and one
- * host set per element, src/ops/unary/mod.rs:213-252): dst is a dense row-major tensor of the
- * view's shape, dst[c] = src[c] > 0 ? 1 : 0 (RTB_MASK_RELU, any dtype) or src[c] > 0 ? 1 : -1
- * (RTB_MASK_ABS, signed integers and floats; 0 and NaN give -1 as in the reference).  src is any
- * view (strided, permuted, negative step); src and dst must not overlap. */
-enum { RTB_MASK_RELU = 1, RTB_MASK_ABS = 2 };
-int rtb_grad_mask(rtb_ctx *ctx, int dtype, int kind, const void *src, size_t rank, const size_t *shape,
-                  const ptrdiff_t *strides, size_t offset, void *dst);
+/* The per-element maps the reference's autograd fills with one host get and one host set per
+ * element, as one kernel each.  dst is a dense row-major tensor of the view's shape; src is any
+ * view (strided, permuted, negative step); src and dst must not overlap.
+ *   RTB_MASK_RELU        dst = src > 0 ? 1 : 0          any dtype        (src/ops/unary/mod.rs:236-252)
+ *   RTB_MASK_ABS         dst = src > 0 ? 1 : -1         signed / float   (src/ops/unary/mod.rs:213-235;
+ *                                                        0 and NaN give -1 as there)
+ *   RTB_MASK_LEAKY_RELU  dst = src > 0 ? 1 : *value     any dtype        (src/ops/scalar/mod.rs:149-166)
+ *   RTB_MASK_RECIPROCAL  dst = 1 / src                  all but boolean  (src/ops/broadcast/div.rs:583-587;
+ *                                                        integer 1/0 gives 0 where the reference panics)
+ * `value` points at one element of `dtype` (the slope) for RTB_MASK_LEAKY_RELU and is ignored
+ * otherwise (may be NULL). */
+enum { RTB_MASK_RELU = 1, RTB_MASK_ABS = 2, RTB_MASK_LEAKY_RELU = 3, RTB_MASK_RECIPROCAL = 4 };
+int rtb_grad_mask(rtb_ctx *ctx, int dtype, int kind, const void *value, const void *src, size_t rank,
+                  const size_t *shape, const ptrdiff_t *strides, size_t offset, void *dst);
 /* SGD::step (src/grad/optim.rs:30-50): u = g*lr rounded, then p = p - u (no FMA) */
 int rtb_sgd_update_f32(rtb_ctx *ctx, float *p, const float *g, float lr, size_t n);
 /* Backend::convert u8 -> f32 followed by `/ divisor` (src/backend/cuda.rs:790-812,

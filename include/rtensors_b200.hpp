@@ -238,10 +238,10 @@ class Cuda {
         if (src.len != dst.len) throw TensorError(RTB_ERR_SHAPE, "Buffer size mismatch in convert");
         check(rtb_convert(ctx_, DTypeOf<T>::value, DTypeOf<N>::value, src.ptr, dst.ptr, src.len));
     }
-    // dense relu / abs gradient map of a view (src/ops/unary/mod.rs:213-252), kind = RTB_MASK_RELU / RTB_MASK_ABS
-    template <typename T> void grad_mask(const Buf<T> &src, const MetaTensor &m, int kind, Buf<T> &dst) const {
+    // dense per-element map of a view (relu / abs / leaky_relu gradient maps, reciprocal), kind = RTB_MASK_*
+    template <typename T> void grad_mask(const Buf<T> &src, const MetaTensor &m, int kind, Buf<T> &dst, T value = T()) const {
         check(rtb_meta_check_extent(m.rank(), m.shape.data(), m.strides.data(), m.offset, src.len));
-        check(rtb_grad_mask(ctx_, DTypeOf<T>::value, kind, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
+        check(rtb_grad_mask(ctx_, DTypeOf<T>::value, kind, &value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
     }
     template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
         check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
@@ -384,12 +384,14 @@ template <typename T> class TensorBase {
     TensorBase abs() const { TensorBase t = owned(); t.abs_inplace(); return t; }
     TensorBase sign() const { TensorBase t = owned(); t.sign_inplace(); return t; }
     TensorBase neg() const { TensorBase t = owned(); t.neg_inplace(); return t; }
-    TensorBase grad_map(int kind) const {
+    TensorBase grad_map(int kind, T value = T()) const {
         MetaTensor m = MetaTensor::contiguous(meta.shape);
         TensorBase t{backend, backend->template alloc<T>(m.size()), m};
-        if (m.size()) backend->grad_mask(*buf, meta, kind, *t.buf);
+        if (m.size()) backend->grad_mask(*buf, meta, kind, *t.buf, value);
         return t;
     }
+    TensorBase leaky_relu_grad_map(T slope) const { return grad_map(RTB_MASK_LEAKY_RELU, slope); }  // src/ops/scalar/mod.rs:149-166
+    TensorBase reciprocal_map() const { return grad_map(RTB_MASK_RECIPROCAL); }                    // src/ops/broadcast/div.rs:583-587
     TensorBase relu_grad_map() const { return grad_map(RTB_MASK_RELU); }
     TensorBase abs_grad_map() const { return grad_map(RTB_MASK_ABS); }
 

@@ -190,15 +190,18 @@ def elementwise(buf: np.ndarray, kind: int, op: int, value, meta: Meta, fast: bo
                                    C.c_size_t(meta.offset)))
 
 
-MASK_RELU, MASK_ABS = 1, 2
+MASK_RELU, MASK_ABS, MASK_LEAKY_RELU, MASK_RECIPROCAL = 1, 2, 3, 4
 
 
-def grad_mask(buf: np.ndarray, kind: int, meta: Meta, fast: bool = False) -> np.ndarray:
-    """The relu / abs gradient map of the view `meta` of `buf` as a dense array (ops/unary/mod.rs:213-252)."""
+def grad_mask(buf: np.ndarray, kind: int, meta: Meta, value=None, fast: bool = False) -> np.ndarray:
+    """The relu / abs / leaky_relu gradient map or the reciprocal map of the view `meta` of `buf` as a
+    dense array (ops/unary/mod.rs:213-252, ops/scalar/mod.rs:149-166, ops/broadcast/div.rs:583-587)."""
     assert buf.flags.c_contiguous and buf.ndim == 1
     out = np.zeros(max(meta.size, 1), dtype=buf.dtype)
-    _chk(lib(fast).orc_grad_mask(C.c_int(_code(buf)), C.c_int(kind), _ptr(buf), C.c_size_t(meta.rank), _sizes(meta.shape),
-                                 _diffs(meta.strides), C.c_size_t(meta.offset), _ptr(out)))
+    v = None if value is None else np.array([value], dtype=buf.dtype)
+    _chk(lib(fast).orc_grad_mask(C.c_int(_code(buf)), C.c_int(kind), None if v is None else _ptr(v), _ptr(buf),
+                                 C.c_size_t(meta.rank), _sizes(meta.shape), _diffs(meta.strides), C.c_size_t(meta.offset),
+                                 _ptr(out)))
     return out[: meta.size]
 
 

@@ -760,12 +760,16 @@ ORC_API void orc_u8_to_f32_div(const uint8_t *src, float *dst, float divisor, si
 }
 
 /* ------------------------------------------------------------------------------------------
- * Gradient maps of relu and abs, ops/unary/mod.rs:213-252: a zeros tensor of the input's shape,
- * then for every coordinate (row-major) map = input > 0 ? 1 : 0 (relu) or input > 0 ? 1 : -1 (abs).
- * kind 1 = relu, 2 = abs.
+ * The per-element maps the autograd builds on the host: a zeros tensor of the input's shape, then
+ * for every coordinate (row-major)
+ *   kind 1 relu        map = input > 0 ? 1 : 0            ops/unary/mod.rs:236-252
+ *   kind 2 abs         map = input > 0 ? 1 : -1           ops/unary/mod.rs:213-235
+ *   kind 3 leaky_relu  map = input > 0 ? 1 : slope        ops/scalar/mod.rs:149-166
+ *   kind 4 reciprocal  map = 1 / input                    ops/broadcast/div.rs:583-587
+ * Integer 1 / 0 panics in the reference; here it yields 0 (precondition, as for division).
  * ---------------------------------------------------------------------------------------- */
 #define DEF_GRAD_MASK(S, T, CODE)                                                            \
-    static void mask_##S(int kind, const T *src, size_t rank, const size_t *shape,           \
+    static void mask_##S(int kind, T slope, const T *src, size_t rank, const size_t *shape,  \
                          const ptrdiff_t *strides, size_t offset, T *dst) {                  \
         if (meta_size(rank, shape) == 0) return;                                             \
         off_iter it;                                                                         \
@@ -773,23 +777,31 @@ ORC_API void orc_u8_to_f32_div(const uint8_t *src, float *dst, float divisor, si
         size_t i = 0;                                                                        \
         while (!it.done) {                                                                   \
             T v = src[it.off];                                                               \
-            dst[i++] = v > (T)0 ? (T)1 : (kind == 1 ? (T)0 : (T)-1);                         \
+            /* (T)0.5 == 0 tells an integer type from a float one */                         \
+            if (kind == 4) dst[i++] = ((T)0.5 == (T)0 && v == (T)0) ? (T)0 : bin_##S(ORC_DIV, (T)1, v); \
+            else dst[i++] = v > (T)0 ? (T)1 : (kind == 1 ? (T)0 : (kind == 2 ? (T)-1 : slope)); \
             it_next(&it);                                                                    \
         }                                                                                    \
     }
 FOR_ALL_TYPES(DEF_GRAD_MASK)
 
-ORC_API int orc_grad_mask(int dtype, int kind, const void *src, size_t rank, const size_t *shape,
-                          const ptrdiff_t *strides, size_t offset, void *dst) {
+ORC_API int orc_grad_mask(int dtype, int kind, const void *value, const void *src, size_t rank,
+                          const size_t *shape, const ptrdiff_t *strides, size_t offset, void *dst) {
     if (rank > ORC_MAX_RANK) return ORC_ERR_DIM;
-    if (kind != 1 && kind != 2) return ORC_ERR_OP;
-    /* -T::ONE needs a signed type */
+    if (kind < 1 || kind > 4 || (kind == 3 && !value)) return ORC_ERR_OP;
+    /* -T::ONE needs a signed type; boolean has no division */
     if (kind == 2 && (dtype == ORC_U8 || dtype == ORC_U16 || dtype == ORC_U32 || dtype == ORC_U64 ||
                       dtype == ORC_U128 || dtype == ORC_BOOL))
         return ORC_ERR_DTYPE;
+    if (kind == 4 && dtype == ORC_BOOL) return ORC_ERR_DTYPE;
     switch (dtype) {
 #define CASE_MASK(S, T, CODE)                                                                \
-    case CODE: mask_##S(kind, (const T *)src, rank, shape, strides, offset, (T *)dst); return ORC_OK;
+    case CODE: {                                                                             \
+        T v; memset(&v, 0, sizeof v);                                                        \
+        if (value) memcpy(&v, value, sizeof v);                                              \
+        mask_##S(kind, v, (const T *)src, rank, shape, strides, offset, (T *)dst);           \
+        return ORC_OK;                                                                       \
+    }
         FOR_ALL_TYPES(CASE_MASK)
     }
     return ORC_ERR_DTYPE;

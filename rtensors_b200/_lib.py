@@ -18,7 +18,7 @@ VARIANCE, LOGSUMEXP, NORM, ARGMAX, ARGMIN = 6, 7, 8, 9, 10
 OK = 0
 
 
-MASK_RELU, MASK_ABS = 1, 2   # rtb_grad_mask kinds
+MASK_RELU, MASK_ABS, MASK_LEAKY_RELU, MASK_RECIPROCAL = 1, 2, 3, 4   # rtb_grad_mask kinds
 # rtb_status codes used by host-side checks (include/rt_b200.h)
 ERR_INVALID, ERR_DTYPE, ERR_BROADCAST, ERR_BOUNDS, ERR_DIM, ERR_SHAPE, ERR_NONCONTIG = -1, -2, -3, -4, -5, -6, -7
 

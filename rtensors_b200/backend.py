@@ -189,13 +189,16 @@ class CudaB200:
                                       meta.c_shape, meta.c_strides, C.c_size_t(meta.offset), self._p(out)))
         return out
 
-    def grad_mask(self, buf: torch.Tensor, meta: Meta, kind: int) -> torch.Tensor:
-        """Dense relu (L.MASK_RELU) or abs (L.MASK_ABS) gradient map of a view, one kernel instead of the
-        reference's per-element get / set loop (src/ops/unary/mod.rs:213-252)."""
+    def grad_mask(self, buf: torch.Tensor, meta: Meta, kind: int, value=None) -> torch.Tensor:
+        """Dense per-element map of a view in one kernel instead of the reference's get / set loops:
+        L.MASK_RELU, L.MASK_ABS (src/ops/unary/mod.rs:213-252), L.MASK_LEAKY_RELU with its slope
+        (src/ops/scalar/mod.rs:149-166), L.MASK_RECIPROCAL (src/ops/broadcast/div.rs:583-587)."""
         out = self.alloc(max(meta.size, 1), buf.dtype)
         if meta.size:
             meta.check_extent(buf.numel())
-            check(lib().rtb_grad_mask(self._ctx, C.c_int(dtype_code(buf)), C.c_int(kind), self._p(buf), C.c_size_t(meta.rank),
+            code = dtype_code(buf)
+            v = None if value is None else _scalar_bytes(code, value)
+            check(lib().rtb_grad_mask(self._ctx, C.c_int(code), C.c_int(kind), v, self._p(buf), C.c_size_t(meta.rank),
                                       meta.c_shape, meta.c_strides, C.c_size_t(meta.offset), self._p(out)))
         return out
 

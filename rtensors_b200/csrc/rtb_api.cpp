@@ -133,17 +133,21 @@ RTB_API int rtb_copy_view(rtb_ctx *c, int dtype, const void *src, size_t rank, c
     return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
 }
 
-RTB_API int rtb_grad_mask(rtb_ctx *c, int dtype, int kind, const void *src, size_t rank, const size_t *shape,
-                          const ptrdiff_t *strides, size_t offset, void *dst) {
+RTB_API int rtb_grad_mask(rtb_ctx *c, int dtype, int kind, const void *value, const void *src, size_t rank,
+                          const size_t *shape, const ptrdiff_t *strides, size_t offset, void *dst) {
     int rc = check_view_args(c, src, rank, shape, strides);
     if (rc) return rc;
     if (!dst) return fail(RTB_ERR_INVALID, "null destination");
-    if (kind != RTB_MASK_RELU && kind != RTB_MASK_ABS) return fail(RTB_ERR_INVALID, "unknown gradient map kind %d", kind);
+    if (kind < RTB_MASK_RELU || kind > RTB_MASK_RECIPROCAL) return fail(RTB_ERR_INVALID, "unknown gradient map kind %d", kind);
+    if (kind == RTB_MASK_LEAKY_RELU && !value) return fail(RTB_ERR_INVALID, "the leaky_relu map needs its slope");
+    const size_t es = dtype_size(dtype);
+    if (es == 0) return fail(RTB_ERR_DTYPE, "unknown dtype %d", dtype);
     if ((rc = use_device(C(c)))) return rc;
     std::vector<ptrdiff_t> dense(rank ? rank : 1);
     rtb_meta_contiguous_strides(rank, shape, dense.data());
     EwCall call{};
     call.dtype = dtype; call.family = kFamCopy; call.op = kind;
+    if (kind == RTB_MASK_LEAKY_RELU) std::memcpy(call.value, value, es);
     call.d = dst; call.l = src; call.r = nullptr;
     return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
 }

@@ -146,6 +146,12 @@ struct FMaskRelu { __device__ __forceinline__ T operator()(T a, T) const { retur
 #if RTB_KIND == 1 || RTB_KIND == 2
 struct FMaskAbs { __device__ __forceinline__ T operator()(T a, T) const { return a > (T)0 ? (T)1 : (T)-1; } };
 #endif
+// leaky_relu's map: x > 0 ? 1 : slope (src/ops/scalar/mod.rs:149-166); and the element-wise reciprocal
+// 1 / x the backward of a broadcast division stores (src/ops/broadcast/div.rs:583-587)
+struct FMaskLeaky { T v; __device__ __forceinline__ T operator()(T a, T) const { return a > (T)0 ? (T)1 : v; } };
+#if RTB_KIND != 3
+struct FRecip { __device__ __forceinline__ T operator()(T a, T) const { return bin<RTB_DIV>((T)1, a); } };
+#endif
 
 // Extended families with a run-time op code (one instantiation each; the switch is noise next to
 // the transcendental it selects).  Formulas are the reference CPU backend's, not libm shortcuts
@@ -690,7 +696,12 @@ int RTB_CAT(ew_dispatch_, RTB_SUFFIX)(Ctx *ctx, const EwCall &c, const rtb_plan 
 #if RTB_KIND == 1 || RTB_KIND == 2
             if (c.op == 2) return launch<FMaskAbs, 1>(ctx, c, plan, FMaskAbs{});
 #endif
-            return fail(RTB_ERR_DTYPE, "abs gradient map needs a signed element type");
+            if (c.op == 2) return fail(RTB_ERR_DTYPE, "abs gradient map needs a signed element type");
+            if (c.op == 3) return launch<FMaskLeaky, 1>(ctx, c, plan, FMaskLeaky{v});
+#if RTB_KIND != 3
+            if (c.op == 4) return launch<FRecip, 1>(ctx, c, plan, FRecip{});
+#endif
+            return fail(RTB_ERR_DTYPE, "the reciprocal map is not defined for boolean");
     }
     return fail(RTB_ERR_INVALID, "unknown elementwise family %d", c.family);
 }

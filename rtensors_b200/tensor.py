@@ -176,6 +176,13 @@ class Tensor:
     def abs_grad_map(self) -> "Tensor":
         return Tensor(self.backend, self.backend.grad_mask(self.buf, self.meta, L.MASK_ABS), Meta.contiguous(self.shape))
 
+    def leaky_relu_grad_map(self, slope) -> "Tensor":  # src/ops/scalar/mod.rs:149-166
+        return Tensor(self.backend, self.backend.grad_mask(self.buf, self.meta, L.MASK_LEAKY_RELU, slope),
+                      Meta.contiguous(self.shape))
+
+    def reciprocal_map(self) -> "Tensor":  # 1 / x, src/ops/broadcast/div.rs:583-587
+        return Tensor(self.backend, self.backend.grad_mask(self.buf, self.meta, L.MASK_RECIPROCAL), Meta.contiguous(self.shape))
+
     # ---- reductions -------------------------------------------------------------------------
     def _reduce(self, op: int, axis: Optional[int]) -> "Tensor":
         # The reference copies a non-contiguous view first (`contiguous()`); here the library reduces

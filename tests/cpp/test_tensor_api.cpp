@@ -215,6 +215,8 @@ int main() {
         ASSERT_EQ(t.relu_grad_map().cpu(), (std::vector<float>{0, 0, 1, 1, 0, 1}));
         ASSERT_EQ(t.abs_grad_map().cpu(), (std::vector<float>{-1, -1, 1, 1, -1, 1}));
         ASSERT_EQ(t.transpose().relu_grad_map().cpu(), (std::vector<float>{0, 1, 0, 0, 1, 1}));
+        ASSERT_EQ(t.leaky_relu_grad_map(0.125f).cpu(), (std::vector<float>{0.125f, 0.125f, 1, 1, 0.125f, 1}));
+        ASSERT_EQ(t.slice(1, Slice::range(2, 3)).reciprocal_map().cpu(), (std::vector<float>{0.5f, 4.0f}));
         auto u = Tensor<uint8_t>::from_buf(cuda, {0, 5}, {2});
         ASSERT_EQ(u.relu_grad_map().cpu(), (std::vector<uint8_t>{0, 1}));
         bool threw = false;

@@ -1398,8 +1398,9 @@ L_MUL, L_RELU, L_SUM, L_MAX, L_VAR, L_ARGMAX = _L.MUL, _L.RELU, _L.SUM, _L.MAX, 
 
 @pytest.mark.parametrize("dt", NP_DTYPES, ids=lambda d: np.dtype(d).name)
 def test_relu_and_abs_gradient_maps_on_views(dt):
-    """rtb_grad_mask against the oracle on a contiguous tensor, a strided / reversed window and a
-    permuted view, every dtype; abs needs a signed type and is refused otherwise."""
+    """rtb_grad_mask (relu, abs, leaky_relu maps and the reciprocal) against the oracle on a contiguous
+    tensor, a strided / reversed window and a permuted view, every dtype; abs needs a signed type and the
+    reciprocal a non-boolean one, refused otherwise.  Integer buffers hold zeros: 1 / 0 gives 0."""
     import rtensors_b200._lib as L
     rng = np.random.default_rng(31 + np.dtype(dt).itemsize)
     buf = _rand(rng, 6 * 40 * 50 + 7, dt)
@@ -1411,16 +1412,24 @@ def test_relu_and_abs_gradient_maps_on_views(dt):
              base.permute((2, 0, 1)), base.slice(0, 1, 2, 1).squeeze()]
     d = _dev(buf)
     signed = np.dtype(dt).kind in "fi"
+    is_bool = np.dtype(dt).kind == "b"
+    slope = True if is_bool else (0.125 if np.dtype(dt).kind == "f" else 3)
     for m in views:
-        for kind in (L.MASK_RELU, L.MASK_ABS):
-            if kind == L.MASK_ABS and not signed:
+        for kind in (L.MASK_RELU, L.MASK_ABS, L.MASK_LEAKY_RELU, L.MASK_RECIPROCAL):
+            value = slope if kind == L.MASK_LEAKY_RELU else None
+            if (kind == L.MASK_ABS and not signed) or (kind == L.MASK_RECIPROCAL and is_bool):
                 with pytest.raises(L.RtbError):
-                    _b().grad_mask(d, _meta_pair(m), kind)
+                    _b().grad_mask(d, _meta_pair(m), kind, value)
                 with pytest.raises(O.OracleError):
-                    O.grad_mask(buf, kind, m)
+                    O.grad_mask(buf, kind, m, value)
                 continue
-            got = _host(_b().grad_mask(d, _meta_pair(m), kind))[: m.size]
-            assert got.tobytes() == O.grad_mask(buf, kind, m).tobytes(), (m, kind)
+            got = _host(_b().grad_mask(d, _meta_pair(m), kind, value))[: m.size]
+            want = O.grad_mask(buf, kind, m, value)
+            if kind == L.MASK_RECIPROCAL and np.dtype(dt).kind == "f":
+                ok = (got.view(np.uint32 if got.itemsize == 4 else np.uint64) == want.view(np.uint32 if got.itemsize == 4 else np.uint64)) | (np.isnan(got) & np.isnan(want))
+                assert ok.all(), (m, kind)
+            else:
+                assert got.tobytes() == want.tobytes(), (m, kind)
 
 
 def test_tensor_gradient_maps():
@@ -1429,3 +1438,5 @@ def test_tensor_gradient_maps():
     assert t.relu_grad_map().cpu().tolist() == [[0, 0, 1], [1, 0, 1]]
     assert t.abs_grad_map().cpu().tolist() == [[-1, -1, 1], [1, -1, 1]]
     assert t.transpose().relu_grad_map().cpu().tolist() == [[0, 1], [0, 0], [1, 1]]
+    assert t.leaky_relu_grad_map(0.125).cpu().tolist() == [[0.125, 0.125, 1], [1, 0.125, 1]]
+    assert t.slice(1, 2, 3).reciprocal_map().cpu().tolist() == [[0.5], [4.0]]
