@@ -300,6 +300,9 @@ int rtb_grad_mask(rtb_ctx *ctx, int dtype, int kind, const void *value, const vo
                   const size_t *shape, const ptrdiff_t *strides, size_t offset, void *dst);
 /* SGD::step (src/grad/optim.rs:30-50): u = g*lr rounded, then p = p - u (no FMA) */
 int rtb_sgd_update_f32(rtb_ctx *ctx, float *p, const float *g, float lr, size_t n);
+/* the same two for f64 (the reference's relu map and SGD::step are generic over the float type) */
+int rtb_relu_mask_f64(rtb_ctx *ctx, double *x, double *mask, size_t n);
+int rtb_sgd_update_f64(rtb_ctx *ctx, double *p, const double *g, double lr, size_t n);
 /* Backend::convert u8 -> f32 followed by `/ divisor` (src/backend/cuda.rs:790-812,
  * examples/mnist/src/main.rs:108-111) */
 int rtb_u8_to_f32_div(rtb_ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n);

@@ -304,12 +304,18 @@ def reduce_to_shape(upstream: np.ndarray, shape: Sequence[int], operand_strides:
 
 def relu_mask(x: np.ndarray):
     mask = np.zeros_like(x)
-    lib().orc_relu_mask_f32(_ptr(x), _ptr(mask), C.c_size_t(x.size))
+    if x.dtype == np.float64:
+        lib().orc_relu_mask_f64(_ptr(x), _ptr(mask), C.c_size_t(x.size))
+    else:
+        lib().orc_relu_mask_f32(_ptr(x), _ptr(mask), C.c_size_t(x.size))
     return mask
 
 
 def sgd_update(p: np.ndarray, g: np.ndarray, lr: float) -> None:
-    lib().orc_sgd_update_f32(_ptr(p), _ptr(g), C.c_float(lr), C.c_size_t(p.size))
+    if p.dtype == np.float64:
+        lib().orc_sgd_update_f64(_ptr(p), _ptr(g), C.c_double(lr), C.c_size_t(p.size))
+    else:
+        lib().orc_sgd_update_f32(_ptr(p), _ptr(g), C.c_float(lr), C.c_size_t(p.size))
 
 
 def u8_to_f32_div(src: np.ndarray, divisor: float = 255.0) -> np.ndarray:

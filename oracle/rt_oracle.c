@@ -755,6 +755,19 @@ ORC_API void orc_sgd_update_f32(float *p, const float *g, float lr, size_t n) {
         p[i] = p[i] - u;
     }
 }
+ORC_API void orc_relu_mask_f64(double *x, double *mask, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        double v = x[i];
+        mask[i] = v > 0.0 ? 1.0 : 0.0;
+        x[i] = v > 0.0 ? v : 0.0;
+    }
+}
+ORC_API void orc_sgd_update_f64(double *p, const double *g, double lr, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+        double u = g[i] * lr;
+        p[i] = p[i] - u;
+    }
+}
 ORC_API void orc_u8_to_f32_div(const uint8_t *src, float *dst, float divisor, size_t n) {
     for (size_t i = 0; i < n; ++i) dst[i] = (float)src[i] / divisor;
 }

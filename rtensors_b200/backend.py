@@ -357,11 +357,15 @@ class CudaB200:
     # -- fused MLP pieces ---------------------------------------------------------------------
     def relu_mask(self, x: torch.Tensor) -> torch.Tensor:
         mask = torch.empty_like(x)
-        check(lib().rtb_relu_mask_f32(self._ctx, self._p(x), self._p(mask), C.c_size_t(x.numel())))
+        fn = lib().rtb_relu_mask_f64 if x.dtype == torch.float64 else lib().rtb_relu_mask_f32
+        check(fn(self._ctx, self._p(x), self._p(mask), C.c_size_t(x.numel())))
         return mask
 
     def sgd_update(self, p: torch.Tensor, g: torch.Tensor, lr: float):
-        check(lib().rtb_sgd_update_f32(self._ctx, self._p(p), self._p(g), C.c_float(lr), C.c_size_t(p.numel())))
+        if p.dtype == torch.float64:
+            check(lib().rtb_sgd_update_f64(self._ctx, self._p(p), self._p(g), C.c_double(lr), C.c_size_t(p.numel())))
+        else:
+            check(lib().rtb_sgd_update_f32(self._ctx, self._p(p), self._p(g), C.c_float(lr), C.c_size_t(p.numel())))
 
     def convert(self, src: torch.Tensor, dst_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`convert::<T, N>` (src/backend/mod.rs:234) into `out`, or into a fresh buffer: every element

@@ -450,6 +450,20 @@ RTB_API int rtb_sgd_update_f32(rtb_ctx *c, float *p, const float *g, float lr, s
     return launch_sgd(C(c), p, g, lr, n);
 }
 
+RTB_API int rtb_relu_mask_f64(rtb_ctx *c, double *x, double *mask, size_t n) {
+    if (!c || !x || !mask) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_relu_mask_f64(C(c), x, mask, n);
+}
+
+RTB_API int rtb_sgd_update_f64(rtb_ctx *c, double *p, const double *g, double lr, size_t n) {
+    if (!c || !p || !g) return fail(RTB_ERR_INVALID, "null argument");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_sgd_f64(C(c), p, g, lr, n);
+}
+
 RTB_API int rtb_convert(rtb_ctx *c, int src_dtype, int dst_dtype, const void *src, void *dst, size_t n) {
     if (!c) return fail(RTB_ERR_INVALID, "null context");
     if (src_dtype < 0 || src_dtype > RTB_BOOL || dst_dtype < 0 || dst_dtype > RTB_BOOL)

@@ -147,6 +147,8 @@ int launch_bcast_reduce(Ctx *ctx, int dtype, int binop, int redop, const void *l
 int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap);
 int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n);
 int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n);
+int launch_relu_mask_f64(Ctx *ctx, double *x, double *mask, size_t n);
+int launch_sgd_f64(Ctx *ctx, double *p, const double *g, double lr, size_t n);
 int launch_convert(Ctx *ctx, int src_dtype, int dst_dtype, const void *src, void *dst, size_t n);
 int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n);
 

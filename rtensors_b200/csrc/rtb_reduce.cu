@@ -655,6 +655,41 @@ __global__ void __launch_bounds__(kBlock) sgd_kernel(float *p, const float *g, f
         p[k] = p[k] - __fmul_rn(g[k], lr);
 }
 
+// f64 forms of the two kernels above (the reference's relu map and SGD::step are generic over the
+// float type); 2 elements per 128-bit access
+__global__ void __launch_bounds__(kBlock) relu_mask_f64_kernel(double *x, double *mask, size_t n) {
+    grid_dep_sync();
+    const size_t nvec = n / 2;
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
+        double2 v = reinterpret_cast<const double2 *>(x)[i];
+        double2 m, o;
+        m.x = v.x > 0.0 ? 1.0 : 0.0; o.x = v.x > 0.0 ? v.x : 0.0;
+        m.y = v.y > 0.0 ? 1.0 : 0.0; o.y = v.y > 0.0 ? v.y : 0.0;
+        reinterpret_cast<double2 *>(x)[i] = o;
+        reinterpret_cast<double2 *>(mask)[i] = m;
+    }
+    if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+        double v = x[n - 1];
+        mask[n - 1] = v > 0.0 ? 1.0 : 0.0;
+        x[n - 1] = v > 0.0 ? v : 0.0;
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) sgd_f64_kernel(double *p, const double *g, double lr, size_t n) {
+    grid_dep_sync();
+    const size_t nvec = n / 2;
+    const size_t stride = (size_t)gridDim.x * kBlock;
+    for (size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += stride) {
+        double2 w = reinterpret_cast<double2 *>(p)[i];
+        double2 q = reinterpret_cast<const double2 *>(g)[i];
+        w.x = w.x - __dmul_rn(q.x, lr);  // two roundings, no FMA
+        w.y = w.y - __dmul_rn(q.y, lr);
+        reinterpret_cast<double2 *>(p)[i] = w;
+    }
+    if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) p[n - 1] = p[n - 1] - __dmul_rn(g[n - 1], lr);
+}
+
 __global__ void __launch_bounds__(kBlock) u8_f32_kernel(const uint8_t *src, float *dst, float divisor, size_t n) {
     grid_dep_sync();
     const size_t nvec = n / 4;
@@ -954,6 +989,20 @@ int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n) {
     unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
     launch_dep(ctx, grid, kBlock, sgd_kernel, p, g, lr, n);
     return check_launch(ctx, "sgd_kernel");
+}
+
+int launch_relu_mask_f64(Ctx *ctx, double *x, double *mask, size_t n) {
+    if ((((uintptr_t)x | (uintptr_t)mask) & 15u) != 0) return fail(RTB_ERR_INVALID, "relu_mask needs 16-byte aligned buffers");
+    unsigned grid = grid_for(ctx, (n / 2 + kBlock - 1) / kBlock, 16);
+    launch_dep(ctx, grid, kBlock, relu_mask_f64_kernel, x, mask, n);
+    return check_launch(ctx, "relu_mask_f64_kernel");
+}
+
+int launch_sgd_f64(Ctx *ctx, double *p, const double *g, double lr, size_t n) {
+    if ((((uintptr_t)p | (uintptr_t)g) & 15u) != 0) return fail(RTB_ERR_INVALID, "sgd_update needs 16-byte aligned buffers");
+    unsigned grid = grid_for(ctx, (n / 2 + kBlock - 1) / kBlock, 16);
+    launch_dep(ctx, grid, kBlock, sgd_f64_kernel, p, g, lr, n);
+    return check_launch(ctx, "sgd_f64_kernel");
 }
 
 int launch_u8_f32(Ctx *ctx, const uint8_t *src, float *dst, float divisor, size_t n) {

@@ -1440,3 +1440,21 @@ def test_tensor_gradient_maps():
     assert t.transpose().relu_grad_map().cpu().tolist() == [[0, 1], [0, 0], [1, 1]]
     assert t.leaky_relu_grad_map(0.125).cpu().tolist() == [[0.125, 0.125, 1], [1, 0.125, 1]]
     assert t.slice(1, 2, 3).reciprocal_map().cpu().tolist() == [[0.5], [4.0]]
+
+
+@pytest.mark.parametrize("n", [1, 2, 4096 * 33 + 3, 100003])
+def test_relu_mask_and_sgd_update_f64(n):
+    rng = np.random.default_rng(600 + n)
+    x = rng.standard_normal(n)
+    x[::9] = 0.0
+    ref = x.copy()
+    wm = O.relu_mask(ref)
+    d = _dev(x)
+    m = _b().relu_mask(d)
+    assert _host(d).tobytes() == ref.tobytes() and _host(m).tobytes() == wm.tobytes()
+    p, g = rng.standard_normal(n), rng.standard_normal(n)
+    rp = p.copy()
+    O.sgd_update(rp, g, 0.0137)
+    dp = _dev(p)
+    _b().sgd_update(dp, _dev(g), 0.0137)
+    assert _host(dp).tobytes() == rp.tobytes()
