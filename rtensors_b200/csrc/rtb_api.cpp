@@ -269,6 +269,11 @@ int reduce_view_impl(rtb_ctx *c, int dtype, int redop, const rtb_reduce_settings
             // B absent and A contiguous (a transposed matrix reduced along its strided dim): the
             // roles swap -- [outer = 1, R, inner = A], dst[a]
             if (nB == 1 && sA == 1) return any_axis(ctx, dtype, redop, set, p0, 1, R, nA, 0, sR, dst);
+            // R is the contiguous dim and the dims around it walk as one strided run (a transposed
+            // matrix reduced along its contiguous dim, a permuted cube ...): rows of R with a pitch,
+            // one per (a, b), and dst[a * nB + b] is the row-major output
+            if (nB > 1 && sR == 1 && (nA == 1 || sA == sB * (ptrdiff_t)nB))
+                return any_axis(ctx, dtype, redop, set, p0, nA * nB, R, 1, sB, sR, dst);
         }
     }
     // General view: materialise it row-major (strided copy kernel), then reduce the copy -- what the

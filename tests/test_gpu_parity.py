@@ -841,6 +841,8 @@ def test_reduce_view_matches_copy_then_reduce():
         base.slice(2, None, None, 2),                             # strided inner -> copy fallback / strided rows
         base.permute((1, 0, 2)),                                  # permuted outer dims
         base.permute((2, 1, 0)),                                  # fully transposed
+        base.permute((2, 0, 1)),                                  # contiguous dim moved to the front: rows with a pitch
+        base.slice(1, 4, 36, 1).permute((2, 0, 1)),               # same over a window (outer dims do not collapse)
         base.index(0, 3).permute((1, 0)),                         # transposed matrix
         base.index(2, 7),                                         # (12, 40) with strides (2560, 64)
     ]
