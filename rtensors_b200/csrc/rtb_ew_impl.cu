@@ -542,6 +542,109 @@ int ilog2(uint64_t v) {
     return k;
 }
 
+// ---- transposing tiles -----------------------------------------------------------------------------
+// For a call whose output is dense along its inner dim X while an input is strided along X but dense
+// along another dim Y (a transposed matrix, a permuted cube being made contiguous or added to a
+// row-major tensor).  The row kernels read such an input one 4-byte element per 32-byte sector; here
+// a CTA owns a 32 x 32 tile of (X, Y): the transposed input is read along Y (dense), parked in
+// shared memory, and read back along X, so both sides of the tile move whole sectors.  Inputs that
+// are dense or broadcast along X are read directly.
+constexpr int kTrTile = 32;
+
+struct TrParams {
+    int rank;            // collapsed rank of the plan, >= 2
+    int ydim;            // the row dim the transposed input is dense along
+    int stage_l, stage_r;  // read that input through shared memory
+    uint32_t tiles_x, tiles_y;
+    uint32_t extent[kMaxPlanRank];
+    int64_t sd[kMaxPlanRank], sl[kMaxPlanRank], sr[kMaxPlanRank];
+};
+
+template <typename F, int NIN>
+__global__ void __launch_bounds__(kBlock) transpose_tiles_kernel(T *d, const T *l, const T *r, const __grid_constant__ TrParams p, F f) {
+    grid_dep_sync();
+    __shared__ T tile_l[kTrTile][kTrTile + 1];
+    __shared__ T tile_r[NIN >= 2 ? kTrTile : 1][kTrTile + 1];
+    const int X = p.rank - 1, Y = p.ydim;
+    uint32_t id = blockIdx.x;
+    const uint32_t bx = id % p.tiles_x; id /= p.tiles_x;
+    const uint32_t by = id % p.tiles_y; id /= p.tiles_y;
+    int64_t od = 0, ol = 0, orr = 0;
+    for (int k = p.rank - 2; k >= 0; --k) {  // the dims other than X and Y
+        if (k == Y) continue;
+        const uint32_t c = id % p.extent[k];
+        id /= p.extent[k];
+        od += (int64_t)c * p.sd[k];
+        if (NIN >= 1) ol += (int64_t)c * p.sl[k];
+        if (NIN >= 2) orr += (int64_t)c * p.sr[k];
+    }
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8 threads
+    const uint32_t x0 = bx * kTrTile, y0 = by * kTrTile;
+    const uint32_t nx = p.extent[X], ny = p.extent[Y];
+    // stage: lanes run along Y
+    if (NIN >= 1 && (p.stage_l || (NIN >= 2 && p.stage_r))) {
+        const uint32_t y = y0 + tx;
+#pragma unroll
+        for (int j = 0; j < kTrTile / 8; ++j) {
+            const uint32_t xl = ty + 8 * j, x = x0 + xl;
+            if (x < nx && y < ny) {
+                if (p.stage_l) tile_l[xl][tx] = l[ol + (int64_t)x * p.sl[X] + (int64_t)y * p.sl[Y]];
+                if (NIN >= 2 && p.stage_r) tile_r[xl][tx] = r[orr + (int64_t)x * p.sr[X] + (int64_t)y * p.sr[Y]];
+            }
+        }
+        __syncthreads();
+    }
+    // compute and store: lanes run along X
+    const uint32_t x = x0 + tx;
+    if (x >= nx) return;
+#pragma unroll
+    for (int j = 0; j < kTrTile / 8; ++j) {
+        const uint32_t yl = ty + 8 * j, y = y0 + yl;
+        if (y >= ny) break;
+        T a = T(), b = T();
+        if (NIN >= 1) a = p.stage_l ? tile_l[tx][yl] : l[ol + (int64_t)x * p.sl[X] + (int64_t)y * p.sl[Y]];
+        if (NIN >= 2) b = p.stage_r ? tile_r[tx][yl] : r[orr + (int64_t)x * p.sr[X] + (int64_t)y * p.sr[Y]];
+        d[od + (int64_t)x * p.sd[X] + (int64_t)y * p.sd[Y]] = f(a, b);
+    }
+}
+
+// Host-side choice: returns true and fills `p` when the call should run on transposing tiles.
+template <int NIN>
+bool plan_transpose(const EwCall &c, const rtb_plan &plan, TrParams *p) {
+    const int R = plan.rank;
+    if (NIN < 1 || R < 2 || plan.stride_d[R - 1] != 1) return false;
+    if (plan.shape[R - 1] < 16) return false;
+    auto dense_dim = [&](const int64_t *st) {  // strided along X, dense along some row dim with room for a tile
+        const int64_t sx = st[R - 1];
+        if (sx == 0 || sx == 1 || sx == -1) return -1;
+        for (int k = R - 2; k >= 0; --k)
+            if (st[k] == 1 && plan.shape[k] >= 16) return k;
+        return -1;
+    };
+    const int yl = dense_dim(plan.stride_l), yr = NIN >= 2 ? dense_dim(plan.stride_r) : -1;
+    // an input that shares the output's buffer is read where it is written only if it is not staged
+    if (yl >= 0 && c.l == c.d) return false;
+    if (yr >= 0 && c.r == c.d) return false;
+    const int y = yl >= 0 ? yl : yr;
+    if (y < 0) return false;
+    std::memset(p, 0, sizeof *p);
+    p->rank = R;
+    p->ydim = y;
+    p->stage_l = yl == y;
+    p->stage_r = yr == y;
+    uint64_t blocks = 1;
+    for (int k = 0; k < R; ++k) {
+        if (plan.shape[k] >= (1ull << 32)) return false;
+        p->extent[k] = (uint32_t)plan.shape[k];
+        p->sd[k] = plan.stride_d[k]; p->sl[k] = plan.stride_l[k]; p->sr[k] = plan.stride_r[k];
+        if (k != y && k != R - 1) blocks *= plan.shape[k];
+    }
+    p->tiles_x = (uint32_t)((plan.shape[R - 1] + kTrTile - 1) / kTrTile);
+    p->tiles_y = (uint32_t)((plan.shape[y] + kTrTile - 1) / kTrTile);
+    blocks *= (uint64_t)p->tiles_x * p->tiles_y;
+    return blocks < (1ull << 31);
+}
+
 template <typename F, int NIN>
 int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
     T *d = reinterpret_cast<T *>(c.d) + plan.base_d;
@@ -555,6 +658,16 @@ int launch(Ctx *ctx, const EwCall &c, const rtb_plan &plan, F f) {
         if (blocks >= (size_t(1) << 31)) return fail(RTB_ERR_TOO_LARGE, "flat launch too large");
         launch_dep(ctx, (unsigned)blocks, FlatShape<NIN>::kThreads, flat_kernel<F, NIN>, d, l, r, n, f);
         return check_launch(ctx, "flat_kernel");
+    }
+    if constexpr (NIN >= 1) {
+        TrParams tp;
+        if (plan_transpose<NIN>(c, plan, &tp)) {
+            uint64_t blocks = (uint64_t)tp.tiles_x * tp.tiles_y;
+            for (int k = 0; k < tp.rank - 1; ++k)
+                if (k != tp.ydim) blocks *= tp.extent[k];
+            launch_dep(ctx, (unsigned)blocks, kBlock, transpose_tiles_kernel<F, NIN>, d, l, r, tp, f);
+            return check_launch(ctx, "transpose_tiles_kernel");
+        }
     }
     RowParams p;
     std::memset(&p, 0, sizeof p);

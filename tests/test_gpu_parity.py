@@ -1460,3 +1460,55 @@ def test_relu_mask_and_sgd_update_f64(n):
     dp = _dev(p)
     _b().sgd_update(dp, _dev(g), 0.0137)
     assert _host(dp).tobytes() == rp.tobytes()
+
+
+# ------------------------------------------------------------------------------------- transposing tiles
+@pytest.mark.parametrize("dt", [np.float32, np.float64, np.int8, np.int16, np.uint8, np.bool_, np.int64],
+                         ids=lambda d: np.dtype(d).name)
+def test_transposed_and_permuted_operands(dt):
+    """Views that are strided along the output's inner dim but dense along another one (transposes,
+    permuted cubes) -- the transposing tile kernel: contiguous() copies, out-of-place and in-place
+    binary ops with one or both operands transposed, ragged tile edges, a broadcast partner, and an
+    operand that shares the output's buffer.  Bit-exact against the oracle."""
+    rng = np.random.default_rng(515 + np.dtype(dt).itemsize)
+    be = _b()
+    for shape, perm in [((70, 45), (1, 0)), ((33, 64), (1, 0)), ((5, 40, 50), (2, 0, 1)), ((6, 37, 41), (0, 2, 1)),
+                        ((3, 4, 20, 35), (0, 3, 1, 2)), ((17, 130), (1, 0))]:
+        base = O.Meta.contiguous(shape)
+        n = base.size
+        a, b = _rand(rng, n, dt), _rand(rng, n, dt)
+        if np.dtype(dt).kind in "iu":
+            a[a == 0] = 1
+            b[b == 0] = 1
+        va = base.permute(perm)
+        da, db = _dev(a), _dev(b)
+        # contiguous() of the permuted view
+        assert _host(be.contiguous(da, _meta_pair(va)))[:n].tobytes() == gather_view(a, va).tobytes(), (shape, perm)
+        dense = O.Meta.contiguous(va.shape)
+        ops = (O.ADD, O.MUL) if np.dtype(dt).kind == "b" else (O.ADD, O.SUB, O.MUL, O.DIV)
+        for op in ops:
+            # a.T (op) b and b (op) a.T, fresh output
+            for (x, mx, y, my) in ((a, va, b, dense), (b, dense, a, va), (a, va, b, va)):
+                want, wm = O.binary(x, mx, y, my, op)
+                got, gm = be.binary(_dev(x), _meta_pair(mx), _dev(y), _meta_pair(my), op)
+                assert tuple(gm.shape) == tuple(wm.shape)
+                assert _host(got)[: want.size].tobytes() == want.tobytes(), (shape, perm, op)
+            # b (op)= a.T in place
+            ref = b.copy()
+            O.broadcast(ref, dense, a, va, ref, dense, op)
+            dd = _dev(b)
+            be.binary_assign(dd, _meta_pair(dense), da, _meta_pair(va), op)
+            assert _host(dd).tobytes() == ref.tobytes(), (shape, perm, op, "in place")
+        # a broadcast partner: a.T + row
+        row_m = O.Meta.contiguous((va.shape[-1],))
+        row = _rand(rng, va.shape[-1], dt)
+        want, _ = O.binary(a, va, row, row_m, O.ADD)
+        got, _ = be.binary(da, _meta_pair(va), _dev(row), _meta_pair(row_m), O.ADD)
+        assert _host(got)[: want.size].tobytes() == want.tobytes(), (shape, perm, "row")
+    # square matrix: a + a.T from the same buffer, fresh output
+    m = O.Meta.contiguous((48, 48))
+    a = _rand(rng, m.size, dt)
+    want, _ = O.binary(a, m, a, m.permute((1, 0)), O.ADD)
+    d = _dev(a)
+    got, _ = be.binary(d, _meta_pair(m), d, _meta_pair(m.permute((1, 0))), O.ADD)
+    assert _host(got)[: want.size].tobytes() == want.tobytes()
