@@ -175,6 +175,19 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     add("sum_at(1) f32 over the same window, copy first (reference recipe)", f"({S},{S}) window of ({S},{2 * S})",
         4 * (S * S + S), S * S, copy_then_reduce, flush=S * S * 4 < (200 << 20),
         note="algorithmic bytes of the reduction alone; the copy moves 2x more")
+    # transposed views: contiguous() (the transposing tile kernel), a reduction along the view's
+    # strided-then-dense dims in place, and a binary op with one transposed operand
+    tview = msq.permute((1, 0))
+    tmp_t = be.alloc(S * S, f32)
+    add("contiguous() of a transposed matrix f32", f"({S},{S}) strides (1,{S})", 8 * S * S, S * S,
+        lambda: be.contiguous(src, tview))
+    for axis in (0, 1):
+        add(f"sum_at({axis}) f32 over the transposed view, no copy", f"({S},{S}) strides (1,{S})", 4 * (S * S + S), S * S,
+            (lambda axis=axis: be.reduce_view(src, tview, axis, L.SUM)), flush=S * S * 4 < (200 << 20))
+    add("a.T + b f32", f"({S},{S})", 12 * S * S, S * S,
+        lambda: be.broadcast((src, tview), (src[S * S:], msq), (tmp_t, msq), L.ADD))
+    del tmp_t
+
     d3 = (64, 512, 1024) if quick else (64, 4096, 1024)
     m3 = Meta.contiguous(d3)
     r3 = be.alloc(d3[0] * d3[2], f32)
