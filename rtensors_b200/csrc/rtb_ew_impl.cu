@@ -587,6 +587,22 @@ __global__ void __launch_bounds__(kBlock) transpose_tiles_kernel(T *d, const T *
     const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;  // 32 x 8 threads
     const uint32_t x0 = bx * kTrRows, y0 = by * kTrTile;
     const uint32_t nx = p.extent[X], ny = p.extent[Y];
+    // Two inputs (32-row tiles): the elements this thread reads directly (lanes along X) are
+    // requested first, so that they are in flight with the staged loads; left to the store loop they
+    // would each wait behind the previous store
+    constexpr int NJ = kTrTile / 8;
+    T pre_l[NJ], pre_r[NJ];
+    if (NIN >= 2) {
+        const uint32_t x = x0 + tx;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const uint32_t y = y0 + ty + 8 * j;
+            if (x < nx && y < ny) {
+                if (!p.stage_l) pre_l[j] = l[ol + (int64_t)x * p.sl[X] + (int64_t)y * p.sl[Y]];
+                if (!p.stage_r) pre_r[j] = r[orr + (int64_t)x * p.sr[X] + (int64_t)y * p.sr[Y]];
+            }
+        }
+    }
     // stage: lanes run along Y
     if (NIN >= 1 && (p.stage_l || (NIN >= 2 && p.stage_r))) {
         const uint32_t y = y0 + tx;
@@ -610,8 +626,12 @@ __global__ void __launch_bounds__(kBlock) transpose_tiles_kernel(T *d, const T *
             const uint32_t yl = ty + 8 * j, y = y0 + yl;
             if (y >= ny) break;
             T a = T(), b = T();
-            if (NIN >= 1) a = p.stage_l ? tile_l[xl][yl] : l[ol + (int64_t)x * p.sl[X] + (int64_t)y * p.sl[Y]];
-            if (NIN >= 2) b = p.stage_r ? tile_r[xl][yl] : r[orr + (int64_t)x * p.sr[X] + (int64_t)y * p.sr[Y]];
+            if (NIN >= 2) {  // kTrRows == 32 here, so h == 0
+                a = p.stage_l ? tile_l[xl][yl] : pre_l[j];
+                b = p.stage_r ? tile_r[xl][yl] : pre_r[j];
+            } else if (NIN >= 1) {
+                a = p.stage_l ? tile_l[xl][yl] : l[ol + (int64_t)x * p.sl[X] + (int64_t)y * p.sl[Y]];
+            }
             d[od + (int64_t)x * p.sd[X] + (int64_t)y * p.sd[Y]] = f(a, b);
         }
     }

@@ -5,6 +5,7 @@ of launches), so that an `ncu` capture ends by itself in a minute or two:
     python -m rtensors_b200.profile_cases red      axis sums of (8192,8192) and (16,4096,1024)
     python -m rtensors_b200.profile_cases ext      variance / logsumexp / L2 norm / argmax of (8192,8192) over both axes
     python -m rtensors_b200.profile_cases convert  dtype conversion of 2^26 elements: f32->f64, f32->i32, u8->f32, f32->u8 (twice each)
+    python -m rtensors_b200.profile_cases transpose  contiguous() of a transposed (8192,8192) f32 matrix and a.T + b (twice each)
     python -m rtensors_b200.profile_cases mid      mid-size ops (and the fused broadcast+reduce) with an L2 flush between them
 """
 import sys
@@ -90,6 +91,17 @@ def main():
             be.broadcast_reduce(A, am, B, bm, L.ADD, 0, L.SUM)
         torch.cuda.synchronize()
         print('done mid')
+    elif which == 'transpose':
+        S = 8192
+        a = torch.randn(S * S, device=dev)
+        b = torch.randn(S * S, device=dev)
+        out = be.alloc(S * S, torch.float32)
+        m = Meta.contiguous((S, S))
+        for _ in range(2):
+            be.contiguous(a, m.permute((1, 0)))
+            be.broadcast((a, m.permute((1, 0))), (b, m), (out, m), L.ADD)
+        torch.cuda.synchronize()
+        print('done transpose')
     elif which == 'convert':
         n = 1 << 26
         x = torch.randn(n, device=dev) * 100
