@@ -97,7 +97,12 @@ typedef struct rtb_ctx rtb_ctx;
  *      churn of `CUDA_BACKENDS`, src/backend/cuda.rs:38-51,155-162) ------------------------- */
 int rtb_ctx_create(int device, rtb_ctx **out);
 void rtb_ctx_destroy(rtb_ctx *ctx);
-/* stream all later calls on this ctx are enqueued on (a cudaStream_t; NULL = legacy default) */
+/* stream all later calls on this ctx are enqueued on (a cudaStream_t; NULL = legacy default).
+ * The context's scratch state (reduction workspace, allocator free list) is ordered by the stream
+ * only, so a change of stream makes the new stream wait (event record + cudaStreamWaitEvent) for
+ * everything this context has enqueued on the old one: calls through one context keep one total
+ * order on the device whatever streams they were issued on.  Use one context per stream for work
+ * that should overlap. */
 int rtb_ctx_set_stream(rtb_ctx *ctx, void *stream);
 void *rtb_ctx_get_stream(rtb_ctx *ctx);
 int rtb_ctx_device(rtb_ctx *ctx);
@@ -106,6 +111,19 @@ int rtb_ctx_sm_count(rtb_ctx *ctx);
 int rtb_ctx_sync(rtb_ctx *ctx);
 /* number of kernels this ctx has launched since creation (bench bookkeeping) */
 uint64_t rtb_ctx_launch_count(rtb_ctx *ctx);
+/* CUDA graphs and the context's device memory.  A captured sequence of calls bakes in the address
+ * of the reduction workspace and of the allocator blocks it used.  Rules that keep replays valid:
+ *   - a workspace that is outgrown is retired, not freed (freed with the context), so an old graph
+ *     never touches released memory;
+ *   - during stream capture nothing is allocated or freed: a call that would have to grow the
+ *     workspace, rtb_alloc without a cached block, and rtb_release_cached return an error instead
+ *     (run the sequence once eagerly, or reserve the workspace, before capturing);
+ *   - rtb_ctx_workspace_generation() changes whenever the workspace moved or cached blocks were
+ *     released; a holder of a graph compares it with the value at capture time and records the
+ *     graph again when it differs (an outdated graph is still safe for the workspace, but uses
+ *     the old, smaller one and may hold released allocator blocks after rtb_release_cached). */
+int rtb_ctx_reserve_workspace(rtb_ctx *ctx, size_t bytes);
+uint64_t rtb_ctx_workspace_generation(rtb_ctx *ctx);
 const char *rtb_last_error_string(void);
 
 /* ---- device memory: caching allocator (Backend::alloc / alloc_from_slice / dump / copy,
@@ -187,8 +205,17 @@ int rtb_copy_view(rtb_ctx *ctx, int dtype, const void *src, size_t rank, const s
 
 /* ---- broadcast binary op (Backend::broadcast, src/backend/mod.rs:296-309; kernel
  *      cuda/kernels/elementwise/binary/broadcast.cu:3-109).  All three views carry the OUTPUT
- *      shape; operands are pre-broadcast by stride 0 on broadcast dims.  dst may alias left with
- *      the same strides and offset (in-place form). ------------------------------------------- */
+ *      shape; operands are pre-broadcast by stride 0 on broadcast dims.  dst may alias left (or
+ *      right) with the same strides and offset (in-place form).
+ *      Overlap rule: an input whose bytes intersect dst's while it walks them differently
+ *      (a += a.T, v += v reversed, a window shifted over itself) is first copied out by the
+ *      strided copy kernel into a block of the context allocator, so EVERY INPUT ELEMENT IS READ
+ *      BEFORE ANY OUTPUT ELEMENT IS WRITTEN.  The reference's CPU walk (src/backend/cpu.rs:292-352)
+ *      reads such an operand while writing it, element by element in row-major order, so its result
+ *      depends on that order; TensorBase cannot express the call (the right-hand view would borrow
+ *      the tensor that `+=` borrows mutably), only the raw Backend::broadcast can, whose contract
+ *      (src/backend/mod.rs:296-302) does not define it.  Views of one buffer that interleave without
+ *      sharing an element take the same copy and give the same result as the reference. -------- */
 int rtb_broadcast(rtb_ctx *ctx, int dtype, int binop, const void *left, const ptrdiff_t *stride_l, size_t off_l,
                   const void *right, const ptrdiff_t *stride_r, size_t off_r, void *dst,
                   const ptrdiff_t *stride_d, size_t off_d, size_t rank, const size_t *shape);
@@ -317,13 +344,82 @@ int rtb_u8_to_f32_div(rtb_ctx *ctx, const uint8_t *src, float *dst, float diviso
  * is alloc + this call. */
 int rtb_convert(rtb_ctx *ctx, int src_dtype, int dst_dtype, const void *src, void *dst, size_t n);
 
-/* ---- multi-GPU sharding (new; the reference is single-device).  Host-only arithmetic: rank
- *      `part` of `parts` gets the half-open slab [*begin, *end) of an extent, earlier ranks
- *      taking the remainder. -------------------------------------------------------------------- */
+/* ---- multi-GPU (new; the reference is single-device: `Cuda::new()` -> device 0 with
+ *      `// TODO multiple devices`, src/backend/cuda.rs:155-162, 815-818).  One rank per GPU, one
+ *      communicator per context.  The path shards by slabs with no data-path collective for
+ *      elementwise and broadcast work; ranks exchange data only where a reduction runs across the
+ *      cut dim.
+ *
+ *      Host-only partition arithmetic (no CUDA call, testable on a CPU): ------------------------- */
+/* rank `part` of `parts` gets the half-open slab [*begin, *end) of an extent, earlier ranks taking
+ * the remainder */
 void rtb_shard_range(size_t extent, size_t parts, size_t part, size_t *begin, size_t *end);
-/* picks the outermost dim of an output shape with extent >= parts (src of the slab split);
- * returns -1 if none */
+/* the outermost dim of an output shape with extent >= parts (the slab dim); -1 if none */
 int rtb_shard_pick_dim(size_t rank, const size_t *shape, size_t parts);
+/* this rank's slab of a broadcast binary op whose operand views carry the output shape: the slab
+ * shape, its range along the cut dim and both operands' offsets inside the slab (an operand with
+ * stride 0 along the cut dim is replicated).  Returns the cut dim or -1 (no dim is wide enough:
+ * part 0 owns everything, the others get an empty slab). */
+int rtb_mg_slab(size_t rank, const size_t *shape, const ptrdiff_t *stride_l, size_t off_l, const ptrdiff_t *stride_r,
+                size_t off_r, size_t parts, size_t part, size_t *slab_shape, size_t *begin, size_t *end,
+                size_t *slab_off_l, size_t *slab_off_r);
+/* which dim to cut for a reduction over `axis`: a kept dim with extent >= parts when there is one
+ * (every rank owns its outputs, no exchange), else the reduced dim (partials are combined), else -1 */
+int rtb_mg_pick_reduce_dim(size_t rank, const size_t *shape, size_t axis, size_t parts);
+
+/*      Communicator.  rtb_mg_unique_id makes the 128-byte id on one rank; the host carries it to
+ *      the others over whatever channel it has (a store, MPI, a file) and every rank calls
+ *      rtb_mg_init with its own context (collective).  NCCL is bound at run time (libnccl.so.2,
+ *      the copy already loaded in the process if there is one).  Besides the NCCL communicator the
+ *      context gets a 4 MiB exchange buffer that every rank maps from every other rank (CUDA IPC):
+ *      small results travel through it as plain stores over NVLink from inside the library's own
+ *      kernels, with no collective launch (*peer_mapped of rtb_mg_info; when the mapping is not
+ *      possible everything falls back to NCCL).  All rtb_mg_* calls below are collective: every
+ *      rank makes the same calls in the same order on its context's stream. ------------------------ */
+#define RTB_MG_ID_BYTES 128
+#define RTB_MG_MAX_RANKS 16
+#define RTB_MG_SMALL_BYTES 65536 /* largest partial vector the peer exchange takes */
+int rtb_mg_unique_id(void *id_out /* RTB_MG_ID_BYTES */);
+int rtb_mg_init(rtb_ctx *ctx, int nranks, int rank, const void *id /* RTB_MG_ID_BYTES */);
+int rtb_mg_finalize(rtb_ctx *ctx); /* collective; rtb_ctx_destroy releases without one */
+int rtb_mg_info(rtb_ctx *ctx, int *nranks, int *rank, int *peer_mapped);
+/* Failure detection.  Every wait inside an exchange kernel is bounded by this limit (default 2 s).
+ * A wait that runs out does not trap or hang: the kernel sets status bit 0, writes NaN as the
+ * result and returns.  rtb_mg_status synchronises the stream and returns the bits (bit 1: NCCL
+ * reported an asynchronous error).  After a failure the ranks' exchange epochs may differ;
+ * rtb_mg_realign (collective, NCCL) brings them back in step and clears the status. */
+int rtb_mg_set_wait_ns(rtb_ctx *ctx, uint64_t ns);
+int rtb_mg_status(rtb_ctx *ctx, unsigned int *bits);
+int rtb_mg_realign(rtb_ctx *ctx);
+/* in-place all-reduce of n elements with NCCL on the context's stream (SUM PROD MAX MIN, MEAN =
+ * sum / (T)(float)mean_count for f32 / f64); u8 i8 i32 u32 i64 u64 f32 f64 */
+int rtb_mg_allreduce(rtb_ctx *ctx, int dtype, int redop, void *buf, size_t n, size_t mean_count);
+/* the same on the communicator's own side stream, ordered after the work enqueued so far:
+ * _begin returns at once and later calls on the context overlap the transfer; _join makes the
+ * context's stream wait for every transfer begun since the last join.  Capturable in a CUDA graph
+ * (fork / join by events). */
+int rtb_mg_allreduce_begin(rtb_ctx *ctx, int dtype, int redop, void *buf, size_t n, size_t mean_count);
+int rtb_mg_allreduce_join(rtb_ctx *ctx);
+/* in-place combine of a per-rank partial result: f32 / f64 buffers of up to RTB_MG_SMALL_BYTES go
+ * through the peer exchange (folded in rank order, so every rank gets the same bits), anything
+ * else through NCCL */
+int rtb_mg_combine(rtb_ctx *ctx, int dtype, int redop, void *buf, size_t n, size_t mean_count);
+/* full reduction of a tensor whose flat range is split across the ranks: src[start .. start +
+ * local_len] is this rank's part of global_len elements; every rank gets the result in dst[0].
+ * One launch: the last CTA of the local reduction exchanges the per-GPU totals through peer memory
+ * (TotalReductionOp over the whole tensor, src/ops/reduction/mod.rs:208-257). */
+int rtb_mg_reduce_flat(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t start, size_t local_len,
+                       size_t global_len, void *dst);
+/* axis reduction whose REDUCED dim is split across the ranks: this rank holds r_local of the
+ * global_r rows of [outer, r, inner] (element (o, k, i) at offset + o*outer_stride + k*row_stride + i);
+ * dst receives the combined outer*inner results on every rank.  (When a kept dim is split instead,
+ * rtb_reduce_axis / rtb_reduce_view on the slab needs no exchange.) */
+int rtb_mg_reduce_axis(rtb_ctx *ctx, int dtype, int redop, const void *src, size_t offset, size_t outer, size_t r_local,
+                       size_t inner, ptrdiff_t outer_stride, ptrdiff_t row_stride, size_t global_r, void *dst);
+/* rtb_l1_loss over tensors split across the ranks: the loss is the global one on every rank and
+ * the gradient map is scaled by the global element count */
+int rtb_mg_l1_loss(rtb_ctx *ctx, int dtype, const void *a, const void *b, size_t local_n, size_t global_n,
+                   int reduction, void *loss, void *grad_map);
 
 #ifdef __cplusplus
 }

@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
         l.rtb_last_error_string.restype = C.c_char_p
         l.rtb_ctx_get_stream.restype = C.c_void_p
         l.rtb_ctx_launch_count.restype = C.c_uint64
+        l.rtb_ctx_workspace_generation.restype = C.c_uint64
         l.rtb_meta_contiguous_strides.restype = None
         l.rtb_shard_range.restype = None
         l.rtb_ctx_destroy.restype = None

@@ -25,7 +25,7 @@ COMMON = ["-std=c++17", "-O3", "-lineinfo", "--fmad=false", "--prec-div=true", "
           "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 EW_DTYPES = list(range(13))
-PLAIN = ["rtb_planner.cpp", "rtb_context.cpp", "rtb_api.cpp", "rtb_abi_v1.cpp", "rtb_reduce.cu", "rtb_reduce_ext.cu", "rtb_noalloc.cu",
+PLAIN = ["rtb_planner.cpp", "rtb_context.cpp", "rtb_api.cpp", "rtb_abi_v1.cpp", "rtb_reduce.cu", "rtb_reduce_ext.cu", "rtb_noalloc.cu", "rtb_mg.cu",
          "rtb_convert.cu"]
 
 
@@ -77,7 +77,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                     print(log, file=sys.stderr)
     objs = [u[1] for u in units]
     if todo or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-ldl"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")

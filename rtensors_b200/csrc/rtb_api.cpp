@@ -57,13 +57,6 @@ int run_elementwise(Ctx *ctx, const EwCall &call, size_t rank, const size_t *sha
     return RTB_OK;
 }
 
-static int use_device(Ctx *ctx) {
-    int cur = -1;
-    RTB_CUDA(cudaGetDevice(&cur));
-    if (cur != ctx->device) RTB_CUDA(cudaSetDevice(ctx->device));
-    return RTB_OK;
-}
-
 static int check_view_args(rtb_ctx *c, const void *buf, size_t rank, const size_t *shape, const ptrdiff_t *strides) {
     if (!c) return fail(RTB_ERR_INVALID, "null ctx");
     if (!buf) return fail(RTB_ERR_INVALID, "null buffer");
@@ -152,6 +145,44 @@ RTB_API int rtb_grad_mask(rtb_ctx *c, int dtype, int kind, const void *value, co
     return run_elementwise(C(c), call, rank, shape, dense.data(), 0, strides, offset, nullptr, 0);
 }
 
+namespace {
+
+// Lowest and one-past-highest byte address a view touches; false for an empty view.
+bool byte_extent(const void *base, size_t es, size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset,
+                 uintptr_t *lo, uintptr_t *hi) {
+    int64_t mn = (int64_t)offset, mx = (int64_t)offset;
+    for (size_t k = 0; k < rank; ++k) {
+        if (shape[k] == 0) return false;
+        int64_t span = (int64_t)(shape[k] - 1) * (int64_t)strides[k];
+        if (span < 0) mn += span; else mx += span;
+    }
+    *lo = (uintptr_t)base + (uintptr_t)(mn * (int64_t)es);
+    *hi = (uintptr_t)base + (uintptr_t)((mx + 1) * (int64_t)es);
+    return true;
+}
+
+// Same element for every coordinate: same first address and the same stride on every dim that is walked.
+bool same_walk(const void *a, const ptrdiff_t *sa, size_t oa, const void *b, const ptrdiff_t *sb, size_t ob, size_t es,
+               size_t rank, const size_t *shape) {
+    if ((uintptr_t)a + oa * es != (uintptr_t)b + ob * es) return false;
+    for (size_t k = 0; k < rank; ++k)
+        if (shape[k] > 1 && sa[k] != sb[k]) return false;
+    return true;
+}
+
+// An input whose bytes intersect dst's while it walks them differently (a += a.T, v += reversed v)
+// would be read while other threads overwrite it.
+bool clashes(const void *in, const ptrdiff_t *si, size_t oi, const void *dst, const ptrdiff_t *sd, size_t od, size_t es,
+             size_t rank, const size_t *shape) {
+    uintptr_t ilo, ihi, dlo, dhi;
+    if (!byte_extent(in, es, rank, shape, si, oi, &ilo, &ihi) || !byte_extent(dst, es, rank, shape, sd, od, &dlo, &dhi))
+        return false;
+    if (ihi <= dlo || dhi <= ilo) return false;
+    return !same_walk(in, si, oi, dst, sd, od, es, rank, shape);
+}
+
+}  // namespace
+
 RTB_API int rtb_broadcast(rtb_ctx *c, int dtype, int binop, const void *left, const ptrdiff_t *sl, size_t ol,
                           const void *right, const ptrdiff_t *sr, size_t orr, void *dst, const ptrdiff_t *sd,
                           size_t od, size_t rank, const size_t *shape) {
@@ -160,12 +191,35 @@ RTB_API int rtb_broadcast(rtb_ctx *c, int dtype, int binop, const void *left, co
     if (rank > RTB_MAX_RANK) return fail(RTB_ERR_DIM, "rank %zu exceeds %d", rank, RTB_MAX_RANK);
     if (rank && (!shape || !sl || !sr || !sd)) return fail(RTB_ERR_INVALID, "null shape or strides");
     if (binop < RTB_ADD || binop > RTB_DIV) return fail(RTB_ERR_INVALID, "unknown binary op %d", binop);
+    const size_t es = dtype_size(dtype);
+    if (!es) return fail(RTB_ERR_DTYPE, "unknown dtype %d", dtype);
     int rc = use_device(C(c));
     if (rc) return rc;
     EwCall call{};
     call.dtype = dtype; call.family = kFamBinary; call.op = binop;
     call.d = dst; call.l = left; call.r = right;
-    return run_elementwise(C(c), call, rank, shape, sd, od, sl, ol, sr, orr);
+    // Operands that overlap dst under a different walk are copied out first (dense, row-major), so
+    // every input element is read before any output element is written.
+    const bool clash_l = clashes(left, sl, ol, dst, sd, od, es, rank, shape);
+    const bool clash_r = clashes(right, sr, orr, dst, sd, od, es, rank, shape);
+    if (!clash_l && !clash_r) return run_elementwise(C(c), call, rank, shape, sd, od, sl, ol, sr, orr);
+    size_t total = 1;
+    for (size_t k = 0; k < rank; ++k) total *= shape[k];
+    std::vector<ptrdiff_t> dense(rank ? rank : 1);
+    rtb_meta_contiguous_strides(rank, shape, dense.data());
+    void *tl = nullptr, *tr = nullptr;
+    if (clash_l) {
+        if ((rc = rtb_alloc(c, total * es, &tl)) == RTB_OK) rc = rtb_copy_view(c, dtype, left, rank, shape, sl, ol, tl);
+        if (rc == RTB_OK) { call.l = tl; sl = dense.data(); ol = 0; }
+    }
+    if (rc == RTB_OK && clash_r) {
+        if ((rc = rtb_alloc(c, total * es, &tr)) == RTB_OK) rc = rtb_copy_view(c, dtype, right, rank, shape, sr, orr, tr);
+        if (rc == RTB_OK) { call.r = tr; sr = dense.data(); orr = 0; }
+    }
+    if (rc == RTB_OK) rc = run_elementwise(C(c), call, rank, shape, sd, od, sl, ol, sr, orr);
+    if (tl) rtb_free(c, tl);  // stream order keeps the blocks alive until the kernels above are done
+    if (tr) rtb_free(c, tr);
+    return rc;
 }
 
 RTB_API int rtb_reduce_flat(rtb_ctx *c, int dtype, int redop, const void *src, size_t start, size_t len, void *dst) {

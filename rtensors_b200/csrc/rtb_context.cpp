@@ -8,22 +8,46 @@ namespace rtb {
 
 static constexpr size_t kCounterBytes = 65536;  // header of completion counters, kept at zero by the kernels
 
+int use_device(Ctx *ctx) {
+    int cur = -1;
+    RTB_CUDA(cudaGetDevice(&cur));
+    if (cur != ctx->device) RTB_CUDA(cudaSetDevice(ctx->device));
+    return RTB_OK;
+}
+
+static bool capturing(Ctx *ctx) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+
+// A superseded workspace is never freed before rtb_ctx_destroy: kernels already enqueued, and CUDA
+// graphs captured earlier, still hold its address.  It moves to ctx->retired instead, and
+// ws_generation tells a holder of a captured graph that the graph should be recorded again.
 int workspace(Ctx *ctx, size_t bytes, void **out) {
     size_t need = kCounterBytes + ((bytes + 255) & ~size_t(255));
     if (need > ctx->ws_bytes) {
+        if (capturing(ctx))
+            return fail(RTB_ERR_INVALID,
+                        "the reduction workspace (%zu bytes) would have to grow to %zu bytes during stream capture: "
+                        "run the sequence once eagerly or call rtb_ctx_reserve_workspace first",
+                        ctx->ws_bytes, need);
         size_t grow = need < (size_t(1) << 20) ? (size_t(1) << 20) : need;
         void *p = nullptr;
-        // earlier kernels may still be using the old workspace
-        RTB_CUDA(cudaStreamSynchronize(ctx->stream));
         RTB_CUDA(cudaMalloc(&p, grow));
+        // cudaMemset on the stream: ordered before every later kernel of this context
         cudaError_t e = cudaMemsetAsync(p, 0, kCounterBytes, ctx->stream);
         if (e != cudaSuccess) {
             cudaFree(p);
             return cuda_fail(e, "cudaMemsetAsync(workspace)");
         }
-        if (ctx->ws) cudaFree(ctx->ws);
+        if (ctx->ws) ctx->retired.push_back(ctx->ws);
         ctx->ws = p;
         ctx->ws_bytes = grow;
+        ctx->ws_generation.fetch_add(1, std::memory_order_relaxed);
     }
     *out = ctx->ws;
     return RTB_OK;
@@ -88,24 +112,55 @@ RTB_API void rtb_ctx_destroy(rtb_ctx *c) {
     Ctx *ctx = C(c);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    rtb::mg_release(ctx);
     rtb_release_cached(c);
     for (auto &kv : ctx->live_blocks) cudaFree(kv.first);
     if (ctx->ws) cudaFree(ctx->ws);
+    for (void *p : ctx->retired) cudaFree(p);
+    if (ctx->order_event) cudaEventDestroy(ctx->order_event);
     delete ctx;
 }
 
+// The context's state (workspace counters and partial slots, the allocator's free list) is only
+// ordered by the stream.  When the stream changes, the new stream is made to wait for everything
+// enqueued so far on the old one, so that work issued through this context keeps one total order.
 RTB_API int rtb_ctx_set_stream(rtb_ctx *c, void *stream) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
-    C(c)->stream = reinterpret_cast<cudaStream_t>(stream);
+    Ctx *ctx = C(c);
+    cudaStream_t next = reinterpret_cast<cudaStream_t>(stream);
+    if (next == ctx->stream) return RTB_OK;
+    int rc = rtb::use_device(ctx);
+    if (rc) return rc;
+    if (!ctx->order_event) RTB_CUDA(cudaEventCreateWithFlags(&ctx->order_event, cudaEventDisableTiming));
+    if (!rtb::capturing(ctx)) {
+        // (an old stream that is being captured cannot be joined from outside its graph; the caller
+        // owns the ordering then)
+        RTB_CUDA(cudaEventRecord(ctx->order_event, ctx->stream));
+        RTB_CUDA(cudaStreamWaitEvent(next, ctx->order_event, 0));
+    }
+    ctx->stream = next;
     return RTB_OK;
 }
 RTB_API void *rtb_ctx_get_stream(rtb_ctx *c) { return c ? (void *)C(c)->stream : nullptr; }
 RTB_API int rtb_ctx_device(rtb_ctx *c) { return c ? C(c)->device : -1; }
 RTB_API int rtb_ctx_sm_count(rtb_ctx *c) { return c ? C(c)->sm_count : 0; }
 RTB_API uint64_t rtb_ctx_launch_count(rtb_ctx *c) { return c ? C(c)->launches.load() : 0; }
+RTB_API uint64_t rtb_ctx_workspace_generation(rtb_ctx *c) { return c ? C(c)->ws_generation.load() : 0; }
+
+RTB_API int rtb_ctx_reserve_workspace(rtb_ctx *c, size_t bytes) {
+    if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
+    Ctx *ctx = C(c);
+    int rc = rtb::use_device(ctx);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
+    void *p = nullptr;
+    return rtb::workspace(ctx, bytes, &p);
+}
 
 RTB_API int rtb_ctx_sync(rtb_ctx *c) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
+    int rc = rtb::use_device(C(c));
+    if (rc) return rc;
     RTB_CUDA(cudaStreamSynchronize(C(c)->stream));
     return RTB_OK;
 }
@@ -113,6 +168,8 @@ RTB_API int rtb_ctx_sync(rtb_ctx *c) {
 RTB_API int rtb_alloc(rtb_ctx *c, size_t bytes, void **out) {
     if (!c || !out) return rtb::fail(RTB_ERR_INVALID, "null argument");
     Ctx *ctx = C(c);
+    int rc = rtb::use_device(ctx);
+    if (rc) return rc;
     size_t want = rtb::round_block(bytes);
     std::lock_guard<std::mutex> lock(ctx->mu);
     auto it = ctx->free_blocks.lower_bound(want);
@@ -123,12 +180,19 @@ RTB_API int rtb_alloc(rtb_ctx *c, size_t bytes, void **out) {
         ctx->free_blocks.erase(it);
         return RTB_OK;
     }
+    // Nothing is allocated or freed while the stream is being captured: a graph must only hold
+    // addresses that stay valid for its replays.
+    if (rtb::capturing(ctx))
+        return rtb::fail(RTB_ERR_ALLOC, "rtb_alloc: no cached block of %zu bytes during stream capture "
+                         "(run the sequence once eagerly so the allocator holds the blocks)", want);
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, want);
     if (e == cudaErrorMemoryAllocation) {  // give cached blocks back and retry once
         cudaGetLastError();
+        cudaStreamSynchronize(ctx->stream);  // kernels enqueued earlier may still use freed blocks
         for (auto &kv : ctx->free_blocks) cudaFree(kv.second);
         ctx->free_blocks.clear();
+        ctx->ws_generation.fetch_add(1, std::memory_order_relaxed);  // addresses a graph may hold are gone
         e = cudaMalloc(&p, want);
     }
     if (e != cudaSuccess) return rtb::cuda_fail(e, "cudaMalloc");
@@ -153,26 +217,33 @@ RTB_API int rtb_free(rtb_ctx *c, void *ptr) {
 RTB_API int rtb_release_cached(rtb_ctx *c) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
     Ctx *ctx = C(c);
+    int rc = rtb::use_device(ctx);
+    if (rc) return rc;
+    if (rtb::capturing(ctx)) return rtb::fail(RTB_ERR_INVALID, "rtb_release_cached during stream capture");
     std::lock_guard<std::mutex> lock(ctx->mu);
     cudaStreamSynchronize(ctx->stream);
     for (auto &kv : ctx->free_blocks) cudaFree(kv.second);
+    if (!ctx->free_blocks.empty()) ctx->ws_generation.fetch_add(1, std::memory_order_relaxed);
     ctx->free_blocks.clear();
     return RTB_OK;
 }
 
 RTB_API int rtb_h2d(rtb_ctx *c, void *dst, const void *src, size_t bytes) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
+    if (int rc = rtb::use_device(C(c))) return rc;
     RTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, C(c)->stream));
     return RTB_OK;
 }
 RTB_API int rtb_d2h(rtb_ctx *c, void *dst, const void *src, size_t bytes) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
+    if (int rc = rtb::use_device(C(c))) return rc;
     RTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, C(c)->stream));
     RTB_CUDA(cudaStreamSynchronize(C(c)->stream));
     return RTB_OK;
 }
 RTB_API int rtb_d2d(rtb_ctx *c, void *dst, const void *src, size_t bytes) {
     if (!c) return rtb::fail(RTB_ERR_INVALID, "null ctx");
+    if (int rc = rtb::use_device(C(c))) return rc;
     RTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, C(c)->stream));
     return RTB_OK;
 }

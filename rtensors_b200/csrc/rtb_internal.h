@@ -32,6 +32,7 @@ int cuda_fail(cudaError_t e, const char *what);
 size_t dtype_size(int dtype);  // 0 for an unknown code
 
 // ---- context -----------------------------------------------------------------------------------
+struct Mg;  // multi-GPU communicator state (rtb_mg.cu)
 struct Ctx {
     int device = 0;
     int sm_count = 0;
@@ -44,6 +45,10 @@ struct Ctx {
     std::mutex ws_mu;
     void *ws = nullptr;
     size_t ws_bytes = 0;
+    std::vector<void *> retired;              // superseded workspaces, freed only with the context
+    std::atomic<uint64_t> ws_generation{0};   // bumped whenever device memory a captured graph may hold goes away
+    cudaEvent_t order_event = nullptr;        // joins the old stream into the new one in rtb_ctx_set_stream
+    Mg *mg = nullptr;                         // set by rtb_mg_init
     // caching allocator: free blocks by rounded size; live blocks by pointer
     std::mutex mu;
     std::multimap<size_t, void *> free_blocks;
@@ -54,6 +59,8 @@ struct Ctx {
 // header holds completion counters that kernels leave at zero; it is zeroed when the workspace is
 // created.
 int workspace(Ctx *ctx, size_t bytes, void **out);
+void mg_release(Ctx *ctx);  // frees ctx->mg without any collective (context teardown)
+int use_device(Ctx *ctx);  // makes ctx->device current for the calling thread
 Ctx *default_ctx();  // ctx on the current device bound to the legacy default stream (ABI v1)
 
 inline void count_launch(Ctx *ctx) { ctx->launches.fetch_add(1, std::memory_order_relaxed); }

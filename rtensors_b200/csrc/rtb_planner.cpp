@@ -350,3 +350,41 @@ RTB_API int rtb_shard_pick_dim(size_t rank, const size_t *shape, size_t parts) {
         if (shape[k] >= parts) return (int)k;
     return -1;
 }
+
+// This rank's slab of a broadcast binary op: the outermost output dim with extent >= parts is cut;
+// an operand that is broadcast along it (stride 0) is replicated, any other operand's offset moves
+// to the slab.  Returns the cut dim, or -1 when no dim is wide enough (part 0 then owns everything
+// and the other parts get an empty slab on dim 0).
+RTB_API int rtb_mg_slab(size_t rank, const size_t *shape, const ptrdiff_t *stride_l, size_t off_l, const ptrdiff_t *stride_r,
+                        size_t off_r, size_t parts, size_t part, size_t *slab_shape, size_t *begin, size_t *end,
+                        size_t *slab_off_l, size_t *slab_off_r) {
+    for (size_t k = 0; k < rank; ++k) slab_shape[k] = shape[k];
+    *slab_off_l = off_l;
+    *slab_off_r = off_r;
+    if (parts == 0) parts = 1;
+    int dim = parts > 1 ? rtb_shard_pick_dim(rank, shape, parts) : -1;
+    if (dim < 0) {
+        *begin = 0;
+        *end = rank ? shape[0] : 1;
+        if (parts > 1 && part > 0) {
+            *end = 0;
+            if (rank) slab_shape[0] = 0;
+        }
+        return -1;
+    }
+    rtb_shard_range(shape[dim], parts, part, begin, end);
+    slab_shape[dim] = *end - *begin;
+    *slab_off_l = (size_t)((ptrdiff_t)off_l + (ptrdiff_t)*begin * stride_l[dim]);
+    *slab_off_r = (size_t)((ptrdiff_t)off_r + (ptrdiff_t)*begin * stride_r[dim]);
+    return dim;
+}
+
+// Which dim of `shape` to cut for an axis reduction over `axis`: a kept dim (outermost first) with
+// extent >= parts gives every rank its own outputs and needs no exchange; only when there is none is
+// the reduced dim itself cut (partial results are then combined across ranks).  -1: nothing to cut.
+RTB_API int rtb_mg_pick_reduce_dim(size_t rank, const size_t *shape, size_t axis, size_t parts) {
+    for (size_t k = 0; k < rank; ++k)
+        if (k != axis && shape[k] >= parts) return (int)k;
+    if (axis < rank && shape[axis] >= parts) return (int)axis;
+    return -1;
+}

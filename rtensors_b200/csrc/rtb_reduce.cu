@@ -9,8 +9,10 @@
 // why sums carry a tolerance while max / min are exact.  Every kernel combines in a fixed order,
 // so results are run-to-run deterministic.
 #include <cfloat>
+#include <type_traits>
 
 #include "rtb_internal.h"
+#include "rtb_mg.cuh"
 
 namespace rtb {
 namespace {
@@ -138,9 +140,11 @@ template <typename T> struct SrcL1 {
 
 // ---- flat: grid-wide partials, the last CTA to finish folds them ---------------------------------
 // ws layout: counter [0] of the header (left at zero), partials start after the header.
-template <typename T, int OP, typename Src>
+// Peers = MgPeers: the last CTA also exchanges this GPU's total with the other ranks over peer memory
+// (rtb_mg.cuh) and `count` is the global element count; Peers = NoPeers: single GPU, count = n.
+template <typename T, int OP, typename Src, typename Peers>
 __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, T *partials, unsigned int *counter,
-                                                             T *out, int mean) {
+                                                             T *out, int mean, size_t count, Peers peers) {
     grid_dep_wait();
     __shared__ T smem[kWarps];
     __shared__ bool is_last;
@@ -196,8 +200,10 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
     T t = Comb<T, OP>::identity();
     for (unsigned int k = threadIdx.x; k < gridDim.x; k += kBlock) t = Comb<T, OP>::apply(t, __ldcg(partials + k));
     t = block_reduce<T, OP>(t, smem);
+    if constexpr (std::is_same<Peers, MgPeers>::value)
+        t = mg_exchange_scalar<T>(t, peers, [](T a, T b) { return Comb<T, OP>::apply(a, b); });
     if (threadIdx.x == 0) {
-        out[0] = finish(t, mean, n);
+        out[0] = finish(t, mean, count);
         *counter = 0;  // ready for the next launch on this stream
     }
 }
@@ -712,8 +718,9 @@ unsigned grid_for(Ctx *ctx, size_t work_items, unsigned per_sm) {
     return (unsigned)(g ? g : 1);
 }
 
-template <typename T, int OP, typename Src>
-int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
+template <typename T, int OP, typename Src, typename Peers = NoPeers>
+int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean, size_t count = 0, Peers peers = Peers{}) {
+    if (!std::is_same<Peers, MgPeers>::value) count = n;
     constexpr int N = VecOf<T>::N;
     // one CTA per 4 KiB-vector-iterations, capped at 4 CTAs per SM: a read-bandwidth probe on B200 gives
     // 7.29 TB/s at 4 CTAs/SM, 7.14 at 8 and 6.97 at 16 (fewer concurrent streams, better DRAM locality)
@@ -724,18 +731,18 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean) {
     if (rc != RTB_OK) return rc;
     unsigned int *counter = reinterpret_cast<unsigned int *>(ws);
     T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
-    launch_dep(ctx, grid, kBlock, flat_reduce_kernel<T, OP, Src>, src, n, partials, counter, out, mean);
+    launch_dep(ctx, grid, kBlock, flat_reduce_kernel<T, OP, Src, Peers>, src, n, partials, counter, out, mean, count, peers);
     return check_launch(ctx, "flat_reduce_kernel");
 }
 
-template <typename T, typename Src>
-int flat_by_op(Ctx *ctx, int redop, Src src, size_t n, T *out) {
+template <typename T, typename Src, typename Peers = NoPeers>
+int flat_by_op(Ctx *ctx, int redop, Src src, size_t n, T *out, size_t count = 0, Peers peers = Peers{}) {
     switch (redop) {
-        case RTB_SUM: return flat_launch<T, RTB_SUM, Src>(ctx, src, n, out, 0);
-        case RTB_MEAN: return flat_launch<T, RTB_SUM, Src>(ctx, src, n, out, 1);
-        case RTB_PROD: return flat_launch<T, RTB_PROD, Src>(ctx, src, n, out, 0);
-        case RTB_MAX: return flat_launch<T, RTB_MAX, Src>(ctx, src, n, out, 0);
-        case RTB_MIN: return flat_launch<T, RTB_MIN, Src>(ctx, src, n, out, 0);
+        case RTB_SUM: return flat_launch<T, RTB_SUM, Src, Peers>(ctx, src, n, out, 0, count, peers);
+        case RTB_MEAN: return flat_launch<T, RTB_SUM, Src, Peers>(ctx, src, n, out, 1, count, peers);
+        case RTB_PROD: return flat_launch<T, RTB_PROD, Src, Peers>(ctx, src, n, out, 0, count, peers);
+        case RTB_MAX: return flat_launch<T, RTB_MAX, Src, Peers>(ctx, src, n, out, 0, count, peers);
+        case RTB_MIN: return flat_launch<T, RTB_MIN, Src, Peers>(ctx, src, n, out, 0, count, peers);
     }
     return fail(RTB_ERR_INVALID, "unsupported reduction code %d", redop);
 }
@@ -968,6 +975,36 @@ static int l1_typed(Ctx *ctx, const T *a, const T *b, size_t n, int reduction, T
     uintptr_t pa = (uintptr_t)a & 15u, pb = (uintptr_t)b & 15u, pg = g ? ((uintptr_t)g & 15u) : pa;
     SrcL1<T> src{a, b, g, reduction == 0 ? (T)(float)n : (T)1, (pa == pb && pa == pg) ? 1 : 0};
     return flat_launch<T, RTB_SUM, SrcL1<T>>(ctx, src, n, loss, reduction == 0 ? 1 : 0);
+}
+
+// the same over a tensor split across ranks: the gradient map is scaled by the GLOBAL count and
+// the per-GPU sums of |a - b| are exchanged by the last CTA
+template <typename T>
+static int l1_typed_mg(Ctx *ctx, const T *a, const T *b, size_t n, int reduction, T *loss, T *g, const MgPeers &peers,
+                       size_t global_count) {
+    uintptr_t pa = (uintptr_t)a & 15u, pb = (uintptr_t)b & 15u, pg = g ? ((uintptr_t)g & 15u) : pa;
+    SrcL1<T> src{a, b, g, reduction == 0 ? (T)(float)global_count : (T)1, (pa == pb && pa == pg) ? 1 : 0};
+    return flat_launch<T, RTB_SUM, SrcL1<T>, MgPeers>(ctx, src, n, loss, reduction == 0 ? 1 : 0, global_count, peers);
+}
+
+int launch_l1_mg(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap,
+                 const MgPeers &peers, size_t global_count) {
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
+    if (dtype == RTB_F32)
+        return l1_typed_mg<float>(ctx, (const float *)a, (const float *)b, n, reduction, (float *)loss, (float *)gmap, peers, global_count);
+    if (dtype == RTB_F64)
+        return l1_typed_mg<double>(ctx, (const double *)a, (const double *)b, n, reduction, (double *)loss, (double *)gmap, peers, global_count);
+    return fail(RTB_ERR_DTYPE, "l1 loss is defined for f32 and f64 only");
+}
+
+int launch_reduce_flat_mg(Ctx *ctx, int dtype, int redop, const void *src, size_t len, void *dst, const MgPeers &peers,
+                          size_t global_count) {
+    std::lock_guard<std::mutex> lock(ctx->ws_mu);
+    if (dtype == RTB_F32)
+        return flat_by_op<float, SrcPlain<float>, MgPeers>(ctx, redop, SrcPlain<float>{(const float *)src}, len, (float *)dst, global_count, peers);
+    if (dtype == RTB_F64)
+        return flat_by_op<double, SrcPlain<double>, MgPeers>(ctx, redop, SrcPlain<double>{(const double *)src}, len, (double *)dst, global_count, peers);
+    return fail(RTB_ERR_DTYPE, "reductions are defined for f32 and f64 only");
 }
 
 int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap) {

@@ -97,3 +97,30 @@ def test_no_device_allocation_happens():
     free1, _ = torch.cuda.mem_get_info()
     assert free1 == free0
     assert abs(float(out.item()) - float(x.sum(dtype=torch.float64))) <= 1e-5 * 20 * float(x.abs().sum())
+
+
+@pytest.mark.parametrize("tdt,code", [(torch.float32, F32), (torch.float64, F64)], ids=["f32", "f64"])
+@pytest.mark.parametrize("start", [0, 1, 3])
+def test_edges_of_the_head_vector_tail_split(ctx, tdt, code, start):
+    """Lengths around the kernel's seams: nothing, less than one 16-byte vector behind a misaligned
+    start, and one element either side of the 65 536-element boundary between one and two CTAs."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99 + start)
+    x = torch.rand(65537 + start + 4, device="cuda", dtype=tdt, generator=g) * 0.5 + 0.75   # products stay finite
+    for n in (0, 1, 3, 5, 65535, 65536, 65537):
+        for op in (SUM, PROD, MAX, MIN, MEAN):
+            if op == PROD and n > 5:
+                continue            # 65 536 factors in [0.75, 1.25) under- or overflow; the short runs cover PROD
+            want = torch.full((1,), 3.0, device="cuda", dtype=tdt)
+            got = torch.full((1,), 7.0, device="cuda", dtype=tdt)
+            assert _regular(ctx, code, op, x, start, n, want) == 0
+            assert _noalloc(code, op, x, start, n, got) == 0
+            torch.cuda.synchronize()
+            w, v = float(want.item()), float(got.item())
+            if n == 0 and op == MEAN:
+                assert math.isnan(v) and math.isnan(w)      # 0 / 0, as the CPU backend's mean of nothing
+            elif op in (MAX, MIN) or n <= 1:
+                assert v == w, (n, op, v, w)
+            else:
+                eps_scale = 1e-5 if tdt == torch.float32 else 1e-12
+                assert abs(v - w) <= eps_scale * max(math.log2(n), 1.0) * max(abs(w), 1.0), (n, op, v, w)
