@@ -311,6 +311,11 @@ int rtb_reduce_to_shape(rtb_ctx *ctx, int dtype, const void *upstream, size_t ra
  * relu with its gradient mask in one pass (relu_inplace + the per-element mask loop of
  * src/ops/unary/mod.rs:213-252): x = x>0 ? x : 0, mask = x>0 ? 1 : 0 */
 int rtb_relu_mask_f32(rtb_ctx *ctx, float *x, float *mask, size_t n);
+/* One dense layer's `+ bias` (Backend::broadcast with the (1, cols) bias, src/ops/broadcast/add.rs:14-46),
+ * relu_inplace and its gradient map (src/ops/unary/mod.rs:56-92, 234-252) in one pass over a dense
+ * row-major (rows, cols) activation: z = relu(z + bias), mask = (z + bias) > 0 ? 1 : 0.  The bits equal
+ * those of the three separate calls (one IEEE add, then `x > 0` tests).  f32 / f64. */
+int rtb_bias_relu_mask(rtb_ctx *ctx, int dtype, void *z, const void *bias, void *mask, size_t rows, size_t cols);
 /* The per-element maps the reference's autograd fills with one host get and one host set per
  * element, as one kernel each.  dst is a dense row-major tensor of the view's shape; src is any
  * view (strided, permuted, negative step); src and dst must not overlap.

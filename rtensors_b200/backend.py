@@ -49,12 +49,14 @@ class CudaB200:
         self._ctx = C.c_void_p()
         check(lib().rtb_ctx_create(C.c_int(self.device), C.byref(self._ctx)))
         self._stream = None
+        self.mg_world, self.mg_rank, self.mg_peer_mapped = 1, 0, False
         self.sync_stream()
 
     def close(self):
         if self._ctx:
             lib().rtb_ctx_destroy(self._ctx)
             self._ctx = C.c_void_p()
+            self.mg_world = 1
 
     def __del__(self):  # pragma: no cover
         try:
@@ -254,7 +256,8 @@ class CudaB200:
                                     C.c_size_t(sm.offset), C.c_size_t(outer), C.c_size_t(r), C.c_size_t(inner),
                                     self._p(dst)))
 
-    def reduce_view(self, src: torch.Tensor, meta: Meta, axis: Optional[int], op: int) -> torch.Tensor:
+    def reduce_view(self, src: torch.Tensor, meta: Meta, axis: Optional[int], op: int,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Reduction over an arbitrary view without requiring contiguity (rtb_reduce_view); axis
         None = full reduction.  Returns the row-major result buffer (reduced dim kept as 1)."""
         meta.check_extent(src.numel())
@@ -264,7 +267,10 @@ class CudaB200:
             n_out = 1
             for k, s_ in enumerate(meta.shape):
                 n_out *= 1 if k == axis else s_
-        out = self.alloc(max(n_out, 1), src.dtype)
+        if out is None:
+            out = self.alloc(max(n_out, 1), src.dtype)
+        elif out.numel() < n_out or out.dtype != src.dtype:
+            raise ValueError("reduce_view: the output buffer is too small or of another dtype")
         check(lib().rtb_reduce_view(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(meta.rank),
                                     meta.c_shape, meta.c_strides, C.c_size_t(meta.offset),
                                     C.c_ssize_t(-1 if axis is None else axis), self._p(out)))
@@ -343,11 +349,15 @@ class CudaB200:
                                 C.c_int(reduction), self._p(loss), self._p(g)))
         return loss, g
 
-    def reduce_to_shape(self, upstream: torch.Tensor, shape: Sequence[int], operand_strides: Sequence[int]):
+    def reduce_to_shape(self, upstream: torch.Tensor, shape: Sequence[int], operand_strides: Sequence[int],
+                        out: Optional[torch.Tensor] = None):
         r = len(shape)
         oshape = tuple(1 if s == 0 else n for n, s in zip(shape, operand_strides))
         n_out = int(np.prod(oshape, dtype=np.int64)) if r else 1
-        out = self.alloc(max(n_out, 1), upstream.dtype)
+        if out is None:
+            out = self.alloc(max(n_out, 1), upstream.dtype)
+        elif out.numel() < n_out or out.dtype != upstream.dtype:
+            raise ValueError("reduce_to_shape: the output buffer is too small or of another dtype")
         osh = (C.c_size_t * max(r, 1))()
         check(lib().rtb_reduce_to_shape(self._ctx, C.c_int(dtype_code(upstream)), self._p(upstream), C.c_size_t(r),
                                         sizes(shape), diffs(operand_strides), self._p(out), osh))
@@ -359,6 +369,13 @@ class CudaB200:
         mask = torch.empty_like(x)
         fn = lib().rtb_relu_mask_f64 if x.dtype == torch.float64 else lib().rtb_relu_mask_f32
         check(fn(self._ctx, self._p(x), self._p(mask), C.c_size_t(x.numel())))
+        return mask
+
+    def bias_relu_mask(self, z: torch.Tensor, bias: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+        """z = relu(z + bias) in place over a dense (rows, cols) activation; returns the gradient mask."""
+        mask = torch.empty_like(z)
+        check(lib().rtb_bias_relu_mask(self._ctx, C.c_int(dtype_code(z)), self._p(z), self._p(bias), self._p(mask),
+                                       C.c_size_t(rows), C.c_size_t(cols)))
         return mask
 
     def sgd_update(self, p: torch.Tensor, g: torch.Tensor, lr: float):
@@ -390,3 +407,72 @@ class CudaB200:
         check(lib().rtb_u8_to_f32_div(self._ctx, self._p(src), self._p(out), C.c_float(divisor),
                                       C.c_size_t(src.numel())))
         return out
+
+    # -- multi-GPU (rtb_mg_*): one rank per GPU, the communicator lives in the library context -----
+    @staticmethod
+    def mg_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(lib().rtb_mg_unique_id(buf))
+        return buf.raw
+
+    def mg_init(self, nranks: int, rank: int, unique_id: bytes):
+        """Collective: every rank passes the id made by rank 0's mg_unique_id()."""
+        check(lib().rtb_mg_init(self._ctx, C.c_int(nranks), C.c_int(rank), C.c_char_p(unique_id)))
+        n, r, m = C.c_int(), C.c_int(), C.c_int()
+        check(lib().rtb_mg_info(self._ctx, C.byref(n), C.byref(r), C.byref(m)))
+        self.mg_world, self.mg_rank, self.mg_peer_mapped = n.value, r.value, bool(m.value)
+
+    def mg_finalize(self):
+        check(lib().rtb_mg_finalize(self._ctx))
+        self.mg_world, self.mg_rank, self.mg_peer_mapped = 1, 0, False
+
+    def mg_set_wait_ns(self, ns: int):
+        check(lib().rtb_mg_set_wait_ns(self._ctx, C.c_uint64(ns)))
+
+    def mg_status(self) -> int:
+        bits = C.c_uint()
+        check(lib().rtb_mg_status(self._ctx, C.byref(bits)))
+        return bits.value
+
+    def mg_realign(self):
+        check(lib().rtb_mg_realign(self._ctx))
+
+    def mg_allreduce(self, buf: torch.Tensor, op: int = L.SUM, mean_count: int = 0, overlap: bool = False):
+        fn = lib().rtb_mg_allreduce_begin if overlap else lib().rtb_mg_allreduce
+        check(fn(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(buf.numel()),
+                 C.c_size_t(mean_count)))
+
+    def mg_allreduce_join(self):
+        check(lib().rtb_mg_allreduce_join(self._ctx))
+
+    def mg_combine(self, buf: torch.Tensor, op: int = L.SUM, mean_count: int = 0):
+        check(lib().rtb_mg_combine(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(buf.numel()),
+                                   C.c_size_t(mean_count)))
+
+    def mg_reduce_flat(self, src: torch.Tensor, start: int, local_len: int, global_len: int, op: int,
+                       dst: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if start + local_len > src.numel():
+            raise L.RtbError(-4, "flat reduction range exceeds the buffer")
+        dst = self.alloc(1, src.dtype) if dst is None else dst
+        check(lib().rtb_mg_reduce_flat(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(start),
+                                       C.c_size_t(local_len), C.c_size_t(global_len), self._p(dst)))
+        return dst
+
+    def mg_reduce_axis(self, src: torch.Tensor, offset: int, outer: int, r_local: int, inner: int, global_r: int, op: int,
+                       outer_stride: Optional[int] = None, row_stride: Optional[int] = None,
+                       dst: Optional[torch.Tensor] = None) -> torch.Tensor:
+        dst = self.alloc(max(outer * inner, 1), src.dtype) if dst is None else dst
+        so = r_local * inner if outer_stride is None else outer_stride
+        sr = inner if row_stride is None else row_stride
+        check(lib().rtb_mg_reduce_axis(self._ctx, C.c_int(dtype_code(src)), C.c_int(op), self._p(src), C.c_size_t(offset),
+                                       C.c_size_t(outer), C.c_size_t(r_local), C.c_size_t(inner), C.c_ssize_t(so),
+                                       C.c_ssize_t(sr), C.c_size_t(global_r), self._p(dst)))
+        return dst
+
+    def mg_l1_loss(self, a: torch.Tensor, b: torch.Tensor, global_n: int, reduction: int = 0, with_grad: bool = False):
+        assert a.numel() == b.numel() and a.dtype == b.dtype
+        loss = self.alloc(1, a.dtype)
+        g = self.alloc(a.numel(), a.dtype) if with_grad else None
+        check(lib().rtb_mg_l1_loss(self._ctx, C.c_int(dtype_code(a)), self._p(a), self._p(b), C.c_size_t(a.numel()),
+                                   C.c_size_t(global_n), C.c_int(reduction), self._p(loss), self._p(g)))
+        return loss, g

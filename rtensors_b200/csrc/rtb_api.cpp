@@ -502,6 +502,14 @@ RTB_API int rtb_relu_mask_f32(rtb_ctx *c, float *x, float *mask, size_t n) {
     return launch_relu_mask(C(c), x, mask, n);
 }
 
+RTB_API int rtb_bias_relu_mask(rtb_ctx *c, int dtype, void *z, const void *bias, void *mask, size_t rows, size_t cols) {
+    if (!c || !z || !bias || !mask) return fail(RTB_ERR_INVALID, "null argument");
+    if (z == mask) return fail(RTB_ERR_INVALID, "the mask must not share the activations' buffer");
+    int rc = use_device(C(c));
+    if (rc) return rc;
+    return launch_bias_relu_mask(C(c), dtype, z, bias, mask, rows, cols);
+}
+
 RTB_API int rtb_sgd_update_f32(rtb_ctx *c, float *p, const float *g, float lr, size_t n) {
     if (!c || !p || !g) return fail(RTB_ERR_INVALID, "null argument");
     int rc = use_device(C(c));

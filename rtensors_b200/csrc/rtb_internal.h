@@ -153,6 +153,7 @@ int launch_bcast_reduce(Ctx *ctx, int dtype, int binop, int redop, const void *l
                         const ptrdiff_t sr[3], size_t A, size_t R, size_t B, void *dst);
 int launch_l1(Ctx *ctx, int dtype, const void *a, const void *b, size_t n, int reduction, void *loss, void *gmap);
 int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n);
+int launch_bias_relu_mask(Ctx *ctx, int dtype, void *z, const void *bias, void *mask, size_t rows, size_t cols);
 int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n);
 int launch_relu_mask_f64(Ctx *ctx, double *x, double *mask, size_t n);
 int launch_sgd_f64(Ctx *ctx, double *p, const double *g, double lr, size_t n);

@@ -645,6 +645,64 @@ __global__ void __launch_bounds__(kBlock) relu_mask_kernel(float *x, float *mask
     }
 }
 
+// z[r, c] = relu(z[r, c] + bias[c]) in place, mask[r, c] = (z[r, c] + bias[c]) > 0 ? 1 : 0: the bias
+// broadcast add, relu_inplace and its gradient map (three launches and 5 passes over the
+// activations when run one by one) as ONE pass that reads z once and writes z and mask.  A thread keeps
+// its VW bias values in registers and walks kRowsPerCta rows, all loads issued before the first store.
+// The sum is the same single IEEE add and the comparisons the same `x > 0` as in the separate calls.
+constexpr int kBiasRows = 8;
+template <typename T, int VW>
+__global__ void __launch_bounds__(kBlock) bias_relu_mask_kernel(T *z, const T *bias, T *mask, size_t rows, size_t cols,
+                                                                size_t col_blocks) {
+    grid_dep_sync();
+    using U = typename VecOf<T>::U;
+    const size_t cb = blockIdx.x % col_blocks, rb = blockIdx.x / col_blocks;
+    const size_t c = (cb * kBlock + threadIdx.x) * VW;
+    if (c >= cols) return;
+    const size_t r0 = rb * kBiasRows;
+    T b[VW], v[kBiasRows][VW];
+    if (VW > 1) {
+        U u;
+        u.q = __ldg(reinterpret_cast<const uint4 *>(bias + c));
+#pragma unroll
+        for (int j = 0; j < VW; ++j) b[j] = u.e[j];
+    } else {
+        b[0] = __ldg(bias + c);
+    }
+#pragma unroll
+    for (int k = 0; k < kBiasRows; ++k) {
+        if (r0 + k < rows) {
+            if (VW > 1) {
+                U u;
+                u.q = *reinterpret_cast<const uint4 *>(z + (r0 + k) * cols + c);
+#pragma unroll
+                for (int j = 0; j < VW; ++j) v[k][j] = u.e[j];
+            } else {
+                v[k][0] = z[(r0 + k) * cols + c];
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kBiasRows; ++k) {
+        if (r0 + k < rows) {
+            U o, m;
+#pragma unroll
+            for (int j = 0; j < VW; ++j) {
+                const T t = v[k][j] + b[j];
+                o.e[j] = t > (T)0 ? t : (T)0;
+                m.e[j] = t > (T)0 ? (T)1 : (T)0;
+            }
+            if (VW > 1) {
+                *reinterpret_cast<uint4 *>(z + (r0 + k) * cols + c) = o.q;
+                *reinterpret_cast<uint4 *>(mask + (r0 + k) * cols + c) = m.q;
+            } else {
+                z[(r0 + k) * cols + c] = o.e[0];
+                mask[(r0 + k) * cols + c] = m.e[0];
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kBlock) sgd_kernel(float *p, const float *g, float lr, size_t n) {
     grid_dep_sync();
     const size_t nvec = n / 4;
@@ -1019,6 +1077,26 @@ int launch_relu_mask(Ctx *ctx, float *x, float *mask, size_t n) {
     unsigned grid = grid_for(ctx, (n / 4 + kBlock - 1) / kBlock, 16);
     launch_dep(ctx, grid, kBlock, relu_mask_kernel, x, mask, n);
     return check_launch(ctx, "relu_mask_kernel");
+}
+
+template <typename T>
+static int bias_relu_mask_typed(Ctx *ctx, T *z, const T *bias, T *mask, size_t rows, size_t cols) {
+    constexpr int N = VecOf<T>::N;
+    const bool vec = cols % N == 0 && (((uintptr_t)z | (uintptr_t)bias | (uintptr_t)mask) & 15u) == 0;
+    const size_t per = vec ? (size_t)N : 1;
+    const size_t col_blocks = (cols / per + kBlock - 1) / kBlock;
+    const size_t grid = col_blocks * ((rows + kBiasRows - 1) / kBiasRows);
+    if (grid > 0x7fffffffu) return fail(RTB_ERR_TOO_LARGE, "bias_relu_mask: %zu x %zu is beyond one launch", rows, cols);
+    if (vec) launch_dep(ctx, (unsigned)grid, kBlock, bias_relu_mask_kernel<T, N>, z, bias, mask, rows, cols, col_blocks);
+    else launch_dep(ctx, (unsigned)grid, kBlock, bias_relu_mask_kernel<T, 1>, z, bias, mask, rows, cols, col_blocks);
+    return check_launch(ctx, "bias_relu_mask_kernel");
+}
+
+int launch_bias_relu_mask(Ctx *ctx, int dtype, void *z, const void *bias, void *mask, size_t rows, size_t cols) {
+    if (rows == 0 || cols == 0) return RTB_OK;
+    if (dtype == RTB_F32) return bias_relu_mask_typed<float>(ctx, (float *)z, (const float *)bias, (float *)mask, rows, cols);
+    if (dtype == RTB_F64) return bias_relu_mask_typed<double>(ctx, (double *)z, (const double *)bias, (double *)mask, rows, cols);
+    return fail(RTB_ERR_DTYPE, "bias_relu_mask is defined for f32 and f64 only");
 }
 
 int launch_sgd(Ctx *ctx, float *p, const float *g, float lr, size_t n) {

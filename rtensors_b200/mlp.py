@@ -3,24 +3,31 @@ way the reference's tape computes it (examples/mnist/src/main.rs:17-46 for the m
 src/grad/mod.rs:432-495 and src/grad/backwards.rs for the backward pass, src/grad/optim.rs:30-50 for
 the update), with every non-GEMM op on this library's kernels:
 
-  u8 -> f32 / 255            rtb_u8_to_f32_div
-  x @ W                      cuBLAS through torch.matmul (matmul stays on cuBLAS by design)
-  + bias (1,out) in place    rtb_broadcast, in-place form
-  relu + gradient mask       rtb_relu_mask_f32          (reference: per-element get/set loop)
-  mean_l1_loss + grad map    rtb_l1_loss                 (reference: 5 launches, 2 temporaries)
-  grad_map * seed            rtb_scalar_op (scalar multiply in place)
-  mask * upstream            rtb_broadcast (same-shape multiply, in place)
-  bias gradient              rtb_reduce_to_shape         (column sum of the upstream)
-  p -= g * lr                rtb_sgd_update_f32 over one flat parameter buffer
+  u8 -> f32 / 255              rtb_u8_to_f32_div
+  x @ W                        cuBLAS through torch.matmul (matmul stays on cuBLAS by design)
+  + bias, relu, gradient mask  rtb_bias_relu_mask, ONE pass (reference: broadcast add, relu, and a
+                               per-element get/set loop for the mask); the last layer's plain
+                               `+ bias` is rtb_broadcast in place
+  mean_l1_loss + grad map      rtb_l1_loss / rtb_mg_l1_loss (reference: 5 launches, 2 temporaries)
+  grad_map * seed              rtb_broadcast with the rank-0 loss tensor as right operand (no host
+                               read of the loss), as backwards_l1 does (src/grad/backwards.rs:148-161)
+  mask * upstream              rtb_broadcast (same-shape multiply, in place)
+  bias gradient                rtb_reduce_to_shape, written straight into the gradient bucket
+  p -= g * lr                  rtb_sgd_update_f32 over one flat parameter buffer
+
+This class is the fused, fixed-graph form of the step; `rtensors_b200.grad` runs the same step
+through a tape with the reference's node types, and the two agree bit for bit.
 
 Two modes.  intended: backward seed 1 and the bias gradient is the batch sum.  ref_quirks: the
 reference's observable behaviour -- the seed is the loss VALUE (src/grad/mod.rs:441-447) and the
 bias "gradient" is row 0 of the upstream (src/grad/backwards.rs:527 keeps only the meta of the sum).
 
-Data parallel: each rank holds batch/world rows; the loss partial sums are all-reduced (the seed
-needs the global loss in ref_quirks mode), gradients live in ONE flat bucket that is all-reduced
-once, and every rank applies the same update.  Parameters live in one flat buffer with the same
-layout as the bucket.
+Data parallel (the engine owns a communicator, `CudaB200.mg_init`): each rank holds batch/world
+rows; the loss is combined inside the L1 kernel's last CTA over peer memory (the seed needs the
+global loss in ref_quirks mode); every layer's gradients (dW, db -- adjacent in the flat bucket) are
+all-reduced with NCCL on the communicator's side stream as soon as they exist, overlapping the
+next layer's backward GEMMs; every rank applies the same update.  The whole step, collectives
+included, can be captured in a CUDA graph (`step_graphed`).
 """
 from __future__ import annotations
 
@@ -28,9 +35,9 @@ from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
-import torch.distributed as dist
 
 from . import _lib as L
+from ._lib import lib
 from .backend import CudaB200
 from .meta import Meta
 
@@ -67,6 +74,12 @@ class DenseMlp:
     def grad_weight(self, layer: int): return self._view(self.grads, 2 * layer)
     def grad_bias(self, layer: int): return self._view(self.grads, 2 * layer + 1)
 
+    def layer_bucket(self, layer: int) -> torch.Tensor:
+        """dW and db of one layer: adjacent in the flat gradient buffer, all-reduced as one message."""
+        lo = self.offsets[2 * layer]
+        hi = self.offsets[2 * layer + 2] if 2 * layer + 2 < len(self.offsets) else self.n_flat
+        return self.grads[lo:hi]
+
     def host_params(self) -> List[np.ndarray]:
         return [self._view(self.params, k).detach().cpu().numpy().copy() for k in range(len(self.shapes))]
 
@@ -77,9 +90,10 @@ class DenseMlp:
     # ------------------------------------------------------------------------------------------
     def step(self, images_u8: torch.Tensor, targets: torch.Tensor, global_batch: Optional[int] = None):
         """images_u8: (b, 784) uint8 on the device; targets: (b, 10) f32.  Returns the (global) loss
-        as a 1-element device tensor.  b is this rank's share of global_batch."""
+        as a 1-element device tensor.  b is this rank's share of global_batch.  Nothing in the step
+        reads the device from the host."""
         be = self.be
-        world = dist.get_world_size() if dist.is_initialized() else 1
+        world, rank = be.mg_world, be.mg_rank
         b = images_u8.shape[0]
         gb = global_batch or b * world
         n_layers = len(self.sizes) - 1
@@ -89,23 +103,23 @@ class DenseMlp:
         for li in range(n_layers):
             z = torch.matmul(h, self.weight(li))              # cuBLAS
             fo = self.sizes[li + 1]
-            be.binary_assign(z.view(-1), Meta.contiguous((b, fo)), self.bias(li).view(-1), Meta.contiguous((1, fo)), L.ADD)
             if li != n_layers - 1:
-                masks.append(be.relu_mask(z.view(-1)).view(b, fo))
+                masks.append(be.bias_relu_mask(z.view(-1), self.bias(li).view(-1), b, fo).view(b, fo))
+            else:
+                be.binary_assign(z.view(-1), Meta.contiguous((b, fo)), self.bias(li).view(-1), Meta.contiguous((1, fo)), L.ADD)
             acts.append(z)
             h = z
         out = acts[-1]
         n_out = self.sizes[-1]
-        # loss: local sum of |out - target| and the map sign(out - target); both scaled by N_global
-        lsum, gmap = be.l1_loss(out.view(-1), targets.reshape(-1), 1, True)
+        # loss = sum |out - target| / (f32)N over the GLOBAL batch, map = sign(out - target) / (f32)N
         if world > 1:
-            dist.all_reduce(lsum, op=dist.ReduceOp.SUM)
-        n_global = np.float32(gb * n_out)
-        loss = lsum / float(n_global)                                   # mean = sum / (f32)N
-        m_all = Meta.contiguous((gmap.numel(),))
-        be.scalar_apply(gmap, L.DIV, float(n_global), m_all)            # grad_map = sign / N
-        if self.ref_quirks:
-            be.scalar_apply(gmap, L.MUL, float(loss.item()), m_all)     # seed = the loss value
+            loss, gmap = be.mg_l1_loss(out.view(-1), targets.reshape(-1), gb * n_out, 0, True)
+        else:
+            loss, gmap = be.l1_loss(out.view(-1), targets.reshape(-1), 0, True)
+        if self.ref_quirks:                                             # seed = the loss value
+            shp = (gmap.numel(),)
+            mg_ = Meta.contiguous(shp)
+            be.broadcast((gmap, mg_), (loss, Meta(shp, (0,), 0)), (gmap, mg_), L.MUL)
         up = gmap.view(b, n_out)
         for li in reversed(range(n_layers)):
             fo = self.sizes[li + 1]
@@ -113,14 +127,14 @@ class DenseMlp:
             torch.matmul(a_in.t(), up, out=self.grad_weight(li))        # dW = x^T . U   (cuBLAS)
             gb_view = self.grad_bias(li).view(-1)
             if self.ref_quirks:
-                rank = dist.get_rank() if dist.is_initialized() else 0
                 if rank == 0:
-                    gb_view.copy_(up[0])                                # row 0 of the upstream
+                    gb_view.copy_(up[0])                                # row 0 of the (global) upstream
                 else:
                     gb_view.zero_()
             else:
-                red, _ = be.reduce_to_shape(up.reshape(-1), (b, fo), (0, 1))
-                gb_view.copy_(red[:fo])
+                be.reduce_to_shape(up.reshape(-1), (b, fo), (0, 1), out=gb_view)
+            if world > 1:                                               # this layer's bucket, overlapped
+                be.mg_allreduce(self.layer_bucket(li), L.SUM, overlap=True)
             if li > 0:
                 dh = torch.matmul(up, self.weight(li).t())              # dx = U . W^T   (cuBLAS)
                 fi = self.sizes[li]
@@ -128,27 +142,24 @@ class DenseMlp:
                 be.broadcast((dh.view(-1), mm), (masks[li - 1].view(-1), mm), (dh.view(-1), mm), L.MUL)
                 up = dh
         if world > 1:
-            dist.all_reduce(self.grads, op=dist.ReduceOp.SUM)           # one flat bucket
+            be.mg_allreduce_join()
         be.sgd_update(self.params, self.grads, self.lr)
         return loss
 
-
     # ------------------------------------------------------------------------------------------
     def step_graphed(self, images_u8: torch.Tensor, targets: torch.Tensor, global_batch: Optional[int] = None):
-        """The same step replayed from a CUDA graph: about thirty launches (library kernels and
-        cuBLAS GEMMs) become one graph launch.  The first call for a batch shape runs the step eagerly
-        (that sizes the library's workspace and allocator cache) and records the graph; later calls
-        copy the inputs into the graph's static buffers and replay it.  Single-GPU, intended-semantics
-        mode only -- with several ranks or the reference-quirks seed (which reads the loss back to the
-        host) it falls through to step()."""
-        world = dist.get_world_size() if dist.is_initialized() else 1
-        if world > 1 or self.ref_quirks:
-            return self.step(images_u8, targets, global_batch)
+        """The same step replayed from a CUDA graph: about thirty launches (library kernels, cuBLAS
+        GEMMs and, with several ranks, the peer exchange and the NCCL all-reduces) become one graph
+        launch.  The first call for a batch shape runs the step eagerly (that sizes the library's
+        workspace and allocator cache) and records the graph; later calls copy the inputs into the
+        graph's static buffers and replay it.  The graph is recorded again when the library reports
+        that device memory it may hold has moved (rtb_ctx_workspace_generation)."""
+        be = self.be
         key = (tuple(images_u8.shape), tuple(targets.shape), global_batch)
-        if getattr(self, "_graph_key", None) != key:
+        gen = int(lib().rtb_ctx_workspace_generation(be._ctx))
+        if getattr(self, "_graph_key", None) != key or getattr(self, "_graph_gen", None) != gen:
             loss = self.step(images_u8, targets, global_batch)
             self._g_img, self._g_tgt = images_u8.clone(), targets.clone()
-            be = self.be
             cur = torch.cuda.current_stream(be.device)
             side = torch.cuda.Stream(device=f"cuda:{be.device}")
             side.wait_stream(cur)
@@ -160,6 +171,8 @@ class DenseMlp:
             cur.wait_stream(side)
             be.sync_stream()
             self._graph, self._graph_key = graph, key
+            self._graph_gen = int(lib().rtb_ctx_workspace_generation(be._ctx))
+            # the capture ran no kernel: the eager step above is this call's step
             return loss
         self._g_img.copy_(images_u8, non_blocking=True)
         self._g_tgt.copy_(targets, non_blocking=True)
@@ -175,3 +188,28 @@ def synthetic_batch(batch: int, device: str, seed: int = 0x5EED + 50, rank: int 
     tgt = np.zeros((batch, 10), dtype=np.float32)
     tgt[np.arange(batch), lab] = 1.0
     return torch.from_numpy(img).to(device), torch.from_numpy(tgt).to(device), img, tgt
+
+
+def tape_step(be: CudaB200, params, images_u8: torch.Tensor, targets: torch.Tensor, lr: float, ref_quirks: bool):
+    """The same SGD step written the way a user of the reference writes it -- tensors, operators,
+    `grad.enabled`, `ctx.backwards(loss)`, `SGD.step` (examples/mnist/src/main.rs:17-46) -- on the
+    tape of rtensors_b200.grad.  params: [W1, b1, W2, b2, ...] as Tensors, updated in place.
+    -> loss Tensor (rank 0)."""
+    from . import grad
+    from .tensor import Tensor, mean_l1_loss_tracked
+    b = images_u8.shape[0]
+    with grad.enabled(ref_quirks=ref_quirks) as ctx:
+        opt = grad.SGD(lr)
+        opt.register_parameters(params)
+        x = Tensor(be, be.u8_to_f32_div(images_u8.reshape(-1), 255.0), Meta.contiguous((b, images_u8.shape[1])))
+        t = Tensor(be, targets.reshape(-1), Meta.contiguous(tuple(targets.shape)))
+        h = x
+        n_layers = len(params) // 2
+        for li in range(n_layers):
+            h = h.matmul(params[2 * li]) + params[2 * li + 1]
+            if li != n_layers - 1:
+                h = h.relu()
+        loss = mean_l1_loss_tracked(h, t)
+        ctx.backwards(loss)
+        opt.step()
+    return loss

@@ -9,6 +9,8 @@ s*(rows*cols + cols); relu with mask 3*s*n; SGD update 3*s*n.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -57,17 +59,24 @@ def _time(fn, reps=10, rounds=5, warm=3, flush=False, dev=None):
     return float(np.median(ts)), float(np.min(ts))
 
 
+def _sig(x, n=4):
+    if not isinstance(x, float) or x == 0 or not math.isfinite(x):
+        return x
+    return round(x, n - 1 - int(math.floor(math.log10(abs(x)))))
+
+
 def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False):
+    """-> rows {op, shape, ms, gbs, frac (of the measured copy peak), bytes [, l2: "flushed"] [, note]};
+    elements/s = elements of `shape` / ms."""
     dev = f"cuda:{be.device}"
     rows = []
 
     def add(name, shape, nbytes, elems, fn, flush=False, note=None):
         med, best = _time(fn, flush=flush, dev=dev)
         gbs = nbytes / (med * 1e-3) / 1e9
-        row = {"op": name, "shape": shape, "ms": med, "ms_best": best, "gbs": gbs, "elements_per_s": elems / (med * 1e-3),
-               "frac": gbs / peak_gbs, "bytes": nbytes}
+        row = {"op": name, "shape": shape, "ms": _sig(med), "gbs": _sig(gbs), "frac": _sig(gbs / peak_gbs), "bytes": nbytes}
         if flush:
-            row["l2"] = "flushed between iterations (working set could sit in L2)"
+            row["l2"] = "flushed"
         if note:
             row["note"] = note
         rows.append(row)
@@ -106,6 +115,15 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     io = torch.empty_like(ia)
     add("tensor_add i32", f"2^{int(np.log2(n2))}", 12 * n2, n2, lambda: be.broadcast((ia, m2), (ib, m2), (io, m2), L.ADD))
     add("fill f32", f"2^{int(np.log2(n2))}", 4 * n2, n2, lambda: be.fill(x, 1.5, m2), note="pure-write probe")
+
+    def config2_step():
+        be.scalar_apply(x, L.MUL, 3.0, m2)
+        be.scalar_apply(x, L.ADD, 2.0, m2)
+        be.scalar_apply(x, L.SUB, 1.0, m2)
+        be.broadcast((ia, m2), (ib, m2), (io, m2), L.ADD)
+    add("configs[1] step: f32 a*=3; a+=2; a-=1 and i32 a+b", f"2^{int(np.log2(n2))} per tensor", (3 * 8 + 12) * n2, 4 * n2,
+        config2_step, note="four launches back to back")
+    x.uniform_(-1, 1, generator=g)
     del ia, ib, io
     # other element sizes through the same kernels (1-byte and 8-byte lanes of the 128-bit vectors)
     nb = n2 * 4
@@ -217,14 +235,27 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
             lambda: be.apply_reduce_contiguous_flat(src, r0, 0, nflat, L.SUM))
     else:
         import torch.distributed as dist
-        per = nflat // world
+        from . import sharding
+        lo_f, hi_f = sharding.scalar_slab(nflat, world, rank)
 
-        def sharded_sum():
-            be.apply_reduce_contiguous_flat(src, r0, 0, per, L.SUM)
-            dist.all_reduce(r0, op=dist.ReduceOp.SUM)
-        add("sum (full) f32, per-GPU partial + NCCL allreduce", f"2^{int(np.log2(nflat))} over {world} GPUs",
-            4 * nflat + 4, nflat, sharded_sum, note=f"aggregate bytes over all GPUs / this rank's time; frac is of {world} x peak")
-        rows[-1]["frac"] = rows[-1]["gbs"] / (peak_gbs * world)
+        def sharded_sum_nccl():
+            be.apply_reduce_contiguous_flat(src, r0, lo_f, hi_f - lo_f, L.SUM)
+            be.mg_allreduce(r0, L.SUM)
+        for name, fn in (("sum (full) f32, per-GPU partial + peer-memory exchange in the last CTA (rtb_mg_reduce_flat)",
+                          lambda: be.mg_reduce_flat(src, lo_f, hi_f - lo_f, nflat, L.SUM, dst=r0)),
+                         ("sum (full) f32, per-GPU partial + ncclAllReduce of one element", sharded_sum_nccl)):
+            add(name, f"2^{int(np.log2(nflat))} over {world} GPUs", 4 * nflat + 4, nflat, fn,
+                note=f"aggregate bytes / this rank's time; frac is of {world} x peak")
+            rows[-1]["frac"] = _sig(rows[-1]["gbs"] / (peak_gbs * world))
+        one = torch.ones(1, device=dev)
+        t_peer, _ = _time(lambda: be.mg_combine(one, L.MAX), reps=20)
+        t_nccl, _ = _time(lambda: be.mg_allreduce(one, L.MAX), reps=20)
+        vec = torch.ones(8192, device=dev)
+        t_peer_v, _ = _time(lambda: be.mg_combine(vec, L.MAX), reps=20)
+        t_nccl_v, _ = _time(lambda: be.mg_allreduce(vec, L.MAX), reps=20)
+        rows.append({"op": "combine of per-GPU partials alone: peer-memory exchange kernel vs ncclAllReduce", "shape": f"{world} GPUs",
+                     "us_peer_4B": _sig(t_peer * 1e3), "us_nccl_4B": _sig(t_nccl * 1e3), "us_peer_32KiB": _sig(t_peer_v * 1e3),
+                     "us_nccl_32KiB": _sig(t_nccl_v * 1e3), "peer_mapped": bool(be.mg_peer_mapped)})
     nl = (1024 if quick else 4096) ** 2
     ta, tb = src[:nl], src[nl:2 * nl]
     add("mean_l1_loss f32", f"two ({int(nl ** 0.5)},{int(nl ** 0.5)})", 8 * nl + 4, nl,
@@ -241,41 +272,36 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     add("bias add in place f32", "(4096,1024)+=(1,1024)", 4 * (2 * Bt * H + H), Bt * H,
         lambda: be.binary_assign(act, ma, bias, mb, L.ADD), flush=True)
     add("relu + mask f32", "(4096,1024)", 12 * Bt * H, Bt * H, lambda: be.relu_mask(act), flush=True)
+    add("bias add + relu + mask in one pass f32 (rtb_bias_relu_mask)", "(4096,1024)+(1,1024)", 4 * (3 * Bt * H + H), Bt * H,
+        lambda: be.bias_relu_mask(act, bias, Bt, H), flush=True)
     add("reduce_to_shape (bias grad) f32", "(4096,1024)->(1,1024)", 4 * (Bt * H + H), Bt * H,
         lambda: be.reduce_to_shape(act, (Bt, H), (0, 1)), flush=True)
     nw = 784 * 1024 + 1024 * 1024 + 1024 * 10 + 2058
     nw -= nw % 4
     w, gw = src[:nw], src[nw:2 * nw]
     add("sgd_update f32", f"{nw} params", 12 * nw, nw, lambda: be.sgd_update(w, gw, 0.0), flush=True)
-    # ---- multi-GPU (strong scaling of single ops): slab-sharded view broadcast with no collective,
-    # axis sum over the sharded dim with one all-reduce of the partial vector
+    # ---- multi-GPU (strong scaling of single ops): an axis sum whose kept dim is cut needs no exchange;
+    # the same sum with the REDUCED dim cut (data that already lives row-sharded) combines 32 KiB partials
     if world > 1:
         import torch.distributed as dist
         from . import sharding
 
-        def add_sharded(name, shape, nbytes, elems, fn):
-            med, best = _time(fn)
+        def add_sharded(name, shape, nbytes, elems, fn, note=None):
+            med, best = _time(fn, flush=True, dev=dev)
             t = torch.tensor([med], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)  # slowest rank
             med = float(t.item())
             gbs = nbytes / (med * 1e-3) / 1e9
-            rows.append({"op": name, "shape": shape, "ms": med, "ms_best": best, "gbs": gbs,
-                         "elements_per_s": elems / (med * 1e-3), "frac": gbs / (peak_gbs * world), "bytes": nbytes,
-                         "note": f"aggregate over {world} GPUs / slowest rank's time; frac is of {world} x peak"})
-        slab = sharding.binary_slab(Am, Bm, world, rank)
-        sdm = Meta.contiguous(slab.shape)
-        sout = out3[: sdm.size]
-        add_sharded("broadcast_add f32 permuted A, step -1 B, slab-sharded", f"{shape3} over {world} GPUs",
-                    4 * (dm3.size + K * 16 + 65536), dm3.size,
-                    lambda: be.broadcast((bufa, slab.left), (bufb, slab.right), (sout, sdm), L.ADD))
+            rows.append({"op": name, "shape": shape, "ms": _sig(med), "gbs": _sig(gbs), "frac": _sig(gbs / (peak_gbs * world)),
+                         "bytes": nbytes, "l2": "flushed",
+                         "note": (note + "; " if note else "") + f"aggregate over {world} GPUs / slowest rank; frac is of {world} x peak"})
+        for axis in (0, 1):
+            add_sharded(f"sum_at({axis}) f32, kept dim cut by the partitioner, no exchange", f"({S},{S}) over {world} GPUs",
+                        4 * (S * S + S), S * S, (lambda axis=axis: sharding.sharded_reduce_view(be, src, msq, axis, L.SUM, world, rank)))
         lo, hi = sharding.scalar_slab(S, world, rank)
-        part_rows = src[lo * S: hi * S]
-        add_sharded("sum_at(0) f32, rows sharded + all-reduce of the partial vector", f"({S},{S}) over {world} GPUs",
-                    4 * (S * S + S), S * S,
-                    lambda: sharding.sharded_reduce_axis(be, part_rows, 1, hi - lo, S, L.SUM, "r", S))
-        add_sharded("sum_at(1) f32, rows sharded, no collective", f"({S},{S}) over {world} GPUs", 4 * (S * S + S), S * S,
-                    lambda: sharding.sharded_reduce_axis(be, part_rows, hi - lo, S, 1, L.SUM, "outer", S))
-
+        add_sharded("sum_at(0) f32, rows resident per GPU: partial vector + peer-memory combine (rtb_mg_reduce_axis)",
+                    f"({S},{S}) over {world} GPUs", 4 * (S * S + S), S * S,
+                    lambda: be.mg_reduce_axis(src, lo * S, 1, hi - lo, S, S, L.SUM))
     # ---- a launch-bound chain of small calls, eager and replayed from a CUDA graph (config-1 sized
     # pieces: outer-product add, two in-place passes, column sum, row variance, fused add + row sum)
     cr, cc = 512, 1024
@@ -310,27 +336,167 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     cur.wait_stream(side)
     be.sync_stream()
     rows.append({"op": "chain of 6 small calls (2 MiB tensor): eager from Python / replayed from a CUDA graph",
-                 "shape": f"({cr},1)+(1,{cc}), *=, relu, sum_at(0), var_at(1), fused add+sum_at(1)", "ms": med_g, "ms_best": best_g,
-                 "ms_eager": med_e, "note": "same kernels, same results; the graph removes the host cost of six enqueues"})
+                 "shape": f"({cr},1)+(1,{cc}), *=, relu, sum_at(0), var_at(1), fused add+sum_at(1)", "ms": _sig(med_g),
+                 "ms_eager": _sig(med_e), "note": "same kernels, same results; the graph removes the host cost of six enqueues"})
 
     # ---- config 5 as a whole: one SGD step of the 784-1024-1024-10 MLP, global batch 4096 split
     # across the ranks (data parallel: loss all-reduce + one flat gradient bucket all-reduce)
     from .mlp import DenseMlp, synthetic_batch
     torch.backends.cuda.matmul.allow_tf32 = False
-    model = DenseMlp(be, (784, 1024, 1024, 10), lr=0.01)
+    sizes = (784, 1024, 1024, 10)
+    model = DenseMlp(be, sizes, lr=0.01)
     local_b = 4096 // world
     img, tgt, _, _ = synthetic_batch(local_b, dev, rank=rank)
     med, best = _time(lambda: model.step(img, tgt, 4096), reps=5, rounds=5)
     gemm_flops = 2 * 4096 * (784 * 1024 + 1024 * 1024 + 1024 * 10) * 3 - 2 * 4096 * 784 * 1024
+    # the step's library GEMMs alone (same shapes and operand layouts), and its gradient all-reduces alone
+    xs = [torch.randn(local_b, n, device=dev) for n in sizes]
+
+    def gemms():
+        for li in range(3):
+            torch.matmul(xs[li], model.weight(li))
+            torch.matmul(xs[li].t(), xs[li + 1], out=model.grad_weight(li))
+            if li:
+                torch.matmul(xs[li + 1], model.weight(li).t())
+    t_gemm, _ = _time(gemms, reps=5, rounds=5)
+    t_ar = 0.0
+    if world > 1:
+        def buckets():
+            for li in reversed(range(3)):
+                be.mg_allreduce(model.layer_bucket(li), L.SUM)
+        t_ar, _ = _time(buckets, reps=5, rounds=5)
+    model.step_graphed(img, tgt, 4096)  # eager step + capture (all ranks capture the same sequence)
+    med_g, best_g = _time(lambda: model.step_graphed(img, tgt, 4096), reps=5, rounds=5)
+    for v in (med, med_g, t_gemm, t_ar):
+        pass
+    if world > 1:
+        import torch.distributed as dist
+        tt = torch.tensor([med, med_g, t_gemm, t_ar], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        med, med_g, t_gemm, t_ar = [float(v) for v in tt.tolist()]
     rows.append({"op": "MLP SGD step 784-1024-1024-10 (GEMMs on cuBLAS, rest on this library)",
-                 "shape": f"global batch 4096, {local_b} per GPU x {world}", "ms": med, "ms_best": best,
-                 "samples_per_s": 4096 / (med * 1e-3), "gemm_tflops": gemm_flops / (med * 1e-3) / 1e12,
-                 "note": "whole step incl. cuBLAS GEMMs and, at N>1, two NCCL all-reduces (loss, 7.45 MB gradient bucket)"})
-    if world == 1:
-        model.step_graphed(img, tgt, 4096)  # eager step + capture
-        med_g, best_g = _time(lambda: model.step_graphed(img, tgt, 4096), reps=5, rounds=5)
-        rows.append({"op": "MLP SGD step, replayed from a CUDA graph", "shape": "global batch 4096, 1 GPU", "ms": med_g,
-                     "ms_best": best_g, "samples_per_s": 4096 / (med_g * 1e-3), "gemm_tflops": gemm_flops / (med_g * 1e-3) / 1e12,
-                     "note": "same kernels as the row above, one graph launch per step"})
+                 "shape": f"global batch 4096, {local_b} per GPU x {world}", "ms": _sig(med), "ms_graph": _sig(med_g),
+                 "ms_gemms_alone": _sig(t_gemm), "ms_allreduce_alone": _sig(t_ar),
+                 "ms_rest": _sig(max(med_g - t_gemm, 0.0)), "samples_per_s": _sig(4096 / (med_g * 1e-3)),
+                 "gemm_tflops": _sig(gemm_flops / world / (t_gemm * 1e-3) / 1e12),
+                 "note": "ms = eager from Python, ms_graph = one CUDA-graph launch per step (collectives captured); ms_rest = ms_graph - "
+                         "GEMMs alone = this library's kernels plus whatever of the gradient all-reduces (three per-layer buckets on a "
+                         "side stream) is not hidden behind the backward GEMMs"})
     torch.cuda.synchronize()
     return rows
+
+
+def small_case(be, which: str, arg=None):
+    """Small cases of the hot-path kernels for profiling (a few hundred MB -- larger than L2 -- and a
+    handful of launches, so that an `ncu` capture ends by itself in a minute or two).  Run as
+    `python bench.py --case NAME [--case-arg K]`:
+      flat       the config-2 chain (f32 a*=3; a+=2; a-=1 and i32 a+b) on 2^K elements per tensor (default 26), 5 times
+      c3         strided / negative-step broadcast add with K rows in dim 2 (default 64), 4 launches
+      red        axis sums of (8192,8192) over both axes and of (16,4096,1024) over axis 1, 3 launches each
+      ext        variance / logsumexp / L2 norm / argmax of (8192,8192) over both axes, twice each
+      convert    dtype conversion of 2^26 elements: f32->f64, f32->i32, u8->f32, f32->u8, twice each
+      transpose  contiguous() of a transposed (8192,8192) f32 matrix and a.T + b, twice each
+      l1         mean_l1_loss of two (4096,4096) without and with the gradient map, 3 times, L2 flushed between
+      mid        mid-size ops (L1 loss, config-1 add and fused add+sum, bias add, reduce-to-shape) with L2 flushes
+      mlp        the fused bias+relu+mask kernel, reduce-to-shape and SGD update at MLP sizes, L2 flushed between"""
+    dev = f"cuda:{be.device}"
+    f32 = torch.float32
+    if which == "flat":
+        n = 1 << (arg or 26)
+        x = torch.rand(n, device=dev) * 2 - 1
+        ia = torch.randint(-(1 << 20), 1 << 20, (n,), device=dev, dtype=torch.int32)
+        ib = torch.randint(-(1 << 20), 1 << 20, (n,), device=dev, dtype=torch.int32)
+        io = torch.empty_like(ia)
+        m = Meta.contiguous((n,))
+        for _ in range(5):
+            be.scalar_apply(x, L.MUL, 3.0, m)
+            be.scalar_apply(x, L.ADD, 2.0, m)
+            be.scalar_apply(x, L.SUB, 1.0, m)
+            be.broadcast((ia, m), (ib, m), (io, m), L.ADD)
+    elif which == "c3":
+        K = arg or 64
+        bufa = torch.rand(K * 16, device=dev) * 2 - 1
+        bufb = torch.rand(64 * 1024, device=dev) * 2 - 1
+        Am = Meta.contiguous((K, 16, 1, 1)).view_as((1, K, 16, 1)).permute((2, 0, 1, 3))
+        Bm = Meta.contiguous((1, 64, 1, 1024)).slice(3, None, None, -1)
+        shape, sa, sb = broadcast_params(Am, Bm)
+        dm = Meta.contiguous(shape)
+        out = be.alloc(dm.size, f32)
+        for _ in range(4):
+            be.broadcast((bufa, Meta(shape, sa, Am.offset)), (bufb, Meta(shape, sb, Bm.offset)), (out, dm), L.ADD)
+    elif which == "red":
+        S = 8192
+        src = torch.randn(S * S, device=dev)
+        m = Meta.contiguous((S, S))
+        r1 = be.alloc(S, f32)
+        for _ in range(3):
+            be.apply_reduce((src, m), r1, 0, L.SUM)
+            be.apply_reduce((src, m), r1, 1, L.SUM)
+        m3 = Meta.contiguous((16, 4096, 1024))
+        r3 = be.alloc(16 * 1024, f32)
+        for _ in range(3):
+            be.apply_reduce((src, m3), r3, 1, L.SUM)
+    elif which == "ext":
+        S = 8192
+        src = torch.randn(S * S, device=dev)
+        m = Meta.contiguous((S, S))
+        r1, ri = be.alloc(S, f32), be.alloc(S, torch.int64)
+        for op, out in ((L.VARIANCE, r1), (L.LOGSUMEXP, r1), (L.NORM, r1), (L.ARGMAX, ri)):
+            for axis in (0, 1):
+                for _ in range(2):
+                    be.apply_reduce_ex((src, m), out, axis, op, True, False, 2)
+    elif which == "convert":
+        n = 1 << 26
+        x = torch.randn(n, device=dev) * 100
+        u = torch.randint(0, 255, (n,), device=dev, dtype=torch.uint8)
+        o64, o32, o8 = be.alloc(n, torch.float64), be.alloc(n, torch.int32), be.alloc(n, torch.uint8)
+        for _ in range(2):
+            be.convert(x, torch.float64, out=o64)
+            be.convert(x, torch.int32, out=o32)
+            be.convert(u, f32, out=x)
+            be.convert(x, torch.uint8, out=o8)
+    elif which == "transpose":
+        S = 8192
+        a, b = torch.randn(S * S, device=dev), torch.randn(S * S, device=dev)
+        out = be.alloc(S * S, f32)
+        m = Meta.contiguous((S, S))
+        for _ in range(2):
+            be.contiguous(a, m.permute((1, 0)))
+            be.broadcast((a, m.permute((1, 0))), (b, m), (out, m), L.ADD)
+    elif which in ("l1", "mid", "mlp"):
+        n = 4096 * 4096
+        src = torch.randn(2 * n, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        A, B = torch.rand(4096, device=dev), torch.rand(4096, device=dev)
+        am, bm = Meta.contiguous((4096, 1)), Meta.contiguous((1, 4096))
+        shape, sa, sb = broadcast_params(am, bm)
+        dm = Meta.contiguous(shape)
+        bias = torch.zeros(1024, device=dev)
+        act = src[:4096 * 1024]
+        for _ in range(3):
+            flush.add_(1)
+            be.l1_loss(src[:n], src[n:], 0, False)
+            flush.add_(1)
+            be.l1_loss(src[:n], src[n:], 0, True)
+            if which == "mid":
+                flush.add_(1)
+                be.broadcast((A, Meta(shape, sa, 0)), (B, Meta(shape, sb, 0)), (src[:n], dm), L.ADD)
+                flush.add_(1)
+                be.apply_reduce((src[:n], dm), be.alloc(4096, f32), 1, L.SUM)
+                flush.add_(1)
+                be.broadcast_reduce(A, am, B, bm, L.ADD, 1, L.SUM)
+                flush.add_(1)
+                be.broadcast_reduce(A, am, B, bm, L.ADD, 0, L.SUM)
+            if which in ("mid", "mlp"):
+                flush.add_(1)
+                be.binary_assign(act, Meta.contiguous((4096, 1024)), bias, Meta.contiguous((1, 1024)), L.ADD)
+                flush.add_(1)
+                be.bias_relu_mask(act, bias, 4096, 1024)
+                flush.add_(1)
+                be.reduce_to_shape(act, (4096, 1024), (0, 1))
+                flush.add_(1)
+                be.sgd_update(src[:1 << 21], src[1 << 21: 1 << 22], 0.0)
+    else:
+        raise SystemExit(f"unknown case {which!r}")
+    torch.cuda.synchronize()
+    print(f"case {which}: {be.launches} launches, done")

@@ -1,15 +1,18 @@
 """Multi-GPU layer (new: the reference is single-device, `Cuda::new()` -> device 0,
 src/backend/cuda.rs:155-162, 815-818).  One process per GPU; the path shards by outer-dimension
-slabs with NO data-path collective for elementwise / broadcast work.  A collective appears only
-where the path has a real exchange: a reduction over the sharded dim combines per-GPU partials with
-one all-reduce (NCCL over NVLink on GPUs, gloo in the CPU tests).
+slabs with NO data-path collective for elementwise / broadcast work.  Ranks exchange data only where
+the path has a real exchange: a reduction over the cut dim combines per-GPU partials.
 
-Everything here is host logic over an `engine` with the Backend-mirror methods (`broadcast`,
-`apply_reduce_contiguous_flat`, `reduce_axis_ori`, `l1_loss`, `alloc`), so the slab arithmetic is
-testable on CPU with any engine that implements them.
+This module is a binding over the library's `rtb_mg_*` entry points: the partition arithmetic
+(`rtb_mg_slab`, `rtb_mg_pick_reduce_dim`, `rtb_shard_range`) is host-only C and runs without a GPU;
+with an engine that owns a communicator (`CudaB200.mg_init`) the combines run inside the library --
+fused peer-memory exchange for small results, NCCL for large buffers.  An engine without one (the
+CPU engine of the gloo tests) combines through `torch.distributed`, so the same host logic is
+testable on CPU.
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -18,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib as L
+from ._lib import diffs, lib, sizes
 from .meta import Meta, broadcast_params, shard_range
 
 
@@ -27,12 +31,32 @@ def world_info() -> Tuple[int, int]:
     return 1, 0
 
 
+def init_communicator(be) -> None:
+    """Gives the engine's library context its communicator (collective over torch.distributed's
+    default group, which only carries the 128-byte id from rank 0 to the others)."""
+    world, rank = world_info()
+    if world == 1 or getattr(be, "mg_world", 1) == world:
+        return
+    box = [be.mg_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    be.mg_init(world, rank, box[0])
+
+
+def _in_library(engine) -> bool:
+    return getattr(engine, "mg_world", 1) > 1
+
+
 def pick_shard_dim(shape, parts: int) -> Optional[int]:
     """Outermost dim with extent >= parts (the slab dim), or None if the tensor is too small."""
-    for k, n in enumerate(shape):
-        if n >= parts:
-            return k
-    return None
+    d = lib().rtb_shard_pick_dim(C.c_size_t(len(shape)), sizes(shape), C.c_size_t(parts))
+    return None if d < 0 else d
+
+
+def pick_reduce_dim(shape, axis: int, parts: int) -> Optional[int]:
+    """Dim to cut for a reduction over `axis`: a kept dim when one is wide enough (no exchange), else
+    the reduced dim, else None."""
+    d = lib().rtb_mg_pick_reduce_dim(C.c_size_t(len(shape)), sizes(shape), C.c_size_t(axis), C.c_size_t(parts))
+    return None if d < 0 else d
 
 
 @dataclass(frozen=True)
@@ -50,19 +74,18 @@ class BinarySlab:
 
 def binary_slab(am: Meta, bm: Meta, world: int, rank: int) -> BinarySlab:
     shape, sa, sb = broadcast_params(am, bm)
-    dim = pick_shard_dim(shape, world) if world > 1 else None
-    if dim is None:
-        # not shardable (or single rank): rank 0 owns everything, the others an empty slab on dim 0
-        if world > 1 and rank > 0:
-            eshape = (0,) + tuple(shape[1:]) if shape else (0,)
-            return BinarySlab(tuple(shape), None, 0, 0, eshape, Meta(eshape, sa if shape else (0,), am.offset),
-                              Meta(eshape, sb if shape else (0,), bm.offset))
-        return BinarySlab(tuple(shape), None, 0, shape[0] if shape else 1, tuple(shape), Meta(shape, sa, am.offset),
-                          Meta(shape, sb, bm.offset))
-    b, e = shard_range(shape[dim], world, rank)
-    sshape = tuple(e - b if k == dim else n for k, n in enumerate(shape))
-    return BinarySlab(tuple(shape), dim, b, e, sshape, Meta(sshape, sa, am.offset + b * sa[dim]),
-                      Meta(sshape, sb, bm.offset + b * sb[dim]))
+    r = len(shape)
+    if r == 0:
+        sa, sb = (0,), (0,)
+    osh = (C.c_size_t * max(r, 1))()
+    b, e, ol, orr = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+    dim = lib().rtb_mg_slab(C.c_size_t(r), sizes(shape), diffs(sa), C.c_size_t(am.offset), diffs(sb), C.c_size_t(bm.offset),
+                            C.c_size_t(world), C.c_size_t(rank), osh, C.byref(b), C.byref(e), C.byref(ol), C.byref(orr))
+    sshape = tuple(osh[:r]) if r else ((0,) if e.value == 0 else ())
+    if r == 0 and e.value == 0:
+        return BinarySlab((), None, 0, 0, (0,), Meta((0,), (0,), am.offset), Meta((0,), (0,), bm.offset))
+    return BinarySlab(tuple(shape), None if dim < 0 else dim, b.value, e.value, sshape,
+                      Meta(sshape, tuple(sa[:r]), ol.value), Meta(sshape, tuple(sb[:r]), orr.value))
 
 
 def sharded_binary(engine, a, am: Meta, b, bm: Meta, op: int, world: Optional[int] = None, rank: Optional[int] = None):
@@ -105,6 +128,8 @@ def sharded_reduce_flat(engine, local, local_len: int, global_len: int, op: int,
     """Full reduction of a tensor whose flat range is split across ranks: per-GPU partial (one
     launch) + one all-reduce of a single element.  `local` holds this rank's elements."""
     world, _ = world_info()
+    if _in_library(engine):   # one launch: local reduction + peer exchange in its last CTA
+        return engine.mg_reduce_flat(local, 0, local_len, global_len, op)
     part = engine.alloc(1, local.dtype)
     engine.apply_reduce_contiguous_flat(local, part, 0, local_len, L.SUM if op == L.MEAN else op)
     t = _as_torch(part)
@@ -121,6 +146,8 @@ def sharded_reduce_axis(engine, local, outer: int, r: int, inner: int, op: int, 
     world, _ = world_info()
     if sharded == "outer" or world == 1:
         return _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, op))
+    if _in_library(engine):
+        return engine.mg_reduce_axis(local, 0, outer, r, inner, global_r, op)
     part = _as_torch(engine.reduce_axis_ori(local, 0, outer, r, inner, L.SUM if op == L.MEAN else op))
     _all_reduce(part, _RED[op], group)
     return finish_mean(part, global_r) if op == L.MEAN else part
@@ -186,8 +213,33 @@ def sharded_reduce_ex(engine, local, outer: int, r: int, inner: int, op: int, sh
 def sharded_mean_l1_loss(engine, a_local, b_local, global_n: int, group=None):
     """mean(|a-b|) over tensors split across ranks: local sum of |a-b| -> all-reduce -> / (T)(float)N."""
     world, _ = world_info()
+    if _in_library(engine):
+        return engine.mg_l1_loss(a_local, b_local, global_n, 0, False)[0]
     loss, _ = engine.l1_loss(a_local, b_local, 1, False)  # reduction 1 = sum
     t = _as_torch(loss)
     if world > 1:
         _all_reduce(t, "sum", group)
     return finish_mean(t, global_n)
+
+
+def sharded_reduce_view(engine, buf, meta: Meta, axis: int, op: int, world: Optional[int] = None, rank: Optional[int] = None):
+    """`t.<op>_at(axis)` of a GLOBAL tensor every rank can address (buf, meta), each rank computing its
+    share.  A kept dim with extent >= world is cut when there is one: the rank reduces its slab view in
+    place (a strided window for an inner dim) and owns the outputs [begin, end) along that dim -- no
+    exchange at all.  Otherwise the reduced dim is cut and the partial results are combined, every
+    rank ending with the full result.  -> (result, cut dim or None, begin, end)"""
+    if world is None:
+        world, rank = world_info()
+    dim = pick_reduce_dim(meta.shape, axis, world) if world > 1 else None
+    if dim is None:
+        return _as_torch(engine.reduce_view(buf, meta, axis, op)), None, 0, meta.shape[axis] if meta.shape else 1
+    b, e = shard_range(meta.shape[dim], world, rank)
+    slab = meta.slice(dim, b, e, 1)
+    if dim != axis:
+        return _as_torch(engine.reduce_view(buf, slab, axis, op)), dim, b, e
+    part = _as_torch(engine.reduce_view(buf, slab, axis, L.SUM if op == L.MEAN else op))
+    if _in_library(engine):
+        engine.mg_combine(part, op, meta.shape[axis])
+        return part, dim, b, e
+    _all_reduce(part, _RED[op])
+    return (finish_mean(part, meta.shape[axis]) if op == L.MEAN else part), dim, b, e

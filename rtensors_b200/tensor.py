@@ -13,6 +13,7 @@ import numpy as np
 import torch
 
 from . import _lib as L
+from . import grad as _grad
 from .backend import CODE_TO_NP, CudaB200, dtype_code
 from .meta import Meta
 
@@ -36,6 +37,17 @@ def default_backend() -> CudaB200:
 class Tensor:
     def __init__(self, backend: CudaB200, buf: torch.Tensor, meta: Meta):
         self.backend, self.buf, self.meta = backend, buf, meta
+        self.op = None      # key of the tape node that produced this tensor (rtensors_b200.grad)
+        self.grad = None    # GradHolder of a leaf (set by param())
+
+    @property
+    def np_dtype(self):
+        return CODE_TO_NP[dtype_code(self.buf)]
+
+    def param(self) -> "Tensor":
+        """Marks the tensor as a trainable leaf of the current grad context (TensorBase::param)."""
+        _grad.make_leaf(self)
+        return self
 
     # ---- constructors -----------------------------------------------------------------------
     @staticmethod
@@ -86,7 +98,12 @@ class Tensor:
     def is_contiguous(self): return self.meta.is_contiguous()
 
     def _view(self, meta: Meta) -> "Tensor": return Tensor(self.backend, self.buf, meta)
-    def view(self): return self._view(self.meta)
+
+    def view(self):
+        v = self._view(self.meta)
+        v.op, v.grad = self.op, self.grad
+        return v
+
     def slice(self, dim, start=None, end=None, step=1): return self._view(self.meta.slice(dim, start, end, step))
     def index(self, dim, i): return self._view(self.meta.index(dim, i))
     def permute(self, dims): return self._view(self.meta.permute(dims))
@@ -133,10 +150,32 @@ class Tensor:
     def _binary(self, other, op: int) -> "Tensor":
         if isinstance(other, Tensor):
             out, dm = self.backend.binary(self.buf, self.meta, other.buf, other.meta, op)
-            return Tensor(self.backend, out, dm)
+            res = Tensor(self.backend, out, dm)
+            if op in _BROADCAST_NODE:
+                _grad.attach_broadcast(_BROADCAST_NODE[op], res, self, other)
+            return res
         t = self.owned()
         t.backend.scalar_apply(t.buf, op, other, t.meta)
+        if op == L.ADD or op == L.SUB:
+            _grad.attach_unary("AddScalar", t, self)
+        elif op == L.MUL:
+            _grad.attach_unary("MulScalar", t, self, scalar=other)
         return t
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        """2-D matrix product on cuBLAS (matmul stays a library GEMM by design; the reference calls
+        cuBLAS too, src/backend/cuda.rs:2139-2280).  Operands may be transposed / strided views."""
+        if self.rank != 2 or other.rank != 2 or self.shape[1] != other.shape[0]:
+            raise ValueError(f"matmul needs (m,k) x (k,n), got {self.shape} x {other.shape}")
+
+        def as_torch(t):
+            if any(st < 0 for st in t.strides):
+                t = t.contiguous()
+            return torch.as_strided(t.buf, t.shape, t.strides, t.offset)
+        out = torch.matmul(as_torch(self), as_torch(other))
+        res = Tensor(self.backend, out.reshape(-1), Meta.contiguous((self.shape[0], other.shape[1])))
+        _grad.attach_matmul(res, self, other)
+        return res
 
     def _assign(self, other, op: int) -> "Tensor":
         if isinstance(other, Tensor):
@@ -163,10 +202,20 @@ class Tensor:
     def abs_inplace(self): return self._unary_inplace(L.ABS)
     def sign_inplace(self): return self._unary_inplace(L.SIGN)
     def neg_inplace(self): return self._unary_inplace(L.NEG)
-    def relu(self): return self.owned().relu_inplace()
+    def relu(self):
+        out = self.owned().relu_inplace()
+        if _grad.is_enabled():   # the map of the pre-activation, one kernel (the reference: a get/set loop)
+            _grad.attach_unary("ReLU", out, self, grad_map=self.relu_grad_map())
+        return out
+
     def abs(self): return self.owned().abs_inplace()
     def sign(self): return self.owned().sign_inplace()
-    def neg(self): return self.owned().neg_inplace()
+
+    def neg(self):
+        out = self.owned().neg_inplace()
+        _grad.attach_unary("Negate", out, self)
+        return out
+
     def __neg__(self): return self.neg()
 
     # gradient maps the reference's autograd stores for relu and abs (src/ops/unary/mod.rs:213-252)
@@ -248,3 +297,16 @@ def mean_l1_loss(a: Tensor, b: Tensor, with_grad: bool = False):
     if with_grad:
         return lt, Tensor(a.backend, g, Meta.contiguous(a.shape))
     return lt
+
+
+_BROADCAST_NODE = {L.ADD: "BroadcastAdd", L.SUB: "BroadcastSub", L.MUL: "BroadcastMul"}
+
+
+def mean_l1_loss_tracked(a: Tensor, b: Tensor) -> Tensor:
+    """mean_l1_loss under a grad context: the loss and the gradient map sign(a - b) / N come out of one
+    fused kernel and an L1 node goes on the tape (attach_l1_grad, src/ops/broadcast/l1.rs:16-46)."""
+    if not _grad.is_enabled():
+        return mean_l1_loss(a, b)
+    loss, gmap = mean_l1_loss(a, b, with_grad=True)
+    _grad.attach_l1(loss, a, b, gmap)
+    return loss

@@ -40,6 +40,14 @@ class OracleBackendMirror:
     def l1_loss(self, a, b, reduction, with_grad):
         return O.l1_loss(a, b, reduction, with_grad)
 
+    def reduce_view(self, src, meta, axis, op):
+        """What the reference does for a non-contiguous tensor: copy the view row-major, then reduce."""
+        from golden_runner import gather_view
+        dense = gather_view(src, meta)
+        if axis is None:
+            return O.reduce_flat(dense, 0, dense.size, op)
+        return O.reduce_axis(dense, O.Meta.contiguous(meta.shape), axis, op)[0]
+
     def reduce_ext_ori(self, src, offset, outer, r, inner, op, unbiased=True, is_std=False, norm_type=2):
         blk = np.ascontiguousarray(src[offset:offset + outer * r * inner])
         if op in (O.ARGMAX, O.ARGMIN):
@@ -122,6 +130,20 @@ def _worker(rank, world, port, out_dir):
             want = O.argreduce_ori(z.reshape(-1), 3, 50, 8, op).astype(np.int64)
             assert np.array_equal(got, want), (op, got, want)
         assert sharding.sharded_reduce_ex(eng, local, 3, hi - lo, 8, L.ARGMAX, "r", 50, lo).numpy().reshape(3, 8)[1, 3] == 7
+        # 4c. the partitioner prefers a kept dim: sum_at(0) of a matrix cuts the COLUMNS (each rank reduces a
+        # strided window and owns its outputs, no exchange); only a tensor with no wide kept dim cuts the
+        # reduced dim and combines
+        mat = rng.standard_normal((30, 12)).astype(np.float32)
+        mm = Meta.contiguous((30, 12))
+        for axis in (0, 1):
+            got, dim, b, e = sharding.sharded_reduce_view(eng, mat.reshape(-1), mm, axis, L.SUM)
+            assert dim == 1 - axis and (b, e) == sharding.scalar_slab(mat.shape[dim], world, rank)
+            want = mat.sum(axis=axis, dtype=np.float64)[b:e]
+            assert np.allclose(got.numpy().reshape(-1), want, rtol=1e-5, atol=1e-5)
+        tall = rng.standard_normal((40, 1)).astype(np.float32)
+        for op, ref in ((L.SUM, tall.sum(dtype=np.float64)), (L.MEAN, tall.mean(dtype=np.float64)), (L.MAX, tall.max())):
+            got, dim, b, e = sharding.sharded_reduce_view(eng, tall.reshape(-1), Meta.contiguous((40, 1)), 0, op)
+            assert dim == 0 and abs(float(got.numpy().reshape(-1)[0]) - float(ref)) <= 1e-5 * 40
         # 5. mean_l1_loss over sharded tensors
         p, q = rng.standard_normal(4000).astype(np.float32), rng.standard_normal(4000).astype(np.float32)
         lo, hi = sharding.scalar_slab(4000, world, rank)
@@ -148,6 +170,9 @@ def test_binary_slab_covers_output_exactly():
             assert s0.end == s1.begin
         for s in slabs:
             assert s.left.offset == s.begin and s.right.offset == 0  # left sliced, right replicated
+    assert sharding.pick_reduce_dim((8192, 8192), 0, 8) == 1 and sharding.pick_reduce_dim((8192, 8192), 1, 8) == 0
+    assert sharding.pick_reduce_dim((64, 4096, 1024), 1, 8) == 0 and sharding.pick_reduce_dim((4, 4096, 2), 1, 8) == 1
+    assert sharding.pick_reduce_dim((4, 4, 2), 1, 8) is None
     # too small to shard: rank 0 owns everything
     s0 = sharding.binary_slab(Meta.contiguous((3,)), Meta.contiguous((3,)), 8, 0)
     s1 = sharding.binary_slab(Meta.contiguous((3,)), Meta.contiguous((3,)), 8, 5)
