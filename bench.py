@@ -523,10 +523,10 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     h_a = torch.from_numpy(d["bufa_h"]).pin_memory()
     h_b = torch.from_numpy(d["bufb_h"]).pin_memory()
     Mfull = d["Mx"].view(sh.m)
-    h_m0 = Mfull[:, m0b:m0e].contiguous().cpu().pin_memory() if world > 1 else Mfull.cpu().pin_memory()
-    h_m1 = Mfull[m1b:m1e].contiguous().cpu().pin_memory() if world > 1 else None   # N = 1: the same matrix serves both sums
+    h_m0 = (Mfull[:, m0b:m0e] if world > 1 else Mfull).contiguous().reshape(-1).cpu().pin_memory()
+    h_m1 = Mfull[m1b:m1e].contiguous().reshape(-1).cpu().pin_memory() if world > 1 else None   # N = 1: one matrix serves both sums
     Tfull = d["Tx"].view(sh.t)
-    h_t = (Tfull[t1b:t1e] if world > 1 else Tfull).contiguous().cpu().pin_memory()
+    h_t = (Tfull[t1b:t1e] if world > 1 else Tfull).contiguous().reshape(-1).cpu().pin_memory()
     h_f = d["Fx"][flo:fhi].cpu().pin_memory()
     h_out = torch.empty(n_slabs * per, dtype=torch.float32).pin_memory()
     r_m0, r_m1, r_t1, r_f = d["outs"]

@@ -15,14 +15,15 @@ int use_device(Ctx *ctx) {
     return RTB_OK;
 }
 
-static bool capturing(Ctx *ctx) {
+static bool stream_capturing(cudaStream_t stream) {
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess) {
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
     return st != cudaStreamCaptureStatusNone;
 }
+static bool capturing(Ctx *ctx) { return stream_capturing(ctx->stream); }
 
 // A superseded workspace is never freed before rtb_ctx_destroy: kernels already enqueued, and CUDA
 // graphs captured earlier, still hold its address.  It moves to ctx->retired instead, and
@@ -132,9 +133,9 @@ RTB_API int rtb_ctx_set_stream(rtb_ctx *c, void *stream) {
     int rc = rtb::use_device(ctx);
     if (rc) return rc;
     if (!ctx->order_event) RTB_CUDA(cudaEventCreateWithFlags(&ctx->order_event, cudaEventDisableTiming));
-    if (!rtb::capturing(ctx)) {
-        // (an old stream that is being captured cannot be joined from outside its graph; the caller
-        // owns the ordering then)
+    if (!rtb::capturing(ctx) && !rtb::stream_capturing(next)) {
+        // (a stream that is being captured cannot be joined with work outside its graph: whoever set
+        // up the capture has ordered the capturing stream after the earlier work)
         RTB_CUDA(cudaEventRecord(ctx->order_event, ctx->stream));
         RTB_CUDA(cudaStreamWaitEvent(next, ctx->order_event, 0));
     }
