@@ -253,6 +253,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of the timed buffers")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--scale-log2", type=int, default=0, help="run the step at 1/2^s of every tensor (small profiling runs)")
     ap.add_argument("--case", default=None, help="run one small profiling case and exit: " + ", ".join(
         ("flat", "c3", "red", "ext", "convert", "transpose", "mid", "l1", "mlp")))
@@ -430,6 +431,29 @@ def main():
         from rtensors_b200 import opbench
         ops = opbench.run(be, peak, world, rank, quick=args.scale_log2 > 0)
 
+    # the reference's own CUDA kernels on the same GPU, beside the rows they correspond to
+    ref_note = None
+    if ops is not None and world == 1 and rank == 0 and not args.no_ref_cuda:
+        rc = ref_cuda_times(dev, args.scale_log2 > 0)
+        if rc is None:
+            ref_note = "baseline/_ref/libref_cuda.so absent (built from the reference checkout by __graft_entry__.build())"
+        else:
+            for row in ops:
+                ms = rc.get((row["op"], row.get("shape")))
+                if ms is not None:
+                    row["ref_cuda_ms"] = sig(ms)
+            for name, key in (("broadcast_add", ("broadcast_add f32 permuted A, step -1 B", str(tuple(sh.c3)))),
+                              ("sum_at(0) matrix", ("sum_at(0) f32", f"({sh.m[0]},{sh.m[1]})")),
+                              ("sum_at(1) matrix", ("sum_at(1) f32", f"({sh.m[0]},{sh.m[1]})")),
+                              ("sum_at(1) cube", ("sum_at(1) f32", str(sh.t))), ("sum (full)", ("sum (full) f32", f"2^{30 - sh.s}"))):
+                if key in rc:
+                    split[name]["ref_cuda_ms"] = sig(rc[key])
+            if all("ref_cuda_ms" in v for v in split.values()):
+                ref_ms = sum(v["ref_cuda_ms"] for v in split.values())
+                ref_note = {"step_ms": sig(ref_ms), "step_gbs": sig(sh.step_bytes() / (ref_ms * 1e-3) / 1e9),
+                            "what": "the reference's own CUDA kernels recompiled for sm_100a with its release flags, kernel time only "
+                                    "(its host-side zero upload and per-call index-array allocations excluded)"}
+
     cpu = None
     if rank == 0 and not args.no_cpu and world == 1:
         reps = 120
@@ -451,13 +475,78 @@ def main():
             "elements_per_s": sig(sh.step_elems() / (ms_step * 1e-3), 5),
             "frac_of_peak": sig(value / world / peak), "peaks": {"measured_copy": peak, "probe_read": PROBE_READ_GBS,
                                                                   "probe_write": PROBE_WRITE_GBS, "nominal": NOMINAL_GBS},
-            "step_ops": split, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "verified": verified,
+            "step_ops": split, "ref_cuda": ref_note, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "verified": verified,
             "gpu_launches": int(launches), "mg_status": mg_status, "clocks": clocks, "ops": ops,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         be.mg_finalize()
         dist.destroy_process_group()
+
+
+def ref_cuda_times(dev: str, quick: bool):
+    """Device time of the REFERENCE's own CUDA kernels (recompiled for sm_100a with its release flags,
+    baseline/_ref/libref_cuda.so) on the ops of configs 1-4, launched the way its Rust host launches
+    them: block 256, index arrays in device memory, legacy default stream.  Kernel time only -- the
+    host-side costs of the reference (zero upload of every output, per-call cudaMalloc of the index
+    arrays) are not included, so this is a lower bound on what the reference spends.
+    -> {(op name, shape string): ms} keyed like the rows of the op table."""
+    import torch
+    from baseline import ref_cuda as R
+    from rtensors_b200 import opbench
+    from rtensors_b200.meta import Meta, broadcast_params
+    if not R.available():
+        return None
+    f32 = torch.float32
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x5EED)
+
+    def t(fn, flush=False):
+        return opbench._time(fn, reps=5, rounds=3, warm=1, flush=flush, dev=dev)[0]
+    # config 1
+    A, B = torch.rand(4096, device=dev, generator=g), torch.rand(4096, device=dev, generator=g)
+    am, bm = Meta.contiguous((4096, 1)), Meta.contiguous((1, 4096))
+    shape, sa, sb = broadcast_params(am, bm)
+    dm = Meta.contiguous(shape)
+    o1 = torch.empty(dm.size, device=dev)
+    out[("broadcast_add f32", "(4096,1)+(1,4096)")] = t(R.Broadcast(A, Meta(shape, sa, 0), B, Meta(shape, sb, 0), o1, dm, R.ADD), True)
+    r1 = torch.empty(8192, device=dev)
+    out[("sum_at(1) f32", "(4096,4096)")] = t(lambda: R.reduce_nd(o1, r1, 0, 4096, 4096, 1, R.SUM), True)
+    del o1
+    # config 2
+    n2 = 1 << (24 if quick else 28)
+    lg = int(math.log2(n2))
+    x = torch.rand(n2, device=dev, generator=g)
+    out[("scalar_mul f32 in place", f"2^{lg}")] = t(lambda: R.scalar_contiguous(x, "mul", 1.0001))
+    ia = torch.randint(-(1 << 20), 1 << 20, (n2,), device=dev, generator=g, dtype=torch.int32)
+    io = torch.empty_like(ia)
+    m2 = Meta.contiguous((n2,))
+    out[("tensor_add i32", f"2^{lg}")] = t(R.Broadcast(ia, m2, ia, m2, io, m2, R.ADD))
+    del ia, io, x
+    # config 3
+    sh = Shapes(4 if quick else 0)
+    bufa = torch.rand(sh.n_a, device=dev, generator=g)
+    bufb = torch.rand(sh.n_b, device=dev, generator=g)
+    Am, Bm = c3_views(Meta, sh)
+    shape3, sa3, sb3 = broadcast_params(Am, Bm)
+    dm3 = Meta.contiguous(shape3)
+    o3 = torch.empty(dm3.size, device=dev)
+    out[("broadcast_add f32 permuted A, step -1 B", str(tuple(shape3)))] = t(
+        R.Broadcast(bufa, Meta(shape3, sa3, Am.offset), bufb, Meta(shape3, sb3, Bm.offset), o3, dm3, R.ADD))
+    # config 4 (o3 re-used as the normal(0,1) source)
+    o3.normal_(generator=g)
+    S = 2048 if quick else 8192
+    rs = torch.empty(64 * 1024, device=dev)
+    out[("sum_at(0) f32", f"({S},{S})")] = t(lambda: R.reduce_nd(o3, rs, 0, 1, S, S, R.SUM), S * S * 4 < (200 << 20))
+    out[("sum_at(1) f32", f"({S},{S})")] = t(lambda: R.reduce_nd(o3, rs, 0, S, S, 1, R.SUM), S * S * 4 < (200 << 20))
+    d3 = (64, 512, 1024) if quick else (64, 4096, 1024)
+    out[("sum_at(1) f32", str(d3))] = t(lambda: R.reduce_nd(o3, rs, 0, d3[0], d3[1], d3[2], R.SUM))
+    nf = dm3.size
+    out[("sum (full) f32", f"2^{int(math.log2(nf))}")] = t(lambda: R.reduce_flat(o3, rs, 0, nf, R.SUM))
+    torch.cuda.synchronize()
+    assert not R.alloc_failed()
+    return out
 
 
 def verify(be, sh, world, rank, d) -> bool:

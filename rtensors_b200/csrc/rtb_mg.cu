@@ -13,6 +13,7 @@
 // loaded), so the library itself has no link dependency on it and single-GPU hosts need no NCCL.
 #include <dlfcn.h>
 #include <nccl.h>
+#include <unistd.h>
 
 #include "rtb_mg.cuh"
 
@@ -75,7 +76,8 @@ struct Mg {
     int nranks = 1, rank = 0;
     uint2 *local = nullptr;                 // this rank's exchange buffer
     uint2 *slots[kMgMaxRanks] = {};         // every rank's buffer as seen from this process
-    bool mapped = false;                    // peers' buffers are mapped (CUDA IPC)
+    bool mapped = false;                    // peers' buffers are mapped (CUDA IPC, or peer access inside one process)
+    bool same_process[kMgMaxRanks] = {};    // slots[p] is a raw pointer of this process: nothing to close
     unsigned int *state = nullptr;          // device: epoch, status, counter, pad
     unsigned long long wait_ns = 2000000000ull;
     cudaStream_t side = nullptr;
@@ -250,7 +252,7 @@ void destroy_mg(Mg *mg) {
     if (!mg) return;
     if (mg->mapped)
         for (int p = 0; p < mg->nranks; ++p)
-            if (p != mg->rank && mg->slots[p]) cudaIpcCloseMemHandle(mg->slots[p]);
+            if (p != mg->rank && mg->slots[p] && !mg->same_process[p]) cudaIpcCloseMemHandle(mg->slots[p]);
     if (mg->comm) g_nccl.CommDestroy(mg->comm);
     if (mg->local) cudaFree(mg->local);
     if (mg->state) cudaFree(mg->state);
@@ -334,15 +336,23 @@ RTB_API int rtb_mg_init(rtb_ctx *c, int nranks, int rank, const void *id_bytes) 
     }
     // Exchange the IPC handles of the buffers with one all-gather, then map every peer's buffer.  Each
     // record carries a flag saying whether the handle could be made; mapping is all or nothing.
+    // A rank in the SAME process (one host thread per device) cannot open an IPC handle of its own
+    // process; there the raw pointer is used directly after enabling peer access to its device.
     struct Record {
         cudaIpcMemHandle_t handle;
         int ok;
-        int pad[15];
+        int device;
+        long long pid;
+        unsigned long long ptr;
+        int pad[10];
     };
     static_assert(sizeof(Record) == 128, "record size");
     Record mine{};
     mine.ok = cudaIpcGetMemHandle(&mine.handle, mg->local) == cudaSuccess ? 1 : 0;
     if (!mine.ok) cudaGetLastError();
+    mine.device = ctx->device;
+    mine.pid = (long long)getpid();
+    mine.ptr = (unsigned long long)(uintptr_t)mg->local;
     Record *dev = nullptr;
     if ((e = cudaMalloc(&dev, sizeof(Record) * (size_t)nranks)) != cudaSuccess) return bail(cuda_fail(e, "cudaMalloc(handles)"));
     std::vector<Record> all((size_t)nranks);
@@ -359,8 +369,24 @@ RTB_API int rtb_mg_init(rtb_ctx *c, int nranks, int rank, const void *id_bytes) 
     if (every) {
         for (int p = 0; p < nranks && every; ++p) {
             if (p == rank) continue;
+            const Record &r = all[(size_t)p];
+            if (r.pid == mine.pid) {
+                int can = 0;
+                if (r.device != ctx->device && cudaDeviceCanAccessPeer(&can, ctx->device, r.device) == cudaSuccess && can) {
+                    cudaError_t pe = cudaDeviceEnablePeerAccess(r.device, 0);
+                    if (pe == cudaSuccess || pe == cudaErrorPeerAccessAlreadyEnabled) {
+                        cudaGetLastError();
+                        mg->slots[p] = reinterpret_cast<uint2 *>((uintptr_t)r.ptr);
+                        mg->same_process[p] = true;
+                        continue;
+                    }
+                }
+                cudaGetLastError();
+                every = false;
+                continue;
+            }
             void *ptr = nullptr;
-            if (cudaIpcOpenMemHandle(&ptr, all[(size_t)p].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            if (cudaIpcOpenMemHandle(&ptr, r.handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
                 cudaGetLastError();
                 every = false;
             } else {
@@ -381,7 +407,7 @@ RTB_API int rtb_mg_init(rtb_ctx *c, int nranks, int rank, const void *id_bytes) 
     if (!mg->mapped) {
         for (int p = 0; p < nranks; ++p)
             if (p != rank && mg->slots[p]) {
-                cudaIpcCloseMemHandle(mg->slots[p]);
+                if (!mg->same_process[p]) cudaIpcCloseMemHandle(mg->slots[p]);
                 mg->slots[p] = nullptr;
             }
     }
@@ -402,7 +428,7 @@ RTB_API int rtb_mg_finalize(rtb_ctx *c) {
         if (mg->mapped) {
             for (int p = 0; p < mg->nranks; ++p)
                 if (p != mg->rank && mg->slots[p]) {
-                    cudaIpcCloseMemHandle(mg->slots[p]);
+                    if (!mg->same_process[p]) cudaIpcCloseMemHandle(mg->slots[p]);
                     mg->slots[p] = nullptr;
                 }
             mg->mapped = false;

@@ -11,11 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIBDIR = os.path.join(ROOT, "rtensors_b200")
 
 
-def _build(tmp_path):
+def _build(tmp_path, name="test_tensor_api"):
     rt.lib()  # the shared library must exist
-    exe = str(tmp_path / "test_tensor_api")
-    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"),
-           os.path.join(ROOT, "tests", "cpp", "test_tensor_api.cpp"), "-o", exe,
+    exe = str(tmp_path / name)
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-pthread", "-I", os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "cpp", name + ".cpp"), "-o", exe,
            "-L", LIBDIR, "-lrt_b200", f"-Wl,-rpath,{LIBDIR}"]
     p = subprocess.run(cmd, capture_output=True, text=True)
     assert p.returncode == 0, p.stderr
@@ -32,3 +32,17 @@ def test_cpp_mirror_reference_tests(tmp_path):
     p = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert p.returncode == 0, p.stdout + p.stderr
     assert "ok:" in p.stdout
+
+
+def test_cpp_multi_gpu_case_compiles_and_links(tmp_path):
+    _build(tmp_path, "test_mg_two_threads")
+
+
+@pytest.mark.gpu
+def test_cpp_two_ranks_in_one_process(tmp_path):
+    """rtb_mg_* from compiled code, one host thread per device (prints "skipped" on a 1-GPU box)."""
+    exe = _build(tmp_path, "test_mg_two_threads")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([exe], capture_output=True, text=True, timeout=180, env=env)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert "ok:" in p.stdout or "skipped" in p.stdout

@@ -1473,7 +1473,10 @@ def test_transposed_and_permuted_operands(dt):
     rng = np.random.default_rng(515 + np.dtype(dt).itemsize)
     be = _b()
     for shape, perm in [((70, 45), (1, 0)), ((33, 64), (1, 0)), ((5, 40, 50), (2, 0, 1)), ((6, 37, 41), (0, 2, 1)),
-                        ((3, 4, 20, 35), (0, 3, 1, 2)), ((17, 130), (1, 0))]:
+                        ((3, 4, 20, 35), (0, 3, 1, 2)), ((17, 130), (1, 0)),
+                        # vector-aligned extents and strides: the 16-byte tile kernel (full, ragged and many tiles)
+                        ((72, 44), (1, 0)), ((260, 300), (1, 0)), ((8, 40, 132), (2, 0, 1)), ((6, 36, 40), (0, 2, 1)),
+                        ((128, 256), (1, 0))]:
         base = O.Meta.contiguous(shape)
         n = base.size
         a, b = _rand(rng, n, dt), _rand(rng, n, dt)
