@@ -18,13 +18,20 @@ from . import _lib as L
 from .meta import Meta, broadcast_params
 
 _FLUSH = None
+_FLUSH_READ = None
 
 
 def _flush_l2(dev):
-    global _FLUSH
+    """Evicts the timed op's data from L2: a 256 MiB buffer is WRITTEN (larger than L2), then a second
+    256 MiB buffer is READ.  The read pass matters: L2 is write-back, so after the write alone about
+    126 MB of dirty lines would be written out during the op that follows, charging it up to ~18 us of
+    DRAM traffic that is not its own.  After the read pass L2 holds clean lines of unrelated data."""
+    global _FLUSH, _FLUSH_READ
     if _FLUSH is None or _FLUSH.device != torch.device(dev):
         _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        _FLUSH_READ = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
     _FLUSH.add_(1)
+    torch.max(_FLUSH_READ)
 
 
 def _span(fn, reps):
@@ -40,8 +47,8 @@ def _span(fn, reps):
 def _time(fn, reps=10, rounds=5, warm=3, flush=False, dev=None):
     """Device time per call in ms: `reps` calls are enqueued back to back between one pair of CUDA
     events, so the host-side enqueue cost of a call is not counted as kernel time.  With
-    flush=True every call is preceded by a write of a 256 MiB buffer (larger than L2) and the
-    time of the same number of flushes alone is subtracted."""
+    flush=True every call is preceded by an L2 flush (_flush_l2: a 256 MiB write, then a 256 MiB read
+    so that no dirty lines are left) and the time of the same number of flushes alone is subtracted."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
