@@ -89,11 +89,20 @@ __device__ __forceinline__ void grid_dep_sync() {
 }
 
 template <typename... KArgs, typename... Args>
+inline void launch_dep_smem(Ctx *ctx, unsigned grid, unsigned block, size_t smem_bytes, void (*kernel)(KArgs...), Args &&...args);
+
+template <typename... KArgs, typename... Args>
 inline void launch_dep(Ctx *ctx, unsigned grid, unsigned block, void (*kernel)(KArgs...), Args &&...args) {
+    launch_dep_smem(ctx, grid, block, 0, kernel, std::forward<Args>(args)...);
+}
+
+// the same with dynamic shared memory (the caller has raised the kernel's limit if it exceeds 48 KB)
+template <typename... KArgs, typename... Args>
+inline void launch_dep_smem(Ctx *ctx, unsigned grid, unsigned block, size_t smem_bytes, void (*kernel)(KArgs...), Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -994,6 +994,38 @@ def test_ext_reductions_match_oracle_and_f64_truth(dt, outer, r, inner):
             assert np.array_equal(_host(out).view(np.uint64), want), (code,)
 
 
+@pytest.mark.parametrize("dt", [np.float32, np.float64], ids=["f32", "f64"])
+@pytest.mark.parametrize("outer,r,inner,pitch", [(1, 4096, 1024, 1024), (2, 1000, 1156, 1156), (1, 257, 2048, 2048), (3, 300, 1024, 1024),
+                                                 (1, 2048, 512, 1024), (1, 4099, 3072, 4096), (5, 67, 640, 640)])
+def test_state_merging_column_reductions_on_aligned_rows(dt, outer, r, inner, pitch):
+    """Few column tiles and 16-byte aligned rows -- the chunked one-wave regime of the vector column
+    kernel (software-pipelined for variance and positions): ragged chunks, a ragged last tile, rows
+    with a pitch.  Every op against the f64 truth, positions exact."""
+    from rtensors_b200.meta import Meta
+    be = _b()
+    rng = np.random.default_rng(outer * 100003 + r * 17 + inner)
+    buf = (rng.standard_normal(outer * r * pitch) * 1.5 + 0.5).astype(dt)
+    x = buf.reshape(outer, r, pitch)[:, :, :inner]
+    x64 = x.astype(np.float64)
+    d = _dev(buf)
+    meta = Meta((outer, r, inner), (r * pitch, pitch, 1), 0)
+    eps = 1e-5 if dt == np.float32 else 1e-13
+    tol = eps * math.log2(r)
+    for code, unbiased, is_std, norm_type in [(O.VARIANCE, True, False, 2), (O.VARIANCE, False, True, 2), (O.LOGSUMEXP, True, False, 2),
+                                              (O.NORM, True, False, 1), (O.NORM, True, False, 2)]:
+        got = _host(be.reduce_view_ex(d, meta, 1, code, unbiased, is_std, norm_type)).astype(np.float64).reshape(outer, inner)
+        truth = _ext_truth(x64, code, unbiased, is_std, norm_type)
+        assert np.all(np.abs(got - truth) <= tol * np.maximum(np.abs(truth), 1e-30)), (code, unbiased, is_std, norm_type)
+    dense = np.ascontiguousarray(x)
+    for data in (dense, np.round(dense * 2).astype(dt)):
+        wide = np.zeros((outer, r, pitch), dtype=dt)
+        wide[:, :, :inner] = data
+        dd = _dev(wide.reshape(-1))
+        for code in (O.ARGMAX, O.ARGMIN):
+            got = _host(be.reduce_view_ex(dd, meta, 1, code)).view(np.uint64)
+            assert np.array_equal(got, O.argreduce_ori(data.reshape(-1), outer, r, inner, code)), code
+
+
 def test_ext_reductions_flat_rank1_and_edge_values():
     from rtensors_b200.meta import Meta
     b = _b()
