@@ -392,8 +392,9 @@ def main():
                 "achieved": sig(k_gbs), "peak": peak, "unit": "GB/s", "frac": sig(k_gbs / peak), "peak_kind": peak_kind,
                 "frac_of_probe": sig(k_gbs / PROBE_WRITE_GBS), "frac_of_nominal": sig(k_gbs / NOMINAL_GBS),
                 "ms_per_launch": sig(k_ms),
-                "traffic": None if traffic is None else sig(traffic["dram_bytes_per_output_byte"] * 4.0 * sdm.size),
-                "traffic_source": None if traffic is None else traffic["source"]}
+                "traffic": None if traffic is None else sig(max(4.0 * sdm.size * (1.0 + traffic["read_bytes_per_output_byte"])
+                                                                - traffic["dirty_bytes_left_in_l2"], 0.0)),
+                "traffic_source": None if traffic is None else "profiles/roofline_traffic.json: " + traffic["rule"]}
 
     # clocks under load: the timed region above is short, so sample while the same step keeps running
     t_load0 = sampler.mark()
