@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(kBlock) transpose_tiles_kernel(T *d, const T *
 
 // The same tiles with 16-byte accesses on BOTH sides, for 4- and 8-byte elements whose views are
 // vector-aligned (the common case: a transposed matrix or a permuted cube of f32 / f64 / i32 / i64).
-// V = elements per 16 bytes.  A CTA owns 128 (X) x 8V (Y) elements.  Staging: a thread loads four
+// V = elements per 16 bytes.  A CTA owns 128 (X) x 8V (Y) elements (twice that along Y for a one-input copy).  Staging: a thread loads four
 // vectors of V consecutive Y-elements (8 lanes cover 128 contiguous bytes of one X-row, a warp four
 // X-rows) -- all four in flight before the first shared-memory store -- and parks them element by
 // element in a tile whose pitch is one element more than its width, which makes the scattered stores
@@ -649,15 +649,18 @@ __global__ void __launch_bounds__(kBlock) transpose_tiles_kernel(T *d, const T *
 // the staging loads are issued.  Measured against the element-wise tiles above (every global access
 // one element): transposed 8192 x 8192 f32 copy and a.T + b, see the kernel table of the design notes.
 constexpr int kTvX = 128;
+// YT = number of 8V-wide Y sub-tiles a CTA owns: 1 for two inputs, 2 for a plain strided copy (one
+// input), where twice the staged vectors in flight per thread is what the kernel is short of.
+template <int NIN> struct TvYT { static constexpr int value = NIN >= 2 ? 1 : 2; };
 template <typename F, int NIN>
 __global__ void __launch_bounds__(kBlock) transpose_vec_kernel(T *d, const T *l, const T *r, const __grid_constant__ TrParams p, F f) {
     grid_dep_sync();
-    constexpr int V = 16 / (int)sizeof(T), TY = 8 * V, NY = 2 * V;
+    constexpr int V = 16 / (int)sizeof(T), TY = 8 * V, NY = 2 * V, YT = TvYT<NIN>::value;
     union Vec {
         uint4 q;
         T e[V];
     };
-    __shared__ T tile[kTvX][TY + 1];
+    __shared__ T tile[kTvX][YT * TY + 1];
     const int X = p.rank - 1, Y = p.ydim;
     uint32_t id = blockIdx.x;
     const uint32_t bx = id % p.tiles_x; id /= p.tiles_x;
@@ -672,14 +675,14 @@ __global__ void __launch_bounds__(kBlock) transpose_vec_kernel(T *d, const T *l,
         if (NIN >= 2) orr += (int64_t)c * p.sr[k];
     }
     const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5, l8 = lane & 7u, h4 = lane >> 3;
-    const uint32_t x0 = bx * kTvX, y0 = by * TY;
+    const uint32_t x0 = bx * kTvX, y0 = by * (YT * TY);
     const uint32_t nx = p.extent[X], ny = p.extent[Y];
     const bool staged_is_l = p.stage_l != 0;
     const T *sp = staged_is_l ? l + ol : r + orr;                     // staged input: dense along Y
     const int64_t ssx = staged_is_l ? p.sl[X] : p.sr[X];
     const T *dp = staged_is_l ? r + orr : l + ol;                     // direct input (NIN == 2): dense along X
     const int64_t dsy = staged_is_l ? p.sr[Y] : p.sl[Y];
-    Vec pre[4], st[4];
+    Vec pre[4], st[YT][4];
     if (NIN >= 2) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -689,33 +692,39 @@ __global__ void __launch_bounds__(kBlock) transpose_vec_kernel(T *d, const T *l,
         }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t x = x0 + 4u * (w + 8u * j) + h4, y = y0 + V * l8;
-        if (x < nx && y < ny) st[j].q = *reinterpret_cast<const uint4 *>(sp + (int64_t)x * ssx + (int64_t)y);
-    }
+    for (int t = 0; t < YT; ++t)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t xr = 4u * (w + 8u * j) + h4;
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t x = x0 + 4u * (w + 8u * j) + h4, y = y0 + t * TY + V * l8;
+            if (x < nx && y < ny) st[t][j].q = *reinterpret_cast<const uint4 *>(sp + (int64_t)x * ssx + (int64_t)y);
+        }
 #pragma unroll
-        for (int t = 0; t < V; ++t) tile[xr][V * l8 + t] = st[j].e[t];
-    }
+    for (int t = 0; t < YT; ++t)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t xr = 4u * (w + 8u * j) + h4;
+#pragma unroll
+            for (int e = 0; e < V; ++e) tile[xr][t * TY + V * l8 + e] = st[t][j].e[e];
+        }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t q = w + 8u * j, yg = q % NY, xg = q / NY;
-        const uint32_t xl = 8u * V * xg + V * l8, yl = 4u * yg + h4;
-        const uint32_t x = x0 + xl, y = y0 + yl;
-        if (x < nx && y < ny) {
-            Vec o;
+    for (int t = 0; t < YT; ++t)
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const T a = tile[xl + i][yl];
-                if (NIN >= 2) o.e[i] = staged_is_l ? f(a, pre[j].e[i]) : f(pre[j].e[i], a);
-                else o.e[i] = f(a, T());
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t q = w + 8u * j, yg = q % NY, xg = q / NY;
+            const uint32_t xl = 8u * V * xg + V * l8, yl = t * TY + 4u * yg + h4;
+            const uint32_t x = x0 + xl, y = y0 + yl;
+            if (x < nx && y < ny) {
+                Vec o;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const T a = tile[xl + i][yl];
+                    if (NIN >= 2) o.e[i] = staged_is_l ? f(a, pre[j].e[i]) : f(pre[j].e[i], a);
+                    else o.e[i] = f(a, T());
+                }
+                *reinterpret_cast<uint4 *>(d + od + (int64_t)x + (int64_t)y * p.sd[Y]) = o.q;
             }
-            *reinterpret_cast<uint4 *>(d + od + (int64_t)x + (int64_t)y * p.sd[Y]) = o.q;
         }
-    }
 }
 
 // Can the planned transposing call run on the vector tiles?  (fills the tile counts of `p` if so)
@@ -737,7 +746,8 @@ bool vector_tiles_ok(const T *d, const T *l, const T *r, TrParams *p) {
     if (p->sd[X] != 1 || ss[Y] != 1) return false;
     if (NIN >= 2 && ds[X] != 1) return false;
     p->tiles_x = (p->extent[X] + kTvX - 1) / kTvX;
-    p->tiles_y = (p->extent[Y] + 8 * (uint32_t)V - 1) / (8 * (uint32_t)V);
+    const uint32_t tile_y = 8 * (uint32_t)V * (uint32_t)TvYT<NIN>::value;
+    p->tiles_y = (p->extent[Y] + tile_y - 1) / tile_y;
     uint64_t blocks = (uint64_t)p->tiles_x * p->tiles_y;
     for (int k = 0; k < p->rank - 1; ++k)
         if (k != Y) blocks *= p->extent[k];
