@@ -379,7 +379,8 @@ int rtb_mg_pick_reduce_dim(size_t rank, const size_t *shape, size_t axis, size_t
  *      context gets a 4 MiB exchange buffer that every rank maps from every other rank (CUDA IPC):
  *      small results travel through it as plain stores over NVLink from inside the library's own
  *      kernels, with no collective launch (*peer_mapped of rtb_mg_info; when the mapping is not
- *      possible everything falls back to NCCL).  All rtb_mg_* calls below are collective: every
+ *      possible -- or RTB_MG_NO_PEER=1 is set in the environment of any rank -- everything falls
+ *      back to NCCL).  All rtb_mg_* calls below are collective: every
  *      rank makes the same calls in the same order on its context's stream. ------------------------ */
 #define RTB_MG_ID_BYTES 128
 #define RTB_MG_MAX_RANKS 16

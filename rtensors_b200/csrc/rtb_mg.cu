@@ -15,6 +15,8 @@
 #include <nccl.h>
 #include <unistd.h>
 
+#include <cstdlib>
+
 #include "rtb_mg.cuh"
 
 namespace rtb {
@@ -350,6 +352,10 @@ RTB_API int rtb_mg_init(rtb_ctx *c, int nranks, int rank, const void *id_bytes) 
     Record mine{};
     mine.ok = cudaIpcGetMemHandle(&mine.handle, mg->local) == cudaSuccess ? 1 : 0;
     if (!mine.ok) cudaGetLastError();
+    // RTB_MG_NO_PEER=1 on any rank keeps every rank off the peer-memory path (everything then goes
+    // through NCCL): for hosts that forbid IPC mappings, and for testing that path
+    if (const char *no_peer = std::getenv("RTB_MG_NO_PEER"))
+        if (no_peer[0] == '1') mine.ok = 0;
     mine.device = ctx->device;
     mine.pid = (long long)getpid();
     mine.ptr = (unsigned long long)(uintptr_t)mg->local;

@@ -219,6 +219,18 @@ def test_two_gpu_sharding(tmp_path):
     port = _free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+    assert "peer_mapped=True" in (tmp_path / "ok0").read_text()
+
+
+def test_two_gpu_sharding_without_peer_mapping(tmp_path, monkeypatch):
+    """The same checks with the peer-memory path switched off: every combine goes through NCCL."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    monkeypatch.setenv("RTB_MG_NO_PEER", "1")
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert "peer_mapped=False" in (tmp_path / "ok0").read_text()
 
 
 def test_two_contexts_on_two_devices_in_one_process():
