@@ -46,7 +46,9 @@ class DenseMlp:
     def __init__(self, be: CudaB200, sizes: Sequence[int] = (784, 1024, 1024, 10), lr: float = 0.01,
                  ref_quirks: bool = False, seed: int = 0x5EED + 5):
         self.be, self.sizes, self.lr, self.ref_quirks = be, tuple(sizes), float(lr), ref_quirks
-        dev = f"cuda:{be.device}"
+        # any engine with the Backend-mirror methods this class calls works (the CPU tests drive the
+        # same step logic through an engine made of the oracle's pieces); CudaB200 is the product's
+        dev = getattr(be, "torch_device", None) or f"cuda:{be.device}"
         self.shapes = []
         for fi, fo in zip(sizes[:-1], sizes[1:]):
             self.shapes += [(fi, fo), (1, fo)]
