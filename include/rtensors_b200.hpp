@@ -246,6 +246,48 @@ class Cuda {
     template <typename T> void copy_view(const Buf<T> &src, const MetaTensor &m, Buf<T> &dst) const {
         check(rtb_copy_view(ctx_, DTypeOf<T>::value, src.ptr, m.rank(), m.shape.data(), m.strides.data(), m.offset, dst.ptr));
     }
+    // one dense layer's `+ bias`, relu and relu gradient map in one pass over a dense (rows, cols) activation
+    template <typename T> void bias_relu_mask(Buf<T> &z, const Buf<T> &bias, Buf<T> &mask, size_t rows, size_t cols) const {
+        if (z.len < rows * cols || mask.len < rows * cols || bias.len < cols) throw TensorError(RTB_ERR_BOUNDS, "bias_relu_mask: buffer too small");
+        check(rtb_bias_relu_mask(ctx_, DTypeOf<T>::value, z.ptr, bias.ptr, mask.ptr, rows, cols));
+    }
+
+    // ---- several GPUs: one Cuda per device (one process per GPU, or one host thread per device); the
+    //      reference has a single device (`// TODO multiple devices`, src/backend/cuda.rs:155-162).  All
+    //      mg_* device calls are collective: same calls, same order, on every rank. ------------------------
+    static std::vector<unsigned char> mg_unique_id() {
+        std::vector<unsigned char> id(RTB_MG_ID_BYTES);
+        check(rtb_mg_unique_id(id.data()));
+        return id;
+    }
+    void mg_init(int nranks, int rank, const std::vector<unsigned char> &id) const { check(rtb_mg_init(ctx_, nranks, rank, id.data())); }
+    void mg_finalize() const { check(rtb_mg_finalize(ctx_)); }
+    int mg_world() const { int n = 1; check(rtb_mg_info(ctx_, &n, nullptr, nullptr)); return n; }
+    int mg_rank() const { int r = 0; check(rtb_mg_info(ctx_, nullptr, &r, nullptr)); return r; }
+    bool mg_peer_mapped() const { int m = 0; check(rtb_mg_info(ctx_, nullptr, nullptr, &m)); return m != 0; }
+    unsigned mg_status() const { unsigned b = 0; check(rtb_mg_status(ctx_, &b)); return b; }
+    void mg_realign() const { check(rtb_mg_realign(ctx_)); }
+    void mg_set_wait_ns(uint64_t ns) const { check(rtb_mg_set_wait_ns(ctx_, ns)); }
+    // full reduction of a tensor whose flat range is split across the ranks: src holds this rank's local_len elements
+    template <typename T>
+    void mg_reduce_flat(const Buf<T> &src, size_t start, size_t local_len, size_t global_len, ReductionOpTypes op, Buf<T> &dst) const {
+        if (start + local_len > src.len) throw TensorError(RTB_ERR_BOUNDS, "flat reduction range exceeds the buffer");
+        check(rtb_mg_reduce_flat(ctx_, DTypeOf<T>::value, (int)op, src.ptr, start, local_len, global_len, dst.ptr));
+    }
+    // axis reduction whose reduced dim is split: this rank holds r_local of global_r rows of a dense [outer, r, inner] block
+    template <typename T>
+    void mg_reduce_axis(const Buf<T> &src, size_t offset, size_t outer, size_t r_local, size_t inner, size_t global_r,
+                        ReductionOpTypes op, Buf<T> &dst) const {
+        check(rtb_mg_reduce_axis(ctx_, DTypeOf<T>::value, (int)op, src.ptr, offset, outer, r_local, inner,
+                                 (ptrdiff_t)(r_local * inner), (ptrdiff_t)inner, global_r, dst.ptr));
+    }
+    template <typename T> void mg_combine(Buf<T> &buf, size_t n, ReductionOpTypes op, size_t mean_count = 0) const {
+        check(rtb_mg_combine(ctx_, DTypeOf<T>::value, (int)op, buf.ptr, n, mean_count));
+    }
+    template <typename T> void mg_allreduce(Buf<T> &buf, size_t n, ReductionOpTypes op, bool overlap = false) const {
+        check((overlap ? rtb_mg_allreduce_begin : rtb_mg_allreduce)(ctx_, DTypeOf<T>::value, (int)op, buf.ptr, n, 0));
+    }
+    void mg_allreduce_join() const { check(rtb_mg_allreduce_join(ctx_)); }
 
   private:
     rtb_ctx *ctx_ = nullptr;

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "rt_b200.h"
+#include "rtensors_b200.hpp"
 
 static int g_fail = 0;
 #define CHECK(cond)                                                              \
@@ -51,6 +52,34 @@ static void worker(int rank, int nranks, const unsigned char *id, const std::vec
     CHECK(rtb_free(ctx, dev) == RTB_OK && rtb_free(ctx, res) == RTB_OK);
     CHECK(rtb_mg_finalize(ctx) == RTB_OK);
     rtb_ctx_destroy(ctx);
+}
+
+// The same through the C++ mirror's `Cuda` class (one object per device): mean over the split tensor, a
+// partial-vector combine, and an all-reduce begun on the side stream and joined.
+static void mirror_worker(int rank, int nranks, const std::vector<unsigned char> *id, const std::vector<float> *x, float *out_mean,
+                          float *out_vec) {
+    using namespace rtb200;
+    try {
+        Cuda cuda(rank);
+        cuda.mg_init(nranks, rank, *id);
+        size_t b = 0, e = 0;
+        rtb_shard_range(x->size(), (size_t)nranks, (size_t)rank, &b, &e);
+        auto local = cuda.alloc_from_slice(std::vector<float>(x->begin() + b, x->begin() + e));
+        auto res = cuda.alloc<float>(1);
+        cuda.mg_reduce_flat(*local, 0, e - b, x->size(), ReductionOpTypes::Mean, *res);
+        out_mean[rank] = cuda.dump(*res)[0];
+        auto vec = cuda.alloc_from_slice(std::vector<float>(64, (float)(rank + 1)));
+        cuda.mg_combine(*vec, 64, ReductionOpTypes::Sum);
+        auto big = cuda.alloc_from_slice(std::vector<float>(100000, (float)(rank + 1)));
+        cuda.mg_allreduce(*big, 100000, ReductionOpTypes::Sum, /*overlap=*/true);
+        cuda.mg_allreduce_join();
+        out_vec[rank] = cuda.dump(*vec)[63] + cuda.dump(*big)[99999];
+        if (cuda.mg_status() != 0 || cuda.mg_world() != nranks || cuda.mg_rank() != rank) ++g_fail;
+        cuda.mg_finalize();
+    } catch (const std::exception &ex) {
+        std::printf("FAILED (mirror, rank %d): %s\n", rank, ex.what());
+        ++g_fail;
+    }
 }
 
 int main() {
@@ -107,6 +136,20 @@ int main() {
         for (size_t r = 0; r < x.size() / 256; ++r) want += x[r * 256 + c];
         if (cols[0][c] != cols[1][c] || std::fabs(cols[0][c] - want) > 1e-5 * 12 * 4096) {
             std::printf("FAILED: column %zu: %.6f / %.6f vs %.6f\n", c, cols[0][c], cols[1][c], want);
+            return 1;
+        }
+    }
+    {
+        std::vector<unsigned char> id2 = rtb200::Cuda::mg_unique_id();
+        float means[2] = {0, 0}, vecs[2] = {0, 0};
+        std::thread m0(mirror_worker, 0, nranks, &id2, &x, means, vecs);
+        std::thread m1(mirror_worker, 1, nranks, &id2, &x, means, vecs);
+        m0.join();
+        m1.join();
+        if (g_fail) return 1;
+        const double want_mean = truth / (double)x.size();
+        if (means[0] != means[1] || std::fabs(means[0] - want_mean) > 1e-5 || vecs[0] != 6.0f || vecs[1] != 6.0f) {
+            std::printf("FAILED: mirror mean %.7f / %.7f vs %.7f, sums %.1f %.1f\n", means[0], means[1], want_mean, vecs[0], vecs[1]);
             return 1;
         }
     }
