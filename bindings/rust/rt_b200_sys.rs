@@ -1,6 +1,6 @@
 //! `rt_b200_sys` -- raw FFI declarations of librt_b200.so's v2 C ABI (`include/rt_b200.h`) for the Rust
 //! host of rtensors: what `libs/rtensors/src/backend/cuda.rs` binds instead of the bindgen output of
-//! `cuda/include/kernels.h` once it calls `rtb_*`.
+//! `cuda/include/kernels.h` once it calls `rtb_*` instead of the `launch_*` launchers.
 //!
 //! NOT COMPILED where this repository is built (its image has no Rust toolchain): the file is text
 //! that mirrors the C header one declaration per function.  `tests/test_rust_binding_text.py` checks
