@@ -248,12 +248,76 @@ def _backwards_negate(ctx, node, upstream):
     return [upstream.neg()]
 
 
+def _backwards_div(ctx, node, upstream):
+    sv = node.saved                                    # :84-107
+    lhs, rr = sv["lhs"], sv["rhs_reciprocal"]
+    return [_inverse_broadcast_gradient(ctx, upstream * rr, sv["lhs_strides"], sv["lhs_shape"]),
+            _inverse_broadcast_gradient(ctx, upstream * (lhs * rr.square()).neg(), sv["rhs_strides"], sv["rhs_shape"])]
+
+
+def _backwards_div_scalar(ctx, node, upstream):
+    return [upstream / node.saved["scalar"]]
+
+
+def _backwards_permute(ctx, node, upstream):
+    dims = node.saved["dims"]                          # :163-185: the inverse permutation, meta only
+    inverse = [0] * len(dims)
+    for i, d in enumerate(dims):
+        inverse[d] = i
+    return [upstream.permute(inverse)]
+
+
+def _backwards_unsqueeze(ctx, node, upstream):
+    return [upstream.squeeze(node.saved["dim"]).owned()]
+
+
+def _backwards_reshape(ctx, node, upstream):          # Squeeze and Reshape both go back by reshape
+    return [upstream.reshape(node.saved["original_shape"])]
+
+
+# unary nodes: name -> (what the forward op saves, d/dx as a function of that tensor); :240-510
+_UNARY_BACKWARD = {
+    "Abs": ("grad_map", lambda t: t),
+    "Sigmoid": ("result", lambda r: r * (r.neg() + 1.0)),
+    "Sqrt": ("result", None),                          # upstream / (output * 2): divides instead of multiplying
+    "Ln": ("x_reciprocal", lambda t: t),
+    "Sin": ("input", lambda x: x.cos()),
+    "Cos": ("input", lambda x: x.sin().neg()),
+    "Tan": ("input", lambda x: x.cos().square().reciprocal()),
+    "Tanh": ("result", lambda r: r.square().neg() + 1.0),
+    "Exp": ("result", lambda r: r),
+    "Square": ("input", lambda x: x * 2.0),
+    "Cube": ("input", lambda x: x.square() * 3.0),
+    "Reciprocal": ("result", lambda r: r.square().neg()),
+    "Rsqrt": ("result", lambda r: r.cube() * -0.5),
+    "Sinh": ("input", lambda x: x.cosh()),
+    "Cosh": ("input", lambda x: x.sinh()),
+    "ExpM1": ("input", lambda x: x.exp()),
+    "Ln1p": ("input", lambda x: (x + 1.0).reciprocal()),
+}
+
+
+def _unary_backward(kind):
+    key, dfdx = _UNARY_BACKWARD[kind]
+
+    def run(ctx, node, upstream):
+        t = node.saved[key]
+        if kind == "Sqrt":
+            return [upstream / (t * 2.0)]
+        return [dfdx(t) * upstream]
+    return run
+
+
 _BACKWARD = {
     "Leaf": _accumulate_grad, "None": lambda ctx, node, up: [],
     "BroadcastAdd": _backwards_add, "BroadcastSub": _backwards_sub, "BroadcastMul": _backwards_mul,
+    "BroadcastDiv": _backwards_div,
     "L1": _backwards_l1, "ReLU": _backwards_relu, "MatMul": _backwards_matmul,
-    "AddScalar": _backwards_add_scalar, "MulScalar": _backwards_mul_scalar, "Negate": _backwards_negate,
+    "AddScalar": _backwards_add_scalar, "MulScalar": _backwards_mul_scalar, "DivScalar": _backwards_div_scalar,
+    "Negate": _backwards_negate, "Permute": _backwards_permute, "Unsqueeze": _backwards_unsqueeze,
+    "Squeeze": _backwards_reshape, "Reshape": _backwards_reshape,
 }
+_BACKWARD.update({k: _unary_backward(k) for k in _UNARY_BACKWARD})
 
 
 # ---- attach helpers called by the Tensor operators -------------------------------------------------
@@ -264,7 +328,10 @@ def attach_broadcast(kind: str, out, a, b) -> None:
     shape, sa, sb = broadcast_params(a.meta, b.meta)
     saved = {"lhs_strides": tuple(sa), "rhs_strides": tuple(sb), "lhs_shape": tuple(a.shape), "rhs_shape": tuple(b.shape)}
     if kind == "BroadcastMul":
-        saved["lhs"], saved["rhs"] = a, b            # read in place; the reference copies both (its D13)
+        saved["lhs"], saved["rhs"] = a, b            # read in place; the reference copies both operands
+    if kind == "BroadcastDiv":
+        with no_grad():                               # the reciprocal map in one kernel (reference: a get / set loop)
+            saved["lhs"], saved["rhs_reciprocal"] = a, b.reciprocal_map()
     ctx.attach(out, GradNode(kind, [a.op, b.op], saved))
 
 

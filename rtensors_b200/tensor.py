@@ -106,10 +106,24 @@ class Tensor:
 
     def slice(self, dim, start=None, end=None, step=1): return self._view(self.meta.slice(dim, start, end, step))
     def index(self, dim, i): return self._view(self.meta.index(dim, i))
-    def permute(self, dims): return self._view(self.meta.permute(dims))
-    def transpose(self): return self._view(self.meta.transpose())
-    def squeeze(self, dim=None): return self._view(self.meta.squeeze(dim))
-    def unsqueeze(self, dim): return self._view(self.meta.unsqueeze(dim))
+
+    def permute(self, dims):
+        v = self._view(self.meta.permute(dims))
+        _grad.attach_unary("Permute", v, self, dims=tuple(dims))
+        return v
+
+    def transpose(self): return self.permute(tuple(reversed(range(self.rank))))
+
+    def squeeze(self, dim=None):
+        v = self._view(self.meta.squeeze(dim))
+        _grad.attach_unary("Squeeze", v, self, original_shape=tuple(self.shape))
+        return v
+
+    def unsqueeze(self, dim):
+        v = self._view(self.meta.unsqueeze(dim))
+        _grad.attach_unary("Unsqueeze", v, self, dim=dim)
+        return v
+
     def view_as(self, shape): return self._view(self.meta.view_as(shape))
 
     def contiguous(self) -> "Tensor":
@@ -120,7 +134,9 @@ class Tensor:
     def reshape(self, shape) -> "Tensor":
         """contiguous() then view_as: always a fresh buffer (src/core/tensor.rs:238-243)."""
         c = self.contiguous()
-        return Tensor(c.backend, c.buf, c.meta.view_as(shape))
+        out = Tensor(c.backend, c.buf, c.meta.view_as(shape))
+        _grad.attach_unary("Reshape", out, self, original_shape=tuple(self.shape))
+        return out
 
     def into_dtype(self, dtype) -> "Tensor":
         """A tensor of the same meta over a converted copy of the whole buffer
@@ -160,6 +176,8 @@ class Tensor:
             _grad.attach_unary("AddScalar", t, self)
         elif op == L.MUL:
             _grad.attach_unary("MulScalar", t, self, scalar=other)
+        elif op == L.DIV:
+            _grad.attach_unary("DivScalar", t, self, scalar=other)
         return t
 
     def matmul(self, other: "Tensor") -> "Tensor":
@@ -208,7 +226,12 @@ class Tensor:
             _grad.attach_unary("ReLU", out, self, grad_map=self.relu_grad_map())
         return out
 
-    def abs(self): return self.owned().abs_inplace()
+    def abs(self):
+        out = self.owned().abs_inplace()
+        if _grad.is_enabled():
+            _grad.attach_unary("Abs", out, self, grad_map=self.abs_grad_map())
+        return out
+
     def sign(self): return self.owned().sign_inplace()
 
     def neg(self):
@@ -299,7 +322,40 @@ def mean_l1_loss(a: Tensor, b: Tensor, with_grad: bool = False):
     return lt
 
 
-_BROADCAST_NODE = {L.ADD: "BroadcastAdd", L.SUB: "BroadcastSub", L.MUL: "BroadcastMul"}
+_BROADCAST_NODE = {L.ADD: "BroadcastAdd", L.SUB: "BroadcastSub", L.MUL: "BroadcastMul", L.DIV: "BroadcastDiv"}
+
+# The float-only unary families (src/ops/unary/mod.rs): `t.sigmoid()` copies then works in place, as the
+# reference's owned forms do; under a grad context each attaches its node with the tensor its backward
+# function needs -- the input, the result, or (ln) the reciprocal of the input.
+_UNARY_NODES = {"sigmoid": (L.SIGMOID, "Sigmoid", "result"), "tanh": (L.TANH, "Tanh", "result"), "sqrt": (L.SQRT, "Sqrt", "result"),
+                "exp": (L.EXP, "Exp", "result"), "reciprocal": (L.RECIPROCAL, "Reciprocal", "result"),
+                "rsqrt": (L.RSQRT, "Rsqrt", "result"), "ln": (L.LN, "Ln", "x_reciprocal"), "sin": (L.SIN, "Sin", "input"),
+                "cos": (L.COS, "Cos", "input"), "tan": (L.TAN, "Tan", "input"), "square": (L.SQUARE, "Square", "input"),
+                "cube": (L.CUBE, "Cube", "input"), "sinh": (L.SINH, "Sinh", "input"), "cosh": (L.COSH, "Cosh", "input"),
+                "expm1": (L.EXPM1, "ExpM1", "input"), "ln1p": (L.LN1P, "Ln1p", "input")}
+
+
+def _make_unary(name, code, node, saves):
+    def inplace(self):
+        return self._unary_inplace(code)
+
+    def owned(self):
+        out = self.owned()._unary_inplace(code)
+        if _grad.is_enabled():
+            if saves == "result":
+                _grad.attach_unary(node, out, self, result=out)
+            elif saves == "input":
+                _grad.attach_unary(node, out, self, input=self)
+            else:
+                _grad.attach_unary(node, out, self, x_reciprocal=self.reciprocal_map())
+        return out
+    inplace.__name__, owned.__name__ = name + "_inplace", name
+    setattr(Tensor, name + "_inplace", inplace)
+    setattr(Tensor, name, owned)
+
+
+for _name, (_code, _node, _saves) in _UNARY_NODES.items():
+    _make_unary(_name, _code, _node, _saves)
 
 
 def mean_l1_loss_tracked(a: Tensor, b: Tensor) -> Tensor:

@@ -116,3 +116,70 @@ def test_linear_model_loss_decreases_under_sgd():
     assert losses[-1] < 0.5 * losses[0]
     with grad.no_grad():
         assert not grad.is_enabled()
+
+
+_UNARY_CASES = {
+    # name: (f, f', domain)
+    "sigmoid": (lambda x: 1 / (1 + np.exp(-x)), lambda x: (1 / (1 + np.exp(-x))) * (1 - 1 / (1 + np.exp(-x))), (-2, 2)),
+    "tanh": (np.tanh, lambda x: 1 - np.tanh(x) ** 2, (-2, 2)),
+    "sqrt": (np.sqrt, lambda x: 0.5 / np.sqrt(x), (0.5, 3)),
+    "exp": (np.exp, np.exp, (-1, 1)),
+    "reciprocal": (lambda x: 1 / x, lambda x: -1 / x ** 2, (0.5, 2)),
+    "rsqrt": (lambda x: x ** -0.5, lambda x: -0.5 * x ** -1.5, (0.5, 2)),
+    "ln": (np.log, lambda x: 1 / x, (0.5, 3)),
+    "sin": (np.sin, np.cos, (-2, 2)),
+    "cos": (np.cos, lambda x: -np.sin(x), (-2, 2)),
+    "tan": (np.tan, lambda x: 1 / np.cos(x) ** 2, (-1, 1)),
+    "square": (lambda x: x * x, lambda x: 2 * x, (-2, 2)),
+    "cube": (lambda x: x ** 3, lambda x: 3 * x * x, (-2, 2)),
+    "sinh": (np.sinh, np.cosh, (-2, 2)),
+    "cosh": (np.cosh, np.sinh, (-2, 2)),
+    "expm1": (np.expm1, np.exp, (-1, 1)),
+    "ln1p": (np.log1p, lambda x: 1 / (1 + x), (0.0, 2)),
+    "abs": (np.abs, np.sign, (-2, 2)),
+    "neg": (lambda x: -x, lambda x: -np.ones_like(x), (-2, 2)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(_UNARY_CASES))
+def test_unary_nodes_backpropagate_the_analytic_derivative(name):
+    """loss = mean_l1_loss(f(x), t) with t far below f(x): dL/dx = f'(x) / N (src/grad/backwards.rs:240-510)."""
+    from rtensors_b200 import grad
+    from rtensors_b200.tensor import Tensor, mean_l1_loss_tracked
+    be = _b()
+    f, df, (lo, hi) = _UNARY_CASES[name]
+    rng = np.random.default_rng(len(name))
+    xh = rng.uniform(lo, hi, (6, 50)).astype(np.float64)
+    xh[np.abs(xh) < 0.05] = 0.3
+    x = Tensor.from_buf(xh, xh.shape, dtype=np.float64, backend=be)
+    t = Tensor.full(xh.shape, -100.0, dtype=np.float64, backend=be)
+    with grad.enabled() as ctx:
+        x.param()
+        y = getattr(x, name)()
+        assert np.allclose(y.cpu(), f(xh), rtol=1e-12, atol=1e-12)
+        loss = mean_l1_loss_tracked(y, t)
+        ctx.backwards(loss)
+    assert np.allclose(x.grad.value.cpu(), df(xh) / xh.size, rtol=1e-10, atol=1e-14), name
+
+
+def test_division_scalar_division_and_view_nodes():
+    """z = ((a / b).permute(1,0) / 2).unsqueeze(0).squeeze().reshape(-1): gradients flow back through
+    BroadcastDiv (with b broadcast over the rows), DivScalar, Permute, Unsqueeze, Squeeze and Reshape."""
+    from rtensors_b200 import grad
+    from rtensors_b200.tensor import Tensor, mean_l1_loss_tracked
+    be = _b()
+    rng = np.random.default_rng(9)
+    ah = rng.uniform(1, 2, (5, 7)).astype(np.float64)
+    bh = rng.uniform(1, 2, (1, 7)).astype(np.float64)
+    a = Tensor.from_buf(ah, ah.shape, dtype=np.float64, backend=be)
+    b = Tensor.from_buf(bh, bh.shape, dtype=np.float64, backend=be)
+    t = Tensor.full((35,), -100.0, dtype=np.float64, backend=be)
+    with grad.enabled() as ctx:
+        a.param(); b.param()
+        z = ((a / b).permute((1, 0)) / 2.0).unsqueeze(0).squeeze().reshape((35,))
+        assert np.allclose(z.cpu(), ((ah / bh).T / 2).reshape(-1))
+        loss = mean_l1_loss_tracked(z, t)
+        ctx.backwards(loss)
+    n = 35.0
+    assert np.allclose(a.grad.value.cpu(), (1 / bh) / 2 / n * np.ones_like(ah), rtol=1e-12)
+    assert np.allclose(b.grad.value.cpu().reshape(-1), (-(ah / bh ** 2) / 2 / n).sum(axis=0), rtol=1e-12)
