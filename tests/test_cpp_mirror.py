@@ -46,3 +46,17 @@ def test_cpp_two_ranks_in_one_process(tmp_path):
     p = subprocess.run([exe], capture_output=True, text=True, timeout=180, env=env)
     assert p.returncode == 0, p.stdout + p.stderr
     assert "ok:" in p.stdout or "skipped" in p.stdout
+
+
+def test_cpp_tape_compiles_and_links(tmp_path):
+    _build(tmp_path, "test_grad_tape")
+
+
+@pytest.mark.gpu
+def test_cpp_tape_gradients_and_reference_models(tmp_path):
+    """include/rtensors_b200_grad.hpp: analytic gradients in both modes, then the first four models of the
+    reference's autograd test trained with SGD."""
+    exe = _build(tmp_path, "test_grad_tape")
+    p = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert "ok:" in p.stdout
