@@ -610,8 +610,8 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     cols = sh.m[1]
     # host copies of this rank's share of every input, pinned.  The column window of the matrix (the
     # axis-0 sum's share at N > 1) is a dense (rows, e - b) block on the host.
-    h_a = torch.from_numpy(d["bufa_h"]).pin_memory()
-    h_b = torch.from_numpy(d["bufb_h"]).pin_memory()
+    h_a = torch.from_numpy(d["bufa_h"]).reshape(-1).pin_memory()
+    h_b = torch.from_numpy(d["bufb_h"]).reshape(-1).pin_memory()
     Mfull = d["Mx"].view(sh.m)
     h_m0 = (Mfull[:, m0b:m0e] if world > 1 else Mfull).contiguous().reshape(-1).cpu().pin_memory()
     h_m1 = Mfull[m1b:m1e].contiguous().reshape(-1).cpu().pin_memory() if world > 1 else None   # N = 1: one matrix serves both sums
@@ -621,11 +621,6 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     h_out = torch.empty(n_slabs * per, dtype=torch.float32).pin_memory()
     r_m0, r_m1, r_t1, r_f = d["outs"]
     h_res = [torch.empty_like(r, device="cpu").pin_memory() for r in (r_m0, r_m1, r_t1, r_f)]
-    d_m0 = torch.empty(h_m0.numel(), device=dev)
-    d_m1 = torch.empty(h_m1.numel(), device=dev) if h_m1 is not None else d_m0
-    d_t = torch.empty(h_t.numel(), device=dev)
-    d_f = torch.empty(h_f.numel(), device=dev)
-    staging = [torch.empty(per, device=dev) for _ in range(min(3, n_slabs))]
     rows = sh.m[0]
     m0_meta = Meta.contiguous((rows, m0e - m0b) if world > 1 else sh.m)
     m1_meta = Meta.contiguous((m1e - m1b, cols) if world > 1 else sh.m)
@@ -634,33 +629,31 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     d2h = 4 * (h_out.numel() + sum(h.numel() for h in h_res))
 
     def e2e_step():
-        cur = torch.cuda.current_stream(be.device)
-        # (broadcast_to_host starts by ordering the three streams after everything enqueued so far)
-        pipe.broadcast_to_host(h_a, d["Am"], h_b, d["Bm"], L.ADD, h_out, staging, d["bufa"], d["bufb"], (slab.begin, slab.end))
-        evs = [pipe.upload_chunked(h_m0, d_m0, 2)]
-        if h_m1 is not None:
-            evs.append(pipe.upload_chunked(h_m1, d_m1, 2))
-        evs.append(pipe.upload_chunked(h_t, d_t, 4))
-        evs.append(pipe.upload_chunked(h_f, d_f, 8))
-        with torch.cuda.stream(pipe.s_run):
-            be.sync_stream()
-            pipe.s_run.wait_event(evs[0])
-            be.reduce_view(d_m0, m0_meta, 0, L.SUM, out=r_m0)
-            if h_m1 is not None:
-                pipe.s_run.wait_event(evs[1])
-            be.reduce_view(d_m1, m1_meta, 1, L.SUM, out=r_m1)
-            pipe.s_run.wait_event(evs[-2])
-            be.reduce_view(d_t, t_meta, 1, L.SUM, out=r_t1)
-            pipe.s_run.wait_event(evs[-1])
-            if world > 1:
-                be.mg_reduce_flat(d_f, 0, d_f.numel(), sh.f, L.SUM, dst=r_f)
-            else:
-                be.apply_reduce_contiguous_flat(d_f, r_f, 0, d_f.numel(), L.SUM)
-            for h, r in zip(h_res, (r_m0, r_m1, r_t1, r_f)):
-                h.copy_(r, non_blocking=True)                     # the step's results, read back
-        cur.wait_stream(pipe.s_run)
-        cur.wait_stream(pipe.s_in)
         be.sync_stream()
+        # the broadcast first: its kernels start at once and are paced by the copy-out of its stages, while
+        # the uploads below run on the upload lane; each reduction waits for its own input only
+        pipe.broadcast_to_host(h_a, d["Am"], h_b, d["Bm"], L.ADD, h_out, (slab.begin, slab.end))
+        b_m0 = be.host_stage_in(h_m0)
+        b_m1 = be.host_stage_in(h_m1) if h_m1 is not None else b_m0
+        b_t = be.host_stage_in(h_t)
+        b_f = be.host_stage_in(h_f)
+        be.host_ready(b_m0)
+        be.reduce_view(b_m0, m0_meta, 0, L.SUM, out=r_m0)
+        if h_m1 is not None:
+            be.host_ready(b_m1)
+        be.reduce_view(b_m1, m1_meta, 1, L.SUM, out=r_m1)
+        be.host_ready(b_t)
+        be.reduce_view(b_t, t_meta, 1, L.SUM, out=r_t1)
+        be.host_ready(b_f)
+        if world > 1:
+            be.mg_reduce_flat(b_f, 0, h_f.numel(), sh.f, L.SUM, dst=r_f)
+        else:
+            be.apply_reduce_contiguous_flat(b_f, r_f, 0, h_f.numel(), L.SUM)
+        for h, r in zip(h_res, (r_m0, r_m1, r_t1, r_f)):
+            be.host_stage_out(r, h)                                  # the step's results, read back
+        for blk in ((b_m0, b_t, b_f) if h_m1 is None else (b_m0, b_m1, b_t, b_f)):
+            be.host_release(blk)
+        be.host_join()                                               # the stream the step is timed on waits for both lanes
     esteps = max(1, min(args.steps, 5))
     e2e_step()
     barrier()
@@ -678,8 +671,9 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     same = all(np.array_equal(h.numpy(), r.cpu().numpy()) for h, r in zip(h_res, (r_m0, r_m1, r_t1, r_f)))
     return {"value": sig(sh.step_bytes() / (e_ms * 1e-3) / 1e9), "unit": "GB/s", "ms_per_step": sig(e_ms),
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": esteps, "results_read_back": bool(same),
-            "how": "HostPipeline: broadcast result copied out slab by slab behind the next slab's kernel, reduction inputs uploaded "
-                   "in chunks on a second stream, pinned host buffers; bytes are this rank's"}
+            "how": "the library's host-buffer operations (rtb_host_*): broadcast result produced in 64 MiB stages into a ring of "
+                   "three device blocks and copied out behind the next stage's kernel, reduction inputs uploaded on the upload lane, "
+                   "each reduction waiting for its own input only; pinned host buffers; bytes are this rank's"}
 
 
 if __name__ == "__main__":

@@ -146,6 +146,23 @@ extern "C" {
     pub fn rtb_mg_reduce_axis(ctx: *mut rtb_ctx, dtype: c_int, redop: c_int, src: *const c_void, offset: usize, outer: usize, r_local: usize, inner: usize, outer_stride: isize, row_stride: isize, global_r: usize, dst: *mut c_void) -> c_int;
     pub fn rtb_mg_l1_loss(ctx: *mut rtb_ctx, dtype: c_int, a: *const c_void, b: *const c_void, local_n: usize, global_n: usize, reduction: c_int, loss: *mut c_void, grad_map: *mut c_void) -> c_int;
 
+
+    // host-buffer operations: transfer lanes and the pool of device blocks
+    pub fn rtb_host_alloc(bytes: usize, out: *mut *mut c_void) -> c_int;
+    pub fn rtb_host_free(ptr: *mut c_void) -> c_int;
+    pub fn rtb_host_pin(ptr: *mut c_void, bytes: usize) -> c_int;
+    pub fn rtb_host_unpin(ptr: *mut c_void) -> c_int;
+    pub fn rtb_host_stage_in(ctx: *mut rtb_ctx, src_host: *const c_void, bytes: usize, dev_out: *mut *mut c_void) -> c_int;
+    pub fn rtb_host_scratch(ctx: *mut rtb_ctx, bytes: usize, dev_out: *mut *mut c_void) -> c_int;
+    pub fn rtb_host_ready(ctx: *mut rtb_ctx, dev: *const c_void) -> c_int;
+    pub fn rtb_host_stage_out(ctx: *mut rtb_ctx, src_dev: *const c_void, dst_host: *mut c_void, bytes: usize) -> c_int;
+    pub fn rtb_host_release(ctx: *mut rtb_ctx, dev: *mut c_void) -> c_int;
+    pub fn rtb_host_join(ctx: *mut rtb_ctx) -> c_int;
+    pub fn rtb_host_wait(ctx: *mut rtb_ctx) -> c_int;
+    pub fn rtb_host_trim(ctx: *mut rtb_ctx) -> c_int;
+    pub fn rtb_host_set_stage_bytes(ctx: *mut rtb_ctx, bytes: usize) -> c_int;
+    pub fn rtb_host_reduce_view(ctx: *mut rtb_ctx, dtype: c_int, redop: c_int, settings: *const rtb_reduce_settings, src_host: *const c_void, src_len: usize, rank: usize, shape: *const usize, strides: *const isize, offset: usize, axis: isize, dst_host: *mut c_void) -> c_int;
+    pub fn rtb_host_broadcast(ctx: *mut rtb_ctx, dtype: c_int, binop: c_int, left_host: *const c_void, left_len: usize, stride_l: *const isize, off_l: usize, right_host: *const c_void, right_len: usize, stride_r: *const isize, off_r: usize, dst_host: *mut c_void, rank: usize, shape: *const usize, begin: usize, end: usize) -> c_int;
 }
 
 /// Maps a status code to the crate's error type the way `cuda.rs` would:

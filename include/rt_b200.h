@@ -107,7 +107,8 @@ int rtb_ctx_set_stream(rtb_ctx *ctx, void *stream);
 void *rtb_ctx_get_stream(rtb_ctx *ctx);
 int rtb_ctx_device(rtb_ctx *ctx);
 int rtb_ctx_sm_count(rtb_ctx *ctx);
-/* waits for the ctx stream (Cuda::sync, src/backend/cuda.rs:164-185) */
+/* waits for the ctx stream (Cuda::sync, src/backend/cuda.rs:164-185) and for the transfer lanes of the
+ * host-buffer operations, if any were used */
 int rtb_ctx_sync(rtb_ctx *ctx);
 /* number of kernels this ctx has launched since creation (bench bookkeeping) */
 uint64_t rtb_ctx_launch_count(rtb_ctx *ctx);
@@ -136,6 +137,63 @@ int rtb_release_cached(rtb_ctx *ctx);
 int rtb_h2d(rtb_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int rtb_d2h(rtb_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes); /* synchronises */
 int rtb_d2d(rtb_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+
+/* ---- host-buffer operations: inputs and results in HOST memory.  The reference moves whole tensors
+ *      with one blocking copy each way (alloc_from_slice / dump, src/backend/cuda.rs:668-680, 770-788).
+ *      Here the context owns an upload lane and a download lane (two more streams) and a pool of
+ *      device blocks; uploads, kernels and copy-outs of independent work run concurrently and are
+ *      ordered by events.  Every call below only enqueues, except rtb_host_wait and rtb_host_trim;
+ *      rtb_ctx_sync also waits for the lanes.  Host memory should be page-locked (rtb_host_alloc, or
+ *      rtb_host_pin for memory the caller already owns): a copy from pageable memory is staged by the
+ *      driver and does not overlap.  None of these calls can be captured into a CUDA graph.
+ *      The pool: a request takes a free block of its kind (upload target / result) that fits and is at
+ *      most twice as large, preferring one whose last readers are done; while every candidate is still in
+ *      use, up to three blocks per kind and size class are allocated rather than waited for (an upload, the
+ *      kernels and a copy-out each hold one), after which the request shares a busy block and its first
+ *      writer waits.  Blocks stay in the pool until rtb_host_trim or rtb_ctx_destroy.
+ *
+ *      rtb_host_stage_in    takes a block from the pool and starts host -> block on the upload lane.
+ *                           The compute stream does NOT wait for it until rtb_host_ready(block): work
+ *                           enqueued in between runs while the upload is in flight.
+ *      rtb_host_scratch     a block of the pool for a result the compute stream will write.
+ *      rtb_host_stage_out   device -> host on the download lane, after everything enqueued on the compute
+ *                           stream so far; src may be any device address (a pool block, part of one, or
+ *                           memory of rtb_alloc, which the caller then keeps alive until the copy is done).
+ *      rtb_host_release     gives a block back.  Kernels and copy-outs already enqueued on it stay valid:
+ *                           the block's next user waits for them.
+ *      rtb_host_join        the compute stream waits for both lanes (stream-ordered completion).
+ *      rtb_host_wait        the host waits for the compute stream and both lanes.
+ *      rtb_host_trim        waits, then frees the pool's unused blocks.
+ *
+ *      rtb_host_reduce_view rtb_reduce_view_ex of a tensor whose buffer (src_len elements) is in host
+ *                           memory; the result (one element, or the view's shape without `axis`; uint64_t
+ *                           for argmax / argmin) is written to dst_host.
+ *      rtb_host_broadcast   rtb_broadcast with operand BUFFERS (left_len / right_len elements) in host
+ *                           memory and the result written row-major to dst_host, restricted to indices
+ *                           [begin, end) of the outermost output dim (dst_host receives only that part: a
+ *                           rank's share).  The output never exists as a whole on the device: it is
+ *                           produced in stages of about 64 MiB (rtb_host_set_stage_bytes; a stage is
+ *                           at least one index of the outermost dim) into a ring of three blocks, stage
+ *                           k's copy-out running behind stage k+1's kernel. -------------------------- */
+int rtb_host_alloc(size_t bytes, void **out);
+int rtb_host_free(void *ptr);
+int rtb_host_pin(void *ptr, size_t bytes);
+int rtb_host_unpin(void *ptr);
+int rtb_host_stage_in(rtb_ctx *ctx, const void *src_host, size_t bytes, void **dev_out);
+int rtb_host_scratch(rtb_ctx *ctx, size_t bytes, void **dev_out);
+int rtb_host_ready(rtb_ctx *ctx, const void *dev);
+int rtb_host_stage_out(rtb_ctx *ctx, const void *src_dev, void *dst_host, size_t bytes);
+int rtb_host_release(rtb_ctx *ctx, void *dev);
+int rtb_host_join(rtb_ctx *ctx);
+int rtb_host_wait(rtb_ctx *ctx);
+int rtb_host_trim(rtb_ctx *ctx);
+int rtb_host_set_stage_bytes(rtb_ctx *ctx, size_t bytes);
+int rtb_host_reduce_view(rtb_ctx *ctx, int dtype, int redop, const rtb_reduce_settings *settings, const void *src_host,
+                         size_t src_len, size_t rank, const size_t *shape, const ptrdiff_t *strides, size_t offset,
+                         ptrdiff_t axis, void *dst_host);
+int rtb_host_broadcast(rtb_ctx *ctx, int dtype, int binop, const void *left_host, size_t left_len, const ptrdiff_t *stride_l,
+                       size_t off_l, const void *right_host, size_t right_len, const ptrdiff_t *stride_r, size_t off_r,
+                       void *dst_host, size_t rank, const size_t *shape, size_t begin, size_t end);
 
 /* ---- view arithmetic (host only; no CUDA call).  out arrays need room for `rank` (+1 for
  *      unsqueeze) entries. --------------------------------------------------------------------- */

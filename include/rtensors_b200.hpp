@@ -9,6 +9,7 @@
 //                                                           418-524, src/ops/{scalar,unary,broadcast,reduction}
 // Errors are exceptions carrying the library status (TensorError variants map to status codes).
 #pragma once
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <memory>
@@ -252,6 +253,59 @@ class Cuda {
         check(rtb_bias_relu_mask(ctx_, DTypeOf<T>::value, z.ptr, bias.ptr, mask.ptr, rows, cols));
     }
 
+    // ---- tensors in HOST memory (rtb_host_*): the context's upload and download lanes overlap a tensor's
+    //      upload, the kernels and the copy-out of results; every call enqueues, host_wait() completes.
+    //      The reference uploads and dumps whole tensors with blocking copies (src/backend/cuda.rs:668-680,
+    //      770-788).  HostVec<T> is page-locked memory from the library. -------------------------------------
+    template <typename T> struct HostVec {
+        T *ptr = nullptr;
+        size_t len = 0;
+        explicit HostVec(size_t n) : len(n) { check(rtb_host_alloc(n * sizeof(T), (void **)&ptr)); }
+        HostVec(const std::vector<T> &v) : HostVec(v.size()) { std::copy(v.begin(), v.end(), ptr); }
+        HostVec(const HostVec &) = delete;
+        HostVec &operator=(const HostVec &) = delete;
+        ~HostVec() { rtb_host_free(ptr); }
+        T &operator[](size_t i) { return ptr[i]; }
+        const T &operator[](size_t i) const { return ptr[i]; }
+        std::vector<T> to_vector() const { return std::vector<T>(ptr, ptr + len); }
+    };
+    // `l op r` with both operand buffers in host memory; out receives indices [begin, end) of the
+    // outermost output dim, row-major
+    template <typename T>
+    void host_broadcast(const HostVec<T> &l, const MetaTensor &lm, const HostVec<T> &r, const MetaTensor &rm, BinaryOpType op,
+                        HostVec<T> &out, size_t begin, size_t end) const;
+    template <typename T, typename Out>
+    void host_reduce_view(const HostVec<T> &src, const MetaTensor &m, ptrdiff_t axis, ReductionOpTypes op, HostVec<Out> &dst,
+                          bool unbiased = true, bool is_std = false, NormType norm = NormType::L2) const {
+        rtb_reduce_settings st{unbiased, is_std, (int)norm};
+        size_t n_out = 1;
+        for (size_t d = 0; d < m.rank(); ++d)
+            if (axis >= 0 && (ptrdiff_t)d != axis) n_out *= m.shape[d];
+        if (dst.len < n_out) throw TensorError(RTB_ERR_BOUNDS, "host_reduce_view: the result does not fit");
+        check(rtb_host_reduce_view(ctx_, DTypeOf<T>::value, (int)op, &st, src.ptr, src.len, m.rank(), m.shape.data(), m.strides.data(),
+                                   m.offset, axis, dst.ptr));
+    }
+    // the primitives: a pool block that is being uploaded (the compute stream waits for it at host_ready),
+    // a scratch block, a copy-out behind the work enqueued so far, and the block's return to the pool
+    template <typename T> T *host_stage_in(const HostVec<T> &src) const {
+        void *dev = nullptr;
+        check(rtb_host_stage_in(ctx_, src.ptr, src.len * sizeof(T), &dev));
+        return (T *)dev;
+    }
+    template <typename T> T *host_scratch(size_t n) const {
+        void *dev = nullptr;
+        check(rtb_host_scratch(ctx_, n * sizeof(T), &dev));
+        return (T *)dev;
+    }
+    void host_ready(const void *dev) const { check(rtb_host_ready(ctx_, dev)); }
+    template <typename T> void host_stage_out(const T *dev, HostVec<T> &dst, size_t n) const {
+        if (n > dst.len) throw TensorError(RTB_ERR_BOUNDS, "host_stage_out: the host buffer is too small");
+        check(rtb_host_stage_out(ctx_, dev, dst.ptr, n * sizeof(T)));
+    }
+    void host_release(void *dev) const { check(rtb_host_release(ctx_, dev)); }
+    void host_join() const { check(rtb_host_join(ctx_)); }
+    void host_wait() const { check(rtb_host_wait(ctx_)); }
+
     // ---- several GPUs: one Cuda per device (one process per GPU, or one host thread per device); the
     //      reference has a single device (`// TODO multiple devices`, src/backend/cuda.rs:155-162).  All
     //      mg_* device calls are collective: same calls, same order, on every rank. ------------------------
@@ -300,6 +354,19 @@ inline void broadcast_params(const MetaTensor &a, const MetaTensor &b, std::vect
     check(rtb_broadcast_params(a.rank(), a.shape.data(), a.strides.data(), b.rank(), b.shape.data(), b.strides.data(), &out_r,
                                shape.data(), sa.data(), sb.data()));
     shape.resize(out_r); sa.resize(out_r); sb.resize(out_r);
+}
+
+template <typename T>
+void Cuda::host_broadcast(const HostVec<T> &l, const MetaTensor &lm, const HostVec<T> &r, const MetaTensor &rm, BinaryOpType op,
+                          HostVec<T> &out, size_t begin, size_t end) const {
+    std::vector<size_t> shape;
+    std::vector<ptrdiff_t> sl, sr;
+    broadcast_params(lm, rm, shape, sl, sr);
+    size_t per = 1;
+    for (size_t d = 1; d < shape.size(); ++d) per *= shape[d];
+    if (end < begin || out.len < (end - begin) * per) throw TensorError(RTB_ERR_BOUNDS, "host_broadcast: the result does not fit");
+    check(rtb_host_broadcast(ctx_, DTypeOf<T>::value, (int)op, l.ptr, l.len, sl.data(), lm.offset, r.ptr, r.len, sr.data(), rm.offset,
+                             out.ptr, shape.size(), shape.data(), begin, end));
 }
 
 // ---- TensorBase<T, Cuda> (owned tensors and views share this type; views share the buffer) -------

@@ -36,6 +36,17 @@ def _scalar_bytes(code: int, value) -> bytes:
     return np.array(value, dtype=CODE_TO_NP[code]).tobytes()
 
 
+_TYPESTR = {torch.float32: "<f4", torch.float64: "<f8", torch.int32: "<i4", torch.int64: "<i8", torch.int16: "<i2",
+            torch.int8: "|i1", torch.uint8: "|u1", torch.bool: "|b1"}
+
+
+class _DeviceBlock:
+    """A raw device address as an object torch can wrap without copying (CUDA array interface)."""
+
+    def __init__(self, ptr: int, n: int, dtype: torch.dtype):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": _TYPESTR[dtype], "data": (int(ptr), False), "version": 2}
+
+
 class CudaB200:
     """One instance per device (`Cuda` of the reference, src/backend/cuda.rs:38-186): owns the
     library context (stream, workspace, allocator).  Calls are enqueued on torch's current
@@ -444,6 +455,72 @@ class CudaB200:
 
     def mg_allreduce_join(self):
         check(lib().rtb_mg_allreduce_join(self._ctx))
+
+    # -- host-buffer operations (rtb_host_*): two transfer lanes and a pool of device blocks inside the library --
+    def _pool_tensor(self, ptr: int, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """A torch view of a block of the library's pool (no copy; valid until host_release)."""
+        return torch.as_tensor(_DeviceBlock(ptr, int(n), dtype), device=f"cuda:{self.device}")
+
+    def host_stage_in(self, host: torch.Tensor) -> torch.Tensor:
+        """Starts the upload of a (pinned) host tensor; the compute stream waits only at host_ready."""
+        out = C.c_void_p()
+        check(lib().rtb_host_stage_in(self._ctx, C.c_void_p(host.data_ptr()), C.c_size_t(host.numel() * host.element_size()),
+                                      C.byref(out)))
+        return self._pool_tensor(out.value, max(host.numel(), 1), host.dtype)
+
+    def host_scratch(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        out = C.c_void_p()
+        check(lib().rtb_host_scratch(self._ctx, C.c_size_t(int(n) * torch.empty(0, dtype=dtype).element_size()), C.byref(out)))
+        return self._pool_tensor(out.value, max(int(n), 1), dtype)
+
+    def host_ready(self, dev: torch.Tensor):
+        check(lib().rtb_host_ready(self._ctx, self._p(dev)))
+
+    def host_stage_out(self, dev: torch.Tensor, host: torch.Tensor):
+        if host.numel() * host.element_size() > dev.numel() * dev.element_size():
+            raise L.RtbError(-4, "host_stage_out: the host tensor is larger than the device block")
+        check(lib().rtb_host_stage_out(self._ctx, self._p(dev), C.c_void_p(host.data_ptr()),
+                                       C.c_size_t(host.numel() * host.element_size())))
+
+    def host_release(self, dev: torch.Tensor):
+        check(lib().rtb_host_release(self._ctx, self._p(dev)))
+
+    def host_join(self):
+        check(lib().rtb_host_join(self._ctx))
+
+    def host_wait(self):
+        check(lib().rtb_host_wait(self._ctx))
+
+    def host_trim(self):
+        check(lib().rtb_host_trim(self._ctx))
+
+    def host_set_stage_bytes(self, n: int):
+        check(lib().rtb_host_set_stage_bytes(self._ctx, C.c_size_t(int(n))))
+
+    def host_reduce_view(self, host: torch.Tensor, meta: Meta, axis: Optional[int], op: int, host_out: torch.Tensor,
+                         unbiased: bool = True, is_std: bool = False, norm_type: int = 2):
+        """Reduction of a tensor whose buffer is in host memory; the result goes to host_out (enqueues only)."""
+        st = L.ReduceSettings(bool(unbiased), bool(is_std), int(norm_type))
+        check(lib().rtb_host_reduce_view(self._ctx, C.c_int(dtype_code(host)), C.c_int(op), C.byref(st), C.c_void_p(host.data_ptr()),
+                                         C.c_size_t(host.numel()), C.c_size_t(meta.rank), meta.c_shape, meta.c_strides,
+                                         C.c_size_t(meta.offset), C.c_ssize_t(-1 if axis is None else axis),
+                                         C.c_void_p(host_out.data_ptr())))
+
+    def host_broadcast(self, a_host: torch.Tensor, am: Meta, b_host: torch.Tensor, bm: Meta, op: int, out_host: torch.Tensor,
+                       dim_range: Optional[Tuple[int, int]] = None):
+        """`a op b` with operand buffers in host memory, the result written row-major to out_host (this
+        call's range of the outermost output dim only).  Enqueues only."""
+        shape, sa, sb = broadcast_params(am, bm)
+        lo, hi = dim_range if dim_range is not None else (0, shape[0] if shape else 1)
+        per = 1
+        for n in shape[1:]:
+            per *= n
+        if out_host.numel() < (hi - lo) * per or out_host.dtype != a_host.dtype:
+            raise ValueError("host_broadcast: the output tensor is too small or of another dtype")
+        check(lib().rtb_host_broadcast(self._ctx, C.c_int(dtype_code(a_host)), C.c_int(op), C.c_void_p(a_host.data_ptr()),
+                                       C.c_size_t(a_host.numel()), diffs(sa), C.c_size_t(am.offset), C.c_void_p(b_host.data_ptr()),
+                                       C.c_size_t(b_host.numel()), diffs(sb), C.c_size_t(bm.offset), C.c_void_p(out_host.data_ptr()),
+                                       C.c_size_t(len(shape)), sizes(shape), C.c_size_t(lo), C.c_size_t(hi)))
 
     def mg_combine(self, buf: torch.Tensor, op: int = L.SUM, mean_count: int = 0):
         check(lib().rtb_mg_combine(self._ctx, C.c_int(dtype_code(buf)), C.c_int(op), self._p(buf), C.c_size_t(buf.numel()),

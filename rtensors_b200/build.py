@@ -25,7 +25,7 @@ COMMON = ["-std=c++17", "-O3", "-lineinfo", "--fmad=false", "--prec-div=true", "
           "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 EW_DTYPES = list(range(13))
-PLAIN = ["rtb_planner.cpp", "rtb_context.cpp", "rtb_api.cpp", "rtb_abi_v1.cpp", "rtb_reduce.cu", "rtb_reduce_ext.cu", "rtb_noalloc.cu", "rtb_mg.cu",
+PLAIN = ["rtb_planner.cpp", "rtb_context.cpp", "rtb_api.cpp", "rtb_host.cpp", "rtb_abi_v1.cpp", "rtb_reduce.cu", "rtb_reduce_ext.cu", "rtb_noalloc.cu", "rtb_mg.cu",
          "rtb_convert.cu"]
 
 

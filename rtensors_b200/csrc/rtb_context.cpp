@@ -113,6 +113,7 @@ RTB_API void rtb_ctx_destroy(rtb_ctx *c) {
     Ctx *ctx = C(c);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    rtb::host_release(ctx);
     rtb::mg_release(ctx);
     rtb_release_cached(c);
     for (auto &kv : ctx->live_blocks) cudaFree(kv.first);
@@ -163,7 +164,7 @@ RTB_API int rtb_ctx_sync(rtb_ctx *c) {
     int rc = rtb::use_device(C(c));
     if (rc) return rc;
     RTB_CUDA(cudaStreamSynchronize(C(c)->stream));
-    return RTB_OK;
+    return rtb::host_sync(C(c));  // copy-outs of host-buffer operations follow the compute stream
 }
 
 RTB_API int rtb_alloc(rtb_ctx *c, size_t bytes, void **out) {

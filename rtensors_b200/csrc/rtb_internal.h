@@ -32,7 +32,8 @@ int cuda_fail(cudaError_t e, const char *what);
 size_t dtype_size(int dtype);  // 0 for an unknown code
 
 // ---- context -----------------------------------------------------------------------------------
-struct Mg;  // multi-GPU communicator state (rtb_mg.cu)
+struct Mg;         // multi-GPU communicator state (rtb_mg.cu)
+struct HostLanes;  // transfer lanes and device slots of the host-buffer operations (rtb_host.cpp)
 struct Ctx {
     int device = 0;
     int sm_count = 0;
@@ -49,6 +50,7 @@ struct Ctx {
     std::atomic<uint64_t> ws_generation{0};   // bumped whenever device memory a captured graph may hold goes away
     cudaEvent_t order_event = nullptr;        // joins the old stream into the new one in rtb_ctx_set_stream
     Mg *mg = nullptr;                         // set by rtb_mg_init
+    HostLanes *host = nullptr;                // created by the first host-buffer operation
     // caching allocator: free blocks by rounded size; live blocks by pointer
     std::mutex mu;
     std::multimap<size_t, void *> free_blocks;
@@ -60,6 +62,8 @@ struct Ctx {
 // created.
 int workspace(Ctx *ctx, size_t bytes, void **out);
 void mg_release(Ctx *ctx);  // frees ctx->mg without any collective (context teardown)
+void host_release(Ctx *ctx);  // waits for the transfer lanes and frees them with their device slots
+int host_sync(Ctx *ctx);      // waits for the transfer lanes (no-op if there are none)
 int use_device(Ctx *ctx);  // makes ctx->device current for the calling thread
 Ctx *default_ctx();  // ctx on the current device bound to the legacy default stream (ABI v1)
 

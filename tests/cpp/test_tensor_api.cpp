@@ -223,6 +223,42 @@ int main() {
         try { u.abs_grad_map(); } catch (const TensorError &e) { threw = e.code == RTB_ERR_DTYPE; }
         ASSERT_TRUE(threw);
     }
+    {  // tensors in host memory: `a + b.T` and column sums without a resident copy, against host loops
+        const size_t R = 37, Cn = 53;
+        Cuda::HostVec<float> a(R * Cn), b(R * Cn), out(R * Cn), cols(Cn);
+        Cuda::HostVec<uint64_t> arg(R);
+        for (size_t i = 0; i < R * Cn; ++i) { a[i] = (float)((i * 7) % 31) - 15.f; b[i] = (float)((i * 5) % 17) * 0.25f; }
+        MetaTensor am = MetaTensor::contiguous({R, Cn}), bt = MetaTensor::contiguous({Cn, R}).transpose();
+        check(rtb_host_set_stage_bytes(cuda.ctx(), Cn * sizeof(float) * 4));  // four rows per stage: the ring is reused
+        cuda.host_broadcast(a, am, b, bt, BinaryOpType::Add, out, 0, R);
+        cuda.host_reduce_view<float, float>(a, am, 0, ReductionOpTypes::Sum, cols);
+        cuda.host_reduce_view<float, uint64_t>(a, am, 1, ReductionOpTypes::ArgMax, arg);
+        cuda.host_wait();
+        check(rtb_host_set_stage_bytes(cuda.ctx(), size_t(64) << 20));
+        for (size_t i = 0; i < R; ++i)
+            for (size_t j = 0; j < Cn; ++j) ASSERT_EQ(out[i * Cn + j], a[i * Cn + j] + b[j * R + i]);
+        for (size_t j = 0; j < Cn; ++j) {
+            float want = 0;
+            for (size_t i = 0; i < R; ++i) want += a[i * Cn + j];   // small integers: exact in any order
+            ASSERT_EQ(cols[j], want);
+        }
+        for (size_t i = 0; i < R; ++i) {
+            size_t best = 0;
+            for (size_t j = 1; j < Cn; ++j)
+                if (a[i * Cn + j] > a[i * Cn + best]) best = j;
+            ASSERT_EQ(arg[i], (uint64_t)best);
+        }
+        // the primitives: upload, scale on the device, copy out, give the block back
+        float *blk = cuda.host_stage_in(a);
+        cuda.host_ready(blk);
+        float two = 2.f;
+        check(rtb_scalar_op(cuda.ctx(), RTB_F32, (int)BinaryOpType::Mul, blk, &two, am.rank(), am.shape.data(), am.strides.data(), 0));
+        cuda.host_stage_out(blk, out, R * Cn);
+        cuda.host_release(blk);
+        cuda.host_join();
+        cuda.sync();
+        for (size_t i = 0; i < R * Cn; ++i) ASSERT_EQ(out[i], a[i] * 2.f);
+    }
     std::printf("ok: %d checks\n", g_checks);
     return 0;
 }

@@ -678,8 +678,6 @@ def test_host_pipeline_matches_oracle():
     hj = torch.from_numpy(rng.integers(-(1 << 20), 1 << 20, n).astype(np.int32)).pin_memory()
     ra, ri = torch.empty_like(ha).pin_memory(), torch.empty_like(hi).pin_memory()
     be = _b()
-    a, ia, ib, io = (be.alloc(n, torch.float32), be.alloc(n, torch.int32), be.alloc(n, torch.int32),
-                     be.alloc(n, torch.int32))
 
     def compute(v, length):
         mc = Meta.contiguous((length,))
@@ -689,8 +687,8 @@ def test_host_pipeline_matches_oracle():
         be.broadcast((v["ia"], mc), (v["ib"], mc), (v["iout"], mc), O.ADD)
     pipe = HostPipeline(be, chunk_elems=100_000)  # ragged last chunk, unaligned chunk starts
     for _ in range(2):
-        pipe.run(n, {"a": (ha, a), "ia": (hi, ia), "ib": (hj, ib)}, {"a": (ra, a), "iout": (ri, io)}, compute)
-    torch.cuda.synchronize()
+        pipe.run(n, {"a": ha, "ia": hi, "ib": hj}, {"a": (ra, torch.float32), "iout": (ri, torch.int32)}, compute)
+    be.host_wait()
     ref = ha.numpy().copy()
     m = O.Meta.contiguous((n,))
     for op, v in ((O.MUL, 3.0), (O.ADD, 2.0), (O.SUB, 1.0)):
