@@ -389,6 +389,33 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
                  "note": "ms = eager from Python, ms_graph = one CUDA-graph launch per step (collectives captured); ms_rest = ms_graph - "
                          "GEMMs alone = this library's kernels plus whatever of the gradient all-reduces (three per-layer buckets on a "
                          "side stream) is not hidden behind the backward GEMMs"})
+    # ---- how time grows with size for three bandwidth-bound kernels: the fixed part (launch, ramp to full DRAM
+    #      throughput, tail, the last CTA's fold) is what separates a 134 MB op from a 4 GB op of the same kernel
+    if not quick and world == 1:
+        curve = []
+        big = torch.empty(1 << 28, device=dev, dtype=f32).normal_(generator=g)
+        dst = torch.empty(1 << 27, device=dev, dtype=f32)
+        one = be.alloc(1, f32)
+        for lg in (23, 25, 26, 28):
+            n = 1 << lg
+            mflat = Meta.contiguous((n,))
+            t_sum, _ = _time(lambda: be.apply_reduce_contiguous_flat(big, one, 0, n, L.SUM), flush=True, dev=dev)
+            t_fill, _ = _time(lambda: be.fill(big, 1.0, mflat), flush=True, dev=dev)
+            entry = {"bytes": 4 * n, "us_full_sum": _sig(t_sum * 1e3), "us_fill": _sig(t_fill * 1e3)}
+            if n <= dst.numel():
+                t_copy, _ = _time(lambda: dst[:n].copy_(big[:n]), flush=True, dev=dev)
+                entry["us_torch_copy_of_the_same_bytes_read"] = _sig(t_copy * 1e3)
+            curve.append(entry)
+        # least-squares line t = t0 + bytes / bw through the full-sum points
+        xs = np.array([c["bytes"] for c in curve], dtype=np.float64)
+        ys = np.array([c["us_full_sum"] for c in curve], dtype=np.float64)
+        slope, t0 = np.polyfit(xs, ys, 1)
+        rows.append({"op": "time against size: full sum (read), fill (write), torch device copy (read + write of the same element count)",
+                     "shape": "2^23 .. 2^28 f32", "points": curve, "full_sum_fit_us": _sig(float(t0)),
+                     "full_sum_fit_gbs": _sig(1e-3 / float(slope)), "l2": "flushed",
+                     "note": "full_sum_fit_us = the size-independent part of a one-wave reduction's time; every op of a few "
+                             "hundred MB carries it, which is why their fractions sit below the multi-GB ops'"})
+        del big, dst
     torch.cuda.synchronize()
     return rows
 
