@@ -994,7 +994,11 @@ def test_ext_reductions_match_oracle_and_f64_truth(dt, outer, r, inner):
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64], ids=["f32", "f64"])
 @pytest.mark.parametrize("outer,r,inner,pitch", [(1, 4096, 1024, 1024), (2, 1000, 1156, 1156), (1, 257, 2048, 2048), (3, 300, 1024, 1024),
-                                                 (1, 2048, 512, 1024), (1, 4099, 3072, 4096), (5, 67, 640, 640)])
+                                                 (1, 2048, 512, 1024), (1, 4099, 3072, 4096), (5, 67, 640, 640),
+                                                 # rows of at least eight strips: the side-by-side form -- a ragged last strip, idle
+                                                 # warps in the last group, chunk counts that fill the resident CTAs twice over,
+                                                 # and enough (outer, group) items that nothing is chunked
+                                                 (2, 513, 1924, 1924), (1, 130, 1792, 2048), (64, 515, 1024, 1024), (600, 128, 1024, 1024)])
 def test_state_merging_column_reductions_on_aligned_rows(dt, outer, r, inner, pitch):
     """Few column tiles and 16-byte aligned rows -- the chunked one-wave regime of the vector column
     kernel (software-pipelined for variance and positions): ragged chunks, a ragged last tile, rows
