@@ -216,6 +216,18 @@ static int give_back_after_compute(Ctx *ctx, HostSlot &s) {
     return RTB_OK;
 }
 
+// Blocks a composite call holds: whatever is still listed when the call leaves (an error path) goes back
+// to the pool.
+struct Held {
+    HostLanes *h;
+    std::vector<size_t> idx;
+    explicit Held(HostLanes *lanes) : h(lanes) {}
+    ~Held() {
+        for (size_t i : idx) h->slots[i].taken = false;
+    }
+    void done() { idx.clear(); }
+};
+
 static size_t product(const size_t *shape, size_t from, size_t rank) {
     size_t n = 1;
     for (size_t d = from; d < rank; ++d) n *= shape[d];
@@ -375,12 +387,13 @@ RTB_API int rtb_host_reduce_view(rtb_ctx *c, int dtype, int redop, const rtb_red
     if (int rc = rtb::lanes(C(c), &h)) return rc;
     std::lock_guard<std::mutex> lock(h->mu);
     size_t in = 0, out = 0;
+    rtb::Held held(h);
     if (int rc = rtb::stage_in(C(c), h, src_host, src_len * es, &in)) return rc;
-    if (int rc = rtb::take_output(C(c), h, out_elems * out_es, &out)) {
-        h->slots[in].taken = false;
-        return rc;
-    }
+    held.idx.push_back(in);
+    if (int rc = rtb::take_output(C(c), h, out_elems * out_es, &out)) return rc;
+    held.idx.push_back(out);
     RTB_CUDA(cudaStreamWaitEvent(C(c)->stream, h->slots[in].ready, 0));
+    held.done();  // from here on both blocks are returned below, with the events that protect them
     int rc = rtb_reduce_view_ex(c, dtype, redop, settings, h->slots[in].ptr, rank, shape, strides, offset, axis, h->slots[out].ptr);
     if (rc == RTB_OK) rc = rtb::stage_out(C(c), h, h->slots[out].ptr, dst_host, out_elems * out_es, &h->slots[out]);
     h->slots[out].taken = false;  // idle once the copy-out just enqueued is done
@@ -413,12 +426,18 @@ RTB_API int rtb_host_broadcast(rtb_ctx *c, int dtype, int binop, const void *lef
     const size_t n_stages = (end - begin + group - 1) / group;
     const size_t ring = std::min<size_t>(3, n_stages);
     size_t l = 0, r = 0, st[3] = {0, 0, 0};
+    rtb::Held held(h);
     if (int rc = rtb::stage_in(C(c), h, left_host, left_len * es, &l)) return rc;
+    held.idx.push_back(l);
     if (int rc = rtb::stage_in(C(c), h, right_host, right_len * es, &r)) return rc;
-    for (size_t k = 0; k < ring; ++k)
+    held.idx.push_back(r);
+    for (size_t k = 0; k < ring; ++k) {
         if (int rc = rtb::take_output(C(c), h, stage_bytes, &st[k])) return rc;
+        held.idx.push_back(st[k]);
+    }
     RTB_CUDA(cudaStreamWaitEvent(C(c)->stream, h->slots[l].ready, 0));
     RTB_CUDA(cudaStreamWaitEvent(C(c)->stream, h->slots[r].ready, 0));
+    held.done();  // from here on every block is returned below, with the events that protect it
 
     std::vector<size_t> sshape(shape, shape + rank);
     std::vector<ptrdiff_t> sd(rank);
@@ -426,7 +445,13 @@ RTB_API int rtb_host_broadcast(rtb_ctx *c, int dtype, int binop, const void *lef
     for (size_t k = 0, i = begin; i < end && rc == RTB_OK; ++k, i += group) {
         const size_t n = std::min(group, end - i);
         HostSlot &stage = h->slots[st[k % ring]];
-        if (k >= ring) RTB_CUDA(cudaStreamWaitEvent(C(c)->stream, stage.idle_down, 0));  // the block's previous copy-out is done
+        if (k >= ring) {  // the block's previous copy-out is done
+            cudaError_t e = cudaStreamWaitEvent(C(c)->stream, stage.idle_down, 0);
+            if (e != cudaSuccess) {
+                rc = rtb::cuda_fail(e, "cudaStreamWaitEvent(stage)");
+                break;
+            }
+        }
         if (rank) sshape[0] = n;
         rtb_meta_contiguous_strides(rank, sshape.data(), sd.data());
         rc = rtb_broadcast(c, dtype, binop, h->slots[l].ptr, stride_l, off_l + (rank ? i * stride_l[0] : 0), h->slots[r].ptr, stride_r,
