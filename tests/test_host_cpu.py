@@ -229,6 +229,29 @@ def test_no_device_compute_fails_loudly_without_gpu():
         rt.CudaB200(0)
 
 
+def test_host_buffer_entry_points_check_their_arguments_before_any_cuda_call():
+    """Null contexts and null buffers are refused with RTB_ERR_INVALID (-1) on a box without a GPU too."""
+    lib = rt.lib()
+    null = C.c_void_p(0)
+    out = C.c_void_p()
+    one = (C.c_size_t * 1)(4)
+    st = (C.c_ssize_t * 1)(1)
+    assert lib.rtb_host_stage_in(null, null, C.c_size_t(16), C.byref(out)) == -1
+    assert lib.rtb_host_scratch(null, C.c_size_t(16), C.byref(out)) == -1
+    assert lib.rtb_host_ready(null, null) == -1
+    assert lib.rtb_host_stage_out(null, null, null, C.c_size_t(16)) == -1
+    assert lib.rtb_host_release(null, null) == -1
+    assert lib.rtb_host_join(null) == -1 and lib.rtb_host_wait(null) == -1 and lib.rtb_host_trim(null) == -1
+    assert lib.rtb_host_set_stage_bytes(null, C.c_size_t(1 << 20)) == -1
+    assert lib.rtb_host_pin(null, C.c_size_t(16)) == -1
+    assert lib.rtb_host_alloc(C.c_size_t(16), None) == -1
+    assert lib.rtb_host_reduce_view(null, C.c_int(10), C.c_int(1), None, null, C.c_size_t(4), C.c_size_t(1), one, st, C.c_size_t(0),
+                                    C.c_ssize_t(0), null) == -1
+    assert lib.rtb_host_broadcast(null, C.c_int(10), C.c_int(0), null, C.c_size_t(4), st, C.c_size_t(0), null, C.c_size_t(4), st,
+                                  C.c_size_t(0), null, C.c_size_t(1), one, C.c_size_t(0), C.c_size_t(4)) == -1
+    assert b"null" in lib.rtb_last_error_string()
+
+
 # ---- the reference's view-arithmetic tests, replayed on the library's host-side planner (no GPU)
 _HOST_KINDS = ("view_check", "view_set", "view_values", "slice_error", "permute_error", "view_as_error", "strides_of", "meta_check", "broadcast_error", "assign_shape_error")
 
