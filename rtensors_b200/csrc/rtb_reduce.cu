@@ -144,7 +144,7 @@ template <typename T> struct SrcL1 {
 // (rtb_mg.cuh) and `count` is the global element count; Peers = NoPeers: single GPU, count = n.
 template <typename T, int OP, typename Src, typename Peers>
 __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, T *partials, unsigned int *counter,
-                                                             T *out, int mean, size_t count, Peers peers) {
+                                                             T *out, int mean, size_t count, Peers peers, size_t block_vecs) {
     grid_dep_wait();
     __shared__ T smem[kWarps];
     __shared__ bool is_last;
@@ -161,8 +161,15 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
     }
     const size_t tail0 = head + nvec * N;
     const Src body = src.advanced(head);
-    const size_t stride = (size_t)gridDim.x * kBlock;
-    size_t i = (size_t)blockIdx.x * kBlock + threadIdx.x;
+    const size_t gstride = (size_t)gridDim.x * kBlock;
+    // block_vecs == 0: the grid sweeps the array together (CTA b takes vectors b*256 + t, + grid*256, ...);
+    // otherwise CTA b owns the contiguous vectors [b*block_vecs, (b+1)*block_vecs)
+    const size_t stride = block_vecs ? (size_t)kBlock : gstride;
+    size_t i = block_vecs ? (size_t)blockIdx.x * block_vecs + threadIdx.x : (size_t)blockIdx.x * kBlock + threadIdx.x;
+    if (block_vecs) {
+        const size_t hi = ((size_t)blockIdx.x + 1) * block_vecs;
+        if (hi < nvec) nvec = hi;
+    }
     // four independent 16-byte loads in flight per thread
     for (; i + 3 * stride < nvec; i += 4 * stride) {
         T v[4][N];
@@ -180,9 +187,9 @@ __global__ void __launch_bounds__(kBlock) flat_reduce_kernel(Src src, size_t n, 
         for (int j = 0; j < N; ++j) acc[0] = Comb<T, OP>::apply(acc[0], v[j]);
     }
     // scalar head and tail (at most 2*(N-1) elements when vectorised; everything otherwise)
-    for (size_t k = (size_t)blockIdx.x * kBlock + threadIdx.x; k < head; k += stride)
+    for (size_t k = (size_t)blockIdx.x * kBlock + threadIdx.x; k < head; k += gstride)
         acc[1] = Comb<T, OP>::apply(acc[1], src.scalar(k));
-    for (size_t k = tail0 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += stride)
+    for (size_t k = tail0 + (size_t)blockIdx.x * kBlock + threadIdx.x; k < n; k += gstride)
         acc[2] = Comb<T, OP>::apply(acc[2], src.scalar(k));
 
     grid_dep_launch();  // streaming done: the next kernel of the stream may start to move in
@@ -784,12 +791,26 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean, size_t count = 0,
     // 7.29 TB/s at 4 CTAs/SM, 7.14 at 8 and 6.97 at 16 (fewer concurrent streams, better DRAM locality)
     size_t items = (n / N + (size_t)kBlock * 4 - 1) / ((size_t)kBlock * 4);
     unsigned grid = grid_for(ctx, items, kStreamCtasPerSm);
+    // Mid-size plain inputs (more than one wave of 32 KiB blocks, at most 16384 of them = 512 MiB): one CTA per
+    // contiguous 32 KiB block, many waves.  The hardware's CTA scheduler then evens out the SMs, which the
+    // one-wave sweep cannot: measured 2^25 f32 26.2 -> 23.8 us, 2^26 46.4 -> 42.6, 2^27 84.7 -> 79.5; from
+    // 1 GiB on both forms are within 1-2 %, and the two-stream L1 source gains nothing, so those stay as
+    // they were.
+    size_t block_vecs = 0;
+    if (std::is_same<Src, SrcPlain<T>>::value) {
+        constexpr size_t kBlockVecs = 2048;
+        const size_t blocks = (n / N + kBlockVecs - 1) / kBlockVecs;
+        if (blocks > grid && blocks <= 16384) {
+            block_vecs = kBlockVecs;
+            grid = (unsigned)blocks;
+        }
+    }
     void *ws = nullptr;
     int rc = workspace(ctx, (size_t)grid * sizeof(T), &ws);
     if (rc != RTB_OK) return rc;
     unsigned int *counter = reinterpret_cast<unsigned int *>(ws);
     T *partials = reinterpret_cast<T *>(reinterpret_cast<char *>(ws) + kWorkspaceHeader);
-    launch_dep(ctx, grid, kBlock, flat_reduce_kernel<T, OP, Src, Peers>, src, n, partials, counter, out, mean, count, peers);
+    launch_dep(ctx, grid, kBlock, flat_reduce_kernel<T, OP, Src, Peers>, src, n, partials, counter, out, mean, count, peers, block_vecs);
     return check_launch(ctx, "flat_reduce_kernel");
 }
 
