@@ -308,7 +308,10 @@ def _sum_tol(n):
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
-@pytest.mark.parametrize("n,start", [(1, 0), (2, 1), (31, 0), (1025, 3), (4096, 0), ((1 << 20) + 7, 1), (1 << 24, 0)])
+@pytest.mark.parametrize("n,start", [(1, 0), (2, 1), (31, 0), (1025, 3), (4096, 0), ((1 << 20) + 7, 1), (1 << 24, 0),
+                                     # sizes that take one CTA per 32 KiB block: just above the one-wave limit with a
+                                     # ragged last block, and a misaligned start with scalar head and tail elements
+                                     ((5 << 20) + 1, 2), ((1 << 23) + 4099, 3)])
 def test_flat_reductions(dt, n, start):
     rng = np.random.default_rng(n + start)
     x = rng.standard_normal(n + start + 1).astype(dt)
