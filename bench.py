@@ -256,7 +256,7 @@ def main():
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--scale-log2", type=int, default=0, help="run the step at 1/2^s of every tensor (small profiling runs)")
     ap.add_argument("--case", default=None, help="run one small profiling case and exit: " + ", ".join(
-        ("flat", "c3", "red", "ext", "convert", "transpose", "mid", "l1", "mlp")))
+        ("flat", "c3", "red", "ext", "convert", "transpose", "mid", "sum", "host", "l1", "mlp")))
     ap.add_argument("--case-arg", type=int, default=None)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -430,6 +430,8 @@ def small_case(be, which: str, arg=None):
       ext        variance / logsumexp / L2 norm / argmax of (8192,8192) over both axes, twice each
       convert    dtype conversion of 2^26 elements: f32->f64, f32->i32, u8->f32, f32->u8, twice each
       transpose  contiguous() of a transposed (8192,8192) f32 matrix and a.T + b, twice each
+      host       the host-buffer lanes: 4 GiB copied out, 4 GiB uploaded and reduced, and both at once (prints ms)
+      sum        full sums of 2^25 .. 2^28 f32, twice each, L2 flushed between
       l1         mean_l1_loss of two (4096,4096) without and with the gradient map, 3 times, L2 flushed between
       mid        mid-size ops (L1 loss, config-1 add and fused add+sum, bias add, reduce-to-shape) with L2 flushes
       mlp        the fused bias+relu+mask kernel, reduce-to-shape and SGD update at MLP sizes, L2 flushed between"""
@@ -497,6 +499,54 @@ def small_case(be, which: str, arg=None):
         for _ in range(2):
             be.contiguous(a, m.permute((1, 0)))
             be.broadcast((a, m.permute((1, 0))), (b, m), (out, m), L.ADD)
+    elif which == "host":
+        # the host-buffer lanes alone: 4 GiB result copied out by rtb_host_broadcast, a 4 GiB input uploaded and
+        # reduced, and both in either order (CUDA events over 3 repetitions each; prints one line of ms)
+        import json
+        n0, per = 64, 1 << 24
+        h_a, h_b = torch.randn(per).pin_memory(), torch.randn(per).pin_memory()
+        am, bm = Meta((n0, per), (0, 1), 0), Meta.contiguous((per,))
+        h_out = torch.empty(n0 * per).pin_memory()
+        h_f = torch.randn(1 << 30).pin_memory()
+        h_r = torch.empty(1).pin_memory()
+        r = be.alloc(1, f32)
+
+        def bc():
+            be.host_broadcast(h_a, am, h_b, bm, L.ADD, h_out)
+
+        def red():
+            blk = be.host_stage_in(h_f)
+            be.host_ready(blk)
+            be.apply_reduce_contiguous_flat(blk, r, 0, h_f.numel(), L.SUM)
+            be.host_stage_out(r, h_r)
+            be.host_release(blk)
+
+        def timed(fn, reps=3):
+            fn()
+            be.host_join()
+            torch.cuda.synchronize()
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record()
+            for _ in range(reps):
+                fn()
+                be.host_join()
+            e_.record()
+            torch.cuda.synchronize()
+            return round(s_.elapsed_time(e_) / reps, 1)
+        be.sync_stream()
+        print(json.dumps({"case": "host", "bytes_each_way": 4 << 30,
+                          "ms_broadcast_to_host_alone": timed(bc), "ms_upload_and_reduce_alone": timed(red),
+                          "ms_broadcast_then_reduce": timed(lambda: (bc(), red())),
+                          "ms_reduce_then_broadcast": timed(lambda: (red(), bc()))}))
+    elif which == "sum":
+        # full sums of 2^25, 2^26 and 2^27 f32 (one CTA per 32 KiB block) and of 2^28 (one wave), L2 flushed between
+        src = torch.randn(1 << 28, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        one = be.alloc(1, f32)
+        for _ in range(2):
+            for lg in (25, 26, 27, 28):
+                flush.add_(1)
+                be.apply_reduce_contiguous_flat(src, one, 0, 1 << lg, L.SUM)
     elif which in ("l1", "mid", "mlp"):
         n = 4096 * 4096
         src = torch.randn(2 * n, device=dev)
