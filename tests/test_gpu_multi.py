@@ -90,7 +90,8 @@ def _library_combines(be, rank, world, rng):
     from rtensors_b200 import _lib as L
     from rtensors_b200 import sharding
     from rtensors_b200.meta import Meta
-    x = rng.standard_normal((1 << 22) + 10).astype(np.float32)
+    # 6.3 M elements per rank at world 2: the size range where the flat kernel runs one CTA per 32 KiB block
+    x = rng.standard_normal((12 << 20) + 10).astype(np.float32)
     lo, hi = sharding.scalar_slab(x.size, world, rank)
     local = be.alloc_from_slice(x[lo:hi])
     for rep in range(3):                       # repeated: the two epoch-parity buffers are reused
@@ -106,7 +107,7 @@ def _library_combines(be, rank, world, rng):
             if op in (L.MAX, L.MIN):
                 assert g == nccl == want
             else:
-                tol = 1e-5 * 23 * float(np.abs(x).sum()) / (x.size if op == L.MEAN else 1)
+                tol = 1e-5 * 24 * float(np.abs(x).sum()) / (x.size if op == L.MEAN else 1)
                 assert abs(g - nccl) <= tol and abs(g - want) <= tol
             same = [torch.zeros(1, device=got.device) for _ in range(world)]
             dist.all_gather(same, got)
