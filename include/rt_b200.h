@@ -150,7 +150,8 @@ int rtb_d2d(rtb_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
  *      most twice as large, preferring one whose last readers are done; while every candidate is still in
  *      use, up to three blocks per kind and size class are allocated rather than waited for (an upload, the
  *      kernels and a copy-out each hold one), after which the request shares a busy block and its first
- *      writer waits.  Blocks stay in the pool until rtb_host_trim or rtb_ctx_destroy.
+ *      writer waits.  Blocks stay in the pool until rtb_host_trim or rtb_ctx_destroy; when the device has no
+ *      room for a block that is needed, the pool's unused blocks are given back first.
  *
  *      rtb_host_stage_in    takes a block from the pool and starts host -> block on the upload lane.
  *                           The compute stream does NOT wait for it until rtb_host_ready(block): work

@@ -91,6 +91,15 @@ static bool slot_is_idle(const HostSlot &s) {
 // 110 ms for 5.6 GB up and 4.3 GB down).
 static constexpr size_t kPoolDepth = 3;
 
+// frees a block's memory and events; the entry stays in the table as an empty one (ptr == nullptr)
+static void drop_block(HostSlot &s) {
+    cudaFree(s.ptr);
+    cudaEventDestroy(s.ready);
+    cudaEventDestroy(s.idle_compute);
+    cudaEventDestroy(s.idle_down);
+    s = HostSlot();
+}
+
 static int new_slot(HostLanes *h, size_t bytes, bool output, size_t *index) {
     HostSlot s;
     s.output = output;
@@ -110,6 +119,12 @@ static int new_slot(HostLanes *h, size_t bytes, bool output, size_t *index) {
         cudaGetLastError();
         return RTB_ERR_CUDA;
     }
+    for (size_t i = 0; i < h->slots.size(); ++i)
+        if (!h->slots[i].ptr) {  // an empty entry left by drop_block
+            h->slots[i] = s;
+            *index = i;
+            return RTB_OK;
+        }
     h->slots.push_back(s);
     *index = h->slots.size() - 1;
     return RTB_OK;
@@ -121,7 +136,7 @@ static int take_slot(HostLanes *h, size_t bytes, bool output, size_t *index) {
     bool best_idle = false;
     for (size_t i = 0; i < h->slots.size(); ++i) {
         const HostSlot &s = h->slots[i];
-        if (s.output != output || s.bytes < bytes || s.bytes / 2 > bytes) continue;
+        if (!s.ptr || s.output != output || s.bytes < bytes || s.bytes / 2 > bytes) continue;
         ++in_class;
         if (s.taken) continue;
         const bool idle = slot_is_idle(s);
@@ -133,8 +148,19 @@ static int take_slot(HostLanes *h, size_t bytes, bool output, size_t *index) {
     cudaGetLastError();  // cudaEventQuery reports cudaErrorNotReady through the last-error state
     if (best == SIZE_MAX || (!best_idle && in_class < kPoolDepth)) {
         size_t fresh = 0;
-        if (new_slot(h, bytes, output, &fresh) == RTB_OK) best = fresh;
-        else if (best == SIZE_MAX) return fail(RTB_ERR_CUDA, "no device memory for a host-buffer block of %zu bytes", bytes);
+        if (new_slot(h, bytes, output, &fresh) == RTB_OK) {
+            best = fresh;
+        } else if (best == SIZE_MAX) {
+            // the device is full and nothing in the pool fits: give the pool's unused blocks whose readers
+            // are done back to the device (blocks of other sizes pile up when a host moves tensors of many
+            // different sizes) and ask once more.  Entries keep their positions: callers hold indices.
+            for (HostSlot &s : h->slots)
+                if (!s.taken && s.ptr && slot_is_idle(s)) drop_block(s);
+            cudaGetLastError();
+            if (new_slot(h, bytes, output, &fresh) != RTB_OK)
+                return fail(RTB_ERR_CUDA, "no device memory for a host-buffer block of %zu bytes", bytes);
+            best = fresh;
+        }
     }
     h->slots[best].taken = true;
     *index = best;
@@ -152,12 +178,8 @@ void host_release(Ctx *ctx) {
     if (!h) return;
     cudaStreamSynchronize(h->up);
     cudaStreamSynchronize(h->down);
-    for (HostSlot &s : h->slots) {
-        cudaFree(s.ptr);
-        cudaEventDestroy(s.ready);
-        cudaEventDestroy(s.idle_compute);
-        cudaEventDestroy(s.idle_down);
-    }
+    for (HostSlot &s : h->slots)
+        if (s.ptr) drop_block(s);
     cudaStreamDestroy(h->up);
     cudaStreamDestroy(h->down);
     cudaEventDestroy(h->mark);
@@ -345,18 +367,8 @@ RTB_API int rtb_host_trim(rtb_ctx *c) {
     HostLanes *h = C(c)->host;
     if (!h) return RTB_OK;
     std::lock_guard<std::mutex> lock(h->mu);
-    std::vector<HostSlot> kept;
-    for (HostSlot &s : h->slots) {
-        if (s.taken) {
-            kept.push_back(s);
-            continue;
-        }
-        cudaFree(s.ptr);
-        cudaEventDestroy(s.ready);
-        cudaEventDestroy(s.idle_compute);
-        cudaEventDestroy(s.idle_down);
-    }
-    h->slots.swap(kept);
+    for (HostSlot &s : h->slots)
+        if (!s.taken && s.ptr) rtb::drop_block(s);
     return RTB_OK;
 }
 
