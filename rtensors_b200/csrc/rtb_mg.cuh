@@ -5,7 +5,7 @@
 // reader that sees the expected epoch also sees the payload -- no fence, no separate flag.  A rank
 // stores its packets into slot [epoch parity][its rank] of EVERY rank's buffer (its own included)
 // with plain st.global over NVLink, then polls the nranks slots of its own buffer and folds them in
-// rank order, so all ranks compute the same bits.  No TMA, no multicast, no library kernel ever sees
+// rank order, so all ranks compute the same bits.  No bulk-copy engine, no switch-side replication, no library kernel ever sees
 // a peer pointer.
 //
 // Two buffers by epoch parity are enough: a rank can only enter exchange e+2 after it has read every
