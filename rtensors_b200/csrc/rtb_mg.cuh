@@ -5,8 +5,8 @@
 // reader that sees the expected epoch also sees the payload -- no fence, no separate flag.  A rank
 // stores its packets into slot [epoch parity][its rank] of EVERY rank's buffer (its own included)
 // with plain st.global over NVLink, then polls the nranks slots of its own buffer and folds them in
-// rank order, so all ranks compute the same bits.  No bulk-copy engine, no switch-side replication, no library kernel ever sees
-// a peer pointer.
+// rank order, so all ranks compute the same bits.  No bulk-copy engine, no switch-side replication,
+// and no library kernel ever sees a peer pointer.
 //
 // Two buffers by epoch parity are enough: a rank can only enter exchange e+2 after it has read every
 // rank's packets of e+1, and a rank sends those only after it has finished reading exchange e.
