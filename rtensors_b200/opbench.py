@@ -2,6 +2,12 @@
 the launching stream (10 back-to-back launches per event pair, median of 5 pairs), with the
 algorithmic HBM bytes that define its roofline.
 
+L2 between launches: read-only ops below 1 GiB run with the L2 flushed before every launch (a 268 MB input
+is only twice the L2, and what a back-to-back repetition finds there depends on the view); in-place and
+write-only ops on more than the L2 run back to back instead, so that every launch pays the write-back of
+its predecessor's dirty lines -- flushed, up to 126 MB of a launch's own writes would drain after its end
+and go uncharged.
+
 Algorithmic bytes (s = element size): in-place scalar/unary op 2*s*n; same-shape binary 3*s*n;
 broadcast binary s*(n_out + n_A + n_B) (each operand's unique elements once); axis reduce
 s*(outer*R*inner + outer*inner); flat reduce s*n + s; fused mean_l1_loss 2*s*n + s; reduce-to-shape
@@ -179,13 +185,13 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
     for opn, op in (("sum", L.SUM), ("mean", L.MEAN), ("max", L.MAX), ("min", L.MIN)):
         for axis in (0, 1):
             add(f"{opn}_at({axis}) f32", f"({S},{S})", 4 * (S * S + S), S * S,
-                (lambda op=op, axis=axis: be.apply_reduce((src, msq), r1, axis, op)), flush=S * S * 4 < (200 << 20))
+                (lambda op=op, axis=axis: be.apply_reduce((src, msq), r1, axis, op)), flush=S * S * 4 < (1 << 30))
     # reductions over a strided view: an (S,S) window of an (S,2S) matrix, reduced in place, against
     # the reference's recipe for non-contiguous tensors (copy the view contiguous, then reduce)
     win = Meta.contiguous((S, 2 * S)).slice(1, S // 2, S // 2 + S, 1)
     for axis in (0, 1):
         add(f"sum_at({axis}) f32 over a strided window, no copy", f"({S},{S}) window of ({S},{2 * S})", 4 * (S * S + S), S * S,
-            (lambda axis=axis: be.reduce_view(src, win, axis, L.SUM)), flush=S * S * 4 < (200 << 20))
+            (lambda axis=axis: be.reduce_view(src, win, axis, L.SUM)), flush=S * S * 4 < (1 << 30))
 
     # elementwise ops in place on the same window (rows of S elements with a pitch of 2S)
     add("scalar_add f32 in place on a strided window", f"({S},{S}) window of ({S},{2 * S})", 8 * S * S, S * S,
@@ -198,7 +204,7 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
         tmp = be.contiguous(src, win)
         be.apply_reduce((tmp, msq), r1, 1, L.SUM)
     add("sum_at(1) f32 over the same window, copy first (reference recipe)", f"({S},{S}) window of ({S},{2 * S})",
-        4 * (S * S + S), S * S, copy_then_reduce, flush=S * S * 4 < (200 << 20),
+        4 * (S * S + S), S * S, copy_then_reduce, flush=S * S * 4 < (1 << 30),
         note="algorithmic bytes of the reduction alone; the copy moves 2x more")
     # transposed views: contiguous() (the transposing tile kernel), a reduction along the view's
     # strided-then-dense dims in place, and a binary op with one transposed operand
@@ -208,7 +214,7 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
         lambda: be.contiguous(src, tview))
     for axis in (0, 1):
         add(f"sum_at({axis}) f32 over the transposed view, no copy", f"({S},{S}) strides (1,{S})", 4 * (S * S + S), S * S,
-            (lambda axis=axis: be.reduce_view(src, tview, axis, L.SUM)), flush=S * S * 4 < (200 << 20))
+            (lambda axis=axis: be.reduce_view(src, tview, axis, L.SUM)), flush=S * S * 4 < (1 << 30))
     add("a.T + b f32", f"({S},{S})", 12 * S * S, S * S,
         lambda: be.broadcast((src, tview), (src[S * S:], msq), (tmp_t, msq), L.ADD))
     del tmp_t
@@ -228,7 +234,7 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
         for axis in (0, 1):
             add(f"{opn}_at({axis}) f32", f"({S},{S})", 4 * (S * S + S), S * S,
                 (lambda op=op, axis=axis, args=args, o1=o1: be.apply_reduce_ex((src, msq), o1, axis, op, *args)),
-                flush=S * S * 4 < (200 << 20))
+                flush=S * S * 4 < (1 << 30))
         add(f"{opn}_at(1) f32", str(d3), 4 * (m3.size + d3[0] * d3[2]), m3.size,
             (lambda op=op, args=args, o3=o3: be.apply_reduce_ex((src, m3), o3, 1, op, *args)))
     mflat = Meta.contiguous((n4,))
