@@ -420,7 +420,8 @@ def run(be, peak_gbs: float, world: int = 1, rank: int = 0, quick: bool = False)
                      "shape": "2^23 .. 2^28 f32", "points": curve, "full_sum_fit_us": _sig(float(t0)),
                      "full_sum_fit_gbs": _sig(1e-3 / float(slope)), "l2": "flushed",
                      "note": "full_sum_fit_us = the size-independent part of a one-wave reduction's time; every op of a few "
-                             "hundred MB carries it, which is why their fractions sit below the multi-GB ops'"})
+                             "hundred MB carries it, which is why their fractions sit below the multi-GB ops'; the fill points are optimistic by up "
+                             "to 126 MB of write-back that drains from L2 after the kernel has ended"})
         del big, dst
     torch.cuda.synchronize()
     return rows
