@@ -326,6 +326,8 @@ RTB_API int rtb_host_stage_out(rtb_ctx *c, const void *src_dev, void *dst_host, 
     HostSlot *slot = nullptr;
     for (HostSlot &s : h->slots)
         if (s.taken && (const char *)src_dev >= (const char *)s.ptr && (const char *)src_dev < (const char *)s.ptr + s.bytes) slot = &s;
+    if (slot && (const char *)src_dev + bytes > (const char *)slot->ptr + slot->bytes)
+        return rtb::fail(RTB_ERR_BOUNDS, "rtb_host_stage_out: %zu bytes from this address run past the end of its pool block", bytes);
     return rtb::stage_out(C(c), h, src_dev, dst_host, bytes, slot);
 }
 

@@ -152,6 +152,10 @@ def test_pool_blocks_are_reused_without_stale_data_and_without_waiting_for_unuse
         be.host_release(kept)                               # not taken any more
     with pytest.raises(L.RtbError):
         be.host_ready(torch.empty(4, device="cuda"))        # not a pool block
+    small = be.host_scratch(16, torch.float32)
+    rc = L.lib().rtb_host_stage_out(be._ctx, C.c_void_p(small.data_ptr()), C.c_void_p(back.data_ptr()), C.c_size_t(1 << 20))
+    assert rc == L.ERR_BOUNDS                               # a copy-out may not run past the end of its block
+    be.host_release(small)
 
 
 def test_host_operations_are_refused_during_capture():
