@@ -99,7 +99,7 @@ fn check(rc: c_int) -> Result<(), TensorError> {
         RTB_ERR_SHAPE => TensorError::InvalidShape(msg),
         RTB_ERR_DIM => TensorError::InvalidDim(msg),
         RTB_ERR_NONCONTIG => TensorError::WrongDims(msg),
-        _ => TensorError::BackendError(msg),
+        _ => TensorError::CudaError(msg),
     })
 }
 
