@@ -671,7 +671,7 @@ def run_e2e(args, be, sh, world, rank, dev, barrier, d):
     same = all(np.array_equal(h.numpy(), r.cpu().numpy()) for h, r in zip(h_res, (r_m0, r_m1, r_t1, r_f)))
     return {"value": sig(sh.step_bytes() / (e_ms * 1e-3) / 1e9), "unit": "GB/s", "ms_per_step": sig(e_ms),
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": esteps, "results_read_back": bool(same),
-            "how": "the library's host-buffer operations (rtb_host_*): broadcast result produced in 64 MiB stages into a ring of "
+            "how": "the library's host-buffer operations (rtb_host_*): broadcast result produced in stages (about 64 MiB, at least one index of the outermost dim) into a ring of "
                    "three device blocks and copied out behind the next stage's kernel, reduction inputs uploaded on the upload lane, "
                    "each reduction waiting for its own input only; pinned host buffers; bytes are this rank's"}
 
