@@ -207,16 +207,25 @@ static int wait_idle(cudaStream_t writer, const HostSlot &s) {
 static int stage_in(Ctx *ctx, HostLanes *h, const void *src_host, size_t bytes, size_t *index) {
     if (int rc = take_slot(h, bytes, false, index)) return rc;
     HostSlot &s = h->slots[*index];
-    if (int rc = wait_idle(h->up, s)) return rc;
-    if (bytes) RTB_CUDA(cudaMemcpyAsync(s.ptr, src_host, bytes, cudaMemcpyHostToDevice, h->up));
-    RTB_CUDA(cudaEventRecord(s.ready, h->up));
-    return RTB_OK;
+    int rc = wait_idle(h->up, s);
+    if (rc == RTB_OK && bytes) {
+        cudaError_t e = cudaMemcpyAsync(s.ptr, src_host, bytes, cudaMemcpyHostToDevice, h->up);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaMemcpyAsync(host to block)");
+    }
+    if (rc == RTB_OK) {
+        cudaError_t e = cudaEventRecord(s.ready, h->up);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaEventRecord(ready)");
+    }
+    if (rc != RTB_OK) s.taken = false;  // nothing was enqueued on it that a later user would not wait for
+    return rc;
 }
 
 // a slot the compute stream writes first (a result or a staging block)
 static int take_output(Ctx *ctx, HostLanes *h, size_t bytes, size_t *index) {
     if (int rc = take_slot(h, bytes, true, index)) return rc;
-    return wait_idle(ctx->stream, h->slots[*index]);
+    int rc = wait_idle(ctx->stream, h->slots[*index]);
+    if (rc != RTB_OK) h->slots[*index].taken = false;
+    return rc;
 }
 
 static int stage_out(Ctx *ctx, HostLanes *h, const void *src_dev, void *dst_host, size_t bytes, HostSlot *slot) {
