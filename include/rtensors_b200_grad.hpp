@@ -37,6 +37,8 @@ template <typename T> struct Var {
     TensorBase<T> t;
     NodeKey op = 0;
     std::shared_ptr<GradCell<T>> grad;  // set for leaves
+    Var() = default;
+    Var(TensorBase<T> tensor) : t(std::move(tensor)) {}  // an untracked tensor
 };
 
 template <typename T> struct GradNode {
