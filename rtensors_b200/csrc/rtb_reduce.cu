@@ -791,17 +791,21 @@ int flat_launch(Ctx *ctx, Src src, size_t n, T *out, int mean, size_t count = 0,
     // 7.29 TB/s at 4 CTAs/SM, 7.14 at 8 and 6.97 at 16 (fewer concurrent streams, better DRAM locality)
     size_t items = (n / N + (size_t)kBlock * 4 - 1) / ((size_t)kBlock * 4);
     unsigned grid = grid_for(ctx, items, kStreamCtasPerSm);
-    // Mid-size plain inputs (more than one wave of 32 KiB blocks, at most 16384 of them = 512 MiB): one CTA per
-    // contiguous 32 KiB block, many waves.  The hardware's CTA scheduler then evens out the SMs, which the
-    // one-wave sweep cannot: measured 2^25 f32 26.2 -> 23.8 us, 2^26 46.4 -> 42.6, 2^27 84.7 -> 79.5; from
-    // 1 GiB on both forms are within 1-2 %, and the two-stream L1 source gains nothing, so those stay as
-    // they were.
+    // Plain inputs of more than one wave of 32 KiB blocks: one CTA per contiguous block, many waves, the block
+    // size doubled until at most 16384 blocks remain (their partials are folded by one CTA).  The hardware's
+    // CTA scheduler then evens out the SMs, which the one-wave sweep cannot: measured 2^25 f32 26.2 -> 23.8 us,
+    // 2^26 46.4 -> 42.6, 2^27 84.7 -> 79.5, 2^28 158.8 -> 152.8, 2^30 595.4 -> 590.4.  The two-stream L1
+    // source gains nothing and keeps the sweep.
     size_t block_vecs = 0;
     if (std::is_same<Src, SrcPlain<T>>::value) {
-        constexpr size_t kBlockVecs = 2048;
-        const size_t blocks = (n / N + kBlockVecs - 1) / kBlockVecs;
-        if (blocks > grid && blocks <= 16384) {
-            block_vecs = kBlockVecs;
+        size_t bv = 2048;
+        size_t blocks = (n / N + bv - 1) / bv;
+        if (blocks > grid) {
+            while (blocks > 16384) {
+                bv *= 2;
+                blocks = (n / N + bv - 1) / bv;
+            }
+            block_vecs = bv;
             grid = (unsigned)blocks;
         }
     }
